@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One step = one pass of the hot path (esp_attn_forward: attention kernel + combine) over one
+batch of seeded synthetic input with the shapes of the benchmark configuration. The default
+workload is the batched paged decode (32 sequences per GPU, context ~ U[512, 32768],
+H32/Hkv4/HD128 bf16, 16-token pages scattered by a seeded page table); the metric is the
+HBM bandwidth the pass achieves = algorithmic K/V bytes / time. With N > 1 (torchrun, one
+process per GPU) every rank runs its own batch: the path shards by sequence, there is no
+collective on the data path ("scaling": "weak"). The split-KV workload (c5) is the one path
+with an exchange step: ranks all-gather their partial records (NCCL) and combine locally.
+
+`--impl reference` times the CPU restatement of the reference's kernels (oracle/) on the
+host cores instead; the reference itself is Metal-only and cannot run on this box.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_attn_hbm_bandwidth"
+UNIT = "GB/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+        except Exception:
+            pass
+    return 6650.0, 1590.0, "fallback"
+
+
+def build_workload(name: str, rank: int, small: bool = False):
+    from espetero_b200 import workloads as wl
+    seed_shift = 1000 * rank
+    if name == "c1":
+        return wl.config_c1(0xE5B201 + seed_shift)
+    if name == "c2":
+        return wl.config_c2(0xE5B202 + seed_shift, n_seqs=4 if small else 32, hi=4096 if small else 32768)
+    if name == "c4":
+        return wl.config_c4(0xE5B204 + seed_shift, n_seqs=2 if small else 16, prefix=512 if small else 4096)
+    if name == "c5":
+        return wl.config_c5(0xE5B205 + seed_shift, ctx=8192 if small else 131072)
+    if name == "c3":
+        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=1 if small else 4, rows=512 if small else 8192)
+    raise SystemExit(f"unknown workload {name}")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(self.gpu)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        time.sleep(0.15)
+        self.p.terminate()  # the exact process started above
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        try:
+            os.unlink(self.f.name)
+        except OSError:
+            pass
+        return out
+
+
+def cpu_sample_workload(name: str):
+    """A bounded sample of the workload for the CPU arm (about 10-30 s of host work)."""
+    from espetero_b200 import workloads as wl
+    if name == "c2":
+        return wl.config_c2(0xE5B202, n_seqs=32, hi=32768), "the full batch: 32 sequences, context ~ U[512, 32768]"
+    if name == "c1":
+        return wl.config_c1(), "full"
+    if name == "c4":
+        return wl.config_c4(), "full"
+    if name == "c5":
+        return wl.config_c5(), "full"
+    return wl.config_c3(n_seqs=1, rows=1024), "1 sequence x 1024 rows"
+
+
+def time_cpu(name: str, repeats: int = 1):
+    """Time the multithreaded fp32 restatement of the reference kernels (oracle/) on the host."""
+    import oracle
+    w, sample = cpu_sample_workload(name)
+    threads = oracle.hw_threads()
+    tiles, jobs, nparts = oracle.plan_tiles(w.trees, w.Hkv, split=512)
+    single = all(int(t["M"]) == 1 for t in w.trees)
+    fn = oracle.decode_gqa_f32 if single else oracle.flash_f32
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O, lse, parts = fn(w, tiles, 8, nparts, threads)
+        if len(jobs):
+            oracle.combine_f32(w, parts, jobs, O, lse, 8, threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return w.kv_bytes_read() / best / 1e9, threads, sample, best
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # the CPU arm runs on rank 0 alone
+    steps = max(1, args.steps)
+    vals = []
+    for _ in range(min(args.warmup, 1)):
+        time_cpu(args.workload)
+    t_all = 0.0
+    for _ in range(steps):
+        v, threads, sample, dt = time_cpu(args.workload)
+        vals.append(v)
+        t_all += dt
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t_all / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "CPU restatement of the reference's Metal kernels (oracle/), fp32, std::thread"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from espetero_b200 import capi, host, workloads as wl
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    W = max(3, args.warmup)
+
+    w = build_workload(args.workload, rank, args.small)
+    tile_rows = 8
+    op = host.AttnOp.for_workload(w, tile_rows, local)
+    groups = args.groups or 148 * 2 * 8
+    plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
+    dp = op.upload(w, plan)
+    a_full = op.make_args(dp)
+    a_attn = op.make_args(dp)
+    a_attn.n_jobs = 0  # attention kernel alone (no combine), for the per-kernel roofline figure
+    bytes_step = w.kv_bytes_read()
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        barrier()
+        return e0.elapsed_time(e1) / 1e3  # seconds
+
+    # ---- device-resident throughput (value)
+    step = lambda: op.forward(dp, a_full)
+    for _ in range(W):
+        step()
+    op.check_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = op.launch_count
+    t_total = timed(step, args.steps)
+    launches = op.launch_count - n0
+    # ---- attention kernel alone (roofline of the dominant kernel)
+    step_attn = lambda: op.forward(dp, a_attn)
+    for _ in range(3):
+        step_attn()
+    t_attn = timed(step_attn, args.steps) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    op.check_status()
+
+    # ---- end to end through the C ABI from host buffers: the step's inputs (Q, Kb, Vb and the
+    # plan tables) come from pinned host memory, the result goes back; the KV pool is device state.
+    def pinned(t):
+        return t.cpu().pin_memory()
+    h_in = [pinned(x) for x in (dp.Q, dp.Kb, dp.Vb, dp.tiles, dp.trees, dp.blocks) if x is not None]
+    d_in = [x for x in (dp.Q, dp.Kb, dp.Vb, dp.tiles, dp.trees, dp.blocks) if x is not None]
+    h_out = torch.empty_like(dp.O, device="cpu").pin_memory()
+    h2d = sum(x.numel() * x.element_size() for x in h_in)
+    d2h = h_out.numel() * h_out.element_size()
+
+    def step_e2e():
+        for h, d in zip(h_in, d_in):
+            d.copy_(h, non_blocking=True)
+        op.forward(dp, a_full)
+        h_out.copy_(dp.O, non_blocking=True)
+    for _ in range(3):
+        step_e2e()
+    t_e2e = timed(step_e2e, args.steps)
+
+    # ---- aggregate over ranks: max time, summed bytes
+    tt = torch.tensor([t_total, t_attn, t_e2e], dtype=torch.float64, device=dev)
+    bb = torch.tensor([float(bytes_step)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dist.all_reduce(bb, op=dist.ReduceOp.SUM)
+    t_total, t_attn_max, t_e2e = [float(x) for x in tt.cpu()]
+    bytes_all = float(bb.cpu()[0])
+
+    if rank == 0:
+        hbm_peak, _, which = measured_peaks()
+        value = bytes_all * args.steps / t_total / 1e9
+        achieved = bytes_step / t_attn / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": W,
+            "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if w.kv_dtype != wl.E4M3 else "e4m3->f16", "data": "synthetic",
+            "config": {"workload": w.name, "sequences_per_gpu": len(w.trees), "H": w.H, "Hkv": w.Hkv, "HD": w.HD, "page": w.bt,
+                       "kv_bytes_per_gpu": bytes_step, "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": op.last_kernel,
+                       "l2": "inputs larger than L2" if bytes_step > 2 * 126e6 else "inputs fit L2: warm-cache number",
+                       "sharding": "sequences per rank, no collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": None, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},
+            "e2e": {"value": bytes_all * args.steps / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "Q/Kb/Vb + plan tables from pinned host memory, O back to the host; the KV pool is resident device state"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            v, threads, sample, dt = time_cpu(args.workload)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
+        print(json.dumps(line), flush=True)
+    op.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,331 @@
+// C-ABI entry points of the attention path: context, options, host-side validation,
+// kernel selection and launches. Mirrors the attention() / kv_save() / kv_cow_copy()
+// dispatch code of the reference (src/model/impl/forest.h:2855-2947, :1438-1449).
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include "host_util.h"
+#include "launch.h"
+
+using esp::fail;
+
+struct esp_attn_ctx {
+  int device = 0;
+  esp_attn_shape shape{};
+  int G = 1;
+  int tile_rows = 8;
+  // options (NativeModel::set_option analogue)
+  int opt_attn_gqa = 1;
+  int opt_attn_umma = 1;
+  int opt_validate = 1;
+  // host-side fault injection: every Nth pass of 64 rows or more fails before launch
+  // (ESPETERO_FAIL_PASS of the reference, forest.h:2521-2531)
+  int fail_every = 0;
+  uint64_t pass_count = 0;
+  uint64_t launches = 0;
+  const char* last_kernel = "";
+  int* d_status = nullptr;
+  // driver entry point for tensor maps, resolved without linking libcuda
+  void* encode_tiled = nullptr;
+  // cached pool tensor map
+  CUtensorMap pool_map{};
+  const void* map_kv = nullptr;
+  uint64_t map_base = 0;
+  int32_t map_blocks = 0, map_bt = 0, map_ld = 0;
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(ESP_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+int elem_bytes(int dt) { return dt == ESP_E4M3 ? 1 : 2; }
+
+int check_shape(const esp_attn_shape& s) {
+  if (s.H <= 0 || s.Hkv <= 0 || s.H % s.Hkv != 0) return fail(ESP_ERR_INVALID, "shape: H=%d must be a positive multiple of Hkv=%d", s.H, s.Hkv);
+  if (s.HD != 64 && s.HD != 128 && s.HD != 256) return fail(ESP_ERR_UNSUPPORTED, "shape: head dim %d (64, 128 or 256)", s.HD);
+  if (s.bt <= 0) return fail(ESP_ERR_INVALID, "shape: bt=%d", s.bt);
+  if (s.q_dtype != ESP_F16 && s.q_dtype != ESP_BF16) return fail(ESP_ERR_UNSUPPORTED, "shape: q_dtype %d (fp16 or bf16)", s.q_dtype);
+  if (s.kv_dtype != s.q_dtype && s.kv_dtype != ESP_E4M3)
+    return fail(ESP_ERR_UNSUPPORTED, "shape: kv_dtype %d must equal q_dtype or be E4M3", s.kv_dtype);
+  if (s.tile_rows != 0 && s.tile_rows != 8 && s.tile_rows != 16 && s.tile_rows != 128)
+    return fail(ESP_ERR_UNSUPPORTED, "shape: tile_rows %d (8, 16 or 128)", s.tile_rows);
+  if (!(s.scale > 0.0f)) return fail(ESP_ERR_INVALID, "shape: scale must be positive");
+  return ESP_OK;
+}
+
+int check_params(const esp_attn_ctx* c, const esp_attn_params& p) {
+  const esp_attn_shape& s = c->shape;
+  if (p.H != s.H || p.Hkv != s.Hkv || p.bt != s.bt) return fail(ESP_ERR_INVALID, "params: H/Hkv/bt (%d/%d/%d) differ from the context's (%d/%d/%d)", p.H, p.Hkv, p.bt, s.H, s.Hkv, s.bt);
+  if (p.q_ld < s.H * s.HD || p.q_ld % 8) return fail(ESP_ERR_INVALID, "params: q_ld=%d (>= H*HD, multiple of 8)", p.q_ld);
+  if (p.kv_ld < s.Hkv * s.HD || p.kv_ld % 16) return fail(ESP_ERR_INVALID, "params: kv_ld=%d (>= Hkv*HD, multiple of 16)", p.kv_ld);
+  if (p.kv_base % 16) return fail(ESP_ERR_INVALID, "params: kv_base must be a multiple of 16 elements");
+  if ((s.flags & ESP_ATTN_FLAG_GATE) && (p.g_ld < s.H * 2 * s.HD || p.g_ld % 4)) return fail(ESP_ERR_INVALID, "params: g_ld=%d (>= 2*H*HD, multiple of 4)", p.g_ld);
+  return ESP_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The checks run_forest makes before it encodes a pass (forest.h:2136-2280), on the host
+// mirrors of the plan. Nothing is launched when one fails.
+int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
+  const esp_attn_shape& s = c->shape;
+  const int TR = c->tile_rows;
+  if (a.n_tiles < 0 || a.n_trees < 0 || a.n_jobs < 0 || a.n_rows < 0) return fail(ESP_ERR_INVALID, "forward: negative count");
+  if (a.n_tiles == 0) return ESP_OK;
+  if (!a.Q || !a.Kb || !a.Vb || !a.O || !a.tiles || !a.trees) return fail(ESP_ERR_INVALID, "forward: null Q/Kb/Vb/O/tiles/trees");
+  if (!aligned16(a.Q) || !aligned16(a.Kb) || !aligned16(a.Vb) || !aligned16(a.O) || !aligned16(a.kv) || !aligned16(a.parts))
+    return fail(ESP_ERR_INVALID, "forward: data pointers must be 16-byte aligned");
+  if (s.kv_dtype == ESP_E4M3 && !a.kv_scales) return fail(ESP_ERR_INVALID, "forward: E4M3 pool needs kv_scales");
+  if ((s.flags & ESP_ATTN_FLAG_GATE) && !a.X) return fail(ESP_ERR_INVALID, "forward: gate flag set but X is null");
+  if ((s.flags & ESP_ATTN_FLAG_ANC_MASK) ? !a.anc_mask : !a.desc) return fail(ESP_ERR_INVALID, "forward: the row mask (desc or anc_mask) is null");
+  if (a.n_jobs > 0 && (!a.jobs || !a.parts)) return fail(ESP_ERR_INVALID, "forward: combine jobs need jobs and parts");
+  if (!c->opt_validate || !a.trees_host || !a.tiles_host) return ESP_OK;
+  bool any_cached = false;
+  for (int i = 0; i < a.n_trees; ++i) {
+    const esp_attn_tree& t = a.trees_host[i];
+    if (t.base < 0 || t.M < 0 || t.P < 0 || t.table < 0) return fail(ESP_ERR_INVALID, "tree %d: negative field", i);
+    if (int64_t(t.base) + t.M > a.n_rows) return fail(ESP_ERR_INVALID, "tree %d: rows [%d, %d) beyond the pass's %d rows", i, t.base, t.base + t.M, a.n_rows);
+    if (t.P > 0) {
+      any_cached = true;
+      if (int64_t(t.table) + (t.P + s.bt - 1) / s.bt > a.n_block_entries)
+        return fail(ESP_ERR_INVALID, "tree %d: block list [%d, +%d) beyond the %d entries of blocks", i, t.table, (t.P + s.bt - 1) / s.bt, a.n_block_entries);
+    }
+    if ((s.flags & ESP_ATTN_FLAG_ANC_MASK) && t.M > 64) return fail(ESP_ERR_UNSUPPORTED, "tree %d: %d rows with a 64-bit ancestor mask", i, t.M);
+  }
+  if (any_cached && (!a.kv || !a.blocks || a.n_blocks <= 0)) return fail(ESP_ERR_INVALID, "forward: cached keys but no pool / block table");
+  for (int i = 0; i < a.n_tiles; ++i) {
+    const esp_attn_tile& t = a.tiles_host[i];
+    if (t.tree < 0 || t.tree >= a.n_trees) return fail(ESP_ERR_INVALID, "tile %d: tree %d of %d", i, t.tree, a.n_trees);
+    const esp_attn_tree& tr = a.trees_host[t.tree];
+    if (t.r0 < tr.base || t.r0 >= tr.base + tr.M) return fail(ESP_ERR_INVALID, "tile %d: first row %d outside its tree [%d, %d)", i, t.r0, tr.base, tr.base + tr.M);
+    if (t.k0 < 0 || t.k0 > t.k1 || t.k1 > tr.P) return fail(ESP_ERR_INVALID, "tile %d: key range [%d, %d) outside [0, %d]", i, t.k0, t.k1, tr.P);
+    if (t.part >= a.n_parts) return fail(ESP_ERR_INVALID, "tile %d: record %d of %d", i, t.part, a.n_parts);
+    if (t.part >= 0 && !a.parts) return fail(ESP_ERR_INVALID, "tile %d: writes a record but parts is null", i);
+  }
+  if (a.jobs_host)
+    for (int i = 0; i < a.n_jobs; ++i) {
+      const esp_attn_combine& j = a.jobs_host[i];
+      if (j.rows < 0 || j.rows > TR || j.r0 < 0 || int64_t(j.r0) + j.rows > a.n_rows) return fail(ESP_ERR_INVALID, "job %d: rows [%d, +%d)", i, j.r0, j.rows);
+      if (j.part0 < 0 || j.nparts < 0 || int64_t(j.part0) + j.nparts > a.n_parts) return fail(ESP_ERR_INVALID, "job %d: records [%d, +%d) of %d", i, j.part0, j.nparts, a.n_parts);
+    }
+  return ESP_OK;
+}
+
+// Tensor map of one layer region of the pool, as the decode kernel reads it:
+// [128-byte line][rows][lines per row], box [line, 16 rows, lines of one head].
+int pool_tensor_map(esp_attn_ctx* c, const esp_attn_args& a) {
+  const esp_attn_shape& s = c->shape;
+  if (c->map_kv == a.kv && c->map_base == a.p.kv_base && c->map_blocks == a.n_blocks && c->map_bt == a.p.bt && c->map_ld == a.p.kv_ld)
+    return ESP_OK;
+  const int esz = elem_bytes(s.kv_dtype);
+  const cuuint64_t line_elems = 128 / esz;
+  const cuuint64_t gdim[3] = {line_elems, cuuint64_t(a.n_blocks) * 2 * cuuint64_t(a.p.bt), cuuint64_t(a.p.kv_ld) * esz / 128};
+  const cuuint64_t gstride[2] = {cuuint64_t(a.p.kv_ld) * esz, 128};
+  const cuuint32_t box[3] = {cuuint32_t(line_elems), cuuint32_t(esp::kDecodeKeyBlock), cuuint32_t(s.HD * esz / 128)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  void* base = const_cast<uint8_t*>(static_cast<const uint8_t*>(a.kv)) + a.p.kv_base * esz;
+  const CUresult r = reinterpret_cast<EncodeTiledFn>(c->encode_tiled)(
+      &c->pool_map, esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, gdim, gstride, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    c->map_kv = nullptr;
+    return fail(ESP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  }
+  c->map_kv = a.kv, c->map_base = a.p.kv_base, c->map_blocks = a.n_blocks, c->map_bt = a.p.bt, c->map_ld = a.p.kv_ld;
+  return ESP_OK;
+}
+
+int* option_slot(esp_attn_ctx* c, const char* name) {
+  if (!std::strcmp(name, "attn_gqa")) return &c->opt_attn_gqa;
+  if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
+  if (!std::strcmp(name, "validate")) return &c->opt_validate;
+  if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
+  return nullptr;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* esp_attn_last_error(void) { return esp::last_error_buffer(); }
+int esp_attn_abi_version(void) { return ESP_ATTN_ABI_VERSION; }
+
+int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape) {
+  if (!out || !shape) return fail(ESP_ERR_INVALID, "esp_attn_create: null argument");
+  *out = nullptr;
+  if (int rc = check_shape(*shape)) return rc;
+  int n_dev = 0;
+  cudaError_t e = cudaGetDeviceCount(&n_dev);
+  if (e != cudaSuccess || n_dev <= 0) return fail(ESP_ERR_NO_DEVICE, "esp_attn_create: no CUDA device (%s); this library has no CPU path", cudaGetErrorString(e));
+  if (device < 0 || device >= n_dev) return fail(ESP_ERR_INVALID, "esp_attn_create: device %d of %d", device, n_dev);
+  cudaDeviceProp prop{};
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+  if (prop.major != 10) return fail(ESP_ERR_NO_DEVICE, "esp_attn_create: device %d is sm_%d%d; the kernels are built for sm_100a only", device, prop.major, prop.minor);
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  auto* c = new esp_attn_ctx;
+  c->device = device;
+  c->shape = *shape;
+  c->G = shape->H / shape->Hkv;
+  c->tile_rows = shape->tile_rows > 0 ? shape->tile_rows : 8;
+  c->shape.tile_rows = c->tile_rows;
+  if (const char* env = std::getenv("ESPETERO_FAIL_PASS")) c->fail_every = std::atoi(env);
+  cudaDriverEntryPointQueryResult qres{};
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &c->encode_tiled, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !c->encode_tiled) {
+    delete c;
+    return fail(ESP_ERR_CUDA, "esp_attn_create: cuTensorMapEncodeTiled not available from the driver");
+  }
+  if ((e = esp::decode_gqa_setup()) != cudaSuccess) {
+    delete c;
+    return cuda_fail(e, "decode kernel setup");
+  }
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&c->d_status), sizeof(int))) != cudaSuccess) {
+    delete c;
+    return cuda_fail(e, "cudaMalloc(status word)");
+  }
+  if ((e = cudaMemset(c->d_status, 0, sizeof(int))) != cudaSuccess) {
+    cudaFree(c->d_status);
+    delete c;
+    return cuda_fail(e, "cudaMemset(status word)");
+  }
+  *out = c;
+  return ESP_OK;
+}
+
+int esp_attn_destroy(esp_attn_ctx* c) {
+  if (!c) return ESP_OK;
+  cudaSetDevice(c->device);
+  if (c->d_status) cudaFree(c->d_status);
+  delete c;
+  return ESP_OK;
+}
+
+int esp_attn_set_option(esp_attn_ctx* c, const char* name, int value) {
+  if (!c || !name) return fail(ESP_ERR_INVALID, "esp_attn_set_option: null argument");
+  int* slot = option_slot(c, name);
+  if (!slot) return fail(ESP_ERR_INVALID, "esp_attn_set_option: unknown option '%s'", name);
+  *slot = value;
+  return ESP_OK;
+}
+
+int esp_attn_get_option(const esp_attn_ctx* c, const char* name, int* value) {
+  if (!c || !name || !value) return fail(ESP_ERR_INVALID, "esp_attn_get_option: null argument");
+  int* slot = option_slot(const_cast<esp_attn_ctx*>(c), name);
+  if (!slot) return fail(ESP_ERR_INVALID, "esp_attn_get_option: unknown option '%s'", name);
+  *value = *slot;
+  return ESP_OK;
+}
+
+const char* esp_attn_last_kernel(const esp_attn_ctx* c) { return c ? c->last_kernel : ""; }
+uint64_t esp_attn_launch_count(const esp_attn_ctx* c) { return c ? c->launches : 0; }
+
+// Reads the device status word (a kernel whose bounded wait ran out leaves a code there)
+// and clears it. Synchronises the stream: meant for tests and post-mortems, not the hot path.
+int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
+  if (!c) return fail(ESP_ERR_INVALID, "esp_attn_check_status: null context");
+  int st = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the status word");
+  if (st != 0) {
+    cudaMemsetAsync(c->d_status, 0, sizeof(int), s);
+    return fail(ESP_ERR_CUDA, "a kernel gave up a bounded wait (status %d: %s)", st,
+                st == esp::kStatusTmaTimeout ? "TMA load never completed" : st == esp::kStatusMmaTimeout ? "MMA never completed" : "bad block id");
+  }
+  return ESP_OK;
+}
+
+int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
+  if (!c || !ap) return fail(ESP_ERR_INVALID, "esp_attn_forward: null argument");
+  const esp_attn_args& a = *ap;
+  const esp_attn_shape& s = c->shape;
+  if (int rc = check_params(c, a.p)) return rc;
+  if (int rc = validate(c, a)) return rc;
+  ++c->pass_count;
+  if (c->fail_every > 0 && a.n_rows >= 64 && c->pass_count % uint64_t(c->fail_every) == 0)
+    return fail(ESP_ERR_INJECTED, "attention pass failed: injected (ESPETERO_FAIL_PASS)");
+  if (a.n_tiles == 0) return ESP_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  esp::KernelArgs k{};
+  k.Q = a.Q, k.Kb = a.Kb, k.Vb = a.Vb, k.kv = a.kv, k.kv_scales = a.kv_scales, k.blocks = a.blocks;
+  k.desc = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? nullptr : a.desc;
+  k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
+  k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
+  k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status;
+  k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
+  k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
+
+  // Kernel choice, as forest.h:2864-2868: single-row trees with G <= 8 take the decode kernel.
+  bool single = c->G <= 8 && a.trees_host != nullptr && a.tiles_host != nullptr;
+  for (int i = 0; single && i < a.n_trees; ++i) single = a.trees_host[i].M == 1;
+  bool decode = single && c->opt_attn_gqa && esp::decode_gqa_supports(s.HD, c->G, s.bt, s.q_dtype, s.kv_dtype) && a.kv != nullptr && a.n_blocks > 0 &&
+                (size_t(a.p.kv_ld) * elem_bytes(s.kv_dtype)) % 128 == 0 && (a.p.kv_base * elem_bytes(s.kv_dtype)) % 128 == 0;
+  for (int i = 0; decode && i < a.n_tiles; ++i) decode = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+
+  cudaError_t e;
+  if (decode) {
+    if (int rc = pool_tensor_map(c, a)) return rc;
+    c->last_kernel = "decode_gqa";
+    e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
+  } else {
+    c->last_kernel = "flash_general";
+    e = esp::launch_flash_general(k, stream, &c->launches);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, c->last_kernel);
+  if (a.n_jobs > 0) return esp_attn_combine_parts(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs);
+  return ESP_OK;
+}
+
+int esp_attn_combine_parts(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
+                           const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs) {
+  if (!c || !p) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
+  if (n_jobs <= 0) return ESP_OK;
+  if (!parts || !O || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
+  if (int rc = check_params(c, *p)) return rc;
+  const esp_attn_shape& s = c->shape;
+  if ((s.flags & ESP_ATTN_FLAG_GATE) && !X) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: gate flag set but X is null");
+  esp::CombineArgs k{};
+  k.parts = parts, k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? X : nullptr, k.O = O, k.lse = lse, k.jobs = jobs, k.p = *p;
+  k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_jobs = n_jobs, k.q_dtype = s.q_dtype;
+  const cudaError_t e = esp::launch_combine(k, static_cast<cudaStream_t>(stream), &c->launches);
+  if (e != cudaSuccess) return cuda_fail(e, "attention_combine");
+  return ESP_OK;
+}
+
+int esp_kv_save(esp_attn_ctx* c, void* stream, const void* Kb, const void* Vb, void* kv, const float* kv_scales,
+                const esp_kv_save_entry* entries, int32_t n, const esp_attn_params* p) {
+  if (!c || !p) return fail(ESP_ERR_INVALID, "esp_kv_save: null argument");
+  if (n <= 0) return ESP_OK;
+  if (!Kb || !Vb || !kv || !entries) return fail(ESP_ERR_INVALID, "esp_kv_save: null Kb / Vb / kv / entries");
+  if (int rc = check_params(c, *p)) return rc;
+  if (c->shape.kv_dtype == ESP_E4M3 && !kv_scales) return fail(ESP_ERR_INVALID, "esp_kv_save: E4M3 pool needs kv_scales");
+  const cudaError_t e = esp::launch_kv_save(Kb, Vb, kv, kv_scales, entries, n, *p, c->shape.HD, c->shape.q_dtype, c->shape.kv_dtype,
+                                            static_cast<cudaStream_t>(stream), &c->launches);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_save");
+  return ESP_OK;
+}
+
+int esp_kv_copy_blocks(esp_attn_ctx* c, void* stream, void* kv, const int32_t* pairs, int32_t n_pairs, const esp_attn_params* p,
+                       uint64_t region_elems, int32_t n_layers) {
+  if (!c || !p) return fail(ESP_ERR_INVALID, "esp_kv_copy_blocks: null argument");
+  if (n_pairs <= 0 || n_layers <= 0) return ESP_OK;
+  if (!kv || !pairs) return fail(ESP_ERR_INVALID, "esp_kv_copy_blocks: null kv / pairs");
+  if (n_pairs > 65535 || n_layers > 65535) return fail(ESP_ERR_UNSUPPORTED, "esp_kv_copy_blocks: at most 65535 pairs and layers per call");
+  if (int rc = check_params(c, *p)) return rc;
+  const int esz = elem_bytes(c->shape.kv_dtype);
+  if ((region_elems * esz) % 16) return fail(ESP_ERR_INVALID, "esp_kv_copy_blocks: region size must be a multiple of 16 bytes");
+  const cudaError_t e = esp::launch_kv_copy_blocks(kv, pairs, n_pairs, *p, region_elems, n_layers, esz, static_cast<cudaStream_t>(stream), &c->launches);
+  if (e != cudaSuccess) return cuda_fail(e, "kv_copy_blocks");
+  return ESP_OK;
+}
+
+}  // extern "C"

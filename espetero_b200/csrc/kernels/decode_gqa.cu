@@ -1,0 +1,423 @@
+// Paged-KV GQA decode attention for single-row trees (sm_100a).
+//
+// Replaces attn_decode_gqa of the reference (kernels/40_attention.metal:598-781; the
+// generic-head-dim twin g4_attention_dec, kernels/80_gemma.metal:371-550): one CTA per
+// (kv head, tile), tile = cached key range [k0, k1) of a tree with one row, plus the row's
+// own batch key when tile.last; output = flash_attention's partial record when
+// tile.part >= 0, else the gated, normalised row (and its LSE).
+//
+// B200 structure (bandwidth-bound: every K/V byte is read once from HBM):
+//  - the pool region is one 3-D TMA tensor [128-byte line][row][lines per row]; a 16-key
+//    block of one kv head (K tile + V tile, 16 rows x HD) is fetched by two bulk tensor
+//    loads with the hardware 128-byte swizzle, rows found through the page table;
+//  - every warp runs its own ring of STAGES tiles with one mbarrier per slot and takes
+//    the tile's 16-key blocks round-robin, so there is no CTA-wide barrier in the loop;
+//  - scores are computed transposed, S^T[16 keys x 8 heads] = K . Q^T with mma.sync
+//    m16n8k16 (the G <= 8 query heads of the kv head are the N = 8 columns, so no MMA row
+//    is padding), online softmax in the exp2 domain with warp shuffles over the key lanes,
+//    P^T goes back in as the B operand through movmatrix, O^T[HD x 8 heads] += V^T . P^T
+//    with V fragments from ldmatrix.trans;
+//  - E4M3 pools: codes are widened to fp16 in registers (exact), the K scale of the page
+//    multiplies the score, the V scale multiplies p before it is rounded to fp16;
+//  - the warps' (m, l, O) are merged through shared memory, then the row's own key is
+//    folded in on CUDA cores, then the record / output is written.
+// All waits are bounded: a TMA that never lands sets the context's status word and the
+// warp leaves its loop.
+#include "common.cuh"
+#include "../launch.h"
+
+namespace esp {
+namespace {
+
+template <int HD_, int KVDT_, int QDT_, int NW_, int STAGES_>
+struct DecodeCfg {
+  static constexpr int HD = HD_, KVDT = KVDT_, QDT = QDT_, NW = NW_, STAGES = STAGES_;
+  static constexpr bool FP8 = KVDT == ESP_E4M3;
+  static constexpr int CDT = FP8 ? ESP_F16 : KVDT;  // MMA operand type
+  static constexpr int ESZ = FP8 ? 1 : 2;
+  static constexpr int ROW_BYTES = HD * ESZ;         // one key of one kv head
+  static constexpr int NCH = ROW_BYTES / 128;        // 128-byte lines per row
+  static constexpr int TILE_BYTES = 16 * ROW_BYTES;  // K or V tile of a 16-key block
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int OLD = HD + 4;                 // row stride of the merge scratch
+  static constexpr int SCRATCH_BYTES = (8 * OLD + 16) * 4;
+  static constexpr int SMEM_BYTES = NW * WARP_BYTES + 1024;
+  static constexpr int NMT = HD / 16;                // m-tiles of O^T
+  static_assert(SCRATCH_BYTES <= WARP_BYTES, "merge scratch must fit in a warp's ring");
+  static_assert(ROW_BYTES % 128 == 0, "row must be whole 128-byte lines");
+};
+
+// Byte offset of (key row r, byte b of the head's row) in a K or V tile:
+// [line][16 rows][128 B], each 16 x 128 B group swizzled by TMA.
+__device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t b) { return (b >> 7) * 2048u + swz128(r, b & 127u); }
+
+template <class C>
+__global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 : 1)
+    decode_gqa_kernel(const __grid_constant__ CUtensorMap pool_map, const KernelArgs a) {
+  constexpr int HD = C::HD, NW = C::NW, STAGES = C::STAGES, NMT = C::NMT, OLD = C::OLD;
+  using QE = Elem16<C::QDT>;
+  using CE = Elem16<C::CDT>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[NW][STAGES];
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const esp_attn_params& p = a.p;
+  const int kvh = blockIdx.x % p.Hkv;
+  const esp_attn_tile tile = a.tiles[blockIdx.x / p.Hkv];
+  const esp_attn_tree tree = a.trees[tile.tree];
+  const int G = a.G;
+  const int row = tile.r0;
+  const float sl2 = a.scale * kLog2e;
+
+  uint8_t* wsm = smem + size_t(warp) * C::WARP_BYTES;
+  if (threadIdx.x == 0) tma_prefetch_desc(&pool_map);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[warp][s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // ---- Q fragments (B operand: k = dim, n = head g), kept in registers for the whole tile
+  uint32_t qf[HD / 16][2];
+  {
+    const int hq = min(g, G - 1);
+    const typename QE::T* qrow = static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(kvh * G + hq) * HD;
+    if constexpr (!C::FP8) {
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        qf[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t);
+        qf[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 8 + 2 * t);
+      }
+    } else {
+      // K fragments of an E4M3 tile hold dims 4t..4t+3 of each 16-dim group: MMA column pairs
+      // (2t, 2t+1) and (2t+8, 2t+9) stand for dims (4t, 4t+1) and (4t+2, 4t+3).
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint2 w = *reinterpret_cast<const uint2*>(qrow + 16 * ks + 4 * t);
+        const float2 f0 = QE::unpack2(w.x), f1 = QE::unpack2(w.y);
+        qf[ks][0] = CE::pack2(f0.x, f0.y);
+        qf[ks][1] = CE::pack2(f1.x, f1.y);
+      }
+    }
+  }
+
+  // ---- this warp's 16-key blocks: warp, warp + NW, ... of the tile's cached range
+  const int nblk = (tile.k1 - tile.k0 + 15) >> 4;
+  const int n_it = nblk > warp ? (nblk - warp + NW - 1) / NW : 0;
+
+  // Lane L of a window keeps the metadata of iteration win + L (page-table lookups are
+  // done 32 at a time, off the critical path of a single block).
+  int iss_win = -32, iss_y = 0;
+  int use_win = -32;
+  float use_ks = 1.0f, use_vs = 1.0f;
+  auto block_of_it = [&](int it, int& j0) {
+    j0 = tile.k0 + 16 * (warp + it * NW);
+    return a.blocks[tree.table + j0 / p.bt];
+  };
+  auto issue = [&](int it) {
+    if (it - iss_win >= 32) {
+      iss_win = it;
+      const int mine = it + lane;
+      if (mine < n_it) {
+        int j0;
+        const int b = block_of_it(mine, j0);
+        iss_y = b * 2 * p.bt + j0 % p.bt;
+      }
+    }
+    const int y = __shfl_sync(0xffffffffu, iss_y, it - iss_win);
+    if (lane == 0) {
+      const int slot = it % STAGES;
+      uint8_t* dst = wsm + slot * C::STAGE_BYTES;
+      mbar_arrive_expect_tx(&full_bar[warp][slot], C::STAGE_BYTES);
+      tma_load_3d(dst, &pool_map, &full_bar[warp][slot], 0, y, kvh * C::NCH);
+      tma_load_3d(dst + C::TILE_BYTES, &pool_map, &full_bar[warp][slot], 0, y + p.bt, kvh * C::NCH);
+    }
+  };
+
+  float o[NMT][4];
+#pragma unroll
+  for (int i = 0; i < NMT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // heads 2t, 2t+1 (l: this lane's keys only)
+
+  const int mi = lane >> 3, rj = lane & 7;
+  const uint32_t key_k = rj + 8 * (mi & 1), sel_k = mi >> 1;  // K: ldmatrix
+  const uint32_t key_v = rj + 8 * (mi >> 1), sel_v = mi & 1;  // V: ldmatrix.trans
+
+  for (int s = 0; s < STAGES - 1 && s < n_it; ++s) issue(s);
+
+  for (int it = 0; it < n_it; ++it) {
+    if (it + STAGES - 1 < n_it) issue(it + STAGES - 1);
+    const int slot = it % STAGES;
+    float kscale = 1.0f, vscale = 1.0f;
+    if constexpr (C::FP8) {
+      if (it - use_win >= 32) {
+        use_win = it;
+        const int mine = it + lane;
+        if (mine < n_it) {
+          int j0;
+          const int b = block_of_it(mine, j0);
+          use_ks = a.kv_scales[size_t(b * 2) * p.Hkv + kvh];
+          use_vs = a.kv_scales[size_t(b * 2 + 1) * p.Hkv + kvh];
+        }
+      }
+      kscale = __shfl_sync(0xffffffffu, use_ks, it - use_win);
+      vscale = __shfl_sync(0xffffffffu, use_vs, it - use_win);
+    }
+    if (!mbar_wait(&full_bar[warp][slot], (it / STAGES) & 1)) {
+      if (lane == 0) atomicExch(a.status, kStatusTmaTimeout);
+      break;
+    }
+    const uint8_t* kt = wsm + slot * C::STAGE_BYTES;
+    uint8_t* vt = wsm + slot * C::STAGE_BYTES + C::TILE_BYTES;
+    const int n_valid = min(16, tile.k1 - (tile.k0 + 16 * (warp + it * NW)));
+    if (n_valid < 16) {
+      // Tail block: rows past the range hold other keys (or stale bytes); V must be zero
+      // there (0 * NaN), K is masked by selection below.
+      const int n = (16 - n_valid) * C::NCH * 8;
+      for (int i = lane; i < n; i += 32) {
+        const int r = n_valid + i / (C::NCH * 8), rem = i % (C::NCH * 8);
+        *reinterpret_cast<uint4*>(vt + (rem >> 3) * 2048 + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+    }
+    const uint32_t kt_u = smem_u32(kt), vt_u = smem_u32(vt);
+
+    // ---- S^T = K . Q^T (two accumulators to shorten the dependent chain)
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (!C::FP8) {
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t af[4];
+        ldmatrix_x4(af, kt_u + (ks >> 2) * 2048 + key_k * 128 + (((((ks & 3) << 1) + sel_k) ^ (key_k & 7)) << 4));
+        if (ks & 1) mma_16816<C::CDT>(sb, af, qf[ks][0], qf[ks][1]);
+        else mma_16816<C::CDT>(sa, af, qf[ks][0], qf[ks][1]);
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < HD / 32; ++kk) {
+        uint32_t r[4];
+        ldmatrix_x4(r, kt_u + (kk >> 2) * 2048 + key_k * 128 + (((((kk & 3) << 1) + sel_k) ^ (key_k & 7)) << 4));
+        uint32_t a0[4] = {e4m3x2_to_f16x2(uint16_t(r[0] & 0xFFFFu)), e4m3x2_to_f16x2(uint16_t(r[1] & 0xFFFFu)),
+                          e4m3x2_to_f16x2(uint16_t(r[0] >> 16)), e4m3x2_to_f16x2(uint16_t(r[1] >> 16))};
+        uint32_t a1[4] = {e4m3x2_to_f16x2(uint16_t(r[2] & 0xFFFFu)), e4m3x2_to_f16x2(uint16_t(r[3] & 0xFFFFu)),
+                          e4m3x2_to_f16x2(uint16_t(r[2] >> 16)), e4m3x2_to_f16x2(uint16_t(r[3] >> 16))};
+        mma_16816<C::CDT>(sa, a0, qf[2 * kk][0], qf[2 * kk][1]);
+        mma_16816<C::CDT>(sb, a1, qf[2 * kk + 1][0], qf[2 * kk + 1][1]);
+      }
+    }
+    // lane: s[0] = (key g, head 2t), s[1] = (key g, head 2t+1), s[2], s[3] = key g + 8
+    const float sc = sl2 * kscale;
+    float s0 = (sa[0] + sb[0]) * sc, s1 = (sa[1] + sb[1]) * sc, s2 = (sa[2] + sb[2]) * sc, s3 = (sa[3] + sb[3]) * sc;
+    if (g >= n_valid) s0 = s1 = -INFINITY;
+    if (g + 8 >= n_valid) s2 = s3 = -INFINITY;
+
+    // ---- online softmax per head over the 16 keys (key lanes: xor 4, 8, 16)
+    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+    for (int off = 4; off <= 16; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: key 0 of the block is live
+    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+    const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1), p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
+    l0 = l0 * c0 + (p0 + p2);
+    l1 = l1 * c1 + (p1 + p3);
+    m0 = mn0;
+    m1 = mn1;
+    // P^T as the B operand (k = key, n = head): transpose the two 8 x 8 halves
+    const uint32_t pb0 = movmatrix_trans(CE::pack2(p0 * vscale, p1 * vscale));
+    const uint32_t pb1 = movmatrix_trans(CE::pack2(p2 * vscale, p3 * vscale));
+
+    // ---- O^T = O^T * corr + V^T . P^T
+    if constexpr (!C::FP8) {
+#pragma unroll
+      for (int i = 0; i < NMT; ++i) {
+        uint32_t af[4];
+        ldmatrix_x4_trans(af, vt_u + (i >> 2) * 2048 + key_v * 128 + (((((i & 3) << 1) + sel_v) ^ (key_v & 7)) << 4));
+        o[i][0] *= c0, o[i][1] *= c1, o[i][2] *= c0, o[i][3] *= c1;
+        mma_16816<C::CDT>(o[i], af, pb0, pb1);
+      }
+    } else {
+      // Per 32 dims: this lane reads dims 32u + 4g .. + 3 of keys 2t, 2t+1, 2t+8, 2t+9 and
+      // pairs them by key: m-tile 2u has rows g <-> dim 32u+4g, g+8 <-> 32u+4g+1, m-tile
+      // 2u+1 has rows g <-> 32u+4g+2, g+8 <-> 32u+4g+3.
+#pragma unroll
+      for (int u = 0; u < HD / 32; ++u) {
+        const uint32_t bcol = uint32_t(32 * u + 4 * g);
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t key = uint32_t(2 * t + (q & 1) + 8 * (q >> 1));
+          w[q] = *reinterpret_cast<const uint32_t*>(vt + tile_off(key, bcol));
+        }
+        const uint32_t alo = e4m3x2_to_f16x2(uint16_t(w[0] & 0xFFFFu)), ahi = e4m3x2_to_f16x2(uint16_t(w[0] >> 16));
+        const uint32_t blo = e4m3x2_to_f16x2(uint16_t(w[1] & 0xFFFFu)), bhi = e4m3x2_to_f16x2(uint16_t(w[1] >> 16));
+        const uint32_t clo = e4m3x2_to_f16x2(uint16_t(w[2] & 0xFFFFu)), chi = e4m3x2_to_f16x2(uint16_t(w[2] >> 16));
+        const uint32_t dlo = e4m3x2_to_f16x2(uint16_t(w[3] & 0xFFFFu)), dhi = e4m3x2_to_f16x2(uint16_t(w[3] >> 16));
+        const uint32_t fa[4] = {__byte_perm(alo, blo, 0x5410), __byte_perm(alo, blo, 0x7632), __byte_perm(clo, dlo, 0x5410),
+                                __byte_perm(clo, dlo, 0x7632)};
+        const uint32_t fb[4] = {__byte_perm(ahi, bhi, 0x5410), __byte_perm(ahi, bhi, 0x7632), __byte_perm(chi, dhi, 0x5410),
+                                __byte_perm(chi, dhi, 0x7632)};
+        o[2 * u][0] *= c0, o[2 * u][1] *= c1, o[2 * u][2] *= c0, o[2 * u][3] *= c1;
+        mma_16816<C::CDT>(o[2 * u], fa, pb0, pb1);
+        o[2 * u + 1][0] *= c0, o[2 * u + 1][1] *= c1, o[2 * u + 1][2] *= c0, o[2 * u + 1][3] *= c1;
+        mma_16816<C::CDT>(o[2 * u + 1], fb, pb0, pb1);
+      }
+    }
+    __syncwarp();  // every lane is done with the slot before lane 0 refills it
+  }
+
+  // ---- merge the warps through shared memory (their rings are idle now)
+#pragma unroll
+  for (int off = 4; off <= 16; off <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  }
+  __syncthreads();
+  {
+    float* osm = reinterpret_cast<float*>(wsm);
+    float* msm = osm + 8 * OLD;
+#pragma unroll
+    for (int i = 0; i < NMT; ++i) {
+      int d_lo, d_hi;
+      if constexpr (!C::FP8) {
+        d_lo = 16 * i + g, d_hi = 16 * i + 8 + g;
+      } else {
+        d_lo = 32 * (i >> 1) + 4 * g + 2 * (i & 1), d_hi = d_lo + 1;
+      }
+      osm[(2 * t) * OLD + d_lo] = o[i][0];
+      osm[(2 * t + 1) * OLD + d_lo] = o[i][1];
+      osm[(2 * t) * OLD + d_hi] = o[i][2];
+      osm[(2 * t + 1) * OLD + d_hi] = o[i][3];
+    }
+    if (g == 0) {
+      msm[2 * t] = m0, msm[2 * t + 1] = m1;
+      msm[8 + 2 * t] = l0, msm[8 + 2 * t + 1] = l1;
+    }
+  }
+  __syncthreads();
+
+  constexpr int DPL = HD / 32;
+  for (int hg = warp; hg < G; hg += NW) {
+    const int h = kvh * G + hg;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, reinterpret_cast<const float*>(smem + size_t(w) * C::WARP_BYTES)[8 * OLD + hg]);
+    float l = 0.0f, acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float* ow = reinterpret_cast<const float*>(smem + size_t(w) * C::WARP_BYTES);
+      const float mw = ow[8 * OLD + hg];
+      const float wg = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
+      l = fmaf(wg, ow[8 * OLD + 8 + hg], l);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[i] = fmaf(wg, ow[hg * OLD + lane + 32 * i], acc[i]);
+    }
+    if (tile.last) {
+      // the row's own key and value (batch row tree.base), kernels/40_attention.metal:647-657
+      const typename QE::T* qrow = static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(h) * HD;
+      const typename QE::T* krow = static_cast<const typename QE::T*>(a.Kb) + size_t(tree.base) * p.kv_ld + size_t(kvh) * HD;
+      const typename QE::T* vrow = static_cast<const typename QE::T*>(a.Vb) + size_t(tree.base) * p.kv_ld + size_t(kvh) * HD;
+      float dot = 0.0f;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) dot = fmaf(QE::to_f32(qrow[lane + 32 * i]), QE::to_f32(krow[lane + 32 * i]), dot);
+#pragma unroll
+      for (int off = 16; off; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      const float s = dot * sl2;
+      const float M2 = fmaxf(M, s);
+      const float c = (M == -INFINITY) ? 0.0f : fast_exp2(M - M2);
+      const float pw = fast_exp2(s - M2);
+      l = l * c + pw;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pw, QE::to_f32(vrow[lane + 32 * i]), acc[i] * c);
+      M = M2;
+    }
+    if (tile.part >= 0) {
+      float* rec = a.parts + ((size_t(tile.part) * p.Hkv + kvh) * a.tile_rows * G + hg) * (HD + 2);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) rec[lane + 32 * i] = acc[i];
+      if (lane == 0) {
+        rec[HD] = M * kLn2;
+        rec[HD + 1] = l;
+      }
+    } else {
+      const float inv_l = l > 0.0f ? 1.0f / l : 0.0f;
+      typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        float v = acc[i] * inv_l;
+        if (a.X) v *= sigmoid_gate(a.X[size_t(row) * p.g_ld + size_t(h) * 2 * HD + HD + lane + 32 * i]);
+        op[lane + 32 * i] = QE::from_f32(v);
+      }
+      if (a.lse && lane == 0) a.lse[size_t(row) * p.H + h] = l > 0.0f ? M * kLn2 + __logf(l) : -INFINITY;
+    }
+  }
+}
+
+template <class C>
+cudaError_t setup_one() {
+  return cudaFuncSetAttribute(decode_gqa_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+}
+template <class C>
+cudaError_t launch_one(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream) {
+  decode_gqa_kernel<C><<<dim3(unsigned(a.n_tiles) * unsigned(a.p.Hkv)), dim3(C::NW * 32), C::SMEM_BYTES, stream>>>(m, a);
+  return cudaGetLastError();
+}
+
+// Instantiations: (HD, pool type, Q type, warps, stages). Rings are sized for two CTAs per
+// SM (<= 110 KB each) so that one CTA's ramp-up and merge overlap the other's streaming.
+using D128H = DecodeCfg<128, ESP_F16, ESP_F16, 4, 3>;
+using D128B = DecodeCfg<128, ESP_BF16, ESP_BF16, 4, 3>;
+using D256H = DecodeCfg<256, ESP_F16, ESP_F16, 4, 3>;
+using D256B = DecodeCfg<256, ESP_BF16, ESP_BF16, 4, 3>;
+using D128EH = DecodeCfg<128, ESP_E4M3, ESP_F16, 4, 4>;
+using D128EB = DecodeCfg<128, ESP_E4M3, ESP_BF16, 4, 4>;
+using D256EH = DecodeCfg<256, ESP_E4M3, ESP_F16, 4, 3>;
+using D256EB = DecodeCfg<256, ESP_E4M3, ESP_BF16, 4, 3>;
+
+}  // namespace
+
+bool decode_gqa_supports(int32_t HD, int32_t G, int32_t bt, int32_t q_dtype, int32_t kv_dtype) {
+  if (HD != 128 && HD != 256) return false;
+  if (G < 1 || G > 8) return false;
+  if (bt <= 0 || bt % 16 != 0) return false;
+  if (q_dtype != ESP_F16 && q_dtype != ESP_BF16) return false;
+  return kv_dtype == q_dtype || kv_dtype == ESP_E4M3;
+}
+
+cudaError_t decode_gqa_setup() {
+  cudaError_t e;
+  if ((e = setup_one<D128H>()) != cudaSuccess) return e;
+  if ((e = setup_one<D128B>()) != cudaSuccess) return e;
+  if ((e = setup_one<D256H>()) != cudaSuccess) return e;
+  if ((e = setup_one<D256B>()) != cudaSuccess) return e;
+  if ((e = setup_one<D128EH>()) != cudaSuccess) return e;
+  if ((e = setup_one<D128EB>()) != cudaSuccess) return e;
+  if ((e = setup_one<D256EH>()) != cudaSuccess) return e;
+  return setup_one<D256EB>();
+}
+
+cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream, uint64_t* launches) {
+  if (a.n_tiles <= 0) return cudaSuccess;
+  cudaError_t e = cudaErrorInvalidValue;
+  const bool f16 = a.q_dtype == ESP_F16;
+  if (a.kv_dtype == ESP_E4M3) {
+    if (a.HD == 128) e = f16 ? launch_one<D128EH>(a, m, stream) : launch_one<D128EB>(a, m, stream);
+    else if (a.HD == 256) e = f16 ? launch_one<D256EH>(a, m, stream) : launch_one<D256EB>(a, m, stream);
+  } else {
+    if (a.HD == 128) e = f16 ? launch_one<D128H>(a, m, stream) : launch_one<D128B>(a, m, stream);
+    else if (a.HD == 256) e = f16 ? launch_one<D256H>(a, m, stream) : launch_one<D256B>(a, m, stream);
+  }
+  if (e == cudaSuccess) ++*launches;
+  return e;
+}
+
+}  // namespace esp

@@ -1,0 +1,81 @@
+// Internal interface between the C-ABI layer (abi.cpp) and the kernel translation
+// units. Not installed; the public surface is include/espetero_attn.h.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/espetero_attn.h"
+
+namespace esp {
+
+// Values a kernel may leave in the context's device status word when a bounded wait runs out.
+enum : int { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusBadBlock = 3 };
+
+// What every attention kernel receives: the bindings of the reference dispatch
+// (src/model/impl/forest.h:2902-2913) plus the shape constants.
+struct KernelArgs {
+  const void* Q;
+  const void* Kb;
+  const void* Vb;
+  const void* kv;
+  const float* kv_scales;
+  const int32_t* blocks;
+  const int32_t* desc;
+  const uint64_t* anc_mask;
+  const float* X;
+  void* O;
+  float* lse;
+  float* parts;
+  const esp_attn_tile* tiles;
+  const esp_attn_tree* trees;
+  int* status;  // device status word of the context
+  esp_attn_params p;
+  int32_t HD;
+  int32_t G;
+  int32_t tile_rows;
+  int32_t n_tiles;
+  int32_t q_dtype;
+  int32_t kv_dtype;
+  int32_t n_blocks;
+  float scale;
+};
+
+struct CombineArgs {
+  const float* parts;
+  const float* X;
+  void* O;
+  float* lse;
+  const esp_attn_combine* jobs;
+  esp_attn_params p;
+  int32_t HD;
+  int32_t G;
+  int32_t tile_rows;
+  int32_t n_jobs;
+  int32_t q_dtype;
+};
+
+// Each launcher enqueues on `stream`, returns cudaGetLastError() of the launch and
+// adds the number of kernels it launched to *launches.
+cudaError_t launch_flash_general(const KernelArgs& a, cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& pool_map, cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_combine(const CombineArgs& a, cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_kv_save(const void* Kb, const void* Vb, void* kv, const float* kv_scales, const esp_kv_save_entry* entries,
+                           int32_t n, const esp_attn_params& p, int32_t HD, int32_t q_dtype, int32_t kv_dtype,
+                           cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pairs, const esp_attn_params& p,
+                                  uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
+                                  uint64_t* launches);
+
+// Shapes the decode kernel covers (the ABI layer falls back to the general kernel otherwise).
+bool decode_gqa_supports(int32_t HD, int32_t G, int32_t bt, int32_t q_dtype, int32_t kv_dtype);
+// One-time per-device setup (raises dynamic shared memory limits).
+cudaError_t decode_gqa_setup();
+
+// Geometry of the pool tensor map the decode kernel expects: a 3-D view
+// [bytes of one 128-byte line][rows = n_blocks * 2 * bt][lines per row] of one layer region,
+// box = [128 B, 16 rows, lines of one head], 128-byte swizzle.
+constexpr int kDecodeKeyBlock = 16;
+
+}  // namespace esp

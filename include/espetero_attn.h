@@ -1,0 +1,241 @@
+/*
+ * espetero_attn.h - C ABI of the B200 attention path.
+ *
+ * Drop-in for the attention step of the reference's forest pass: the dispatch
+ * lambda `attention(plan, ...)` and its neighbours `kv_save` / `kv_cow_copy`
+ * in src/model/impl/forest.h:2855-2947 and :1438-1449, the integer planner
+ * `plan_tiles` (forest.h:1378-1433; generic-head-dim twin `g4_plan_tiles`,
+ * src/model/impl/gemma.h:77-116) and the kernels of kernels/40_attention.metal
+ * (flash_attention :156, attn_decode_gqa :598, attention_combine :811, kv_save
+ * :875, kv_copy_blocks :894) with their generic-HD instantiations
+ * (kernels/80_gemma.metal:157-342, kernels/82_qwen3_omni.metal:97-106).
+ *
+ * Conventions
+ *  - every function returns 0 on success and a negative esp_status otherwise;
+ *    esp_attn_last_error() gives the message of the calling thread's last
+ *    failure. No exception crosses this boundary.
+ *  - one context per GPU; a context is not thread-safe (the reference has one
+ *    scheduler thread, src/model/api.h:4-6).
+ *  - the caller owns every buffer. Unless a function says otherwise, nothing
+ *    here allocates device memory, and all device work is enqueued on the
+ *    caller's stream without a host synchronisation.
+ *  - pointers named *_host are host memory, all other data pointers are device
+ *    memory of the context's GPU.
+ *  - metadata buffers (tiles, trees, blocks, desc, jobs) must stay unchanged
+ *    while a pass that reads them is in flight (docs/design.md:237-243).
+ */
+#ifndef ESPETERO_ATTN_H
+#define ESPETERO_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ESP_ATTN_ABI_VERSION 1
+
+/* ---------------------------------------------------------------- status */
+typedef enum esp_status {
+  ESP_OK = 0,
+  ESP_ERR_INVALID = -1,      /* bad argument (validation failed; nothing was launched) */
+  ESP_ERR_UNSUPPORTED = -2,  /* shape / dtype outside what the kernels cover */
+  ESP_ERR_CUDA = -3,         /* a CUDA runtime or driver call failed */
+  ESP_ERR_CAPACITY = -4,     /* an output array of the caller is too small */
+  ESP_ERR_INJECTED = -5,     /* host-side fault injection (ESPETERO_FAIL_PASS) */
+  ESP_ERR_NO_DEVICE = -6     /* no usable sm_100 device */
+} esp_status;
+
+/* -------------------------------------------------------------- records */
+/* Bit-identical to the kernel-side records of the reference
+ * (kernels/40_attention.metal:124-150, :804-809, :868-873; host mirrors
+ * forest.h:1308-1319, :1342-1345). */
+
+typedef struct esp_attn_params {
+  int32_t H;        /* query heads */
+  int32_t Hkv;      /* KV head groups of the grid */
+  int32_t q_ld;     /* Q / O row stride in elements (H * HD) */
+  int32_t kv_ld;    /* K / V row width in elements (Hkv * HD), batch rows and pool */
+  int32_t g_ld;     /* row stride of the fused projection X (gate source), in floats */
+  int32_t bt;       /* tokens per KV block */
+  uint64_t kv_base; /* element offset of this layer's region in the KV pool */
+} esp_attn_params;
+
+typedef struct esp_attn_tree {
+  int32_t base;  /* absolute first row of the tree in this pass */
+  int32_t P;     /* cached keys */
+  int32_t table; /* first entry of its block list in `blocks` */
+  int32_t M;     /* rows of the tree in this pass */
+} esp_attn_tree;
+
+typedef struct esp_attn_tile {
+  int32_t tree;
+  int32_t r0;   /* absolute first query row */
+  int32_t k0;   /* cached key range [k0, k1) */
+  int32_t k1;
+  int32_t part; /* -1: write O; else index of the partial record */
+  int32_t last; /* also scan the batch keys */
+  int32_t pad0;
+  int32_t pad1;
+} esp_attn_tile;
+
+typedef struct esp_attn_combine {
+  int32_t r0;     /* absolute first row */
+  int32_t rows;   /* rows of the group (<= tile_rows) */
+  int32_t part0;  /* first record */
+  int32_t nparts; /* records, merged in this order */
+} esp_attn_combine;
+
+typedef struct esp_kv_save_entry {
+  int32_t src_row;
+  int32_t block;
+  int32_t pos;
+  int32_t pad;
+} esp_kv_save_entry;
+
+/* ---------------------------------------------------------------- shape */
+typedef enum esp_dtype {
+  ESP_F16 = 0,
+  ESP_BF16 = 1,
+  ESP_E4M3 = 2 /* KV pool only: e4m3fn codes + one fp32 scale per (block, K|V, kv head) */
+} esp_dtype;
+
+enum {
+  ESP_ATTN_FLAG_GATE = 1,    /* O *= sigmoid(gate), gate = X[row*g_ld + h*2*HD + HD + d] (40_attention.metal:334-342) */
+  ESP_ATTN_FLAG_ANC_MASK = 2 /* batch-key visibility from a 64-bit ancestor mask per row instead of `desc` */
+};
+
+typedef struct esp_attn_shape {
+  int32_t H;        /* query heads */
+  int32_t Hkv;      /* KV heads; G = H / Hkv in {1,2,4,8} for the decode kernel */
+  int32_t HD;       /* head dim: 128 or 256 */
+  int32_t bt;       /* tokens per KV block (any value; multiples of 16 take the fast paths) */
+  int32_t q_dtype;  /* ESP_F16 | ESP_BF16: Q, Kb, Vb, O */
+  int32_t kv_dtype; /* pool type: same as q_dtype, or ESP_E4M3 */
+  int32_t tile_rows;/* query rows per tile: 8 (reference), 16 or 128 */
+  int32_t flags;
+  float scale;      /* softmax(scale * q.k); the reference folds 1/sqrt(HD) here (40_attention.metal:199, :692) */
+  int32_t reserved[3];
+} esp_attn_shape;
+
+typedef struct esp_attn_ctx esp_attn_ctx;
+
+/* Create / destroy a context on `device`. Creation resolves the driver entry
+ * point used to build tensor maps and raises the kernels' shared-memory limits;
+ * it allocates one 4-byte device status word, freed by destroy. */
+int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape);
+int esp_attn_destroy(esp_attn_ctx* ctx);
+const char* esp_attn_last_error(void);
+int esp_attn_abi_version(void);
+
+/* Runtime options, as NativeModel::set_option(name, int) (src/model/model.mm:936-1004).
+ * Names: "attn_gqa" (1: single-row trees take the decode kernel; default 1),
+ * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
+ * default 1), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
+ * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
+ * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
+ * reference's host-side fault injection, forest.h:2521-2531). */
+int esp_attn_set_option(esp_attn_ctx* ctx, const char* name, int value);
+int esp_attn_get_option(const esp_attn_ctx* ctx, const char* name, int* value);
+
+/* -------------------------------------------------------------- planner */
+typedef enum esp_plan_mode {
+  ESP_PLAN_REFERENCE = 0, /* plan_tiles, forest.h:1378-1433: bit-for-bit */
+  ESP_PLAN_G4 = 1,        /* g4_plan_tiles without a window, gemma.h:77-116 */
+  ESP_PLAN_B200 = 2       /* same records; chunks sized so that the CTAs fill `groups` slots evenly */
+} esp_plan_mode;
+
+typedef struct esp_plan_opts {
+  int32_t mode;      /* esp_plan_mode */
+  int32_t split;     /* attn_split: most keys of a split tile (reference default 512); 0 = never split */
+  int32_t min_chunk; /* attn_min_chunk: fewest keys of a split tile (reference default 32) */
+  int32_t groups;    /* CTA target (reference: 256); ESP_PLAN_B200: e.g. 2 * 148 */
+  int32_t tile_rows; /* query rows per tile (reference: 8) */
+  int32_t max_parts; /* most parts per row group (reference: 64) */
+  int32_t reserved[2];
+} esp_plan_opts;
+
+/* Pure host function. Writes up to tiles_cap tiles and jobs_cap combine jobs and
+ * always reports the counts needed (ESP_ERR_CAPACITY if an array was too small;
+ * pass NULL arrays to size them). n_parts = partial records the pass needs; the
+ * caller sizes `parts` as n_parts * Hkv * tile_rows * G * (HD + 2) floats
+ * (forest.h:2716). */
+int esp_attn_plan(const esp_attn_tree* trees_host, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts,
+                  esp_attn_tile* tiles_host, int32_t tiles_cap, esp_attn_combine* jobs_host, int32_t jobs_cap,
+                  int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts);
+
+/* Floats the caller must provide in `parts` for n_parts records. */
+size_t esp_attn_parts_floats(const esp_attn_shape* shape, int32_t n_parts);
+
+/* -------------------------------------------------------------- forward */
+/* The twelve bindings of the reference's attention dispatch
+ * (forest.h:2902-2913) plus what the extensions need. */
+typedef struct esp_attn_args {
+  const void* Q;           /* [rows][q_ld] q_dtype */
+  const void* Kb;          /* [rows][kv_ld] q_dtype: this pass's keys */
+  const void* Vb;          /* [rows][kv_ld] q_dtype */
+  const void* kv;          /* pool; block = [K: bt x kv_ld][V: bt x kv_ld] (forest.h:51-57) */
+  const float* kv_scales;  /* ESP_E4M3 only: [n_blocks][2][Hkv] (K row, then V row), this layer's table */
+  const int32_t* blocks;   /* flattened block lists */
+  const int32_t* desc;     /* int4 per row: (seg_start, 0, anc_len, img_end), relative to the tree's first row */
+  const uint64_t* anc_mask;/* ESP_ATTN_FLAG_ANC_MASK: bit j = batch key j of the tree is visible to the row */
+  const float* X;          /* gate source, or NULL without ESP_ATTN_FLAG_GATE */
+  void* O;                 /* [rows][q_ld] q_dtype */
+  float* lse;              /* optional [rows][H]: m + ln(l) of rows written unsplit or combined; NULL to skip */
+  float* parts;            /* partial records [O(HD) | m | l] fp32 */
+  const esp_attn_tile* tiles;
+  const esp_attn_tree* trees;
+  const esp_attn_combine* jobs;
+  /* host mirrors (the plan the caller built): needed to pick the kernel as
+   * forest.h:2864-2868 does and to validate before launching */
+  const esp_attn_tile* tiles_host;
+  const esp_attn_tree* trees_host;
+  const esp_attn_combine* jobs_host;
+  int32_t n_tiles;
+  int32_t n_trees;
+  int32_t n_jobs;
+  int32_t n_rows;          /* rows of Q / Kb / Vb / O / desc */
+  int32_t n_blocks;        /* blocks of this layer's pool region */
+  int32_t n_block_entries; /* entries of `blocks` */
+  int32_t n_parts;         /* records `parts` can hold */
+  int32_t reserved;
+  esp_attn_params p;
+} esp_attn_args;
+
+/* Attention over the plan's tiles, then the combine jobs: the reference's
+ * attention() lambda. stream is a cudaStream_t. */
+int esp_attn_forward(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args);
+
+/* Only the merge step (attention_combine): used after records of other GPUs
+ * have been gathered next to the local ones (split-KV over several GPUs). */
+int esp_attn_combine_parts(esp_attn_ctx* ctx, void* stream, const float* parts, const float* X, void* O, float* lse,
+                           const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs);
+
+/* kv_save (40_attention.metal:875-889; forest.h:2935-2947). With an ESP_E4M3
+ * pool the rows are quantised with the destination block's scale from kv_scales. */
+int esp_kv_save(esp_attn_ctx* ctx, void* stream, const void* Kb, const void* Vb, void* kv, const float* kv_scales,
+                const esp_kv_save_entry* entries, int32_t n_entries, const esp_attn_params* p);
+
+/* kv_copy_blocks (40_attention.metal:894-905; forest.h:1438-1449): pairs =
+ * (src block, dst block) int32 x 2, copied in each of n_layers regions
+ * region_elems apart. */
+int esp_kv_copy_blocks(esp_attn_ctx* ctx, void* stream, void* kv, const int32_t* pairs, int32_t n_pairs,
+                       const esp_attn_params* p, uint64_t region_elems, int32_t n_layers);
+
+/* Name of the attention kernel the last esp_attn_forward on this context
+ * launched ("decode_gqa", "flash_umma", "flash_general"), for tests and traces. */
+const char* esp_attn_last_kernel(const esp_attn_ctx* ctx);
+
+/* Reads and clears the context's device status word: a kernel whose bounded wait ran
+ * out (a TMA load or an MMA that never completed) leaves a code there instead of
+ * spinning. Synchronises the stream: for tests and post-mortems, not the hot path. */
+int esp_attn_check_status(esp_attn_ctx* ctx, void* stream);
+
+/* Kernel launches enqueued by this context since creation. */
+uint64_t esp_attn_launch_count(const esp_attn_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ESPETERO_ATTN_H */
