@@ -13,7 +13,13 @@ namespace esp {
 namespace {
 
 // One CTA per (job row, head); thread = 4 dims. Records are read 8 at a time so that the
-// loads of a batch are in flight together.
+// loads of a batch are in flight together. A record is HD + 2 floats long, so records are
+// only 8-byte aligned: O is read as float2 pairs.
+__device__ __forceinline__ float4 ld_rec4(const float* p) {
+  const float2 a = *reinterpret_cast<const float2*>(p), b = *reinterpret_cast<const float2*>(p + 2);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 template <int QDT>
 __global__ void combine_kernel(const CombineArgs a) {
   using QE = Elem16<QDT>;
@@ -39,7 +45,7 @@ __global__ void combine_kernel(const CombineArgs a) {
     for (int i = 0; i < 8; ++i) {
       const float* rec = rec0 + size_t(s + i) * stride;
       m8[i] = rec[HD], l8[i] = rec[HD + 1];
-      o8[i] = *reinterpret_cast<const float4*>(rec + 4 * d4);
+      o8[i] = ld_rec4(rec + 4 * d4);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -51,7 +57,7 @@ __global__ void combine_kernel(const CombineArgs a) {
   for (; s < n; ++s) {
     const float* rec = rec0 + size_t(s) * stride;
     const float w = (rec[HD] == -INFINITY) ? 0.0f : __expf(rec[HD] - M);
-    const float4 o = *reinterpret_cast<const float4*>(rec + 4 * d4);
+    const float4 o = ld_rec4(rec + 4 * d4);
     L += w * rec[HD + 1];
     acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
   }
