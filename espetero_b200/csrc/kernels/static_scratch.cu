@@ -1,0 +1,145 @@
+// esp_attn_decode_static: split-K decode for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run
+// attention: an engine that hands the whole GPU to one pre-sized arena at start-up and
+// forbids later allocations, a plugin loaded into a process whose allocator owns all of
+// device memory, a real-time serving loop that treats any allocation (and the implicit
+// device synchronisation cudaFree brings) as a latency fault. The regular path asks two
+// things of them that they may not be able to give: a context (esp_attn_create allocates
+// its status word) and a `parts` buffer for the split-K records. This entry point needs
+// neither. The partial records live in a fixed array inside the library's device image,
+// so the memory exists from the moment the library is loaded on a GPU until the process
+// exits, on every GPU that loads it.
+//
+// It runs the same kernels as esp_attn_forward does for single-row trees (decode_gqa, then
+// attention_combine) and gives bit-identical results; only the home of the records differs.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../host_util.h"
+#include "../launch.h"
+
+namespace {
+
+// Capacity of the record array: 4 Mi floats = 16 MiB per GPU. A pass needs
+// n_parts * Hkv * tile_rows * G * (HD + 2) floats (e.g. 32 records of the long-context
+// FP8 decode, H32/Hkv8/HD256: 2.1 M floats).
+constexpr size_t kStaticPartsFloats = size_t(ESP_ATTN_STATIC_PARTS_FLOATS);
+
+static __device__ __align__(256) float g_static_parts[kStaticPartsFloats];
+static __device__ __align__(256) int g_static_status[64] = {0};
+
+// In host code the two names above are only handles of the symbols, not device addresses;
+// the addresses a kernel can use are looked up once per device and kept here.
+struct DeviceSlot {
+  bool ready = false;
+  float* parts = nullptr;
+  int* status = nullptr;
+  void* encode_tiled = nullptr;
+};
+constexpr int kMaxDevices = 64;
+DeviceSlot g_slots[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return esp::fail(ESP_ERR_CUDA, "esp_attn_decode_static: %s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+// First call on a device, with that device current: resolve the device addresses of the
+// arrays, the tensor-map encoder, and raise the kernels' shared-memory limits. None of
+// these calls allocates device memory.
+int setup_device(int dev) {
+  DeviceSlot& s = g_slots[dev];
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.parts), g_static_parts);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(records)");
+  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.status), g_static_status);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status)");
+  cudaDriverEntryPointQueryResult q{};
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !s.encode_tiled)
+    return esp::fail(ESP_ERR_CUDA, "esp_attn_decode_static: cuTensorMapEncodeTiled not available from the driver");
+  if ((e = esp::decode_gqa_setup()) != cudaSuccess) return cuda_fail(e, "decode kernel setup");
+  s.ready = true;
+  return ESP_OK;
+}
+
+}  // namespace
+
+extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_v, const esp_attn_args* args) {
+  if (!shape || !args) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: null argument");
+  const esp_attn_shape& s = *shape;
+  const esp_attn_args& a = *args;
+  const int TR = s.tile_rows > 0 ? s.tile_rows : 8;
+  if (s.H <= 0 || s.Hkv <= 0 || s.H % s.Hkv) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: H=%d, Hkv=%d", s.H, s.Hkv);
+  const int G = s.H / s.Hkv;
+  const int esz = s.kv_dtype == ESP_E4M3 ? 1 : 2;
+  if (!esp::decode_gqa_supports(s.HD, G, s.bt, s.q_dtype, s.kv_dtype) || !(s.scale > 0.0f))
+    return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: shape outside the decode kernel (HD 128/256, G <= 8, bt %% 16 == 0)");
+  if (a.n_tiles <= 0) return ESP_OK;
+  if (!a.Q || !a.Kb || !a.Vb || !a.O || !a.kv || !a.blocks || !a.tiles || !a.trees || !a.tiles_host || !a.trees_host || a.n_blocks <= 0)
+    return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: null input / output / plan pointer");
+  if (a.n_jobs > 0 && !a.jobs) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: combine jobs without a jobs array");
+  if (s.kv_dtype == ESP_E4M3 && !a.kv_scales) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: E4M3 pool needs kv_scales");
+  if ((s.flags & ESP_ATTN_FLAG_GATE) && !a.X) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: gate flag set but X is null");
+  if (a.p.H != s.H || a.p.Hkv != s.Hkv || a.p.bt != s.bt || a.p.q_ld < s.H * s.HD || a.p.kv_ld < s.Hkv * s.HD ||
+      (size_t(a.p.kv_ld) * esz) % 128 || (a.p.kv_base * esz) % 128)
+    return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: params do not match the shape");
+  for (int i = 0; i < a.n_trees; ++i)
+    if (a.trees_host[i].M != 1) return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: tree %d has %d rows (decode only)", i, a.trees_host[i].M);
+  int max_part = -1;
+  for (int i = 0; i < a.n_tiles; ++i) {
+    const esp_attn_tile& t = a.tiles_host[i];
+    if (t.tree < 0 || t.tree >= a.n_trees || t.k0 < 0 || t.k0 > t.k1 || t.k1 > a.trees_host[t.tree].P || t.k0 % esp::kDecodeKeyBlock)
+      return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: tile %d is malformed or does not start on a 16-key boundary", i);
+    max_part = t.part > max_part ? t.part : max_part;
+  }
+  const size_t need = size_t(max_part + 1) * size_t(s.Hkv) * size_t(TR) * size_t(G) * size_t(s.HD + 2);
+  if (need > kStaticPartsFloats)
+    return esp::fail(ESP_ERR_CAPACITY, "esp_attn_decode_static: the pass needs %zu floats of records, the built-in array holds %zu; use esp_attn_forward with a caller-owned parts buffer",
+                     need, kStaticPartsFloats);
+
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: device index %d", dev);
+  if (!g_slots[dev].ready)
+    if (int rc = setup_device(dev)) return rc;
+  const DeviceSlot& slot = g_slots[dev];
+
+  CUtensorMap map;
+  {
+    const cuuint64_t line_elems = 128 / esz;
+    const cuuint64_t gdim[3] = {line_elems, cuuint64_t(a.n_blocks) * 2 * cuuint64_t(a.p.bt), cuuint64_t(a.p.kv_ld) * esz / 128};
+    const cuuint64_t gstride[2] = {cuuint64_t(a.p.kv_ld) * esz, 128};
+    const cuuint32_t box[3] = {cuuint32_t(line_elems), cuuint32_t(esp::kDecodeKeyBlock), cuuint32_t(s.HD * esz / 128)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    void* base = const_cast<uint8_t*>(static_cast<const uint8_t*>(a.kv)) + a.p.kv_base * esz;
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(slot.encode_tiled)(
+        &map, esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, gdim, gstride, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return esp::fail(ESP_ERR_CUDA, "esp_attn_decode_static: cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  uint64_t launches = 0;
+  esp::KernelArgs k{};
+  k.Q = a.Q, k.Kb = a.Kb, k.Vb = a.Vb, k.kv = a.kv, k.kv_scales = a.kv_scales, k.blocks = a.blocks;
+  k.desc = a.desc, k.anc_mask = nullptr;
+  k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
+  k.O = a.O, k.lse = a.lse, k.parts = slot.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = slot.status;
+  k.p = a.p, k.HD = s.HD, k.G = G, k.tile_rows = TR, k.n_tiles = a.n_tiles;
+  k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
+  // Nothing in the array has to be cleared first: every record the merge reads below is
+  // written in full by the attention kernel of this same call.
+  if ((e = esp::launch_decode_gqa(k, map, stream, &launches)) != cudaSuccess) return cuda_fail(e, "decode_gqa");
+  if (a.n_jobs > 0) {
+    esp::CombineArgs c{};
+    c.parts = slot.parts, c.X = k.X, c.O = a.O, c.lse = a.lse, c.jobs = a.jobs, c.p = a.p;
+    c.HD = s.HD, c.G = G, c.tile_rows = TR, c.n_jobs = a.n_jobs, c.q_dtype = s.q_dtype;
+    if ((e = esp::launch_combine(c, stream, &launches)) != cudaSuccess) return cuda_fail(e, "attention_combine");
+  }
+  return ESP_OK;
+}

@@ -223,6 +223,35 @@ int esp_kv_save(esp_attn_ctx* ctx, void* stream, const void* Kb, const void* Vb,
 int esp_kv_copy_blocks(esp_attn_ctx* ctx, void* stream, void* kv, const int32_t* pairs, int32_t n_pairs,
                        const esp_attn_params* p, uint64_t region_elems, int32_t n_layers);
 
+/* Decode attention for callers that cannot allocate device memory when they run it: an
+ * engine that gave the whole GPU to one arena at start-up, a plugin inside a process whose
+ * allocator owns the device, a serving loop that forbids cudaMalloc / cudaFree (and the
+ * device-wide synchronisation cudaFree implies) after warm-up. It has no counterpart in
+ * the reference, whose passes always draw `parts` from a growable arena
+ * (meta.parts.ensure, src/model/impl/forest.h:2716).
+ *
+ * Same computation and results as esp_attn_forward for single-row trees (decode kernel,
+ * then the combine jobs), but it needs no context and no `parts` buffer: the split-K
+ * records go to an array of ESP_ATTN_STATIC_PARTS_FLOATS floats (16 MiB) that is part of
+ * the library's device image - every GPU that loads the library holds it until the
+ * process exits. args->parts and args->n_parts are ignored; inputs, outputs and the plan
+ * (device and host copies) are passed as for esp_attn_forward. Limits and rules:
+ *  - a pass whose records need more than the array holds
+ *    ((largest part + 1) * Hkv * tile_rows * G * (HD + 2) floats) is refused with
+ *    ESP_ERR_CAPACITY; shapes the decode kernel does not cover, multi-row trees and tiles
+ *    that do not start on a 16-key boundary are refused with ESP_ERR_UNSUPPORTED /
+ *    ESP_ERR_INVALID. Nothing is launched in either case.
+ *  - the call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
+ *  - the first call on each device (with that device current) looks up the array's device
+ *    address and raises the kernels' shared-memory limit; make that call before any stream
+ *    capture begins.
+ *  - all calls on a GPU share the one array, which keeps the previous call's records:
+ *    nothing in it needs clearing (each call overwrites every record it later reads), but
+ *    two calls that overlap on the GPU (different streams, or different threads) race on
+ *    it - serialise them on one stream. */
+#define ESP_ATTN_STATIC_PARTS_FLOATS (4u << 20)
+int esp_attn_decode_static(const esp_attn_shape* shape, void* stream, const esp_attn_args* args);
+
 /* Name of the attention kernel the last esp_attn_forward on this context
  * launched ("decode_gqa", "flash_umma", "flash_general"), for tests and traces. */
 const char* esp_attn_last_kernel(const esp_attn_ctx* ctx);
