@@ -33,6 +33,13 @@ struct esp_attn_ctx {
   const void* map_kv = nullptr;
   uint64_t map_base = 0;
   int32_t map_blocks = 0, map_bt = 0, map_ld = 0;
+  // tensor maps of the tcgen05 kernel: pool pages, Kb rows, Vb rows (64 dims x 16 rows per load)
+  CUtensorMap upool_map{}, kb_map{}, vb_map{};
+  const void* umap_kv = nullptr;
+  const void* umap_kb = nullptr;
+  const void* umap_vb = nullptr;
+  uint64_t umap_base = 0;
+  int32_t umap_blocks = 0, umap_rows = 0, umap_ld = 0;
 };
 
 namespace {
@@ -54,8 +61,8 @@ int check_shape(const esp_attn_shape& s) {
   if (s.q_dtype != ESP_F16 && s.q_dtype != ESP_BF16) return fail(ESP_ERR_UNSUPPORTED, "shape: q_dtype %d (fp16 or bf16)", s.q_dtype);
   if (s.kv_dtype != s.q_dtype && s.kv_dtype != ESP_E4M3)
     return fail(ESP_ERR_UNSUPPORTED, "shape: kv_dtype %d must equal q_dtype or be E4M3", s.kv_dtype);
-  if (s.tile_rows != 0 && s.tile_rows != 8 && s.tile_rows != 16 && s.tile_rows != 128)
-    return fail(ESP_ERR_UNSUPPORTED, "shape: tile_rows %d (8, 16 or 128)", s.tile_rows);
+  if (s.tile_rows != 0 && s.tile_rows != 8 && s.tile_rows != 16 && s.tile_rows != 32 && s.tile_rows != 64 && s.tile_rows != 128)
+    return fail(ESP_ERR_UNSUPPORTED, "shape: tile_rows %d (8, 16, 32, 64 or 128)", s.tile_rows);
   if (!(s.scale > 0.0f)) return fail(ESP_ERR_INVALID, "shape: scale must be positive");
   return ESP_OK;
 }
@@ -142,6 +149,42 @@ int pool_tensor_map(esp_attn_ctx* c, const esp_attn_args& a) {
   return ESP_OK;
 }
 
+// One 3-D map [64 elements][rows][kv_ld / 64] over 16-bit rows of width kv_ld, box = 64 x 16 x 1.
+int rows_tensor_map(esp_attn_ctx* c, CUtensorMap* out, const void* base, uint64_t rows, int32_t kv_ld) {
+  const cuuint64_t gdim[3] = {64, rows, cuuint64_t(kv_ld) / 64};
+  const cuuint64_t gstride[2] = {cuuint64_t(kv_ld) * 2, 128};
+  const cuuint32_t box[3] = {64, 16, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = reinterpret_cast<EncodeTiledFn>(c->encode_tiled)(
+      out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ESP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return ESP_OK;
+}
+
+int umma_tensor_maps(esp_attn_ctx* c, const esp_attn_args& a) {
+  const bool have_pool = a.kv != nullptr && a.n_blocks > 0;
+  if (c->umap_kb != a.Kb || c->umap_vb != a.Vb || c->umap_rows != a.n_rows || c->umap_ld != a.p.kv_ld) {
+    c->umap_kb = c->umap_vb = nullptr;
+    if (int rc = rows_tensor_map(c, &c->kb_map, a.Kb, uint64_t(a.n_rows), a.p.kv_ld)) return rc;
+    if (int rc = rows_tensor_map(c, &c->vb_map, a.Vb, uint64_t(a.n_rows), a.p.kv_ld)) return rc;
+    c->umap_kb = a.Kb, c->umap_vb = a.Vb, c->umap_rows = a.n_rows, c->umap_ld = a.p.kv_ld;
+    c->umap_kv = nullptr;
+  }
+  if (!have_pool) {
+    c->upool_map = c->kb_map;  // never dereferenced: no tile has cached keys
+    c->umap_kv = nullptr;
+    return ESP_OK;
+  }
+  if (c->umap_kv != a.kv || c->umap_base != a.p.kv_base || c->umap_blocks != a.n_blocks) {
+    c->umap_kv = nullptr;
+    const uint8_t* base = static_cast<const uint8_t*>(a.kv) + a.p.kv_base * 2;
+    if (int rc = rows_tensor_map(c, &c->upool_map, base, uint64_t(a.n_blocks) * 2 * uint64_t(a.p.bt), a.p.kv_ld)) return rc;
+    c->umap_kv = a.kv, c->umap_base = a.p.kv_base, c->umap_blocks = a.n_blocks;
+  }
+  return ESP_OK;
+}
+
 int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "attn_gqa")) return &c->opt_attn_gqa;
   if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
@@ -185,6 +228,10 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
   if ((e = esp::decode_gqa_setup()) != cudaSuccess) {
     delete c;
     return cuda_fail(e, "decode kernel setup");
+  }
+  if ((e = esp::flash_umma_setup()) != cudaSuccess) {
+    delete c;
+    return cuda_fail(e, "tcgen05 kernel setup");
   }
   if ((e = cudaMalloc(reinterpret_cast<void**>(&c->d_status), sizeof(int))) != cudaSuccess) {
     delete c;
@@ -271,11 +318,21 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
                 (size_t(a.p.kv_ld) * elem_bytes(s.kv_dtype)) % 128 == 0 && (a.p.kv_base * elem_bytes(s.kv_dtype)) % 128 == 0;
   for (int i = 0; decode && i < a.n_tiles; ++i) decode = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
 
+  // Multi-row tiles: the tcgen05 kernel when the shape fits it (128 (row, head) pairs per CTA).
+  bool umma = !decode && c->opt_attn_umma && a.tiles_host != nullptr &&
+              esp::flash_umma_supports(s.HD, c->G, c->tile_rows, s.bt, s.q_dtype, s.kv_dtype) && a.p.kv_ld % 64 == 0 &&
+              a.p.kv_base % 64 == 0;
+  for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+
   cudaError_t e;
   if (decode) {
     if (int rc = pool_tensor_map(c, a)) return rc;
     c->last_kernel = "decode_gqa";
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
+  } else if (umma) {
+    if (int rc = umma_tensor_maps(c, a)) return rc;
+    c->last_kernel = "flash_umma";
+    e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
   } else {
     c->last_kernel = "flash_general";
     e = esp::launch_flash_general(k, stream, &c->launches);

@@ -113,7 +113,7 @@ typedef struct esp_attn_shape {
   int32_t bt;       /* tokens per KV block (any value; multiples of 16 take the fast paths) */
   int32_t q_dtype;  /* ESP_F16 | ESP_BF16: Q, Kb, Vb, O */
   int32_t kv_dtype; /* pool type: same as q_dtype, or ESP_E4M3 */
-  int32_t tile_rows;/* query rows per tile: 8 (reference), 16 or 128 */
+  int32_t tile_rows;/* query rows per tile: 8 (reference), 16, 32, 64 or 128 */
   int32_t flags;
   float scale;      /* softmax(scale * q.k); the reference folds 1/sqrt(HD) here (40_attention.metal:199, :692) */
   int32_t reserved[3];

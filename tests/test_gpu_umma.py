@@ -1,0 +1,108 @@
+"""Parity of the tcgen05 kernel (flash_umma: 128 (row, head) pairs per CTA, TMEM accumulators)
+with the float64 oracle, through the C ABI: tree verify (16-row tiles x 8 heads), causal prefill
+(128-row tiles), forest masks, chunked prefill over a cached prefix, split-K records + combine,
+and integer-exact mask probes."""
+import numpy as np
+import pytest
+
+from espetero_b200 import capi, host, workloads as wl
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(oracle_lib, w, tile_rows, mode=capi.ESP_PLAN_REFERENCE, groups=256, split=512, with_abs=True, expect="flash_umma"):
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    O, lse, parts, plan, kernel = host.run_pass(w, mode=mode, tile_rows=tile_rows, split=split, groups=groups)
+    assert kernel == expect
+    util.check_output(O, ref, w, ref_abs=ref_abs if with_abs else None, what=w.name)
+    fin = np.isfinite(lse_ref)
+    assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
+    return plan
+
+
+def test_verify_tile_16x8(oracle_lib):
+    w = wl.config_c4(n_seqs=3, prefix=1024)
+    plan = _check(oracle_lib, w, 16, with_abs=False)
+    assert plan.n_parts > 0  # few tiles: the prefix is split and combined
+
+
+def test_verify_b200_plan_unsplit_and_split(oracle_lib):
+    w = wl.config_c4(n_seqs=2, prefix=2000)  # prefix not a multiple of 64: tail block
+    _check(oracle_lib, w, 16, mode=capi.ESP_PLAN_B200, groups=8, split=1 << 20, with_abs=False)     # unsplit
+    _check(oracle_lib, w, 16, mode=capi.ESP_PLAN_B200, groups=592, split=1 << 20, with_abs=False)   # split
+
+
+@pytest.mark.parametrize("rows", [128, 300, 5])
+def test_causal_prefill(oracle_lib, rows):
+    w = wl.config_c3(n_seqs=2, rows=rows)
+    _check(oracle_lib, w, 128)
+
+
+def test_prefill_f16_and_gate(oracle_lib):
+    w = wl.make_pass("prefill_f16", 71, [(0, 200), (0, 129)], 8, 2, 128, 16, wl.F16, gate=True)
+    _check(oracle_lib, w, 128)
+
+
+def test_chunked_prefill_over_cached_prefix(oracle_lib):
+    w = wl.make_pass("chunked", 72, [(300, 150), (1000, 64), (37, 1)], 8, 4, 128, 16, wl.BF16)
+    _check(oracle_lib, w, 128)
+
+
+@pytest.mark.parametrize("mask", ["forest", "tree"])
+@pytest.mark.parametrize("tr,H,Hkv", [(128, 8, 2), (16, 16, 2), (32, 8, 2), (64, 4, 2)])
+def test_masks_and_tile_shapes(oracle_lib, mask, tr, H, Hkv):
+    w = wl.make_pass("masks", 73 + tr, [(40, 20), (0, 9), (100, 16), (33, 1), (200, 50)], H, Hkv, 128, 16, wl.BF16, mask=mask)
+    _check(oracle_lib, w, tr)
+
+
+def test_records_match_f64_without_rounding(oracle_lib):
+    w = wl.config_c4(n_seqs=2, prefix=512)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True)
+    assert kernel == "flash_umma"
+    O64, lse64 = util.records_to_output(parts, w, plan.tiles, plan.jobs, 16)
+    assert np.abs(O64 - ref).max() <= util.TOL_16
+    assert np.abs(lse64 - lse_ref).max() < 1e-3
+
+
+def test_tree_mask_probe_is_exact_on_tensor_cores():
+    """Q = 0 and one-hot V rows: the fp32 record of node n must hold exactly its ancestor set and
+    exact integer sums of the prefix codes (P = 1.0 exactly in bf16, fp32 accumulation in TMEM)."""
+    P, M, H, Hkv, HD, bt = 200, 16, 16, 2, 128, 16
+    w = wl.make_pass("umma_probe", 74, [(P, M), (0, M)], H, Hkv, HD, bt, wl.BF16, mask="tree")
+    w.Q[:] = 0
+    pool = np.full((w.n_blocks, 2, bt, Hkv, HD), 3.0, dtype=np.float32)  # poison
+    for j in range(P):
+        b = int(w.blocks[j // bt])
+        pool[b, 1, j % bt] = 0
+        for kvh in range(Hkv):
+            pool[b, 1, j % bt, kvh, 64:68] = [j % 16, (j // 16) % 16, kvh + 1, 1]
+    w.kv = wl.f32_to_bf16_bits(pool.reshape(-1))
+    vb = np.zeros((w.n_rows, Hkv, HD), dtype=np.float32)
+    for r in range(w.n_rows):
+        vb[r, :, r % M] = 1.0
+    w.Vb = wl.f32_to_bf16_bits(vb.reshape(w.n_rows, -1))
+    O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True, split=0)
+    assert kernel == "flash_umma"
+    G = w.G
+    rec = parts[: plan.n_parts * Hkv * 16 * G * (HD + 2)].reshape(plan.n_parts, Hkv, 16, G, HD + 2)
+    for t in plan.tiles:
+        ti, part = int(t["tree"]), int(t["part"])
+        par = w.extra["parents"][ti]
+        Pt = int(w.trees[ti]["P"])
+        for node in range(M):
+            anc, k = set(), node
+            while k >= 0:
+                anc.add(k)
+                k = par[k]
+            r = rec[part, :, node]
+            assert np.all(r[..., HD] == 0.0)
+            assert np.all(r[..., HD + 1] == Pt + len(anc))
+            want = np.array([1.0 if n in anc else 0.0 for n in range(M)], dtype=np.float32)
+            assert np.all(r[..., :M] == want)
+            if Pt:
+                js = np.arange(Pt)
+                for kvh in range(Hkv):
+                    assert np.all(r[kvh, :, 64] == (js % 16).sum()) and np.all(r[kvh, :, 65] == ((js // 16) % 16).sum())
+                    assert np.all(r[kvh, :, 66] == (kvh + 1) * Pt) and np.all(r[kvh, :, 67] == Pt)
