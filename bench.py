@@ -34,6 +34,24 @@ if ROOT not in sys.path:
 METRIC = "decode_attn_hbm_bandwidth"
 UNIT = "GB/s"
 
+# per workload: query rows per tile, and what the roofline counts
+TILE_ROWS = {"c1": 8, "c2": 8, "c3": 128, "c4": 16, "c5": 8}
+
+
+def attention_flops(w) -> float:
+    """Algorithmic flops of one pass: 2 flop per MAC, Q.K^T and P.V, over the visible (row, key)
+    pairs (cached keys + causal / ancestor batch keys)."""
+    pairs = 0
+    for i, t in enumerate(w.trees):
+        P, M = int(t["P"]), int(t["M"])
+        if w.anc_mask is not None and (w.flags & 2):
+            base = int(t["base"])
+            vis = sum(bin(int(w.anc_mask[base + r])).count("1") for r in range(M))
+        else:
+            vis = M * (M + 1) // 2
+        pairs += M * P + vis
+    return 4.0 * pairs * w.H * w.HD
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -58,7 +76,7 @@ def build_workload(name: str, rank: int, small: bool = False):
     if name == "c5":
         return wl.config_c5(0xE5B205 + seed_shift, ctx=8192 if small else 131072)
     if name == "c3":
-        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=1 if small else 4, rows=512 if small else 8192)
+        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=1 if small else 4, rows=2048 if small else 8192)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -201,7 +219,7 @@ def main():
     W = max(3, args.warmup)
 
     w = build_workload(args.workload, rank, args.small)
-    tile_rows = 8
+    tile_rows = TILE_ROWS[args.workload]
     op = host.AttnOp.for_workload(w, tile_rows, local)
     groups = args.groups or 148 * 2 * 8
     plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
@@ -275,9 +293,12 @@ def main():
     bytes_all = float(bb.cpu()[0])
 
     if rank == 0:
-        hbm_peak, _, which = measured_peaks()
+        hbm_peak, tf_peak, which = measured_peaks()
         value = bytes_all * args.steps / t_total / 1e9
         achieved = bytes_step / t_attn / 1e9
+        flops = attention_flops(w)
+        tensor = {"tflops": flops / t_attn / 1e12, "peak_tflops": tf_peak, "frac": flops / t_attn / 1e12 / tf_peak,
+                  "flops_per_step": flops}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": W,
             "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -290,8 +311,16 @@ def main():
                          "traffic": None, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},
             "e2e": {"value": bytes_all * args.steps / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "Q/Kb/Vb + plan tables from pinned host memory, O back to the host; the KV pool is resident device state"},
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "clocks": clocks, "tensor": tensor,
         }
+        if args.workload == "c3":  # the prefill configuration is bound by the tensor cores, not by HBM
+            line["metric"], line["unit"] = "prefill_attn_tflops", "TFLOP/s"
+            line["value"] = flops * world * args.steps / t_total / 1e12
+            line["roofline"] = {"bound": "tensor", "achieved": tensor["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
+                                "frac": tensor["frac"], "traffic": None, "peak_source": which, "kernel": op.last_kernel,
+                                "ms_per_launch": 1e3 * t_attn}
+            line["e2e"]["value"] = flops * world * args.steps / t_e2e / 1e12
+            line["e2e"]["unit"] = "TFLOP/s"
         if world == 1 and not args.no_cpu:
             v, threads, sample, dt = time_cpu(args.workload)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
