@@ -45,7 +45,9 @@ constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim halves o
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
 constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_TILE + 1024;
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 96;  // S: 64 fp32, P: 32 (64 x 16 bit), O: 128 fp32
+// Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
+// S buffer as 16-bit pairs, once the thread holds its scores in registers), O: 128 fp32 columns.
+constexpr uint32_t COL_S = 0, COL_O = 128;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct PageRef {  // where one 16-key page of a key block comes from
@@ -65,9 +67,10 @@ __global__ void __launch_bounds__(kThreads, 2)
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
   extern __shared__ uint8_t smem_raw[];
-  // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full: MMA -> softmax;
-  // p_full: softmax -> MMA (128 arrivals); o_full: last P.V done
-  __shared__ uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, p_full, o_full;
+  // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
+  // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
+  // o_full: last P.V done
+  __shared__ uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], pv_done, o_full;
   __shared__ uint32_t tmem_slot;
   __shared__ int red[4];  // anc_max, seg_min, anc_min, seg_max
   __shared__ volatile int dead;
@@ -102,8 +105,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, kSoftmaxThreads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], kSoftmaxThreads);
+    }
+    mbar_init(&pv_done, 1);
     mbar_init(&o_full, 1);
     mbar_fence_init();
     red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0;
@@ -255,26 +261,31 @@ __global__ void __launch_bounds__(kThreads, 2)
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint64_t da = umma_smem_desc(qa + (ks >> 2) * HALF_Q + (ks & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc(ka + (ks >> 2) * HALF_KV + (ks & 3) * 32, 16, 1024);
-          umma_ss(tmem + COL_S, da, db, idesc_qk, ks > 0);
+          umma_ss(tmem + COL_S + stage * BN, da, db, idesc_qk, ks > 0);
         }
         umma_commit(&k_empty[stage]);  // K[stage] may be refilled once these MMAs are done
-        umma_commit(&s_full);
+        umma_commit(&s_full[stage]);
       };
+      // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
+      // MMAs run in issue order, so Q.K^T of block b + 2 overwrites buffer b & 1 only after
+      // P.V of block b has read P from it.
       issue_qk(0);
+      if (nb > 1) issue_qk(1);
       for (int b = 0; b < nb; ++b) {
         const int stage = b & 1;
-        wait_bar(&p_full, b & 1, kStatusMmaTimeout);  // P_b is in tensor memory, S_b has been read
+        wait_bar(&p_full[stage], (b >> 1) & 1, kStatusMmaTimeout);  // P_b is in tensor memory
         wait_bar(&v_full[stage], (b >> 1) & 1, kStatusTmaTimeout);
         tc_fence_after_sync();
         const uint32_t va = smem_u32(v_sm + stage * KV_TILE);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           const uint64_t db = umma_smem_desc(va + ks * 2048, HALF_KV, 1024);
-          umma_ts(tmem + COL_O, tmem + COL_P + ks * 8, db, idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(tmem + COL_O, tmem + COL_S + stage * BN + ks * 8, db, idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[stage]);
-        if (b + 1 < nb) issue_qk(b + 1);  // runs behind P.V of block b in the tensor pipe
-        else umma_commit(&o_full);
+        umma_commit(&pv_done);
+        if (b + 2 < nb) issue_qk(b + 2);
+        if (b + 1 == nb) umma_commit(&o_full);
       }
     }
   } else {
@@ -293,11 +304,12 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (use_anc) need_mask = true;
         else need_mask = need_mask || !((j0 + BN - 1 < anc_min) || (j0 >= seg_max && j0 + BN - 1 <= r_first));
       }
-      wait_bar(&s_full, b & 1, kStatusMmaTimeout);  // S_b done, and every MMA issued before it
+      wait_bar(&s_full[stage], (b >> 1) & 1, kStatusMmaTimeout);
       tc_fence_after_sync();
+      const uint32_t t_s = t_lane + COL_S + stage * BN;
       uint32_t sr[2][32];
-      tmem_ld32(t_lane + COL_S, sr[0]);
-      tmem_ld32(t_lane + COL_S + 32, sr[1]);
+      tmem_ld32(t_s, sr[0]);
+      tmem_ld32(t_s + 32, sr[1]);
       tmem_wait_ld();
       float mx = -INFINITY;
       if (need_mask) {
@@ -340,10 +352,13 @@ __global__ void __launch_bounds__(kThreads, 2)
         pk[c] = QE::pack2(p0, p1);
       }
       l_run += ps0 + ps1;
-      tmem_st32(t_lane + COL_P, pk);
+      tmem_st32(t_s, pk);  // over the scores this thread has already read
+      if (b > 0) {
+        wait_bar(&pv_done, (b - 1) & 1, kStatusMmaTimeout);  // O holds blocks 0 .. b-1 and is idle
+        tc_fence_after_sync();
+      }
       if (b > 0 && __any_sync(0xffffffffu, grow)) {
-        // O of this warp's rows *= factor (1 for rows whose reference did not move); P.V of block
-        // b - 1 is complete (s_full of this block was committed after it).
+        // O of this warp's rows *= factor (1 for rows whose reference did not move)
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
@@ -366,7 +381,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         fence_proxy_async_smem();
       }
       tc_fence_before_sync();
-      mbar_arrive(&p_full);
+      mbar_arrive(&p_full[stage]);
     }
 
     // ---- epilogue
