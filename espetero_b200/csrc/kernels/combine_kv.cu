@@ -12,8 +12,9 @@
 namespace esp {
 namespace {
 
-// One CTA per (job row, head); thread = 4 dims. Records are read 8 at a time so that the
-// loads of a batch are in flight together. A record is HD + 2 floats long, so records are
+// One CTA per (job row, group of 512 / HD heads); thread = 4 dims of one head. Records are read
+// 8 at a time so that the loads of a batch are in flight together. The grid covers only
+// rows_max rows per job (1 for decode passes), not the whole tile_rows slot. A record is HD + 2 floats long, so records are
 // only 8-byte aligned: O is read as float2 pairs.
 __device__ __forceinline__ float4 ld_rec4(const float* p) {
   const float2 a = *reinterpret_cast<const float2*>(p), b = *reinterpret_cast<const float2*>(p + 2);
@@ -25,10 +26,12 @@ __global__ void combine_kernel(const CombineArgs a) {
   using QE = Elem16<QDT>;
   const esp_attn_params& p = a.p;
   const int HD = a.HD, G = a.G, TR = a.tile_rows;
-  const int job_i = blockIdx.x / TR, r = blockIdx.x % TR, h = blockIdx.y;
+  const int tpd = HD / 4;  // threads per head
+  const int job_i = blockIdx.x / a.rows_max, r = blockIdx.x % a.rows_max;
+  const int h = blockIdx.y * (blockDim.x / tpd) + threadIdx.x / tpd;
   const esp_attn_combine job = a.jobs[job_i];
-  if (r >= job.rows) return;
-  const int d4 = threadIdx.x;
+  if (r >= job.rows || h >= p.H) return;
+  const int d4 = threadIdx.x % tpd;
   const int kvh = h / G, hg = h % G;
   const size_t stride = size_t(p.Hkv) * TR * G * (HD + 2);
   const float* rec0 = a.parts + ((size_t(job.part0) * p.Hkv + kvh) * TR * G + size_t(r) * G + hg) * (HD + 2);
@@ -132,7 +135,8 @@ __global__ void kv_copy_blocks_kernel(uint4* kv, const int2* pairs, size_t blk2_
 
 cudaError_t launch_combine(const CombineArgs& a, cudaStream_t stream, uint64_t* launches) {
   if (a.n_jobs <= 0) return cudaSuccess;
-  const dim3 grid(unsigned(a.n_jobs) * unsigned(a.tile_rows), unsigned(a.p.H)), block(unsigned(a.HD / 4));
+  const int hpb = 512 / a.HD;  // heads per 128-thread block
+  const dim3 grid(unsigned(a.n_jobs) * unsigned(a.rows_max), unsigned((a.p.H + hpb - 1) / hpb)), block(128);
   if (a.q_dtype == ESP_F16) combine_kernel<ESP_F16><<<grid, block, 0, stream>>>(a);
   else combine_kernel<ESP_BF16><<<grid, block, 0, stream>>>(a);
   const cudaError_t e = cudaGetLastError();

@@ -139,6 +139,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
     esp::CombineArgs c{};
     c.parts = slot.parts, c.X = k.X, c.O = a.O, c.lse = a.lse, c.jobs = a.jobs, c.p = a.p;
     c.HD = s.HD, c.G = G, c.tile_rows = TR, c.n_jobs = a.n_jobs, c.q_dtype = s.q_dtype;
+    c.rows_max = 1;  // decode: one row per job
     if ((e = esp::launch_combine(c, stream, &launches)) != cudaSuccess) return cuda_fail(e, "attention_combine");
   }
   return ESP_OK;

@@ -54,6 +54,7 @@ struct CombineArgs {
   int32_t tile_rows;
   int32_t n_jobs;
   int32_t q_dtype;
+  int32_t rows_max;  // most rows of any job (<= tile_rows): the grid covers only these
 };
 
 // Each launcher enqueues on `stream`, returns cudaGetLastError() of the launch and

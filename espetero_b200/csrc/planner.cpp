@@ -98,6 +98,17 @@ extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_
     if (split > 0 && n_groups < slots) {
       const int64_t want = (ceil_div(work, slots) + 31) / 32 * 32;
       chunk = int32_t(std::clamp<int64_t>(want, std::max(32, opts->min_chunk), std::max(32, split)));
+      // One wave: grow the chunk until the tiles fit the slots (a few tiles over the slot count
+      // would cost a whole second wave).
+      const auto tiles_at = [&](int32_t c) {
+        int64_t n = 0;
+        for (int32_t i = 0; i < n_trees; ++i) {
+          const int64_t rg = (trees[i].M + TR - 1) / TR;
+          n += rg * (trees[i].P >= 64 ? std::min<int64_t>(ceil_div(trees[i].P, c), max_parts) : 1);
+        }
+        return n;
+      };
+      while (chunk < std::max(32, split) && tiles_at(chunk) > slots) chunk += 32;
     }
     for (int32_t ti = 0; ti < n_trees; ++ti) {
       const esp_attn_tree& t = trees[ti];
