@@ -266,18 +266,15 @@ def main():
 
     # ---- end to end through the C ABI from host buffers: the step's inputs (Q, Kb, Vb and the
     # plan tables) come from pinned host memory, the result goes back; the KV pool is device state.
-    def pinned(t):
-        return t.cpu().pin_memory()
-    h_in = [pinned(x) for x in (dp.Q, dp.Kb, dp.Vb, dp.tiles, dp.trees, dp.blocks) if x is not None]
-    d_in = [x for x in (dp.Q, dp.Kb, dp.Vb, dp.tiles, dp.trees, dp.blocks) if x is not None]
+    arena = host.StepArena(dp)
+    a_e2e = arena.patch(op.make_args(dp))
     h_out = torch.empty_like(dp.O, device="cpu").pin_memory()
-    h2d = sum(x.numel() * x.element_size() for x in h_in)
+    h2d = arena.nbytes
     d2h = h_out.numel() * h_out.element_size()
 
     def step_e2e():
-        for h, d in zip(h_in, d_in):
-            d.copy_(h, non_blocking=True)
-        op.forward(dp, a_full)
+        arena.upload()
+        op.forward(dp, a_e2e)
         h_out.copy_(dp.O, non_blocking=True)
     for _ in range(3):
         step_e2e()
@@ -310,7 +307,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": None, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},
             "e2e": {"value": bytes_all * args.steps / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "Q/Kb/Vb + plan tables from pinned host memory, O back to the host; the KV pool is resident device state"},
+                    "note": "Q/Kb/Vb + plan tables in one arena copied from pinned host memory, O back to the host; the KV pool is resident device state"},
             "gpu_launches": int(launches), "clocks": clocks, "tensor": tensor,
         }
         if args.workload == "c3":  # the prefill configuration is bound by the tensor cores, not by HBM

@@ -196,7 +196,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
 }  // namespace
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
-                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max);
+                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max);
 
 extern "C" {
 
@@ -342,12 +342,15 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   }
   if (e != cudaSuccess) return cuda_fail(e, c->last_kernel);
   if (a.n_jobs > 0) {
-    int rows_max = c->tile_rows;
+    int rows_max = c->tile_rows, parts_max = 64;
     if (a.jobs_host) {
-      rows_max = 1;
-      for (int i = 0; i < a.n_jobs; ++i) rows_max = a.jobs_host[i].rows > rows_max ? a.jobs_host[i].rows : rows_max;
+      rows_max = 1, parts_max = 1;
+      for (int i = 0; i < a.n_jobs; ++i) {
+        rows_max = a.jobs_host[i].rows > rows_max ? a.jobs_host[i].rows : rows_max;
+        parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
+      }
     }
-    return combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max);
+    return combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max);
   }
   return ESP_OK;
 }
@@ -355,13 +358,13 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
 int esp_attn_combine_parts(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
                            const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs) {
   if (!c) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
-  return combine_impl(c, stream, parts, X, O, lse, p, jobs, n_jobs, c->tile_rows);
+  return combine_impl(c, stream, parts, X, O, lse, p, jobs, n_jobs, c->tile_rows, 64);
 }
 
 }  // extern "C"
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
-                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max) {
+                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max) {
   if (!c || !p) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
   if (n_jobs <= 0) return ESP_OK;
   if (!parts || !O || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
@@ -372,6 +375,7 @@ static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const
   k.parts = parts, k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? X : nullptr, k.O = O, k.lse = lse, k.jobs = jobs, k.p = *p;
   k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_jobs = n_jobs, k.q_dtype = s.q_dtype;
   k.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
+  k.n_slices = esp::combine_slices(s.HD, parts_max);
   const cudaError_t e = esp::launch_combine(k, static_cast<cudaStream_t>(stream), &c->launches);
   if (e != cudaSuccess) return cuda_fail(e, "attention_combine");
   return ESP_OK;

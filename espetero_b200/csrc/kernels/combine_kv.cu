@@ -12,57 +12,83 @@
 namespace esp {
 namespace {
 
-// One CTA per (job row, group of 512 / HD heads); thread = 4 dims of one head. Records are read
-// 8 at a time so that the loads of a batch are in flight together. The grid covers only
-// rows_max rows per job (1 for decode passes), not the whole tile_rows slot. A record is HD + 2 floats long, so records are
-// only 8-byte aligned: O is read as float2 pairs.
+// One CTA of 128 threads per (job row, group of heads). A head is served by HD / 4 threads (4 dims
+// each) times n_slices record slices: slice k takes the records k, k + n_slices, ... so that many
+// record loads are in flight at once (a single sequential walk over 64 records is latency-bound);
+// passes with few records per job use fewer slices and put more heads in a CTA. The maximum M is
+// found first by all threads of the head, so every slice weighs its records with the final
+// e^(m_s - M); the slices' sums are then added in slice order through shared memory: no atomics,
+// the result does not depend on scheduling. The grid covers only rows_max rows per job (1 for
+// decode passes). A record is HD + 2 floats long, so records are only 8-byte aligned: float2 loads.
 __device__ __forceinline__ float4 ld_rec4(const float* p) {
   const float2 a = *reinterpret_cast<const float2*>(p), b = *reinterpret_cast<const float2*>(p + 2);
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
+constexpr int kCombineThreads = 128;
+
 template <int QDT>
-__global__ void combine_kernel(const CombineArgs a) {
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
   using QE = Elem16<QDT>;
+  __shared__ float red_m[kCombineThreads / 32];
+  __shared__ float red_acc[kCombineThreads][5];
   const esp_attn_params& p = a.p;
   const int HD = a.HD, G = a.G, TR = a.tile_rows;
-  const int tpd = HD / 4;  // threads per head
+  const int tpd = HD / 4, nsl = a.n_slices;  // threads per record, record slices per head
+  const int tph = tpd * nsl;                 // threads per head (a multiple of 32)
   const int job_i = blockIdx.x / a.rows_max, r = blockIdx.x % a.rows_max;
-  const int h = blockIdx.y * (blockDim.x / tpd) + threadIdx.x / tpd;
+  const int hb = threadIdx.x / tph;          // head within the CTA
+  const int h = blockIdx.y * (kCombineThreads / tph) + hb;
+  // The records are written by the attention kernel launched just before on the same stream:
+  // with programmatic dependent launch this grid may start early and waits here for them.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const esp_attn_combine job = a.jobs[job_i];
-  if (r >= job.rows || h >= p.H) return;
-  const int d4 = threadIdx.x % tpd;
+  if (r >= job.rows) return;
+  const int tid = threadIdx.x, sl = (tid % tph) / tpd, d4 = tid % tpd;
   const int kvh = h / G, hg = h % G;
   const size_t stride = size_t(p.Hkv) * TR * G * (HD + 2);
   const float* rec0 = a.parts + ((size_t(job.part0) * p.Hkv + kvh) * TR * G + size_t(r) * G + hg) * (HD + 2);
   const int n = job.nparts;
   float M = -INFINITY;
-  for (int s = 0; s < n; ++s) M = fmaxf(M, rec0[size_t(s) * stride + HD]);
+  for (int s = tid % tph; s < n; s += tph) M = fmaxf(M, rec0[size_t(s) * stride + HD]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if ((tid & 31) == 0) red_m[tid >> 5] = M;
+  __syncthreads();
+  M = -INFINITY;
+  for (int w = hb * (tph / 32); w < (hb + 1) * (tph / 32); ++w) M = fmaxf(M, red_m[w]);
   float L = 0.0f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int s = 0;
-  for (; s + 8 <= n; s += 8) {
-    float m8[8], l8[8];
-    float4 o8[8];
+  int s = sl;
+  for (; s + 3 * nsl < n; s += 4 * nsl) {
+    float m4[4], l4[4];
+    float4 o4[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float* rec = rec0 + size_t(s + i) * stride;
-      m8[i] = rec[HD], l8[i] = rec[HD + 1];
-      o8[i] = ld_rec4(rec + 4 * d4);
+    for (int i = 0; i < 4; ++i) {
+      const float* rec = rec0 + size_t(s + i * nsl) * stride;
+      m4[i] = rec[HD], l4[i] = rec[HD + 1];
+      o4[i] = ld_rec4(rec + 4 * d4);
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float w = (m8[i] == -INFINITY) ? 0.0f : __expf(m8[i] - M);
-      L += w * l8[i];
-      acc.x += w * o8[i].x, acc.y += w * o8[i].y, acc.z += w * o8[i].z, acc.w += w * o8[i].w;
+    for (int i = 0; i < 4; ++i) {
+      const float w = (m4[i] == -INFINITY) ? 0.0f : __expf(m4[i] - M);
+      L += w * l4[i];
+      acc.x += w * o4[i].x, acc.y += w * o4[i].y, acc.z += w * o4[i].z, acc.w += w * o4[i].w;
     }
   }
-  for (; s < n; ++s) {
+  for (; s < n; s += nsl) {
     const float* rec = rec0 + size_t(s) * stride;
     const float w = (rec[HD] == -INFINITY) ? 0.0f : __expf(rec[HD] - M);
     const float4 o = ld_rec4(rec + 4 * d4);
     L += w * rec[HD + 1];
     acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
+  }
+  red_acc[tid][0] = acc.x, red_acc[tid][1] = acc.y, red_acc[tid][2] = acc.z, red_acc[tid][3] = acc.w, red_acc[tid][4] = L;
+  __syncthreads();
+  if (sl != 0) return;
+  for (int k = 1; k < nsl; ++k) {  // fixed order
+    const float* q = red_acc[hb * tph + k * tpd + d4];
+    acc.x += q[0], acc.y += q[1], acc.z += q[2], acc.w += q[3], L += q[4];
   }
   const int row = job.r0 + r;
   const float inv = L > 0.0f ? 1.0f / L : 0.0f;
@@ -135,11 +161,22 @@ __global__ void kv_copy_blocks_kernel(uint4* kv, const int2* pairs, size_t blk2_
 
 cudaError_t launch_combine(const CombineArgs& a, cudaStream_t stream, uint64_t* launches) {
   if (a.n_jobs <= 0) return cudaSuccess;
-  const int hpb = 512 / a.HD;  // heads per 128-thread block
-  const dim3 grid(unsigned(a.n_jobs) * unsigned(a.rows_max), unsigned((a.p.H + hpb - 1) / hpb)), block(128);
-  if (a.q_dtype == ESP_F16) combine_kernel<ESP_F16><<<grid, block, 0, stream>>>(a);
-  else combine_kernel<ESP_BF16><<<grid, block, 0, stream>>>(a);
-  const cudaError_t e = cudaGetLastError();
+  // Programmatic dependent launch: the grid may be scheduled while the attention kernel before
+  // it drains; griddepcontrol.wait in the kernel orders it after that kernel's writes.
+  cudaLaunchConfig_t cfg{};
+  const int hpb = kCombineThreads / ((a.HD / 4) * a.n_slices);  // heads per CTA
+  cfg.gridDim = dim3(unsigned(a.n_jobs) * unsigned(a.rows_max), unsigned((a.p.H + hpb - 1) / hpb));
+  cfg.blockDim = dim3(kCombineThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, combine_kernel<ESP_F16>, a)
+                                       : cudaLaunchKernelEx(&cfg, combine_kernel<ESP_BF16>, a);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;
 }

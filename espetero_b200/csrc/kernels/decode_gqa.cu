@@ -273,6 +273,10 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     __syncwarp();  // every lane is done with the slot before lane 0 refills it
   }
 
+  // The streaming part is over: let a dependent grid (the combine kernel) be scheduled while
+  // this one merges and drains; it still waits for this grid's completion before it reads.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   // ---- merge the warps through shared memory (their rings are idle now)
 #pragma unroll
   for (int off = 4; off <= 16; off <<= 1) {

@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
 
     // ---- epilogue
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine grid may be scheduled
     if (nb > 0) {
       wait_bar(&o_full, 0, kStatusMmaTimeout);
       tc_fence_after_sync();

@@ -140,6 +140,12 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
     c.parts = slot.parts, c.X = k.X, c.O = a.O, c.lse = a.lse, c.jobs = a.jobs, c.p = a.p;
     c.HD = s.HD, c.G = G, c.tile_rows = TR, c.n_jobs = a.n_jobs, c.q_dtype = s.q_dtype;
     c.rows_max = 1;  // decode: one row per job
+    int parts_max = 64;  // same slicing as esp_attn_forward, so that the two give identical bits
+    if (a.jobs_host) {
+      parts_max = 1;
+      for (int i = 0; i < a.n_jobs; ++i) parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
+    }
+    c.n_slices = esp::combine_slices(s.HD, parts_max);
     if ((e = esp::launch_combine(c, stream, &launches)) != cudaSuccess) return cuda_fail(e, "attention_combine");
   }
   return ESP_OK;

@@ -55,7 +55,17 @@ struct CombineArgs {
   int32_t n_jobs;
   int32_t q_dtype;
   int32_t rows_max;  // most rows of any job (<= tile_rows): the grid covers only these
+  int32_t n_slices;  // record slices per head: a power of two, 32 <= (HD / 4) * n_slices <= 128
 };
+
+// Record slices per head for the combine kernel: about a quarter of the job's records per slice,
+// at least one warp per head, at most one CTA (128 threads) per head.
+inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
+  const int tpd = HD / 4;
+  int nsl = 128 / tpd;
+  while (nsl > 1 && nsl * 2 > parts_max && tpd * (nsl / 2) >= 32) nsl /= 2;
+  return nsl;
+}
 
 // Each launcher enqueues on `stream`, returns cudaGetLastError() of the launch and
 // adds the number of kernels it launched to *launches.

@@ -86,6 +86,43 @@ class DevicePass:
         self.parts = torch.zeros(max(4, parts_floats), dtype=torch.float32, device=self.device)
 
 
+class StepArena:
+    """The per-step inputs of a pass (Q, Kb, Vb, tiles, trees, block table) laid out in ONE device
+    buffer with a pinned host mirror, as the reference keeps its per-pass tables in one arena
+    (PassMeta, src/model/impl/forest.h:1678-1735): a step then needs one host-to-device copy."""
+
+    def __init__(self, dp: DevicePass):
+        parts = [("Q", dp.Q), ("Kb", dp.Kb), ("Vb", dp.Vb), ("tiles", dp.tiles), ("trees", dp.trees), ("blocks", dp.blocks)]
+        self.offsets, off = {}, 0
+        for name, t in parts:
+            if t is None:
+                continue
+            self.offsets[name] = (off, t.numel() * t.element_size())
+            off = (off + t.numel() * t.element_size() + 255) // 256 * 256
+        self.nbytes = off
+        self.dev = torch.empty(off, dtype=torch.uint8, device=dp.device)
+        self.host = torch.empty(off, dtype=torch.uint8).pin_memory()
+        for name, t in parts:
+            if t is None:
+                continue
+            o, n = self.offsets[name]
+            self.host[o:o + n] = t.contiguous().view(-1).view(torch.uint8).cpu()
+        self.dev.copy_(self.host)
+
+    def ptr(self, name: str):
+        return self.dev.data_ptr() + self.offsets[name][0] if name in self.offsets else None
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def patch(self, args: capi.Args) -> capi.Args:
+        """Point the step inputs of `args` into the arena."""
+        for name in ("Q", "Kb", "Vb", "tiles", "trees", "blocks"):
+            if name in self.offsets:
+                setattr(args, name, self.ptr(name))
+        return args
+
+
 class AttnOp:
     """One esp_attn_ctx. Not thread-safe, like the reference's NativeModel (src/model/api.h:4-6)."""
 
