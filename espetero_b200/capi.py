@@ -52,6 +52,12 @@ class PlanOpts(C.Structure):
                 ("tile_rows", C.c_int32), ("max_parts", C.c_int32), ("reserved", C.c_int32 * 2)]
 
 
+class TreeSpec(C.Structure):
+    _fields_ = [("root", C.POINTER(C.c_int32)), ("root_len", C.c_int32), ("n_leaves", C.c_int32),
+                ("root_pos", C.POINTER(C.c_int32)), ("leaf_offsets", C.POINTER(C.c_int32)), ("leaf_tokens", C.POINTER(C.c_int32)),
+                ("noncausal", C.c_int32), ("score_root", C.c_int32)]
+
+
 class Args(C.Structure):
     _fields_ = [("Q", C.c_void_p), ("Kb", C.c_void_p), ("Vb", C.c_void_p), ("kv", C.c_void_p), ("kv_scales", C.c_void_p),
                 ("blocks", C.c_void_p), ("desc", C.c_void_p), ("anc_mask", C.c_void_p), ("X", C.c_void_p), ("O", C.c_void_p),
@@ -83,6 +89,21 @@ PROTOTYPES = {
                               C.POINTER(Params)]),
     "esp_kv_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(Params), C.c_uint64,
                                      C.c_int32]),
+    "esp_kv_pool_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32]),
+    "esp_kv_pool_destroy": (C.c_int, [C.c_void_p]),
+    "esp_kv_free_count": (C.c_int32, [C.c_void_p]),
+    "esp_kv_refcount": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "esp_kv_alloc": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "esp_kv_retain": (C.c_int, [C.c_void_p, C.c_int32]),
+    "esp_kv_release": (C.c_int, [C.c_void_p, C.c_int32]),
+    "esp_kv_target_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                       C.c_int32, C.POINTER(C.c_int32), C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "esp_kv_target_new_blocks": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "esp_kv_save_entries": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "esp_kv_row_table": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "esp_forest_tree_rows": (C.c_int, [C.POINTER(TreeSpec), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "esp_forest_anc_masks": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "esp_attn_decode_static": (C.c_int, [C.POINTER(Shape), C.c_void_p, C.POINTER(Args)]),
     "esp_attn_last_kernel": (C.c_char_p, [C.c_void_p]),
     "esp_attn_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -223,6 +223,69 @@ int esp_kv_save(esp_attn_ctx* ctx, void* stream, const void* Kb, const void* Vb,
 int esp_kv_copy_blocks(esp_attn_ctx* ctx, void* stream, void* kv, const int32_t* pairs, int32_t n_pairs,
                        const esp_attn_params* p, uint64_t region_elems, int32_t n_layers);
 
+/* ------------------------------------------------- KV blocks and row metadata (host) */
+/* Pure host functions (no GPU needed): the integer bookkeeping run_forest does before it
+ * encodes a pass. */
+
+/* Refcounted block pool: KVPool::ref / free_list with kv_alloc / kv_retain / kv_release
+ * (src/model/impl/model.h:387-411, :722-737; set-up forest.h:51-62: block 0 is handed out
+ * first). esp_kv_alloc fails with ESP_ERR_CAPACITY ("KV cache full") when no block is free. */
+typedef struct esp_kv_pool esp_kv_pool;
+int esp_kv_pool_create(esp_kv_pool** out, int32_t n_blocks, int32_t bt);
+int esp_kv_pool_destroy(esp_kv_pool* pool);
+int32_t esp_kv_free_count(const esp_kv_pool* pool);
+int32_t esp_kv_refcount(const esp_kv_pool* pool, int32_t block);
+int esp_kv_alloc(esp_kv_pool* pool, int32_t* block);
+int esp_kv_retain(esp_kv_pool* pool, int32_t block);
+int esp_kv_release(esp_kv_pool* pool, int32_t block);
+
+/* Forest::target_blocks (forest.h:1785-1811): the block list of a target that continues a
+ * parent list covering [0, P) and writes positions [w0, end). Blocks entirely below w0 are
+ * shared (retained), the rest are new; a new block that replaces a parent block holding
+ * positions below P is reported as a copy-on-write pair (src, dst); an in-place append keeps
+ * a partial block it owns alone. If the pool cannot supply every new block the call fails
+ * with ESP_ERR_CAPACITY and leaves the pool unchanged (the reference releases them through
+ * its PassGuard, forest.h:2468-2482). With out_blocks == NULL only the counts are reported. */
+int esp_kv_target_blocks(esp_kv_pool* pool, const int32_t* parent_blocks, int32_t n_parent, int32_t P, int32_t w0, int32_t end,
+                         int32_t in_place, int32_t* out_blocks, int32_t out_cap, int32_t* n_out, int32_t* cow_pairs,
+                         int32_t cow_cap, int32_t* n_cow);
+/* target_new_blocks (forest.h:1819-1829): how many blocks the call above would allocate. */
+int32_t esp_kv_target_new_blocks(const esp_kv_pool* pool, const int32_t* parent_blocks, int32_t n_parent, int32_t P, int32_t w0,
+                                 int32_t end, int32_t in_place);
+/* The kv_save records of rows [base_row, base_row + n_rows) written at positions P, P + 1, ...
+ * of a block list (add_saves, forest.h:2488-2499). */
+int esp_kv_save_entries(const int32_t* blocks, int32_t n_blocks_list, int32_t bt, int32_t P, int32_t base_row, int32_t n_rows,
+                        esp_kv_save_entry* out);
+/* kv_row_table (forest.h:1739-1749): per row the (block, pos) x 2 its K/V go to, -1 = none;
+ * table holds max(rows, 1) * 4 ints. A row saved into more than two slots is an error. */
+int esp_kv_row_table(const esp_kv_save_entry* entries, int32_t n, int32_t rows, int32_t* table);
+
+/* One tree of a pass, as far as attention is concerned (TreeSpec, src/model/api.h:105-176). */
+typedef struct esp_tree_spec {
+  const int32_t* root;         /* root_len tokens */
+  int32_t root_len;
+  int32_t n_leaves;
+  const int32_t* root_pos;     /* [root_len][3] M-RoPE positions, or NULL */
+  const int32_t* leaf_offsets; /* n_leaves + 1 */
+  const int32_t* leaf_tokens;
+  int32_t noncausal;           /* root rows see the whole root (no leaves allowed) */
+  int32_t score_root;          /* one more readout at the root's last row */
+} esp_tree_spec;
+
+/* Rows of one tree (forest.h:2201-2220 leaf hosting, :2374-2442 records): host[i] = the leaf
+ * whose rows leaf i is read from (a leaf that is a prefix of another is not given rows),
+ * off[i] = first leaf row of a hosting leaf relative to the end of the root; per row tok,
+ * pos (int4: t, h, w, 0; the root continues at pnext, leaf rows at next_root + j) and desc
+ * (int4: seg_start, 0, anc_len, 0 relative to the tree's first row); readout_rows = the
+ * absolute last row of every leaf, then the root's when score_root or there are no leaves.
+ * base = absolute first row of the tree. */
+int esp_forest_tree_rows(const esp_tree_spec* spec, int32_t base, int32_t pnext, int32_t* host, int32_t* off, int32_t* tok,
+                         int32_t* pos4, int32_t* desc4, int32_t* readout_rows, int32_t rows_cap, int32_t* n_rows,
+                         int32_t* next_root);
+/* Ancestor masks of a general draft tree (node i's parent < i, -1 for a root): bit j of
+ * masks[i] = node j is node i or one of its ancestors. The input of ESP_ATTN_FLAG_ANC_MASK. */
+int esp_forest_anc_masks(const int32_t* parents, int32_t n, uint64_t* masks);
+
 /* Decode attention for callers that cannot allocate device memory when they run it: an
  * engine that gave the whole GPU to one arena at start-up, a plugin inside a process whose
  * allocator owns the device, a serving loop that forbids cudaMalloc / cudaFree (and the
