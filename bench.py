@@ -218,17 +218,54 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     W = max(3, args.warmup)
 
-    w = build_workload(args.workload, rank, args.small)
+    from espetero_b200 import shard
     tile_rows = TILE_ROWS[args.workload]
-    op = host.AttnOp.for_workload(w, tile_rows, local)
-    groups = args.groups or 148 * 2 * 8
-    plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
-    dp = op.upload(w, plan)
-    a_full = op.make_args(dp)
-    a_attn = op.make_args(dp)
-    a_attn.n_jobs = 0  # attention kernel alone (no combine), for the per-kernel roofline figure
+    split_kv = args.workload == "c5" and world > 1
+    groups = args.groups or (148 * 2 if args.workload == "c4" else 148 * 2 * 8)
+    if not split_kv:
+        w = build_workload(args.workload, rank, args.small)
+        op = host.AttnOp.for_workload(w, tile_rows, local)
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
+        dp = op.upload(w, plan)
+        a_full = op.make_args(dp)
+        a_attn = op.make_args(dp)
+        a_attn.n_jobs = 0  # attention kernel alone (no combine), for the per-kernel roofline figure
+        step = lambda: op.forward(dp, a_full)
+        step_attn = lambda: op.forward(dp, a_attn)
+        sharding, scaling = "sequences per rank, no collective", "weak"
+    else:
+        # One long sequence, keys split over the ranks on page boundaries: records for the local
+        # keys -> one reduced record per rank -> NCCL all-gather -> every rank merges the world's
+        # records in rank order. Total work is fixed: strong scaling.
+        ctx_all = 8192 if args.small else 131072
+        lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
+        w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
+        op = host.AttnOp.for_workload(w, tile_rows, local)
+        base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 148 * 2 * 2, tile_rows)
+        tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
+        plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, tile_rows)
+        dp = op.upload(w, plan)
+        for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
+            dist.broadcast(t, src=0)
+        a_attn = op.make_args(dp)
+        a_full = a_attn
+        red_dev = host._dev(red_jobs, dev)
+        merge_dev = host._dev(shard.world_merge_jobs(1, world), dev)
+        rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
+        rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)
+
+        def step():
+            op.forward(dp, a_attn)
+            op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
+            dist.all_gather_into_tensor(rec_world, rec_local)
+            op.combine(dp, rec_world, merge_dev, 1)
+        step_attn = lambda: op.forward(dp, a_attn)
+        sharding, scaling = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank", "strong"
     bytes_step = w.kv_bytes_read()
     stream = torch.cuda.current_stream(dev)
+    # Working sets that fit the 126 MB L2 are flushed out between timed iterations by writing a
+    # 512 MB buffer; larger inputs evict themselves.
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev) if bytes_step < 2 * 126e6 else None
 
     def barrier():
         if world > 1:
@@ -236,17 +273,29 @@ def main():
         torch.cuda.synchronize(dev)
 
     def timed(fn, n):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        """Seconds for n calls of fn: CUDA events on the launching stream, barrier + synchronize on both
+        sides; with an L2 flush each call is timed on its own and the flush stays outside."""
         barrier()
-        e0.record(stream)
+        if flush is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(n):
+                fn()
+            e1.record(stream)
+            barrier()
+            return e0.elapsed_time(e1) / 1e3
+        evs = []
         for _ in range(n):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
             fn()
-        e1.record(stream)
+            e1.record(stream)
+            evs.append((e0, e1))
         barrier()
-        return e0.elapsed_time(e1) / 1e3  # seconds
+        return sum(a.elapsed_time(b) for a, b in evs) / 1e3
 
     # ---- device-resident throughput (value)
-    step = lambda: op.forward(dp, a_full)
     for _ in range(W):
         step()
     op.check_status()
@@ -257,7 +306,6 @@ def main():
     t_total = timed(step, args.steps)
     launches = op.launch_count - n0
     # ---- attention kernel alone (roofline of the dominant kernel)
-    step_attn = lambda: op.forward(dp, a_attn)
     for _ in range(3):
         step_attn()
     t_attn = timed(step_attn, args.steps) / args.steps
@@ -272,9 +320,16 @@ def main():
     h2d = arena.nbytes
     d2h = h_out.numel() * h_out.element_size()
 
+    if split_kv:
+        a_attn.Q, a_attn.Kb, a_attn.Vb = a_e2e.Q, a_e2e.Kb, a_e2e.Vb  # the step reads its inputs from the arena
+        a_attn.tiles, a_attn.trees, a_attn.blocks = a_e2e.tiles, a_e2e.trees, a_e2e.blocks
+
     def step_e2e():
         arena.upload()
-        op.forward(dp, a_e2e)
+        if split_kv:
+            step()
+        else:
+            op.forward(dp, a_e2e)
         h_out.copy_(dp.O, non_blocking=True)
     for _ in range(3):
         step_e2e()
@@ -298,12 +353,12 @@ def main():
                   "flops_per_step": flops}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": W,
-            "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16" if w.kv_dtype != wl.E4M3 else "e4m3->f16", "data": "synthetic",
             "config": {"workload": w.name, "sequences_per_gpu": len(w.trees), "H": w.H, "Hkv": w.Hkv, "HD": w.HD, "page": w.bt,
                        "kv_bytes_per_gpu": bytes_step, "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": op.last_kernel,
-                       "l2": "inputs larger than L2" if bytes_step > 2 * 126e6 else "inputs fit L2: warm-cache number",
-                       "sharding": "sequences per rank, no collective"},
+                       "l2": "inputs larger than L2" if flush is None else "L2 flushed between timed iterations (512 MB write, outside the timed region)",
+                       "sharding": sharding},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": None, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},
             "e2e": {"value": bytes_all * args.steps / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -85,6 +85,8 @@ PROTOTYPES = {
     "esp_attn_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Args)]),
     "esp_attn_combine_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.POINTER(Params), C.c_void_p, C.c_int32]),
+    "esp_attn_reduce_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p,
+                                        C.c_int32]),
     "esp_kv_save": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                               C.POINTER(Params)]),
     "esp_kv_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(Params), C.c_uint64,

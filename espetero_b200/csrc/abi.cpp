@@ -196,7 +196,8 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
 }  // namespace
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
-                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max);
+                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
+                        float* out_parts = nullptr, int32_t out_part0 = 0);
 
 extern "C" {
 
@@ -361,13 +362,20 @@ int esp_attn_combine_parts(esp_attn_ctx* c, void* stream, const float* parts, co
   return combine_impl(c, stream, parts, X, O, lse, p, jobs, n_jobs, c->tile_rows, 64);
 }
 
+int esp_attn_reduce_parts(esp_attn_ctx* c, void* stream, const float* parts, const esp_attn_params* p, const esp_attn_combine* jobs,
+                          int32_t n_jobs, float* parts_out, int32_t out_part0) {
+  if (!c || !parts_out || out_part0 < 0) return fail(ESP_ERR_INVALID, "esp_attn_reduce_parts: null or negative argument");
+  return combine_impl(c, stream, parts, nullptr, nullptr, nullptr, p, jobs, n_jobs, c->tile_rows, 64, parts_out, out_part0);
+}
+
 }  // extern "C"
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
-                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max) {
+                        const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
+                        float* out_parts, int32_t out_part0) {
   if (!c || !p) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
   if (n_jobs <= 0) return ESP_OK;
-  if (!parts || !O || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
+  if (!parts || (!O && !out_parts) || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
   if (int rc = check_params(c, *p)) return rc;
   const esp_attn_shape& s = c->shape;
   if ((s.flags & ESP_ATTN_FLAG_GATE) && !X) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: gate flag set but X is null");
@@ -376,6 +384,7 @@ static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const
   k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_jobs = n_jobs, k.q_dtype = s.q_dtype;
   k.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
   k.n_slices = esp::combine_slices(s.HD, parts_max);
+  k.out_parts = out_parts, k.out_part0 = out_part0;
   const cudaError_t e = esp::launch_combine(k, static_cast<cudaStream_t>(stream), &c->launches);
   if (e != cudaSuccess) return cuda_fail(e, "attention_combine");
   return ESP_OK;

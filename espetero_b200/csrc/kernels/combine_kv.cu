@@ -90,6 +90,18 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
     const float* q = red_acc[hb * tph + k * tpd + d4];
     acc.x += q[0], acc.y += q[1], acc.z += q[2], acc.w += q[3], L += q[4];
   }
+  if (a.out_parts) {
+    // Reduce mode: the merged, still unnormalised record [O | M | L] of the job, for a second
+    // merge level (records of other GPUs).
+    float* rec = a.out_parts + ((size_t(a.out_part0 + job_i) * p.Hkv + kvh) * TR * G + size_t(r) * G + hg) * (HD + 2);
+    *reinterpret_cast<float2*>(rec + 4 * d4) = make_float2(acc.x, acc.y);
+    *reinterpret_cast<float2*>(rec + 4 * d4 + 2) = make_float2(acc.z, acc.w);
+    if (d4 == 0) {
+      rec[HD] = M;
+      rec[HD + 1] = L;
+    }
+    return;
+  }
   const int row = job.r0 + r;
   const float inv = L > 0.0f ? 1.0f / L : 0.0f;
   float o[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};

@@ -140,6 +140,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
     c.parts = slot.parts, c.X = k.X, c.O = a.O, c.lse = a.lse, c.jobs = a.jobs, c.p = a.p;
     c.HD = s.HD, c.G = G, c.tile_rows = TR, c.n_jobs = a.n_jobs, c.q_dtype = s.q_dtype;
     c.rows_max = 1;  // decode: one row per job
+    c.out_parts = nullptr, c.out_part0 = 0;
     int parts_max = 64;  // same slicing as esp_attn_forward, so that the two give identical bits
     if (a.jobs_host) {
       parts_max = 1;

@@ -56,6 +56,8 @@ struct CombineArgs {
   int32_t q_dtype;
   int32_t rows_max;  // most rows of any job (<= tile_rows): the grid covers only these
   int32_t n_slices;  // record slices per head: a power of two, 32 <= (HD / 4) * n_slices <= 128
+  float* out_parts;  // reduce mode: job j's merged record goes to record out_part0 + j here; else NULL
+  int32_t out_part0;
 };
 
 // Record slices per head for the combine kernel: about a quarter of the job's records per slice,

@@ -199,6 +199,13 @@ class AttnOp:
         capi.check(self.lib.esp_attn_combine_parts(self.ctx, C.c_void_p(s), _ptr(parts), _ptr(dp.X), _ptr(dp.O), _ptr(dp.lse),
                                                    C.byref(p), _ptr(jobs_dev), n_jobs))
 
+    def reduce_parts(self, dp: DevicePass, parts, jobs_dev, n_jobs: int, parts_out, out_part0: int = 0, stream: int | None = None):
+        """esp_attn_reduce_parts: job j's records -> one unnormalised record out_part0 + j of parts_out."""
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        p = self.params(dp.w)
+        capi.check(self.lib.esp_attn_reduce_parts(self.ctx, C.c_void_p(s), _ptr(parts), C.byref(p), _ptr(jobs_dev), n_jobs,
+                                                  _ptr(parts_out), out_part0))
+
     def kv_save(self, dp: DevicePass, entries: np.ndarray, stream: int | None = None):
         s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
         e = _dev(np.ascontiguousarray(entries, dtype=KVSAVE_DT), self.device)

@@ -212,6 +212,14 @@ int esp_attn_forward(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args)
 int esp_attn_combine_parts(esp_attn_ctx* ctx, void* stream, const float* parts, const float* X, void* O, float* lse,
                            const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs);
 
+/* First level of a two-level merge (no counterpart in the reference, which has one GPU): job j's
+ * records are merged into ONE still unnormalised record [O | M | L], written as record
+ * out_part0 + j of parts_out (same layout as `parts`). A GPU that holds only part of a
+ * sequence's keys reduces its local records this way, the ranks exchange the reduced records
+ * (33 KB per row for H32 / HD256) and esp_attn_combine_parts finishes the merge. */
+int esp_attn_reduce_parts(esp_attn_ctx* ctx, void* stream, const float* parts, const esp_attn_params* p,
+                          const esp_attn_combine* jobs, int32_t n_jobs, float* parts_out, int32_t out_part0);
+
 /* kv_save (40_attention.metal:875-889; forest.h:2935-2947). With an ESP_E4M3
  * pool the rows are quantised with the destination block's scale from kv_scales. */
 int esp_kv_save(esp_attn_ctx* ctx, void* stream, const void* Kb, const void* Vb, void* kv, const float* kv_scales,
