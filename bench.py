@@ -246,7 +246,7 @@ def main():
         plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, tile_rows)
         dp = op.upload(w, plan)
         for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
-            dist.broadcast(t, src=0)
+            dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
         a_attn = op.make_args(dp)
         a_full = a_attn
         red_dev = host._dev(red_jobs, dev)
