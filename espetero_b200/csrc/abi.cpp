@@ -26,6 +26,8 @@ struct esp_attn_ctx {
   uint64_t launches = 0;
   const char* last_kernel = "";
   int* d_status = nullptr;
+  unsigned long long* trace = nullptr;  // caller-owned device buffer (esp_attn_set_trace)
+  int32_t trace_blocks = 0;
   // driver entry point for tensor maps, resolved without linking libcuda
   void* encode_tiled = nullptr;
   // cached pool tensor map
@@ -274,6 +276,13 @@ int esp_attn_get_option(const esp_attn_ctx* c, const char* name, int* value) {
   return ESP_OK;
 }
 
+int esp_attn_set_trace(esp_attn_ctx* c, void* device_buffer, int32_t n_blocks) {
+  if (!c || n_blocks < 0) return fail(ESP_ERR_INVALID, "esp_attn_set_trace: bad argument");
+  c->trace = n_blocks > 0 ? static_cast<unsigned long long*>(device_buffer) : nullptr;
+  c->trace_blocks = c->trace ? n_blocks : 0;
+  return ESP_OK;
+}
+
 const char* esp_attn_last_kernel(const esp_attn_ctx* c) { return c ? c->last_kernel : ""; }
 uint64_t esp_attn_launch_count(const esp_attn_ctx* c) { return c ? c->launches : 0; }
 
@@ -312,6 +321,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
   k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
   k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status;
+  k.trace = c->trace, k.trace_blocks = c->trace_blocks;
   k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
 

@@ -193,6 +193,12 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   };
 
+  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  auto stamp = [&](int b, int ev) {
+    if (tracing && b < a.trace_blocks) a.trace[8 * b + ev] = global_timer_ns();
+  };
+  if (tracing && tid == 0) a.trace[8 * a.trace_blocks] = global_timer_ns();
+
   if (warp == kTmaWarp) {
     // ================= TMA producer: lane w loads the w-th 16-key page of every block
     if (lane < 4 && nb > 0) {
@@ -232,6 +238,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           tma_load_3d(kd, cur.kind ? &kb_map : &pool_map, &k_full[stage], 0, y, kvh * 2);
           tma_load_3d(kd + HALF_KV, cur.kind ? &kb_map : &pool_map, &k_full[stage], 0, y, kvh * 2 + 1);
         }
+        if (lane == 0) stamp(b, 6);
         wait_bar(&v_empty[stage], par, kStatusMmaTimeout);
         if (cur.kind < 0) {
           mbar_arrive(&v_full[stage]);
@@ -241,6 +248,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           tma_load_3d(vd, cur.kind ? &vb_map : &pool_map, &v_full[stage], 0, y, kvh * 2);
           tma_load_3d(vd + HALF_KV, cur.kind ? &vb_map : &pool_map, &v_full[stage], 0, y, kvh * 2 + 1);
         }
+        if (lane == 0) stamp(b, 7);
         cur = nxt;
         nxt = nx2;
         nx2 = page_of(b + 3);
@@ -274,7 +282,9 @@ __global__ void __launch_bounds__(kThreads, 2)
       for (int b = 0; b < nb; ++b) {
         const int stage = b & 1;
         wait_bar(&p_full[stage], (b >> 1) & 1, kStatusMmaTimeout);  // P_b is in tensor memory
+        stamp(b, 3);
         wait_bar(&v_full[stage], (b >> 1) & 1, kStatusTmaTimeout);
+        stamp(b, 4);
         tc_fence_after_sync();
         const uint32_t va = smem_u32(v_sm + stage * KV_TILE);
 #pragma unroll
@@ -286,6 +296,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         umma_commit(&pv_done);
         if (b + 2 < nb) issue_qk(b + 2);
         if (b + 1 == nb) umma_commit(&o_full);
+        stamp(b, 5);
       }
     }
   } else {
@@ -305,12 +316,14 @@ __global__ void __launch_bounds__(kThreads, 2)
         else need_mask = need_mask || !((j0 + BN - 1 < anc_min) || (j0 >= seg_max && j0 + BN - 1 <= r_first));
       }
       wait_bar(&s_full[stage], (b >> 1) & 1, kStatusMmaTimeout);
+      if (tid == 0) stamp(b, 0);
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + COL_S + stage * BN;
       uint32_t sr[2][32];
       tmem_ld32(t_s, sr[0]);
       tmem_ld32(t_s + 32, sr[1]);
       tmem_wait_ld();
+      if (tid == 0) stamp(b, 1);
       float mx = -INFINITY;
       if (need_mask) {
         // diagonal, tail and tree blocks: visibility per (row, key)
@@ -382,6 +395,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
       tc_fence_before_sync();
       mbar_arrive(&p_full[stage]);
+      if (tid == 0) stamp(b, 2);
     }
 
     // ---- epilogue
@@ -441,6 +455,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (tracing && tid == 0) a.trace[8 * a.trace_blocks + 1] = global_timer_ns();
   if (warp == kMmaWarp) tmem_dealloc(tmem, TMEM_COLS);
 }
 

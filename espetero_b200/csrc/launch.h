@@ -31,6 +31,8 @@ struct KernelArgs {
   const esp_attn_tile* tiles;
   const esp_attn_tree* trees;
   int* status;  // device status word of the context
+  unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
+  int32_t trace_blocks;       // key blocks the trace buffer holds
   esp_attn_params p;
   int32_t HD;
   int32_t G;

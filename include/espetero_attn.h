@@ -332,6 +332,15 @@ const char* esp_attn_last_kernel(const esp_attn_ctx* ctx);
  * spinning. Synchronises the stream: for tests and post-mortems, not the hot path. */
 int esp_attn_check_status(esp_attn_ctx* ctx, void* stream);
 
+/* Timeline of one CTA, for tuning (the reference's counterpart is set_profile,
+ * src/model/model.mm:1041-1054, which times whole dispatches): with a caller-owned device
+ * buffer of (n_blocks + 1) * 8 uint64 set, CTA (0, 0) of the tcgen05 kernel stores
+ * %globaltimer nanoseconds per key block b at [8 * b + e]: e = 0 scores ready (softmax side),
+ * 1 scores in registers, 2 P handed over, 3 P seen by the MMA thread, 4 V tile seen,
+ * 5 MMAs of the block issued, 6 K tile requested, 7 V tile requested; slot 8 * n_blocks holds
+ * the CTA's start and slot 8 * n_blocks + 1 its end. n_blocks = 0 switches tracing off. */
+int esp_attn_set_trace(esp_attn_ctx* ctx, void* device_buffer, int32_t n_blocks);
+
 /* Kernel launches enqueued by this context since creation. */
 uint64_t esp_attn_launch_count(const esp_attn_ctx* ctx);
 
