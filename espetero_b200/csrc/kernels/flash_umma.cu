@@ -43,7 +43,9 @@ constexpr int Q_BYTES = BM * HD * 2;        // [2 halves of 64 dims][128 rows][1
 constexpr int KV_TILE = BN * HD * 2;        // [2 halves][64 rows][128 B]
 constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim halves of the Q tile
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
-constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_TILE + 1024;
+constexpr int KS = 3, VS = 2;                // K and V ring depths (K is requested two blocks ahead)
+constexpr int TILES_BYTES = Q_BYTES + (KS + VS) * KV_TILE;
+constexpr int SMEM_BYTES = TILES_BYTES + 256;  // + mbarriers and bookkeeping; no static shared memory
 constexpr uint32_t TMEM_COLS = 256;
 // Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
 // S buffer as 16-bit pairs, once the thread holds its scores in registers), O: 128 fp32 columns.
@@ -58,27 +60,49 @@ struct PageRef {  // where one 16-key page of a key block comes from
 
 constexpr int kSoftmaxThreads = BM;          // warps 0-3: one thread per (row, head) pair
 constexpr int kMmaWarp = 4;                  // warp 4: MMA issue (one thread), owns tensor memory
-constexpr int kTmaWarp = 5;                  // warp 5: TMA producer (lanes 0-3, one 16-key page each)
-constexpr int kThreads = 6 * 32;
+constexpr int kTmaWarpK = 5;                 // warp 5: TMA producer of K tiles (lanes 0-3, one 16-key page each)
+constexpr int kTmaWarpV = 6;                 // warp 6: TMA producer of V tiles
+constexpr int kThreads = 7 * 32;
+
+// Barriers and bookkeeping live behind the tiles in dynamic shared memory: with no static shared
+// memory the dynamic window starts on a 1024-byte boundary (checked at run time), which the
+// swizzled tiles need, and two CTAs of 112.25 KB fit one SM.
+struct Shared {
+  uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], pv_done, o_full;
+  uint32_t tmem_slot;
+  int red[4];  // anc_max, seg_min, anc_min, seg_max
+  volatile int dead;
+};
+static_assert(sizeof(Shared) <= 256, "bookkeeping must fit behind the tiles");
 
 template <int QDT>
 __global__ void __launch_bounds__(kThreads, 2)
     flash_umma_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
   // o_full: last P.V done
-  __shared__ uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], pv_done, o_full;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int red[4];  // anc_max, seg_min, anc_min, seg_max
-  __shared__ volatile int dead;
-
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
+  uint64_t* k_full = sh.k_full;
+  uint64_t* k_empty = sh.k_empty;
+  uint64_t* v_full = sh.v_full;
+  uint64_t* v_empty = sh.v_empty;
+  uint64_t* s_full = sh.s_full;
+  uint64_t* p_full = sh.p_full;
+  uint64_t& pv_done = sh.pv_done;
+  uint64_t& o_full = sh.o_full;
+  uint32_t& tmem_slot = sh.tmem_slot;
+  int* red = sh.red;
+  volatile int& dead = sh.dead;
+  if ((smem_u32(smem) & 1023u) != 0) {  // never expected; the tiles' swizzle would be wrong
+    if (threadIdx.x == 0) atomicExch(a.status, kStatusBadBlock);
+    return;
+  }
   uint8_t* q_sm = smem;
-  uint8_t* k_sm = smem + Q_BYTES;                 // two stages, KV_TILE apart
-  uint8_t* v_sm = smem + Q_BYTES + 2 * KV_TILE;
+  uint8_t* k_sm = smem + Q_BYTES;                 // KS stages, KV_TILE apart
+  uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS stages
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const esp_attn_params& p = a.p;
@@ -99,10 +123,12 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   // ---- set-up
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < KS; ++s) {
       mbar_init(&k_full[s], 4);
-      mbar_init(&v_full[s], 4);
       mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(&v_full[s], 4);
       mbar_init(&v_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -119,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     tmem_alloc(&tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == kTmaWarp && lane == 0) {
+  if (warp == kTmaWarpK && lane == 0) {
     tma_prefetch_desc(&pool_map);
     tma_prefetch_desc(&kb_map);
     tma_prefetch_desc(&vb_map);
@@ -199,9 +225,17 @@ __global__ void __launch_bounds__(kThreads, 2)
   };
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks] = global_timer_ns();
 
-  if (warp == kTmaWarp) {
-    // ================= TMA producer: lane w loads the w-th 16-key page of every block
+  if (warp == kTmaWarpK || warp == kTmaWarpV) {
+    // ================= TMA producers: warp 5 fills the K ring, warp 6 the V ring, each on its own
+    // schedule (a K tile is free as soon as its Q.K^T is done, a V tile only after its P.V);
+    // lane w loads the w-th 16-key page of every block.
     if (lane < 4 && nb > 0) {
+      const bool is_v = warp == kTmaWarpV;
+      const int depth = is_v ? VS : KS;
+      uint64_t* full = is_v ? v_full : k_full;
+      uint64_t* empty = is_v ? v_empty : k_empty;
+      uint8_t* ring = is_v ? v_sm : k_sm;
+      const CUtensorMap* batch_map = is_v ? &vb_map : &kb_map;
       // The page-table entry is only loaded here; the row arithmetic happens when the page is
       // issued, so the load's latency stays off the critical path.
       auto page_of = [&](int b) {
@@ -224,34 +258,25 @@ __global__ void __launch_bounds__(kThreads, 2)
         return r;
       };
       PageRef cur = page_of(0), nxt = page_of(1), nx2 = page_of(2);
+      int stage = 0;
+      uint32_t par = 1;  // the first use of a stage finds it empty
       for (int b = 0; b < nb; ++b) {
-        const int stage = b & 1;
-        const uint32_t par = ((b >> 1) & 1) ^ 1;  // the first use of a stage finds it empty
-        uint8_t* kd = k_sm + stage * KV_TILE + lane * 2048;
-        uint8_t* vd = v_sm + stage * KV_TILE + lane * 2048;
-        wait_bar(&k_empty[stage], par, kStatusMmaTimeout);
+        uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
+        wait_bar(&empty[stage], par, kStatusMmaTimeout);
         if (cur.kind < 0) {
-          mbar_arrive(&k_full[stage]);
+          mbar_arrive(&full[stage]);
         } else {
-          const int y = cur.kind ? cur.raw : cur.raw * 2 * p.bt + cur.off;
-          mbar_arrive_expect_tx(&k_full[stage], 4096);
-          tma_load_3d(kd, cur.kind ? &kb_map : &pool_map, &k_full[stage], 0, y, kvh * 2);
-          tma_load_3d(kd + HALF_KV, cur.kind ? &kb_map : &pool_map, &k_full[stage], 0, y, kvh * 2 + 1);
+          const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
+          const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
+          mbar_arrive_expect_tx(&full[stage], 4096);
+          tma_load_3d(dst, m, &full[stage], 0, y, kvh * 2);
+          tma_load_3d(dst + HALF_KV, m, &full[stage], 0, y, kvh * 2 + 1);
         }
-        if (lane == 0) stamp(b, 6);
-        wait_bar(&v_empty[stage], par, kStatusMmaTimeout);
-        if (cur.kind < 0) {
-          mbar_arrive(&v_full[stage]);
-        } else {
-          const int y = cur.kind ? cur.raw : (cur.raw * 2 + 1) * p.bt + cur.off;
-          mbar_arrive_expect_tx(&v_full[stage], 4096);
-          tma_load_3d(vd, cur.kind ? &vb_map : &pool_map, &v_full[stage], 0, y, kvh * 2);
-          tma_load_3d(vd + HALF_KV, cur.kind ? &vb_map : &pool_map, &v_full[stage], 0, y, kvh * 2 + 1);
-        }
-        if (lane == 0) stamp(b, 7);
+        if (lane == 0) stamp(b, is_v ? 7 : 6);
         cur = nxt;
         nxt = nx2;
         nx2 = page_of(b + 3);
+        if (++stage == depth) stage = 0, par ^= 1;
       }
     }
   } else if (warp == kMmaWarp) {
@@ -261,17 +286,18 @@ __global__ void __launch_bounds__(kThreads, 2)
       constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
       const uint32_t qa = smem_u32(q_sm);
       auto issue_qk = [&](int b) {
-        const int stage = b & 1;
-        wait_bar(&k_full[stage], (b >> 1) & 1, kStatusTmaTimeout);
+        const int stage = b & 1;               // S buffer
+        const int kst = b % KS;                // K ring slot
+        wait_bar(&k_full[kst], (b / KS) & 1, kStatusTmaTimeout);
         tc_fence_after_sync();
-        const uint32_t ka = smem_u32(k_sm + stage * KV_TILE);
+        const uint32_t ka = smem_u32(k_sm + kst * KV_TILE);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint64_t da = umma_smem_desc(qa + (ks >> 2) * HALF_Q + (ks & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc(ka + (ks >> 2) * HALF_KV + (ks & 3) * 32, 16, 1024);
           umma_ss(tmem + COL_S + stage * BN, da, db, idesc_qk, ks > 0);
         }
-        umma_commit(&k_empty[stage]);  // K[stage] may be refilled once these MMAs are done
+        umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
         umma_commit(&s_full[stage]);
       };
       // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
