@@ -19,6 +19,7 @@ struct esp_attn_ctx {
   int opt_attn_gqa = 1;
   int opt_attn_umma = 1;
   int opt_validate = 1;
+  int opt_umma_rings = 0;  // 0: choose by the pass, 1: short rings (2 CTAs per SM), 2: deep rings (1 CTA per SM)
   // host-side fault injection: every Nth pass of 64 rows or more fails before launch
   // (ESPETERO_FAIL_PASS of the reference, forest.h:2521-2531)
   int fail_every = 0;
@@ -191,6 +192,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "attn_gqa")) return &c->opt_attn_gqa;
   if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
   if (!std::strcmp(name, "validate")) return &c->opt_validate;
+  if (!std::strcmp(name, "umma_rings")) return &c->opt_umma_rings;
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   return nullptr;
 }
@@ -346,7 +348,16 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   } else if (umma) {
     if (int rc = umma_tensor_maps(c, a)) return rc;
     c->last_kernel = "flash_umma";
-    e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+    // Deep rings when the tiles' key work is mostly cached keys (streamed from HBM), short rings
+    // (two CTAs per SM) when it is mostly the pass's own rows.
+    int64_t cached = 0, batch = 0;
+    for (int i = 0; i < a.n_tiles; ++i) {
+      const esp_attn_tile& t = a.tiles_host[i];
+      cached += t.k1 - t.k0;
+      if (t.last) batch += a.trees_host[t.tree].M;
+    }
+    const bool from_hbm = c->opt_umma_rings == 2 || (c->opt_umma_rings == 0 && cached > 2 * batch);
+    e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, from_hbm, stream, &c->launches);
   } else {
     c->last_kernel = "flash_general";
     e = esp::launch_flash_general(k, stream, &c->launches);

@@ -43,9 +43,12 @@ constexpr int Q_BYTES = BM * HD * 2;        // [2 halves of 64 dims][128 rows][1
 constexpr int KV_TILE = BN * HD * 2;        // [2 halves][64 rows][128 B]
 constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim halves of the Q tile
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
-constexpr int KS = 3, VS = 2;                // K and V ring depths (K is requested two blocks ahead)
-constexpr int TILES_BYTES = Q_BYTES + (KS + VS) * KV_TILE;
-constexpr int SMEM_BYTES = TILES_BYTES + 256;  // + mbarriers and bookkeeping; no static shared memory
+// Ring depths come in two flavours: (3, 2) lets two CTAs share an SM (passes whose keys sit in L2:
+// prefill), (6, 6) takes the whole SM for one CTA and keeps ~160 KB of K/V in flight (passes
+// that stream their keys from HBM: verify over a long cached prefix).
+constexpr int kMaxStages = 6;
+constexpr int tiles_bytes(int ks, int vs) { return Q_BYTES + (ks + vs) * KV_TILE; }
+constexpr int smem_bytes(int ks, int vs) { return tiles_bytes(ks, vs) + 384; }  // + mbarriers; no static shared memory
 constexpr uint32_t TMEM_COLS = 256;
 // Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
 // S buffer as 16-bit pairs, once the thread holds its scores in registers), O: 128 fp32 columns.
@@ -66,17 +69,17 @@ constexpr int kThreads = 7 * 32;
 
 // Barriers and bookkeeping live behind the tiles in dynamic shared memory: with no static shared
 // memory the dynamic window starts on a 1024-byte boundary (checked at run time), which the
-// swizzled tiles need, and two CTAs of 112.25 KB fit one SM.
+// swizzled tiles need, and two CTAs of 112.4 KB fit one SM.
 struct Shared {
-  uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], pv_done, o_full;
+  uint64_t k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages], s_full[2], p_full[2], pv_done, o_full;
   uint32_t tmem_slot;
   int red[4];  // anc_max, seg_min, anc_min, seg_max
   volatile int dead;
 };
-static_assert(sizeof(Shared) <= 256, "bookkeeping must fit behind the tiles");
+static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
 
-template <int QDT>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int QDT, int KS, int VS>
+__global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ? 2 : 1)
     flash_umma_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
@@ -84,6 +87,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
   // o_full: last P.V done
+  constexpr int TILES_BYTES = tiles_bytes(KS, VS);
   Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
   uint64_t* k_full = sh.k_full;
   uint64_t* k_empty = sh.k_empty;
@@ -306,19 +310,20 @@ __global__ void __launch_bounds__(kThreads, 2)
       issue_qk(0);
       if (nb > 1) issue_qk(1);
       for (int b = 0; b < nb; ++b) {
-        const int stage = b & 1;
+        const int stage = b & 1;   // S / P buffer
+        const int vst = b % VS;    // V ring slot
         wait_bar(&p_full[stage], (b >> 1) & 1, kStatusMmaTimeout);  // P_b is in tensor memory
         stamp(b, 3);
-        wait_bar(&v_full[stage], (b >> 1) & 1, kStatusTmaTimeout);
+        wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
         stamp(b, 4);
         tc_fence_after_sync();
-        const uint32_t va = smem_u32(v_sm + stage * KV_TILE);
+        const uint32_t va = smem_u32(v_sm + vst * KV_TILE);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           const uint64_t db = umma_smem_desc(va + ks * 2048, HALF_KV, 1024);
           umma_ts(tmem + COL_O, tmem + COL_S + stage * BN + ks * 8, db, idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&v_empty[stage]);
+        umma_commit(&v_empty[vst]);
         umma_commit(&pv_done);
         if (b + 2 < nb) issue_qk(b + 2);
         if (b + 1 == nb) umma_commit(&o_full);
@@ -411,11 +416,12 @@ __global__ void __launch_bounds__(kThreads, 2)
       tmem_wait_st();
       if (n_valid < BN) {
         // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
-        wait_bar(&v_full[stage], (b >> 1) & 1, kStatusTmaTimeout);
+        const int vst = b % VS;
+        wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
         const int n = (BN - n_valid) * 16;  // 16-byte chunks: 2 halves x 8 per row
         for (int i = tid; i < n; i += BM) {
           const int r = n_valid + i / 16, c = i % 16;
-          *reinterpret_cast<uint4*>(v_sm + stage * KV_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(v_sm + vst * KV_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
       }
@@ -495,19 +501,33 @@ bool flash_umma_supports(int32_t HDim, int32_t G, int32_t tile_rows, int32_t bt,
   return bt > 0 && bt % 16 == 0;
 }
 
+template <int QDT, int KS, int VS>
+cudaError_t setup_variant() {
+  return cudaFuncSetAttribute(flash_umma_kernel<QDT, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(KS, VS));
+}
+
 cudaError_t flash_umma_setup() {
-  cudaError_t e = cudaFuncSetAttribute(flash_umma_kernel<ESP_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(flash_umma_kernel<ESP_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e;
+  if ((e = setup_variant<ESP_F16, 3, 2>()) != cudaSuccess) return e;
+  if ((e = setup_variant<ESP_BF16, 3, 2>()) != cudaSuccess) return e;
+  if ((e = setup_variant<ESP_F16, 6, 6>()) != cudaSuccess) return e;
+  return setup_variant<ESP_BF16, 6, 6>();
 }
 
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
-                              cudaStream_t stream, uint64_t* launches) {
+                              bool stream_from_hbm, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
-  if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, a);
-  else flash_umma_kernel<ESP_BF16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, a);
+  if (stream_from_hbm) {
+    constexpr int smem = smem_bytes(6, 6);
+    if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16, 6, 6><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_kernel<ESP_BF16, 6, 6><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  } else {
+    constexpr int smem = smem_bytes(3, 2);
+    if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_kernel<ESP_BF16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  }
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

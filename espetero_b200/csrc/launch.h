@@ -83,8 +83,10 @@ cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pair
                                   uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
                                   uint64_t* launches);
 
+// stream_from_hbm: most keys come from the paged pool (HBM): one CTA per SM with deep K/V rings;
+// else two CTAs per SM with short rings (keys of the pass itself, L2-resident).
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
-                              cudaStream_t stream, uint64_t* launches);
+                              bool stream_from_hbm, cudaStream_t stream, uint64_t* launches);
 // Shapes the tcgen05 kernel covers: HD 128, 16-bit pool of the pass's type, tiles of 16..128 rows
 // whose 128 / tile_rows heads belong to one kv head.
 bool flash_umma_supports(int32_t HD, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype);

@@ -132,7 +132,9 @@ int esp_attn_abi_version(void);
 /* Runtime options, as NativeModel::set_option(name, int) (src/model/model.mm:936-1004).
  * Names: "attn_gqa" (1: single-row trees take the decode kernel; default 1),
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
- * default 1), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
+ * default 1), "umma_rings" (tcgen05 kernel: 0 choose by the pass, 1 short K/V rings and two CTAs
+ * per SM, 2 deep rings and one CTA per SM; default 0), "validate" (1: check host mirrors
+ * before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531). */
