@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
   const int nb = nbc + nbb;
   auto batch_j0 = [&](int i) { return BN * (i < a_hi ? i : b_lo + (i - a_hi)); };
   auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return;  // the common case costs one shared-memory round trip
     if (dead) return;
     if (!mbar_wait(bar, parity)) {
       dead = 1;
@@ -288,18 +289,23 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_qk = umma_idesc<QDT>(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
-      const uint32_t qa = smem_u32(q_sm);
+      // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
+      // its address field (one thread issues everything, so every integer op here is latency).
+      const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
+      const uint64_t k_desc = umma_smem_desc(smem_u32(k_sm), 16, 1024);
+      const uint64_t v_desc = umma_smem_desc(smem_u32(v_sm), HALF_KV, 1024);
       auto issue_qk = [&](int b) {
         const int stage = b & 1;               // S buffer
         const int kst = b % KS;                // K ring slot
         wait_bar(&k_full[kst], (b / KS) & 1, kStatusTmaTimeout);
         tc_fence_after_sync();
-        const uint32_t ka = smem_u32(k_sm + kst * KV_TILE);
+        const uint64_t kd = k_desc + uint64_t(kst * (KV_TILE >> 4));
+        const uint32_t td = tmem + COL_S + stage * BN;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t da = umma_smem_desc(qa + (ks >> 2) * HALF_Q + (ks & 3) * 32, 16, 1024);
-          const uint64_t db = umma_smem_desc(ka + (ks >> 2) * HALF_KV + (ks & 3) * 32, 16, 1024);
-          umma_ss(tmem + COL_S + stage * BN, da, db, idesc_qk, ks > 0);
+          const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
+          const uint64_t db = kd + uint64_t(((ks >> 2) * HALF_KV + (ks & 3) * 32) >> 4);
+          umma_ss(td, da, db, idesc_qk, ks > 0);
         }
         umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
         umma_commit(&s_full[stage]);
@@ -317,12 +323,11 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
         wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
         stamp(b, 4);
         tc_fence_after_sync();
-        const uint32_t va = smem_u32(v_sm + vst * KV_TILE);
+        const uint64_t vd = v_desc + uint64_t(vst * (KV_TILE >> 4));
+        const uint32_t tp = tmem + COL_S + stage * BN;
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint64_t db = umma_smem_desc(va + ks * 2048, HALF_KV, 1024);
-          umma_ts(tmem + COL_O, tmem + COL_S + stage * BN + ks * 8, db, idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < BN / 16; ++ks)
+          umma_ts(tmem + COL_O, tp + ks * 8, vd + uint64_t((ks * 2048) >> 4), idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&v_empty[vst]);
         umma_commit(&pv_done);
         if (b + 2 < nb) issue_qk(b + 2);
