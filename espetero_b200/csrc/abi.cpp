@@ -19,7 +19,7 @@ struct esp_attn_ctx {
   int opt_attn_gqa = 1;
   int opt_attn_umma = 1;
   int opt_validate = 1;
-  int opt_umma_rings = 0;  // 0: choose by the pass, 1: short rings (2 CTAs per SM), 2: deep rings (1 CTA per SM)
+  int opt_umma_kernel = 0;  // 0: choose by the pass, 1: flash_umma (HBM streaming), 2: flash_umma_pair (L2-resident keys)
   // host-side fault injection: every Nth pass of 64 rows or more fails before launch
   // (ESPETERO_FAIL_PASS of the reference, forest.h:2521-2531)
   int fail_every = 0;
@@ -192,7 +192,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "attn_gqa")) return &c->opt_attn_gqa;
   if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
   if (!std::strcmp(name, "validate")) return &c->opt_validate;
-  if (!std::strcmp(name, "umma_rings")) return &c->opt_umma_rings;
+  if (!std::strcmp(name, "umma_kernel")) return &c->opt_umma_kernel;
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   return nullptr;
 }
@@ -237,7 +237,7 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
     delete c;
     return cuda_fail(e, "decode kernel setup");
   }
-  if ((e = esp::flash_umma_setup()) != cudaSuccess) {
+  if ((e = esp::flash_umma_setup()) != cudaSuccess || (e = esp::flash_umma_pair_setup()) != cudaSuccess) {
     delete c;
     return cuda_fail(e, "tcgen05 kernel setup");
   }
@@ -347,17 +347,22 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
   } else if (umma) {
     if (int rc = umma_tensor_maps(c, a)) return rc;
-    c->last_kernel = "flash_umma";
-    // Deep rings when the tiles' key work is mostly cached keys (streamed from HBM), short rings
-    // (two CTAs per SM) when it is mostly the pass's own rows.
+    // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
+    // from HBM, the pass's own rows sit in L2), unless the "umma_kernel" option forces one.
     int64_t cached = 0, batch = 0;
     for (int i = 0; i < a.n_tiles; ++i) {
       const esp_attn_tile& t = a.tiles_host[i];
       cached += t.k1 - t.k0;
       if (t.last) batch += a.trees_host[t.tree].M;
     }
-    const bool from_hbm = c->opt_umma_rings == 2 || (c->opt_umma_rings == 0 && cached > 2 * batch);
-    e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, from_hbm, stream, &c->launches);
+    const bool stream_hbm = c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch);
+    if (stream_hbm) {
+      c->last_kernel = "flash_umma";
+      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+    } else {
+      c->last_kernel = "flash_umma_pair";
+      e = esp::launch_flash_umma_pair(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+    }
   } else {
     c->last_kernel = "flash_general";
     e = esp::launch_flash_general(k, stream, &c->launches);

@@ -1,0 +1,527 @@
+// Forest attention for 128-row tiles on the 5th-generation tensor cores (sm_100a), variant for
+// passes whose keys are mostly the pass's own rows (causal prefill): two CTAs per SM, 64-key
+// blocks, short K/V rings (the keys sit in L2). flash_umma.cu holds the variant that streams a
+// long cached prefix from HBM (one CTA per SM, 128-key blocks, deep rings); both compute the same.
+//
+// Computes what flash_attention computes (kernels/40_attention.metal:156-343 of the
+// reference; generic head dim kernels/80_gemma.metal:157-342): the tile's rows attend to the
+// cached key range [k0, k1) of the paged pool and, when tile.last, to the visible batch keys
+// of their tree (two-level `desc` mask or a 64-bit ancestor mask per row), writing either
+// the partial record [O | m | l] or the gated, normalised output (and its LSE).
+//
+// B200 structure. One CTA = 128 (query row, head) pairs = the 128 lanes of tensor memory:
+// tile_rows rows x (128 / tile_rows) heads of one kv head (16 nodes x 8 heads for a verify
+// tile, 128 rows x 1 head for prefill). Keys are processed 64 at a time:
+//   S[128 x 64]   = Q . K^T      tcgen05.mma, A = Q tile and B = K tile from shared memory
+//                                (K-major, 128-byte swizzle), D in tensor memory (fp32)
+//   softmax        thread i owns row i: tcgen05.ld of its 64 scores, mask, online max / sum
+//                  in the exp2 domain (no shuffles), P as bf16 / fp16 pairs back into tensor
+//                  memory with tcgen05.st
+//   O[128 x HD]  += P . V         tcgen05.mma with A = P from tensor memory, B = V tile from
+//                                shared memory (MN-major), accumulating in tensor memory
+// O stays in tensor memory for the whole tile and is rescaled only when a row's maximum has
+// grown by more than 2^8 since its reference value (warp-uniform decision), so the common
+// step has no accumulator traffic at all. K and V tiles are double-buffered and arrive by
+// TMA: one bulk tensor load per (16-key page, 64-dim half), rows found through the page table
+// for cached keys and directly in Kb / Vb for batch keys. The CTA is warp-specialised: warps
+// 0-3 do the softmax (one thread per row), warp 4 issues every MMA from one thread and owns
+// the tensor memory, warp 5 is the TMA producer; they hand tiles to one another through
+// mbarriers only (TMA complete_tx, tcgen05.commit, and a 128-arrival barrier for P). Blocks
+// that need no mask (all but the diagonal, the tail and tree blocks) take a path with no
+// per-key predicate. Two CTAs share an SM (97 KB of shared memory and 256 tensor-memory
+// columns each) so that one CTA's softmax overlaps the other's MMAs.
+// Every wait is bounded: after a timeout the CTA records a status code, stops waiting,
+// finishes its loop, frees its tensor memory and returns.
+#include "umma.cuh"
+#include "../launch.h"
+
+namespace esp {
+namespace {
+
+constexpr int BM = 128;  // (row, head) pairs per CTA
+constexpr int BN = 64;   // keys per block
+constexpr int HD = 128;  // head dim of this kernel
+constexpr int Q_BYTES = BM * HD * 2;        // [2 halves of 64 dims][128 rows][128 B]
+constexpr int KV_TILE = BN * HD * 2;        // [2 halves][64 rows][128 B]
+constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim halves of the Q tile
+constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
+// Ring depths come in two flavours: (3, 2) lets two CTAs share an SM (passes whose keys sit in L2:
+// prefill), (6, 6) takes the whole SM for one CTA and keeps ~160 KB of K/V in flight (passes
+// that stream their keys from HBM: verify over a long cached prefix).
+constexpr int kMaxStages = 6;
+constexpr int tiles_bytes(int ks, int vs) { return Q_BYTES + (ks + vs) * KV_TILE; }
+constexpr int smem_bytes(int ks, int vs) { return tiles_bytes(ks, vs) + 384; }  // + mbarriers; no static shared memory
+constexpr uint32_t TMEM_COLS = 256;
+// Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
+// S buffer as 16-bit pairs, once the thread holds its scores in registers), O: 128 fp32 columns.
+constexpr uint32_t COL_S = 0, COL_O = 128;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+struct PageRef {  // where one 16-key page of a key block comes from
+  int raw;        // block id as loaded from the page table (pool), or first row (Kb / Vb)
+  int off;        // row inside the block (pool)
+  int kind;       // -1: nothing to load, 0: paged pool, 1: Kb / Vb
+};
+
+constexpr int kSoftmaxThreads = BM;          // warps 0-3: one thread per (row, head) pair
+constexpr int kMmaWarp = 4;                  // warp 4: MMA issue (one thread), owns tensor memory
+constexpr int kTmaWarpK = 5;                 // warp 5: TMA producer of K tiles (lanes 0-3, one 16-key page each)
+constexpr int kTmaWarpV = 6;                 // warp 6: TMA producer of V tiles
+constexpr int kThreads = 7 * 32;
+
+// Barriers and bookkeeping live behind the tiles in dynamic shared memory: with no static shared
+// memory the dynamic window starts on a 1024-byte boundary (checked at run time), which the
+// swizzled tiles need, and two CTAs of 112.4 KB fit one SM.
+struct Shared {
+  uint64_t k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages], s_full[2], p_full[2], pv_done, o_full;
+  uint32_t tmem_slot;
+  int red[4];  // anc_max, seg_min, anc_min, seg_max
+  volatile int dead;
+};
+static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
+
+template <int QDT, int KS, int VS>
+__global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ? 2 : 1)
+    flash_umma_pair_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
+                      const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
+  using QE = Elem16<QDT>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
+  // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
+  // o_full: last P.V done
+  constexpr int TILES_BYTES = tiles_bytes(KS, VS);
+  Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
+  uint64_t* k_full = sh.k_full;
+  uint64_t* k_empty = sh.k_empty;
+  uint64_t* v_full = sh.v_full;
+  uint64_t* v_empty = sh.v_empty;
+  uint64_t* s_full = sh.s_full;
+  uint64_t* p_full = sh.p_full;
+  uint64_t& pv_done = sh.pv_done;
+  uint64_t& o_full = sh.o_full;
+  uint32_t& tmem_slot = sh.tmem_slot;
+  int* red = sh.red;
+  volatile int& dead = sh.dead;
+  if ((smem_u32(smem) & 1023u) != 0) {  // never expected; the tiles' swizzle would be wrong
+    if (threadIdx.x == 0) atomicExch(a.status, kStatusBadBlock);
+    return;
+  }
+  uint8_t* q_sm = smem;
+  uint8_t* k_sm = smem + Q_BYTES;                 // KS stages, KV_TILE apart
+  uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS stages
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const esp_attn_params& p = a.p;
+  const int G = a.G, TR = a.tile_rows, HPC = BM / TR;
+  const esp_attn_tile tile = a.tiles[a.n_tiles - 1 - int(blockIdx.x)];  // long (late) tiles first
+  const esp_attn_tree tree = a.trees[tile.tree];
+  const int kvh = (int(blockIdx.y) * HPC) / G;
+  const int end = tree.base + tree.M;
+  const int rows_live = min(TR, end - tile.r0);
+  const bool use_anc = a.anc_mask != nullptr;
+
+  // per softmax thread: its (row, head)
+  const int fm = (tid & (BM - 1)) / HPC, hh = (tid & (BM - 1)) % HPC;
+  const int head = int(blockIdx.y) * HPC + hh;
+  const bool row_ok = tid < BM && fm < rows_live;
+  const int row = (tid < BM && fm < rows_live) ? tile.r0 + fm : end - 1;
+  const int rr = row - tree.base;
+
+  // ---- set-up
+  if (tid == 0) {
+    for (int s = 0; s < KS; ++s) {
+      mbar_init(&k_full[s], 4);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(&v_full[s], 4);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], kSoftmaxThreads);
+    }
+    mbar_init(&pv_done, 1);
+    mbar_init(&o_full, 1);
+    mbar_fence_init();
+    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0;
+    dead = 0;
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == kTmaWarpK && lane == 0) {
+    tma_prefetch_desc(&pool_map);
+    tma_prefetch_desc(&kb_map);
+    tma_prefetch_desc(&vb_map);
+  }
+  int4 d = make_int4(0, 0, 0, 0);
+  uint64_t am = 0;
+  if (tid < BM) {
+    // Q row of this thread into the K-major swizzled tile
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD);
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<uint4*>(q_sm + c * HALF_Q + tid * 128 + ((i ^ (tid & 7)) << 4)) = src[c * 8 + i];
+    fence_proxy_async_smem();
+    if (tile.last) {
+      if (use_anc) am = a.anc_mask[row];
+      else d = reinterpret_cast<const int4*>(a.desc)[row];
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (tile.last && !use_anc) {
+    if (tid < BM) {
+      int v0 = d.z, v1 = d.x, v2 = d.z, v3 = d.x;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        v0 = max(v0, __shfl_xor_sync(0xffffffffu, v0, o));
+        v1 = min(v1, __shfl_xor_sync(0xffffffffu, v1, o));
+        v2 = min(v2, __shfl_xor_sync(0xffffffffu, v2, o));
+        v3 = max(v3, __shfl_xor_sync(0xffffffffu, v3, o));
+      }
+      if (lane == 0) {
+        atomicMax(&red[0], v0);
+        atomicMin(&red[1], v1);
+        atomicMin(&red[2], v2);
+        atomicMax(&red[3], v3);
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t tmem = tmem_slot;
+
+  // ---- block list: cached 64-key blocks, then the batch blocks some row of the tile can see
+  const int r_first = tile.r0 - tree.base, r_last = r_first + rows_live - 1;
+  const int anc_max = red[0], seg_min = red[1], anc_min = red[2], seg_max = red[3];
+  int k_last = -1, a_hi = 0, b_lo = 0, nbb = 0;
+  if (tile.last) {
+    if (use_anc) {
+      k_last = min(tree.M, 64) - 1;
+      a_hi = (k_last + BN) / BN;
+      nbb = a_hi;
+    } else {
+      k_last = min(tree.M - 1, max(r_last, anc_max - 1));
+      const int n_all = (k_last + BN) / BN;
+      a_hi = min((anc_max + BN - 1) / BN, n_all);                 // blocks below the ancestor range
+      b_lo = max(a_hi, seg_min / BN);                             // blocks of the rows' own segments
+      const int b_hi = min(r_last / BN, n_all - 1);
+      nbb = a_hi + max(0, b_hi - b_lo + 1);
+    }
+  }
+  const int nbc = (tile.k1 - tile.k0 + BN - 1) / BN;
+  const int nb = nbc + nbb;
+  auto batch_j0 = [&](int i) { return BN * (i < a_hi ? i : b_lo + (i - a_hi)); };
+  auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return;  // the common case costs one shared-memory round trip
+    if (dead) return;
+    if (!mbar_wait(bar, parity)) {
+      dead = 1;
+      atomicExch(a.status, code);
+    }
+  };
+
+  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  auto stamp = [&](int b, int ev) {
+    if (tracing && b < a.trace_blocks) a.trace[8 * b + ev] = global_timer_ns();
+  };
+  if (tracing && tid == 0) a.trace[8 * a.trace_blocks] = global_timer_ns();
+
+  if (warp == kTmaWarpK || warp == kTmaWarpV) {
+    // ================= TMA producers: warp 5 fills the K ring, warp 6 the V ring, each on its own
+    // schedule (a K tile is free as soon as its Q.K^T is done, a V tile only after its P.V);
+    // lane w loads the w-th 16-key page of every block.
+    if (lane < 4 && nb > 0) {
+      const bool is_v = warp == kTmaWarpV;
+      const int depth = is_v ? VS : KS;
+      uint64_t* full = is_v ? v_full : k_full;
+      uint64_t* empty = is_v ? v_empty : k_empty;
+      uint8_t* ring = is_v ? v_sm : k_sm;
+      const CUtensorMap* batch_map = is_v ? &vb_map : &kb_map;
+      // The page-table entry is only loaded here; the row arithmetic happens when the page is
+      // issued, so the load's latency stays off the critical path.
+      auto page_of = [&](int b) {
+        PageRef r{0, 0, -1};
+        if (b >= nb) return r;
+        if (b < nbc) {
+          const int j = tile.k0 + BN * b + 16 * lane;
+          if (j < tile.k1) {
+            r.raw = a.blocks[tree.table + j / p.bt];
+            r.off = j % p.bt;
+            r.kind = 0;
+          }
+        } else {
+          const int j = batch_j0(b - nbc) + 16 * lane;
+          if (j <= k_last) {
+            r.raw = tree.base + j;
+            r.kind = 1;
+          }
+        }
+        return r;
+      };
+      PageRef cur = page_of(0), nxt = page_of(1), nx2 = page_of(2);
+      int stage = 0;
+      uint32_t par = 1;  // the first use of a stage finds it empty
+      for (int b = 0; b < nb; ++b) {
+        uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
+        wait_bar(&empty[stage], par, kStatusMmaTimeout);
+        if (cur.kind < 0) {
+          mbar_arrive(&full[stage]);
+        } else {
+          const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
+          const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
+          mbar_arrive_expect_tx(&full[stage], 4096);
+          tma_load_3d(dst, m, &full[stage], 0, y, kvh * 2);
+          tma_load_3d(dst + HALF_KV, m, &full[stage], 0, y, kvh * 2 + 1);
+        }
+        if (lane == 0) stamp(b, is_v ? 7 : 6);
+        cur = nxt;
+        nxt = nx2;
+        nx2 = page_of(b + 3);
+        if (++stage == depth) stage = 0, par ^= 1;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer (one thread)
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc<QDT>(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
+      // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
+      // its address field (one thread issues everything, so every integer op here is latency).
+      const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
+      const uint64_t k_desc = umma_smem_desc(smem_u32(k_sm), 16, 1024);
+      const uint64_t v_desc = umma_smem_desc(smem_u32(v_sm), HALF_KV, 1024);
+      auto issue_qk = [&](int b) {
+        const int stage = b & 1;               // S buffer
+        const int kst = b % KS;                // K ring slot
+        wait_bar(&k_full[kst], (b / KS) & 1, kStatusTmaTimeout);
+        tc_fence_after_sync();
+        const uint64_t kd = k_desc + uint64_t(kst * (KV_TILE >> 4));
+        const uint32_t td = tmem + COL_S + stage * BN;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
+          const uint64_t db = kd + uint64_t(((ks >> 2) * HALF_KV + (ks & 3) * 32) >> 4);
+          umma_ss(td, da, db, idesc_qk, ks > 0);
+        }
+        umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
+        umma_commit(&s_full[stage]);
+      };
+      // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
+      // MMAs run in issue order, so Q.K^T of block b + 2 overwrites buffer b & 1 only after
+      // P.V of block b has read P from it.
+      issue_qk(0);
+      if (nb > 1) issue_qk(1);
+      for (int b = 0; b < nb; ++b) {
+        const int stage = b & 1;   // S / P buffer
+        const int vst = b % VS;    // V ring slot
+        wait_bar(&p_full[stage], (b >> 1) & 1, kStatusMmaTimeout);  // P_b is in tensor memory
+        stamp(b, 3);
+        wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
+        stamp(b, 4);
+        tc_fence_after_sync();
+        const uint64_t vd = v_desc + uint64_t(vst * (KV_TILE >> 4));
+        const uint32_t tp = tmem + COL_S + stage * BN;
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks)
+          umma_ts(tmem + COL_O, tp + ks * 8, vd + uint64_t((ks * 2048) >> 4), idesc_pv, (b > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&v_empty[vst]);
+        umma_commit(&pv_done);
+        if (b + 2 < nb) issue_qk(b + 2);
+        if (b + 1 == nb) umma_commit(&o_full);
+        stamp(b, 5);
+      }
+    }
+  } else {
+    // ================= softmax: thread i owns row i of S and O (TMEM lane i)
+    const uint32_t t_lane = tmem + (uint32_t(warp * 32) << 16);
+    const float sl2 = a.scale * kLog2e;
+    float m_ref = -INFINITY, l_run = 0.0f;  // m_ref in exp2 units of the scaled score
+
+    for (int b = 0; b < nb; ++b) {
+      const int stage = b & 1;
+      const bool cached = b < nbc;
+      const int j0 = cached ? tile.k0 + BN * b : batch_j0(b - nbc);
+      const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, k_last + 1 - j0);
+      bool need_mask = n_valid < BN;
+      if (!cached) {
+        if (use_anc) need_mask = true;
+        else need_mask = need_mask || !((j0 + BN - 1 < anc_min) || (j0 >= seg_max && j0 + BN - 1 <= r_first));
+      }
+      wait_bar(&s_full[stage], (b >> 1) & 1, kStatusMmaTimeout);
+      if (tid == 0) stamp(b, 0);
+      tc_fence_after_sync();
+      const uint32_t t_s = t_lane + COL_S + stage * BN;
+      uint32_t sr[2][32];
+      tmem_ld32(t_s, sr[0]);
+      tmem_ld32(t_s + 32, sr[1]);
+      tmem_wait_ld();
+      if (tid == 0) stamp(b, 1);
+      float mx = -INFINITY;
+      if (need_mask) {
+        // diagonal, tail and tree blocks: visibility per (row, key)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int col = 32 * h + c, j = j0 + col;
+            bool vis = col < n_valid;
+            if (!cached) vis = vis && (use_anc ? ((am >> (j & 63)) & 1ull) != 0 : ((j < d.z) || (j >= d.x && j <= rr)));
+            const float s = vis ? __uint_as_float(sr[h][c]) : -INFINITY;
+            sr[h][c] = __float_as_uint(s);
+            mx = fmaxf(mx, s);
+          }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])));
+      }
+      mx *= sl2;  // scale > 0: the maximum commutes with the scaling
+      // lazy rescale: keep the old reference maximum unless this block exceeds it by 2^8
+      float factor = 1.0f;
+      const bool grow = mx > m_ref + kRescaleThreshold;  // also the first finite maximum (m_ref = -inf)
+      if (grow) {
+        factor = fast_exp2(m_ref - mx);  // 0 when nothing was seen before
+        m_ref = mx;
+        l_run *= factor;
+      }
+      const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+      float ps0 = 0.0f, ps1 = 0.0f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sl2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
+        ps0 += p0;
+        ps1 += p1;
+        pk[c] = QE::pack2(p0, p1);
+      }
+      l_run += ps0 + ps1;
+      tmem_st32(t_s, pk);  // over the scores this thread has already read
+      if (b > 0) {
+        wait_bar(&pv_done, (b - 1) & 1, kStatusMmaTimeout);  // O holds blocks 0 .. b-1 and is idle
+        tc_fence_after_sync();
+      }
+      if (b > 0 && __any_sync(0xffffffffu, grow)) {
+        // O of this warp's rows *= factor (1 for rows whose reference did not move)
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_lane + COL_O + 32 * c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st32(t_lane + COL_O + 32 * c, o);
+        }
+      }
+      tmem_wait_st();
+      if (n_valid < BN) {
+        // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
+        const int vst = b % VS;
+        wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
+        const int n = (BN - n_valid) * 16;  // 16-byte chunks: 2 halves x 8 per row
+        for (int i = tid; i < n; i += BM) {
+          const int r = n_valid + i / 16, c = i % 16;
+          *reinterpret_cast<uint4*>(v_sm + vst * KV_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[stage]);
+      if (tid == 0) stamp(b, 2);
+    }
+
+    // ---- epilogue
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine grid may be scheduled
+    if (nb > 0) {
+      wait_bar(&o_full, 0, kStatusMmaTimeout);
+      tc_fence_after_sync();
+    }
+    const int hg = head % G;
+    float* rec = nullptr;
+    typename QE::T* op = nullptr;
+    const float* gp = nullptr;
+    if (tile.part >= 0) rec = a.parts + ((size_t(tile.part) * p.Hkv + kvh) * TR * G + size_t(fm) * G + hg) * (HD + 2);
+    else {
+      op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(head) * HD;
+      if (a.X) gp = a.X + size_t(row) * p.g_ld + size_t(head) * 2 * HD + HD;
+    }
+    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t o[32];
+      if (nb > 0) {
+        tmem_ld32(t_lane + COL_O + 32 * c, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0;
+      }
+      if (!row_ok) continue;
+      if (rec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          *reinterpret_cast<float2*>(rec + 32 * c + i) = make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          float v[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            v[k] = __uint_as_float(o[i + k]) * inv_l;
+            if (gp) v[k] *= sigmoid_gate(gp[32 * c + i + k]);
+          }
+          uint4 w;
+          w.x = QE::pack2(v[0], v[1]), w.y = QE::pack2(v[2], v[3]), w.z = QE::pack2(v[4], v[5]), w.w = QE::pack2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(op + 32 * c + i) = w;
+        }
+      }
+    }
+    if (row_ok) {
+      if (rec) {
+        rec[HD] = m_ref * kLn2;  // -inf stays -inf
+        rec[HD + 1] = l_run;
+      } else if (a.lse) {
+        a.lse[size_t(row) * p.H + head] = l_run > 0.0f ? m_ref * kLn2 + __logf(l_run) : -INFINITY;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tracing && tid == 0) a.trace[8 * a.trace_blocks + 1] = global_timer_ns();
+  if (warp == kMmaWarp) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace
+
+template <int QDT, int KS, int VS>
+cudaError_t setup_variant() {
+  return cudaFuncSetAttribute(flash_umma_pair_kernel<QDT, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(KS, VS));
+}
+
+cudaError_t flash_umma_pair_setup() {
+  const cudaError_t e = setup_variant<ESP_F16, 3, 2>();
+  if (e != cudaSuccess) return e;
+  return setup_variant<ESP_BF16, 3, 2>();
+}
+
+cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
+                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
+  if (a.n_tiles <= 0) return cudaSuccess;
+  const int hpc = BM / a.tile_rows;
+  const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
+  constexpr int smem = smem_bytes(3, 2);
+  if (a.q_dtype == ESP_F16) flash_umma_pair_kernel<ESP_F16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  else flash_umma_pair_kernel<ESP_BF16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) ++*launches;
+  return e;
+}
+
+}  // namespace esp

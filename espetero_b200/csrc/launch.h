@@ -83,10 +83,14 @@ cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pair
                                   uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
                                   uint64_t* launches);
 
-// stream_from_hbm: most keys come from the paged pool (HBM): one CTA per SM with deep K/V rings;
-// else two CTAs per SM with short rings (keys of the pass itself, L2-resident).
+// Two tcgen05 kernels with the same contract: flash_umma streams a long cached prefix from HBM
+// (one CTA per SM, 128-key blocks, deep K/V rings); flash_umma_pair is for passes whose keys are
+// mostly their own rows and sit in L2 (two CTAs per SM, 64-key blocks, short rings).
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
-                              bool stream_from_hbm, cudaStream_t stream, uint64_t* launches);
+                              cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
+                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
+cudaError_t flash_umma_pair_setup();
 // Shapes the tcgen05 kernel covers: HD 128, 16-bit pool of the pass's type, tiles of 16..128 rows
 // whose 128 / tile_rows heads belong to one kv head.
 bool flash_umma_supports(int32_t HD, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype);

@@ -132,9 +132,9 @@ int esp_attn_abi_version(void);
 /* Runtime options, as NativeModel::set_option(name, int) (src/model/model.mm:936-1004).
  * Names: "attn_gqa" (1: single-row trees take the decode kernel; default 1),
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
- * default 1), "umma_rings" (tcgen05 kernel: 0 choose by the pass, 1 short K/V rings and two CTAs
- * per SM, 2 deep rings and one CTA per SM; default 0), "validate" (1: check host mirrors
- * before launching; default 1), "fail_pass"
+ * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
+ * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "validate" (1:
+ * check host mirrors before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531). */
@@ -326,7 +326,7 @@ int esp_forest_anc_masks(const int32_t* parents, int32_t n, uint64_t* masks);
 int esp_attn_decode_static(const esp_attn_shape* shape, void* stream, const esp_attn_args* args);
 
 /* Name of the attention kernel the last esp_attn_forward on this context
- * launched ("decode_gqa", "flash_umma", "flash_general"), for tests and traces. */
+ * launched ("decode_gqa", "flash_umma", "flash_umma_pair", "flash_general"), for tests and traces. */
 const char* esp_attn_last_kernel(const esp_attn_ctx* ctx);
 
 /* Reads and clears the context's device status word: a kernel whose bounded wait ran

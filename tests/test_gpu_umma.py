@@ -1,5 +1,6 @@
-"""Parity of the tcgen05 kernel (flash_umma: 128 (row, head) pairs per CTA, TMEM accumulators)
-with the float64 oracle, through the C ABI: tree verify (16-row tiles x 8 heads), causal prefill
+"""Parity of the two tcgen05 kernels (flash_umma: one CTA per SM, 128-key blocks, deep rings;
+flash_umma_pair: two CTAs per SM, 64-key blocks; both 128 (row, head) pairs per CTA with TMEM
+accumulators) with the float64 oracle, through the C ABI; every case runs on both: tree verify (16-row tiles x 8 heads), causal prefill
 (128-row tiles), forest masks, chunked prefill over a cached prefix, split-K records + combine,
 and integer-exact mask probes."""
 import numpy as np
@@ -10,14 +11,19 @@ from tests import util
 
 pytestmark = pytest.mark.gpu
 
+KERNELS = {1: "flash_umma", 2: "flash_umma_pair"}
 
-def _check(oracle_lib, w, tile_rows, mode=capi.ESP_PLAN_REFERENCE, groups=256, split=512, with_abs=True, expect="flash_umma"):
+
+def _check(oracle_lib, w, tile_rows, mode=capi.ESP_PLAN_REFERENCE, groups=256, split=512, with_abs=True):
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
-    O, lse, parts, plan, kernel = host.run_pass(w, mode=mode, tile_rows=tile_rows, split=split, groups=groups)
-    assert kernel == expect
-    util.check_output(O, ref, w, ref_abs=ref_abs if with_abs else None, what=w.name)
-    fin = np.isfinite(lse_ref)
-    assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
+    plan = None
+    for opt, name in KERNELS.items():
+        O, lse, parts, plan, kernel = host.run_pass(w, mode=mode, tile_rows=tile_rows, split=split, groups=groups,
+                                                    options={"umma_kernel": opt})
+        assert kernel == name
+        util.check_output(O, ref, w, ref_abs=ref_abs if with_abs else None, what=f"{w.name}/{name}")
+        fin = np.isfinite(lse_ref)
+        assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
     return plan
 
 
@@ -59,14 +65,16 @@ def test_masks_and_tile_shapes(oracle_lib, mask, tr, H, Hkv):
 def test_records_match_f64_without_rounding(oracle_lib):
     w = wl.config_c4(n_seqs=2, prefix=512)
     ref, lse_ref = oracle_lib.attention_f64(w)
-    O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True)
-    assert kernel == "flash_umma"
-    O64, lse64 = util.records_to_output(parts, w, plan.tiles, plan.jobs, 16)
-    assert np.abs(O64 - ref).max() <= util.TOL_16
-    assert np.abs(lse64 - lse_ref).max() < 1e-3
+    for opt, name in KERNELS.items():
+        O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True, options={"umma_kernel": opt})
+        assert kernel == name
+        O64, lse64 = util.records_to_output(parts, w, plan.tiles, plan.jobs, 16)
+        assert np.abs(O64 - ref).max() <= util.TOL_16
+        assert np.abs(lse64 - lse_ref).max() < 1e-3
 
 
-def test_tree_mask_probe_is_exact_on_tensor_cores():
+@pytest.mark.parametrize("umma_kernel", [1, 2], ids=["stream", "pair"])
+def test_tree_mask_probe_is_exact_on_tensor_cores(umma_kernel):
     """Q = 0 and one-hot V rows: the fp32 record of node n must hold exactly its ancestor set and
     exact integer sums of the prefix codes (P = 1.0 exactly in bf16, fp32 accumulation in TMEM)."""
     P, M, H, Hkv, HD, bt = 200, 16, 16, 2, 128, 16
@@ -83,8 +91,8 @@ def test_tree_mask_probe_is_exact_on_tensor_cores():
     for r in range(w.n_rows):
         vb[r, :, r % M] = 1.0
     w.Vb = wl.f32_to_bf16_bits(vb.reshape(w.n_rows, -1))
-    O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True, split=0)
-    assert kernel == "flash_umma"
+    O, lse, parts, plan, kernel = host.run_pass(w, tile_rows=16, force_parts=True, split=0, options={"umma_kernel": umma_kernel})
+    assert kernel == KERNELS[umma_kernel]
     G = w.G
     rec = parts[: plan.n_parts * Hkv * 16 * G * (HD + 2)].reshape(plan.n_parts, Hkv, 16, G, HD + 2)
     for t in plan.tiles:
