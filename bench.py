@@ -221,7 +221,7 @@ def main():
     from espetero_b200 import shard
     tile_rows = TILE_ROWS[args.workload]
     split_kv = args.workload == "c5" and world > 1
-    groups = args.groups or (148 if args.workload == "c4" else 148 * 2 * 8)
+    groups = args.groups or {"c4": 148, "c5": 148 * 2}.get(args.workload, 148 * 2 * 8)
     if not split_kv:
         w = build_workload(args.workload, rank, args.small)
         op = host.AttnOp.for_workload(w, tile_rows, local)

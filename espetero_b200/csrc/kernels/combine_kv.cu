@@ -12,7 +12,7 @@
 namespace esp {
 namespace {
 
-// One CTA of 128 threads per (job row, group of heads). A head is served by HD / 4 threads (4 dims
+// One CTA of 256 threads per (job row, group of heads). A head is served by HD / 4 threads (4 dims
 // each) times n_slices record slices: slice k takes the records k, k + n_slices, ... so that many
 // record loads are in flight at once (a single sequential walk over 64 records is latency-bound);
 // passes with few records per job use fewer slices and put more heads in a CTA. The maximum M is
@@ -25,7 +25,7 @@ __device__ __forceinline__ float4 ld_rec4(const float* p) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
-constexpr int kCombineThreads = 128;
+constexpr int kCombineThreads = 256;
 
 template <int QDT>
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {

@@ -57,16 +57,16 @@ struct CombineArgs {
   int32_t n_jobs;
   int32_t q_dtype;
   int32_t rows_max;  // most rows of any job (<= tile_rows): the grid covers only these
-  int32_t n_slices;  // record slices per head: a power of two, 32 <= (HD / 4) * n_slices <= 128
+  int32_t n_slices;  // record slices per head: a power of two, 32 <= (HD / 4) * n_slices <= 256
   float* out_parts;  // reduce mode: job j's merged record goes to record out_part0 + j here; else NULL
   int32_t out_part0;
 };
 
 // Record slices per head for the combine kernel: about a quarter of the job's records per slice,
-// at least one warp per head, at most one CTA (128 threads) per head.
+// at least one warp per head, at most one CTA (256 threads) per head.
 inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
   const int tpd = HD / 4;
-  int nsl = 128 / tpd;
+  int nsl = 256 / tpd;
   while (nsl > 1 && nsl * 2 > parts_max && tpd * (nsl / 2) >= 32) nsl /= 2;
   return nsl;
 }
