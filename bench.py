@@ -206,6 +206,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -230,6 +231,7 @@ def main():
     tile_rows = TILE_ROWS[args.workload]
     split_kv = args.workload == "c5" and world > 1
     groups = args.groups or {"c4": 148, "c5": 148 * 2}.get(args.workload, 148 * 2 * 8)
+    xch = None
     if not split_kv:
         w = build_workload(args.workload, rank, args.small)
         op = host.AttnOp.for_workload(w, tile_rows, local)
@@ -249,7 +251,7 @@ def main():
         lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
         w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
         op = host.AttnOp.for_workload(w, tile_rows, local)
-        base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 148 * 2 * 2, tile_rows)
+        base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, args.groups or 148 * 2, tile_rows)
         tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
         plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, tile_rows)
         dp = op.upload(w, plan)
@@ -262,13 +264,36 @@ def main():
         rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
         rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)
 
-        def step():
-            op.forward(dp, a_attn)
-            op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
-            dist.all_gather_into_tensor(rec_world, rec_local)
-            op.combine(dp, rec_world, merge_dev, 1)
+        # Preferred: one kernel per rank reduces, stores the record into every rank's buffer over
+        # NVLink peer mappings and merges (esp_attn_exchange_parts). If the peer mappings cannot be
+        # set up on this box (all ranks decide together), the records go through an NCCL all-gather.
+        if args.exchange == "p2p":
+            try:
+                xch = host.PeerExchange(op, n_jobs=1, rows_max=1)
+                ok = 1
+            except Exception as e:  # noqa: BLE001 - reported below, then the NCCL path is used
+                print(f"[rank {rank}] peer exchange unavailable: {e}", file=sys.stderr, flush=True)
+                ok = 0
+            flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                xch = None
+
+        if xch is not None:
+            def step():
+                xch.next_epoch()
+                op.forward(dp, a_attn)
+                op.exchange_parts(dp, dp.parts, red_dev, len(red_jobs), xch, parts_max=n_parts)
+            sharding = "KV range per rank; one kernel per rank merges, exchanges records over NVLink peer stores and finishes"
+        else:
+            def step():
+                op.forward(dp, a_attn)
+                op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
+                dist.all_gather_into_tensor(rec_world, rec_local)
+                op.combine(dp, rec_world, merge_dev, 1)
+            sharding = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank"
         step_attn = lambda: op.forward(dp, a_attn)
-        sharding, scaling = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank", "strong"
+        scaling = "strong"
     bytes_step = w.kv_bytes_read()
     stream = torch.cuda.current_stream(dev)
     # Working sets that fit the 126 MB L2 are flushed out between timed iterations by writing a
@@ -399,6 +424,8 @@ def main():
             v, threads, sample, dt = time_cpu(args.workload)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
         print(json.dumps(line), flush=True)
+    if xch is not None:
+        xch.close()
     op.close()
     if world > 1:
         dist.destroy_process_group()

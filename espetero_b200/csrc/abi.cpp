@@ -300,7 +300,8 @@ int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
   if (st != 0) {
     cudaMemsetAsync(c->d_status, 0, sizeof(int), s);
     return fail(ESP_ERR_CUDA, "a kernel gave up a bounded wait (status %d: %s)", st,
-                st == esp::kStatusTmaTimeout ? "TMA load never completed" : st == esp::kStatusMmaTimeout ? "MMA never completed" : "bad block id");
+                st == esp::kStatusTmaTimeout ? "TMA load never completed" : st == esp::kStatusMmaTimeout ? "MMA never completed"
+               : st == esp::kStatusPeerTimeout ? "a peer GPU never published its records" : "bad block id");
   }
   return ESP_OK;
 }
@@ -392,6 +393,95 @@ int esp_attn_reduce_parts(esp_attn_ctx* c, void* stream, const float* parts, con
                           int32_t n_jobs, float* parts_out, int32_t out_part0) {
   if (!c || !parts_out || out_part0 < 0) return fail(ESP_ERR_INVALID, "esp_attn_reduce_parts: null or negative argument");
   return combine_impl(c, stream, parts, nullptr, nullptr, nullptr, p, jobs, n_jobs, c->tile_rows, 64, parts_out, out_part0);
+}
+
+size_t esp_attn_exchange_floats(const esp_attn_shape* s, int32_t n_jobs, int32_t world) {
+  if (!s || n_jobs <= 0 || world <= 0 || s->Hkv <= 0 || s->H <= 0) return 0;
+  const int TR = s->tile_rows > 0 ? s->tile_rows : 8;
+  return size_t(2) * size_t(world) * size_t(n_jobs) * size_t(s->Hkv) * size_t(TR) * size_t(s->H / s->Hkv) * size_t(s->HD + 2);
+}
+
+size_t esp_attn_exchange_flags(const esp_attn_shape* s, int32_t n_jobs, int32_t rows_max, int32_t world) {
+  if (!s || n_jobs <= 0 || world <= 0 || rows_max <= 0) return 0;
+  return size_t(world) * size_t(n_jobs) * size_t(rows_max) * size_t(s->H);
+}
+
+int esp_attn_exchange_parts(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
+                            const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int32_t rows_max,
+                            int32_t parts_max, const esp_attn_exchange* xp) {
+  if (!c || !p || !xp) return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: null argument");
+  if (n_jobs <= 0) return ESP_OK;
+  const esp_attn_exchange& x = *xp;
+  if (x.world < 1 || x.world > ESP_ATTN_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
+    return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: rank %d of world %d", x.rank, x.world);
+  if (x.phases < 1 || x.phases > 3 || x.wait_ms < 0 || x.epoch == 0)
+    return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: phases %d, wait_ms %d, epoch %llu", x.phases, x.wait_ms,
+                (unsigned long long)x.epoch);
+  for (int q = 0; q < x.world; ++q)
+    if (!x.records[q] || !x.flags[q] || (reinterpret_cast<uintptr_t>(x.records[q]) & 7) || (reinterpret_cast<uintptr_t>(x.flags[q]) & 7))
+      return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: exchange buffer or flag array of rank %d is null or not 8-byte aligned", q);
+  if (!parts || !jobs || ((x.phases & 2) && !O)) return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: null parts / O / jobs");
+  if (int rc = check_params(c, *p)) return rc;
+  const esp_attn_shape& s = c->shape;
+  if ((s.flags & ESP_ATTN_FLAG_GATE) && !X) return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: gate flag set but X is null");
+  esp::ExchangeArgs k{};
+  k.c.parts = parts, k.c.X = (s.flags & ESP_ATTN_FLAG_GATE) ? X : nullptr, k.c.O = O, k.c.lse = lse, k.c.jobs = jobs, k.c.p = *p;
+  k.c.HD = s.HD, k.c.G = c->G, k.c.tile_rows = c->tile_rows, k.c.n_jobs = n_jobs, k.c.q_dtype = s.q_dtype;
+  k.c.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
+  k.c.n_slices = esp::combine_slices(s.HD, parts_max < 1 ? 1 : parts_max);
+  k.rank = x.rank, k.world = x.world, k.phases = x.phases, k.wait_ms = x.wait_ms ? uint32_t(x.wait_ms) : 2000u, k.epoch = x.epoch;
+  for (int q = 0; q < x.world; ++q) k.records[q] = x.records[q], k.flags[q] = reinterpret_cast<unsigned long long*>(x.flags[q]);
+  k.status = c->d_status;
+  // Every CTA may wait for its peers: the grid has to be resident at once (2 CTAs of 256 threads per SM at least).
+  if (esp::exchange_grid_ctas(k.c) > 296)
+    return fail(ESP_ERR_UNSUPPORTED, "esp_attn_exchange_parts: %lld CTAs cannot be resident at once; gather the records with a collective and call esp_attn_combine_parts",
+                (long long)esp::exchange_grid_ctas(k.c));
+  const cudaError_t e = esp::launch_exchange(k, static_cast<cudaStream_t>(stream), &c->launches);
+  if (e != cudaSuccess) return cuda_fail(e, "exchange_parts");
+  return ESP_OK;
+}
+
+int esp_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[ESP_P2P_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == ESP_P2P_HANDLE_BYTES, "IPC handle size");
+  if (!ptr || !handle || bytes == 0) return fail(ESP_ERR_INVALID, "esp_p2p_alloc: null argument or zero size");
+  *ptr = nullptr;
+  void* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "esp_p2p_alloc: cudaMalloc");
+  if ((e = cudaMemset(d, 0, bytes)) == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t hd;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&hd, d);
+  if (e != cudaSuccess) {
+    cudaFree(d);
+    return cuda_fail(e, "esp_p2p_alloc: zero fill / cudaIpcGetMemHandle");
+  }
+  memcpy(handle, &hd, sizeof(hd));
+  *ptr = d;
+  return ESP_OK;
+}
+
+int esp_p2p_open(const unsigned char handle[ESP_P2P_HANDLE_BYTES], void** ptr) {
+  if (!ptr || !handle) return fail(ESP_ERR_INVALID, "esp_p2p_open: null argument");
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle, sizeof(hd));
+  *ptr = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr, hd, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e, "esp_p2p_open: cudaIpcOpenMemHandle");
+  return ESP_OK;
+}
+
+int esp_p2p_close(void* ptr) {
+  if (!ptr) return ESP_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "esp_p2p_close: cudaIpcCloseMemHandle");
+  return ESP_OK;
+}
+
+int esp_p2p_free(void* ptr) {
+  if (!ptr) return ESP_OK;
+  const cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "esp_p2p_free: cudaFree");
+  return ESP_OK;
 }
 
 }  // extern "C"

@@ -9,111 +9,37 @@
 #include "common.cuh"
 #include "../launch.h"
 
+#include "merge.cuh"
+
 namespace esp {
 namespace {
 
-// One CTA of 256 threads per (job row, group of heads). A head is served by HD / 4 threads (4 dims
-// each) times n_slices record slices: slice k takes the records k, k + n_slices, ... so that many
-// record loads are in flight at once (a single sequential walk over 64 records is latency-bound);
-// passes with few records per job use fewer slices and put more heads in a CTA. The maximum M is
-// found first by all threads of the head, so every slice weighs its records with the final
-// e^(m_s - M); the slices' sums are then added in slice order through shared memory: no atomics,
-// the result does not depend on scheduling. The grid covers only rows_max rows per job (1 for
-// decode passes). A record is HD + 2 floats long, so records are only 8-byte aligned: float2 loads.
-__device__ __forceinline__ float4 ld_rec4(const float* p) {
-  const float2 a = *reinterpret_cast<const float2*>(p), b = *reinterpret_cast<const float2*>(p + 2);
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-
-constexpr int kCombineThreads = 256;
-
 template <int QDT>
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
-  using QE = Elem16<QDT>;
-  __shared__ float red_m[kCombineThreads / 32];
-  __shared__ float red_acc[kCombineThreads][5];
+  __shared__ MergeScratch scratch;
   const esp_attn_params& p = a.p;
   const int HD = a.HD, G = a.G, TR = a.tile_rows;
-  const int tpd = HD / 4, nsl = a.n_slices;  // threads per record, record slices per head
-  const int tph = tpd * nsl;                 // threads per head (a multiple of 32)
+  const int tpd = HD / 4, tph = tpd * a.n_slices;
   const int job_i = blockIdx.x / a.rows_max, r = blockIdx.x % a.rows_max;
-  const int hb = threadIdx.x / tph;          // head within the CTA
-  const int h = blockIdx.y * (kCombineThreads / tph) + hb;
+  const int h = blockIdx.y * (kCombineThreads / tph) + threadIdx.x / tph;
   // The records are written by the attention kernel launched just before on the same stream:
   // with programmatic dependent launch this grid may start early and waits here for them.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const esp_attn_combine job = a.jobs[job_i];
   if (r >= job.rows) return;
-  const int tid = threadIdx.x, sl = (tid % tph) / tpd, d4 = tid % tpd;
-  const int kvh = h / G, hg = h % G;
+  const bool live = h < p.H;  // the last CTA of a row may reach past the heads
+  const int d4 = threadIdx.x % tpd, kvh = live ? h / G : 0, hg = live ? h % G : 0;
   const size_t stride = size_t(p.Hkv) * TR * G * (HD + 2);
-  const float* rec0 = a.parts + ((size_t(job.part0) * p.Hkv + kvh) * TR * G + size_t(r) * G + hg) * (HD + 2);
-  const int n = job.nparts;
-  float M = -INFINITY;
-  for (int s = tid % tph; s < n; s += tph) M = fmaxf(M, rec0[size_t(s) * stride + HD]);
-#pragma unroll
-  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-  if ((tid & 31) == 0) red_m[tid >> 5] = M;
-  __syncthreads();
-  M = -INFINITY;
-  for (int w = hb * (tph / 32); w < (hb + 1) * (tph / 32); ++w) M = fmaxf(M, red_m[w]);
-  float L = 0.0f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int s = sl;
-  for (; s + 3 * nsl < n; s += 4 * nsl) {
-    float m4[4], l4[4];
-    float4 o4[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float* rec = rec0 + size_t(s + i * nsl) * stride;
-      m4[i] = rec[HD], l4[i] = rec[HD + 1];
-      o4[i] = ld_rec4(rec + 4 * d4);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float w = (m4[i] == -INFINITY) ? 0.0f : __expf(m4[i] - M);
-      L += w * l4[i];
-      acc.x += w * o4[i].x, acc.y += w * o4[i].y, acc.z += w * o4[i].z, acc.w += w * o4[i].w;
-    }
-  }
-  for (; s < n; s += nsl) {
-    const float* rec = rec0 + size_t(s) * stride;
-    const float w = (rec[HD] == -INFINITY) ? 0.0f : __expf(rec[HD] - M);
-    const float4 o = ld_rec4(rec + 4 * d4);
-    L += w * rec[HD + 1];
-    acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
-  }
-  red_acc[tid][0] = acc.x, red_acc[tid][1] = acc.y, red_acc[tid][2] = acc.z, red_acc[tid][3] = acc.w, red_acc[tid][4] = L;
-  __syncthreads();
-  if (sl != 0) return;
-  for (int k = 1; k < nsl; ++k) {  // fixed order
-    const float* q = red_acc[hb * tph + k * tpd + d4];
-    acc.x += q[0], acc.y += q[1], acc.z += q[2], acc.w += q[3], L += q[4];
-  }
+  const size_t rec_off = ((size_t(kvh) * TR + size_t(r)) * G + hg) * (HD + 2);
+  const Merged m = merge_records(a.parts + size_t(job.part0) * stride + rec_off, live ? job.nparts : 0, stride, HD, a.n_slices, scratch);
+  if (!m.owner || !live) return;
   if (a.out_parts) {
     // Reduce mode: the merged, still unnormalised record [O | M | L] of the job, for a second
     // merge level (records of other GPUs).
-    float* rec = a.out_parts + ((size_t(a.out_part0 + job_i) * p.Hkv + kvh) * TR * G + size_t(r) * G + hg) * (HD + 2);
-    *reinterpret_cast<float2*>(rec + 4 * d4) = make_float2(acc.x, acc.y);
-    *reinterpret_cast<float2*>(rec + 4 * d4 + 2) = make_float2(acc.z, acc.w);
-    if (d4 == 0) {
-      rec[HD] = M;
-      rec[HD + 1] = L;
-    }
+    store_record(a.out_parts + size_t(a.out_part0 + job_i) * stride + rec_off, m, HD, d4);
     return;
   }
-  const int row = job.r0 + r;
-  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-  float o[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
-  if (a.X) {
-    const float4 gt = *reinterpret_cast<const float4*>(a.X + size_t(row) * p.g_ld + size_t(h) * 2 * HD + HD + 4 * d4);
-    o[0] *= sigmoid_gate(gt.x), o[1] *= sigmoid_gate(gt.y), o[2] *= sigmoid_gate(gt.z), o[3] *= sigmoid_gate(gt.w);
-  }
-  uint2 packed;
-  packed.x = QE::pack2(o[0], o[1]);
-  packed.y = QE::pack2(o[2], o[3]);
-  *reinterpret_cast<uint2*>(static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD + 4 * d4) = packed;
-  if (a.lse && d4 == 0) a.lse[size_t(row) * p.H + h] = L > 0.0f ? M + __logf(L) : -INFINITY;
+  finish_row<QDT>(m, a.X, a.O, a.lse, p, HD, job.r0 + r, h, d4);
 }
 
 // 16 bytes per thread; grid (entries, ceil(kv_ld * 2 / 16 / 128)).

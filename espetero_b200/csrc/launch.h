@@ -11,7 +11,7 @@
 namespace esp {
 
 // Values a kernel may leave in the context's device status word when a bounded wait runs out.
-enum : int { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusBadBlock = 3 };
+enum : int { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusBadBlock = 3, kStatusPeerTimeout = 4 };
 
 // What every attention kernel receives: the bindings of the reference dispatch
 // (src/model/impl/forest.h:2902-2913) plus the shape constants.
@@ -62,6 +62,19 @@ struct CombineArgs {
   int32_t out_part0;
 };
 
+// The peer exchange kernel: a merge whose result goes through every rank's exchange buffer.
+struct ExchangeArgs {
+  CombineArgs c;  // parts, X, O, lse, jobs, shape; out_parts unused
+  int32_t rank;
+  int32_t world;
+  int32_t phases;
+  uint32_t wait_ms;
+  unsigned long long epoch;
+  float* records[ESP_ATTN_MAX_PEERS];
+  unsigned long long* flags[ESP_ATTN_MAX_PEERS];
+  int* status;
+};
+
 // Record slices per head for the combine kernel: about a quarter of the job's records per slice,
 // at least one warp per head, at most one CTA (256 threads) per head.
 inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
@@ -76,6 +89,8 @@ inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
 cudaError_t launch_flash_general(const KernelArgs& a, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& pool_map, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_combine(const CombineArgs& a, cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_exchange(const ExchangeArgs& x, cudaStream_t stream, uint64_t* launches);
+int64_t exchange_grid_ctas(const CombineArgs& a);
 cudaError_t launch_kv_save(const void* Kb, const void* Vb, void* kv, const float* kv_scales, const esp_kv_save_entry* entries,
                            int32_t n, const esp_attn_params& p, int32_t HD, int32_t q_dtype, int32_t kv_dtype,
                            cudaStream_t stream, uint64_t* launches);

@@ -206,6 +206,17 @@ class AttnOp:
         capi.check(self.lib.esp_attn_reduce_parts(self.ctx, C.c_void_p(s), _ptr(parts), C.byref(p), _ptr(jobs_dev), n_jobs,
                                                   _ptr(parts_out), out_part0))
 
+    def exchange_parts(self, dp: DevicePass, parts, jobs_dev, n_jobs: int, xch: "PeerExchange", rank: int | None = None,
+                       phases: int = 3, rows_max: int = 1, parts_max: int = 64, wait_ms: int = 0, stream: int | None = None):
+        """esp_attn_exchange_parts: merge the local records, push the result to every rank's exchange
+        buffer over peer memory, wait for the peers' and finish O / lse: one kernel. Advances the
+        exchange's epoch when the launch includes the publishing phase of the last (or only) local rank."""
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        p = self.params(dp.w)
+        x = xch.descriptor(xch.rank if rank is None else rank, phases, wait_ms)
+        capi.check(self.lib.esp_attn_exchange_parts(self.ctx, C.c_void_p(s), _ptr(parts), _ptr(dp.X), _ptr(dp.O), _ptr(dp.lse),
+                                                    C.byref(p), _ptr(jobs_dev), n_jobs, rows_max, parts_max, C.byref(x)))
+
     def kv_save(self, dp: DevicePass, entries: np.ndarray, stream: int | None = None):
         s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
         e = _dev(np.ascontiguousarray(entries, dtype=KVSAVE_DT), self.device)
@@ -269,3 +280,91 @@ def force_partial_records(plan: Plan, trees: np.ndarray) -> Plan:
             jobs.append((int(t["r0"]), min(plan.tile_rows, int(tr["base"]) + int(tr["M"]) - int(t["r0"])), n_parts, 1))
             n_parts += 1
     return Plan(tiles, np.array(jobs, dtype=COMBINE_DT) if jobs else np.zeros(0, dtype=COMBINE_DT), n_parts, plan.tile_rows)
+
+
+class PeerExchange:
+    """The exchange buffers of esp_attn_exchange_parts: this rank's records + flags (esp_p2p_alloc)
+    and the peers' mapped into this process (esp_p2p_open), handles carried by torch.distributed.
+
+    PeerExchange(op, n_jobs, rows_max, group=...) is the multi-process form (one process per GPU).
+    PeerExchange.emulated(op, n_jobs, rows_max, world) keeps `world` buffer sets on ONE GPU in one
+    process, for tests that run the ranks' phases one after another.
+    The caller bumps `epoch` (next_epoch()) once per exchange, on every rank alike."""
+
+    def __init__(self, op: AttnOp, n_jobs: int, rows_max: int = 1, group=None):
+        import torch.distributed as dist
+        self.lib, self.op = op.lib, op
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.epoch = 0
+        self._own, self._opened = [], []
+        rec_bytes, flag_bytes = self._sizes(op, n_jobs, rows_max, self.world)
+        rec, hr = self._alloc(rec_bytes)
+        flg, hf = self._alloc(flag_bytes)
+        mine = torch.tensor(list(hr + hf), dtype=torch.uint8, device=op.device)
+        every = torch.empty(self.world * mine.numel(), dtype=torch.uint8, device=op.device)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        every = bytes(every.cpu().numpy().tobytes())
+        self.records, self.flags = [], []
+        for q in range(self.world):
+            if q == self.rank:
+                self.records.append(rec), self.flags.append(flg)
+                continue
+            h = every[q * 128:(q + 1) * 128]
+            self.records.append(self._open(h[:64])), self.flags.append(self._open(h[64:]))
+        dist.barrier(group)  # every rank has mapped every buffer before anyone writes
+
+    @classmethod
+    def emulated(cls, op: AttnOp, n_jobs: int, rows_max: int, world: int):
+        self = cls.__new__(cls)
+        self.lib, self.op, self.rank, self.world, self.epoch = op.lib, op, 0, world, 0
+        self._own, self._opened = [], []
+        rec_bytes, flag_bytes = cls._sizes(op, n_jobs, rows_max, world)
+        self.sets = []
+        for _ in range(world):
+            self.sets.append((self._alloc(rec_bytes)[0], self._alloc(flag_bytes)[0]))
+        self.records, self.flags = None, None
+        return self
+
+    @staticmethod
+    def _sizes(op, n_jobs, rows_max, world):
+        lib = op.lib
+        nf = lib.esp_attn_exchange_floats(C.byref(op.shape), n_jobs, world)
+        ng = lib.esp_attn_exchange_flags(C.byref(op.shape), n_jobs, rows_max, world)
+        if nf == 0 or ng == 0:
+            raise ValueError("exchange sizes: bad n_jobs / rows_max / world")
+        return 4 * nf, 8 * ng
+
+    def _alloc(self, nbytes):
+        ptr, h = C.c_void_p(), C.create_string_buffer(64)
+        capi.check(self.lib.esp_p2p_alloc(C.byref(ptr), nbytes, h))
+        self._own.append(ptr.value)
+        return ptr.value, h.raw
+
+    def _open(self, handle: bytes):
+        ptr = C.c_void_p()
+        capi.check(self.lib.esp_p2p_open(C.c_char_p(handle), C.byref(ptr)))
+        self._opened.append(ptr.value)
+        return ptr.value
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def descriptor(self, rank: int, phases: int = 3, wait_ms: int = 0) -> capi.Exchange:
+        x = capi.Exchange()
+        x.rank, x.world, x.phases, x.wait_ms, x.epoch = rank, self.world, phases, wait_ms, self.epoch
+        if self.records is None:  # emulated ranks: rank r's own buffers are set r; all are local
+            for q in range(self.world):
+                x.records[q], x.flags[q] = self.sets[q]
+        else:
+            for q in range(self.world):
+                x.records[q], x.flags[q] = self.records[q], self.flags[q]
+        return x
+
+    def close(self):
+        torch.cuda.synchronize(self.op.device)
+        for p in self._opened:
+            capi.check(self.lib.esp_p2p_close(C.c_void_p(p)))
+        for p in self._own:
+            capi.check(self.lib.esp_p2p_free(C.c_void_p(p)))
+        self._opened, self._own = [], []

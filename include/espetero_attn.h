@@ -222,6 +222,54 @@ int esp_attn_combine_parts(esp_attn_ctx* ctx, void* stream, const float* parts, 
 int esp_attn_reduce_parts(esp_attn_ctx* ctx, void* stream, const float* parts, const esp_attn_params* p,
                           const esp_attn_combine* jobs, int32_t n_jobs, float* parts_out, int32_t out_part0);
 
+/* ---- Split-KV over the GPUs of one box: reduce, exchange over peer memory and merge in ONE kernel.
+ * No counterpart in the reference (one GPU). Every rank holds the keys of one range of a long
+ * sequence and has written partial records for them (esp_attn_forward with records-only tiles).
+ * esp_attn_exchange_parts then, in one launch per rank:
+ *   1. merges the rank's records of each job into one unnormalised record [O | M | L];
+ *   2. stores that record into slot `rank` of EVERY rank's exchange buffer with plain stores
+ *      through peer mappings (NVLink), then publishes a per-CTA flag (release, system scope);
+ *   3. waits (bounded) until the same CTA of every rank has published, and merges the `world`
+ *      records in rank order: all ranks produce identical bits, O and lse are final.
+ * The buffers come from esp_p2p_alloc on each rank and are opened on the others with
+ * esp_p2p_open (the caller carries the 64-byte handles between processes). `epoch` must be the
+ * same on all ranks for a call and larger by one for the next call on the same buffers; the
+ * buffers hold two epochs, so a rank may run at most one call ahead of the slowest.
+ * The grid must fit on the GPU at once (jobs * rows * head groups <= 296 CTAs), else
+ * ESP_ERR_UNSUPPORTED: gather with a library collective and call esp_attn_combine_parts.
+ * If a peer never publishes, the kernel gives up after wait_ms, writes nothing to O and
+ * esp_attn_check_status reports it; the context stays usable. */
+#define ESP_ATTN_MAX_PEERS 8
+typedef struct esp_attn_exchange {
+  int32_t rank;
+  int32_t world;     /* 1 .. ESP_ATTN_MAX_PEERS */
+  int32_t phases;    /* 3: the whole exchange in one launch. 1: steps 1-2 only, 2: step 3 only (lets a
+                        test run several emulated ranks one after another on one GPU) */
+  int32_t wait_ms;   /* bound of the wait in step 3; 0 = 2000 */
+  uint64_t epoch;    /* >= 1 */
+  float* records[ESP_ATTN_MAX_PEERS];    /* rank q's exchange buffer as mapped in this process (own included) */
+  uint64_t* flags[ESP_ATTN_MAX_PEERS];   /* rank q's flag array as mapped in this process; zeroed at allocation */
+} esp_attn_exchange;
+
+/* Sizes of one rank's exchange buffer (floats) and flag array (uint64) for a context's shape. */
+size_t esp_attn_exchange_floats(const esp_attn_shape* shape, int32_t n_jobs, int32_t world);
+size_t esp_attn_exchange_flags(const esp_attn_shape* shape, int32_t n_jobs, int32_t rows_max, int32_t world);
+
+/* rows_max: most rows of any job (1 for decode). jobs are device-resident, as for esp_attn_combine_parts;
+ * parts_max: most records of any job (sizes the merge's parallelism; 64 if unknown). */
+int esp_attn_exchange_parts(esp_attn_ctx* ctx, void* stream, const float* parts, const float* X, void* O, float* lse,
+                            const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int32_t rows_max,
+                            int32_t parts_max, const esp_attn_exchange* x);
+
+/* Device memory another process of the same box can map: cudaMalloc + zero fill + an IPC handle
+ * (64 bytes, opaque). esp_p2p_open maps a peer's allocation into this process (peer access is
+ * enabled on first use); esp_p2p_close unmaps it; esp_p2p_free releases an own allocation. */
+#define ESP_P2P_HANDLE_BYTES 64
+int esp_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[ESP_P2P_HANDLE_BYTES]);
+int esp_p2p_open(const unsigned char handle[ESP_P2P_HANDLE_BYTES], void** ptr);
+int esp_p2p_close(void* ptr);
+int esp_p2p_free(void* ptr);
+
 /* kv_save (40_attention.metal:875-889; forest.h:2935-2947). With an ESP_E4M3
  * pool the rows are quantised with the destination block's scale from kv_scales. */
 int esp_kv_save(esp_attn_ctx* ctx, void* stream, const void* Kb, const void* Vb, void* kv, const float* kv_scales,
