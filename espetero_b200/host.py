@@ -351,7 +351,12 @@ class PeerExchange:
         return self.epoch
 
     def descriptor(self, rank: int, phases: int = 3, wait_ms: int = 0) -> capi.Exchange:
-        x = capi.Exchange()
+        cache = self.__dict__.setdefault("_desc", {})
+        x = cache.get((rank, phases, wait_ms))
+        if x is not None:  # only the epoch changes between calls
+            x.epoch = self.epoch
+            return x
+        x = cache[(rank, phases, wait_ms)] = capi.Exchange()
         x.rank, x.world, x.phases, x.wait_ms, x.epoch = rank, self.world, phases, wait_ms, self.epoch
         if self.records is None:  # emulated ranks: rank r's own buffers are set r; all are local
             for q in range(self.world):
