@@ -197,6 +197,41 @@ def run_reference_arm(args):
 NCU_TRAFFIC_BYTES = {"c2": 1.11846e9 + 17.03e6, "c5": 537.78e6 + 5.03e6, "c4": 136.94e6 + 4.6e6}
 
 
+L2_BYTES = 126e6
+
+
+class LayerCycle:
+    """Keeps the keys of a pass out of L2 between timed steps the way a model does: the pool holds
+    one region per attention layer and consecutive passes read consecutive layers. A workload whose
+    K/V bytes are below 2 x L2 gets as many layer regions (copies of its pool) as make the cycle
+    at least 4 x L2 long, and step i reads region i mod n; nothing is flushed and nothing else runs
+    between the timed steps. Larger workloads evict themselves with one region."""
+
+    def __init__(self, op, dp, w):
+        self.op, self.dp, self.w = op, dp, w
+        nbytes = max(1, w.kv_bytes_read())
+        self.n = 1 if nbytes >= 2 * L2_BYTES else min(64, int(-(-4 * L2_BYTES // nbytes)))
+        self.region = dp.replicate_layers(self.n)
+        self.i = 0
+
+    def args(self, n_jobs=None):
+        a = self.op.make_args(self.dp)
+        if n_jobs is not None:
+            a.n_jobs = n_jobs
+        return a
+
+    def next(self, a):
+        a.p.kv_base = self.w.kv_base + (self.i % self.n) * self.region
+        self.i += 1
+        return a
+
+    def describe(self):
+        if self.n == 1:
+            return "inputs larger than L2"
+        return (f"{self.n} layer regions of the pool read in turn ({self.n * self.w.kv_bytes_read() / 1e6:.0f} MB per cycle, "
+                f"L2 is 126 MB): a pass reads keys last touched {self.n - 1} passes ago; no flush kernels")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -237,11 +272,11 @@ def main():
         op = host.AttnOp.for_workload(w, tile_rows, local)
         plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
         dp = op.upload(w, plan)
-        a_full = op.make_args(dp)
-        a_attn = op.make_args(dp)
-        a_attn.n_jobs = 0  # attention kernel alone (no combine), for the per-kernel roofline figure
-        step = lambda: op.forward(dp, a_full)
-        step_attn = lambda: op.forward(dp, a_attn)
+        layers = LayerCycle(op, dp, w)
+        a_full = layers.args()
+        a_attn = layers.args(n_jobs=0)  # attention kernel alone (no combine), for the per-kernel roofline figure
+        step = lambda: op.forward(dp, layers.next(a_full))
+        step_attn = lambda: op.forward(dp, layers.next(a_attn))
         sharding, scaling = "sequences per rank, no collective", "weak"
     else:
         # One long sequence, keys split over the ranks on page boundaries: records for the local
@@ -257,7 +292,8 @@ def main():
         dp = op.upload(w, plan)
         for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
             dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
-        a_attn = op.make_args(dp)
+        layers = LayerCycle(op, dp, w)
+        a_attn = layers.args()
         a_full = a_attn
         red_dev = host._dev(red_jobs, dev)
         merge_dev = host._dev(shard.world_merge_jobs(1, world), dev)
@@ -282,54 +318,35 @@ def main():
         if xch is not None:
             def step():
                 xch.next_epoch()
-                op.forward(dp, a_attn)
+                op.forward(dp, layers.next(a_attn))
                 op.exchange_parts(dp, dp.parts, red_dev, len(red_jobs), xch, parts_max=n_parts)
             sharding = "KV range per rank; one kernel per rank merges, exchanges records over NVLink peer stores and finishes"
         else:
             def step():
-                op.forward(dp, a_attn)
+                op.forward(dp, layers.next(a_attn))
                 op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
                 dist.all_gather_into_tensor(rec_world, rec_local)
                 op.combine(dp, rec_world, merge_dev, 1)
             sharding = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank"
-        step_attn = lambda: op.forward(dp, a_attn)
+        step_attn = lambda: op.forward(dp, layers.next(a_attn))
         scaling = "strong"
     bytes_step = w.kv_bytes_read()
     stream = torch.cuda.current_stream(dev)
-    # Working sets that fit the 126 MB L2 are flushed out between timed iterations by writing a
-    # 512 MB buffer and then reading it back (the read pass pushes the dirty lines out, so that the
-    # timed kernel does not pay for their write-back); larger inputs evict themselves.
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev) if bytes_step < 2 * 126e6 else None
-    flush_sink = torch.zeros((), dtype=torch.int64, device=dev)
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
     def timed(fn, n):
-        """Seconds for n calls of fn: CUDA events on the launching stream, barrier + synchronize on both
-        sides; with an L2 flush each call is timed on its own and the flush stays outside."""
+        """Seconds for n calls of fn: CUDA events on the launching stream, barrier + synchronize on both sides."""
         barrier()
-        if flush is None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(n):
-                fn()
-            e1.record(stream)
-            barrier()
-            return e0.elapsed_time(e1) / 1e3
-        evs = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
         for _ in range(n):
-            flush.fill_(1)
-            flush_sink.copy_(flush.view(torch.int64).max())
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
             fn()
-            e1.record(stream)
-            evs.append((e0, e1))
+        e1.record(stream)
         barrier()
-        return sum(a.elapsed_time(b) for a, b in evs) / 1e3
+        return e0.elapsed_time(e1) / 1e3
 
     # ---- device-resident throughput (value)
     sampler = ClockSampler(local)
@@ -375,7 +392,7 @@ def main():
         if split_kv:
             step()
         else:
-            op.forward(dp, a_e2e)
+            op.forward(dp, layers.next(a_e2e))
         h_out.copy_(dp.O, non_blocking=True)
     for _ in range(3):
         step_e2e()
@@ -404,7 +421,7 @@ def main():
             "dtype": "bf16" if w.kv_dtype != wl.E4M3 else "e4m3->f16", "data": "synthetic",
             "config": {"workload": w.name, "sequences_per_gpu": len(w.trees), "H": w.H, "Hkv": w.Hkv, "HD": w.HD, "page": w.bt,
                        "kv_bytes_per_gpu": bytes_step, "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": op.last_kernel,
-                       "l2": "inputs larger than L2" if flush is None else "L2 flushed between timed iterations (512 MB written, then read back; outside the timed region)",
+                       "l2": layers.describe(),
                        "sharding": sharding},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": traffic, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},

@@ -29,6 +29,7 @@ struct esp_attn_ctx {
   int* d_status = nullptr;
   unsigned long long* trace = nullptr;  // caller-owned device buffer (esp_attn_set_trace)
   int32_t trace_blocks = 0;
+  int opt_trace_ctas = 0;  // per-CTA stamps behind the block events (the buffer must hold 8 * n_blocks + 2 + 4 * this)
   // driver entry point for tensor maps, resolved without linking libcuda
   void* encode_tiled = nullptr;
   // cached pool tensor map
@@ -193,6 +194,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
   if (!std::strcmp(name, "validate")) return &c->opt_validate;
   if (!std::strcmp(name, "umma_kernel")) return &c->opt_umma_kernel;
+  if (!std::strcmp(name, "trace_ctas")) return &c->opt_trace_ctas;
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   return nullptr;
 }
@@ -324,7 +326,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
   k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
   k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status;
-  k.trace = c->trace, k.trace_blocks = c->trace_blocks;
+  k.trace = c->trace, k.trace_blocks = c->trace_blocks, k.trace_ctas = c->trace ? c->opt_trace_ctas : 0;
   k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
 
@@ -359,7 +361,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     const bool stream_hbm = c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch);
     if (stream_hbm) {
       c->last_kernel = "flash_umma";
-      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees, stream, &c->launches);
     } else {
       c->last_kernel = "flash_umma_pair";
       e = esp::launch_flash_umma_pair(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);

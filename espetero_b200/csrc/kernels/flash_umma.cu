@@ -61,6 +61,9 @@ constexpr int kTmaWarpV = 10;               // TMA producer of V tiles
 constexpr int kThreads = 11 * 32;
 constexpr int kPages = BN / 16;             // TMA pages per tile
 
+// The n lowest bits set (n <= 0: none, n >= 64: all).
+__device__ __forceinline__ uint64_t low_bits64(int n) { return n <= 0 ? 0ull : (n >= 64 ? ~0ull : ((1ull << n) - 1ull)); }
+
 struct PageRef {  // where one 16-key page of a key block comes from
   int raw;        // block id as loaded from the page table (pool), or first row (Kb / Vb)
   int off;        // row inside the block (pool)
@@ -85,7 +88,7 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 template <int QDT>
 __global__ void __launch_bounds__(kThreads, 1)
     flash_umma_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
-                      const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
+                      const __grid_constant__ CUtensorMap vb_map, const __grid_constant__ InlinePlan plan, const KernelArgs a) {
   using QE = Elem16<QDT>;
   extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
@@ -114,9 +117,21 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const esp_attn_params& p = a.p;
-  const int G = a.G, TR = a.tile_rows, HPC = BM / TR;
-  const esp_attn_tile tile = a.tiles[a.n_tiles - 1 - int(blockIdx.x)];  // long (late) tiles first
-  const esp_attn_tree tree = a.trees[tile.tree];
+  const int tile_i = int(gridDim.x) - 1 - int(blockIdx.x);  // long (late) tiles first
+  const TileStart& ts = plan.start[min(tile_i, kInlinePlanMax - 1)];
+  const bool inl = ts.valid == tile_i + 1;  // small plan: everything for the first loads sits in one parameter line
+  esp_attn_tile tile;
+  esp_attn_tree tree;
+  if (inl) {
+    tile = ts.tile;
+    tree = ts.tree;
+  } else {
+    tile = a.tiles[tile_i];
+    tree = a.trees[tile.tree];
+  }
+  const int32_t* page_table = inl ? ts.blocks : a.blocks;
+  const int bt = inl ? ts.bt : p.bt;
+  const int G = inl ? tile.pad0 : a.G, TR = inl ? tile.pad1 : a.tile_rows, HPC = BM / TR;
   const int kvh = (int(blockIdx.y) * HPC) / G;
   const int end = tree.base + tree.M;
   const int rows_live = min(TR, end - tile.r0);
@@ -168,6 +183,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (tracing && b < a.trace_blocks) a.trace[8 * b + ev] = global_timer_ns();
   };
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks] = global_timer_ns();
+  // Optional per-CTA stamps (start, first scores seen, last block handed over, exit) behind CTA 0's events.
+  const int cta_lin = blockIdx.y * gridDim.x + blockIdx.x;
+  const bool cta_tracing = a.trace != nullptr && cta_lin < a.trace_ctas;
+  auto cta_stamp = [&](int ev) {
+    if (cta_tracing) a.trace[8 * a.trace_blocks + 2 + 4 * cta_lin + ev] = global_timer_ns();
+  };
+  if (tid == 0) cta_stamp(0);
 
   // Block list: cached 128-key blocks first, then the batch blocks some row of the tile can see
   // (the latter depend on the rows' mask records: see `meta` below).
@@ -207,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_prefetch_desc(&kb_map);
       tma_prefetch_desc(&vb_map);
     }
-    if (lane < kPages) {
+    {
       const bool is_v = warp == kTmaWarpV;
       const int depth = is_v ? VS : KS;
       uint64_t* full = is_v ? v_full : k_full;
@@ -216,13 +238,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       const CUtensorMap* batch_map = is_v ? &vb_map : &kb_map;
       int stage = 0;
       uint32_t par = 1;  // the first use of a slot finds it empty
-      auto issue = [&](const PageRef& r, int b) {
+      auto issue = [&](const PageRef& r, int b) {  // lanes 0 .. kPages-1: one 16-key page each
         uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
         wait_bar(&empty[stage], par, kStatusMmaTimeout);
         if (r.kind < 0) {
           mbar_arrive(&full[stage]);
         } else {
-          const int y = r.kind ? r.raw : (r.raw * 2 + (is_v ? 1 : 0)) * p.bt + r.off;
+          const int y = r.kind ? r.raw : (r.raw * 2 + (is_v ? 1 : 0)) * bt + r.off;
           const CUtensorMap* m = r.kind ? batch_map : &pool_map;
           mbar_arrive_expect_tx(&full[stage], 4096);
           tma_load_3d(dst, m, &full[stage], 0, y, kvh * 2);
@@ -231,26 +253,28 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) stamp(b, is_v ? 7 : 6);
         if (++stage == depth) stage = 0, par ^= 1;
       };
-      // The page-table entry is only loaded here; the row arithmetic happens when the page is
-      // issued, a few iterations later, so the load's latency stays off the critical path.
-      auto cached_page = [&](int b) {
-        PageRef r{0, 0, -1};
-        const int j = tile.k0 + BN * b + 16 * lane;
-        if (b < nbc && j < tile.k1) {
-          r.raw = a.blocks[tree.table + j / p.bt];
-          r.off = j % p.bt;
-          r.kind = 0;
-        }
-        return r;
+      // Page-table entries are fetched by the whole warp, four key blocks per load (lane l holds
+      // the entry of block 4 g + l / 8, page l % 8), two groups ahead of their use: at the start
+      // one round trip to memory lets the first blocks go out back to back, and later the
+      // load's latency never meets the issue loop.
+      auto load_group = [&](int g) {
+        const int b = 4 * g + (lane >> 3);
+        const int j = tile.k0 + BN * b + 16 * (lane & 7);
+        return (b < nbc && j < tile.k1) ? page_table[tree.table + j / bt] : -1;
       };
-      PageRef cur = cached_page(0), nxt = cached_page(1), nx2 = cached_page(2);
+      int g_cur = load_group(0), g_nxt = load_group(1);
       for (int b = 0; b < nbc; ++b) {
-        issue(cur, b);
-        cur = nxt;
-        nxt = nx2;
-        nx2 = cached_page(b + 3);
+        if (b && (b & 3) == 0) {
+          g_cur = g_nxt;
+          g_nxt = load_group((b >> 2) + 1);
+        }
+        const int raw = __shfl_sync(0xffffffffu, g_cur, ((b & 3) << 3) | (lane & 7));
+        if (lane < kPages) {
+          const PageRef r{raw, (tile.k0 + BN * b + 16 * lane) % bt, raw >= 0 ? 0 : -1};
+          issue(r, b);
+        }
       }
-      if (tile.last) {
+      if (tile.last && lane < kPages) {
         if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
         const Meta m = make_meta();
         for (int i = 0; i < m.nbb; ++i) {
@@ -364,7 +388,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t t_lane = tmem + (uint32_t((warp & 3) * 32) << 16);  // this warp's quarter of the lanes
       const uint32_t t_o = t_lane + COL_O + half * HD;
       const float sl2 = a.scale * kLog2e;
-      const uint32_t am_lo = uint32_t(am), am_hi = uint32_t(am >> 32);
       float m_ref = -INFINITY, l_run = 0.0f;  // m_ref in exp2 units of the scaled score
       int vst = 0;
       uint32_t vpar = 0;
@@ -381,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         wait_bar(&s_full[sb], (b >> 1) & 1, kStatusMmaTimeout);
         if (tid == 0) stamp(b, 0);
+        if (tid == 0 && b == 0) cta_stamp(1);
         tc_fence_after_sync();
         const uint32_t t_s = t_lane + COL_S + sb * BN + half * BH;
         uint32_t sr[2][32];
@@ -390,18 +414,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (tid == 0) stamp(b, 1);
         float mx = -INFINITY;
         if (need_mask) {
-          // diagonal, tail and tree blocks: visibility per (row, key)
+          // diagonal, tail and tree blocks: the visibility of this thread's 64 columns as one bit
+          // mask (a few integer operations), then one select per score
+          const int c0 = half * BH;
+          uint64_t vm = low_bits64(n_valid - c0);
+          if (!cached) {
+            if (use_anc) {
+              vm &= half == 0 ? am : 0ull;  // one block, j0 = 0
+            } else {
+              const int jb = j0 + c0;  // batch key of the half's first column
+              vm &= low_bits64(d.z - jb) | (low_bits64(rr - jb + 1) & ~low_bits64(d.x - jb));  // j < d.z || d.x <= j <= rr
+            }
+          }
+          const uint32_t vw[2] = {uint32_t(vm), uint32_t(vm >> 32)};
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-              const int col = half * BH + 32 * h + c, j = j0 + col;
-              bool vis = col < n_valid;
-              if (!cached) {
-                if (use_anc) vis = vis && half == 0 && (((h ? am_hi : am_lo) >> c) & 1u) != 0;  // one block, j0 = 0
-                else vis = vis && ((j < d.z) || (j >= d.x && j <= rr));
-              }
-              const float sc = vis ? __uint_as_float(sr[h][c]) : -INFINITY;
+              const float sc = ((vw[h] >> c) & 1u) ? __uint_as_float(sr[h][c]) : -INFINITY;
               sr[h][c] = __float_as_uint(sc);
               mx = fmaxf(mx, sc);
             }
@@ -467,6 +497,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
 
       // ---- epilogue: merge the two halves of every row, then write
+      if (tid == 0) cta_stamp(2);
       asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine grid may be scheduled
       if (nb > 0) {
         wait_bar(&o_full, 0, kStatusMmaTimeout);
@@ -553,6 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_before_sync();
   __syncthreads();
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks + 1] = global_timer_ns();
+  if (tid == 0) cta_stamp(3);
   if (warp == kMmaWarp) tmem_dealloc(sh.tmem_slot, TMEM_COLS);
 }
 
@@ -573,12 +605,29 @@ cudaError_t flash_umma_setup() {
 }
 
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
+                              const esp_attn_tile* tiles_host, const esp_attn_tree* trees_host, int32_t n_trees,
                               cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
+  InlinePlan plan;
+  for (int i = 0; i < kInlinePlanMax; ++i) plan.start[i].valid = 0;
+  if (tiles_host && trees_host && a.n_tiles <= kInlinePlanMax) {
+    for (int i = 0; i < a.n_tiles; ++i) {
+      const int t = tiles_host[i].tree;
+      if (t < 0 || t >= n_trees) {  // unvalidated plan: leave it to the device copies
+        for (int k = 0; k < i; ++k) plan.start[k].valid = 0;
+        break;
+      }
+      TileStart& ts = plan.start[i];
+      ts.tile = tiles_host[i];
+      ts.tile.pad0 = a.G, ts.tile.pad1 = a.tile_rows;
+      ts.tree = trees_host[t];
+      ts.blocks = a.blocks, ts.bt = a.p.bt, ts.valid = i + 1;
+    }
+  }
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
-  if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, a);
-  else flash_umma_kernel<ESP_BF16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, a);
+  if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, plan, a);
+  else flash_umma_kernel<ESP_BF16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, plan, a);
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

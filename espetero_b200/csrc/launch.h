@@ -33,6 +33,7 @@ struct KernelArgs {
   int* status;  // device status word of the context
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
+  int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2
   esp_attn_params p;
   int32_t HD;
   int32_t G;
@@ -43,6 +44,24 @@ struct KernelArgs {
   int32_t n_blocks;
   float scale;
 };
+
+// Small plans travel in the kernel's parameter space (constant bank), one 64-byte line per tile
+// holding everything a CTA needs to request its first keys: the tile, its tree, the page-table
+// pointer and the page size (G and tile_rows ride in the tile's two unused words). A CTA then
+// opens its timeline with one constant-cache miss and one page-table load instead of a chain of
+// parameter-line misses and two dependent global loads.
+constexpr int kInlinePlanMax = 48;
+struct alignas(64) TileStart {
+  esp_attn_tile tile;  // pad0 = G, pad1 = tile_rows
+  esp_attn_tree tree;
+  const int32_t* blocks;
+  int32_t bt;
+  int32_t valid;  // tile index + 1; 0: the record is not in use
+};
+struct alignas(64) InlinePlan {
+  TileStart start[kInlinePlanMax];
+};
+static_assert(sizeof(TileStart) == 64, "one constant-cache line per tile");
 
 struct CombineArgs {
   const float* parts;
@@ -102,6 +121,7 @@ cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pair
 // (one CTA per SM, 128-key blocks, deep K/V rings); flash_umma_pair is for passes whose keys are
 // mostly their own rows and sit in L2 (two CTAs per SM, 64-key blocks, short rings).
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
+                              const esp_attn_tile* tiles_host, const esp_attn_tree* trees_host, int32_t n_trees,
                               cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);

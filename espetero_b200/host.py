@@ -79,6 +79,15 @@ class DevicePass:
         self.tiles = self.jobs = self.parts = None
         self.plan: Plan | None = None
 
+    def replicate_layers(self, n_layers: int) -> int:
+        """Lay the pool out as n_layers equal layer regions (the reference's pool holds one region
+        per attention layer, src/model/impl/forest.h:1336-1377), each a copy of the workload's
+        pool; layer r's pass uses kv_base = w.kv_base + r * (returned elements per region)."""
+        region = self.kv.numel()
+        if n_layers > 1:
+            self.kv = self.kv.reshape(1, -1).repeat(n_layers, 1).reshape(-1)
+        return region
+
     def set_plan(self, plan: Plan, parts_floats: int):
         self.plan = plan
         self.tiles = _dev(plan.tiles, self.device) if len(plan.tiles) else None

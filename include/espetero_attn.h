@@ -388,8 +388,15 @@ int esp_attn_check_status(esp_attn_ctx* ctx, void* stream);
  * %globaltimer nanoseconds per key block b at [8 * b + e]: e = 0 scores ready (softmax side),
  * 1 scores in registers, 2 P handed over, 3 P seen by the MMA thread, 4 V tile seen,
  * 5 MMAs of the block issued, 6 K tile requested, 7 V tile requested; slot 8 * n_blocks holds
- * the CTA's start and slot 8 * n_blocks + 1 its end. n_blocks = 0 switches tracing off. */
+ * the CTA's start and slot 8 * n_blocks + 1 its end. n_blocks = 0 switches tracing off.
+ * With the option "trace_ctas" = N (> 0) the flash_umma kernel also stores four stamps for each of
+ * its first N CTAs (linear CTA index c) at [8 * n_blocks + 2 + 4 * c + e]: e = 0 start, 1 first
+ * scores seen, 2 last block handed over, 3 exit; the buffer must then hold
+ * 8 * n_blocks + 2 + 4 * N values. */
 int esp_attn_set_trace(esp_attn_ctx* ctx, void* device_buffer, int32_t n_blocks);
+/* Enqueue a one-thread kernel that stores %globaltimer (the trace's clock) into *device_slot:
+ * before and after a pass it brackets the pass in the trace's time base. */
+int esp_attn_stamp(void* stream, uint64_t* device_slot);
 
 /* Kernel launches enqueued by this context since creation. */
 uint64_t esp_attn_launch_count(const esp_attn_ctx* ctx);
