@@ -24,7 +24,8 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
   const int h = blockIdx.y * (kCombineThreads / tph) + threadIdx.x / tph;
   // The records are written by the attention kernel launched just before on the same stream:
   // with programmatic dependent launch this grid may start early and waits here for them.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  pdl_wait();
+  pdl_launch_dependents();  // short CTAs: the next pass's grid may queue up behind them right away
   const esp_attn_combine job = a.jobs[job_i];
   if (r >= job.rows) return;
   const bool live = h < p.H;  // the last CTA of a row may reach past the heads

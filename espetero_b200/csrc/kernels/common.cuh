@@ -94,6 +94,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may be
+// scheduled while the kernel before it on the stream drains. pdl_wait() returns once that kernel has
+// completed and its writes are visible: it must precede the first access to any buffer another
+// kernel may have written (and any write another kernel may still read). pdl_launch_dependents()
+// tells the scheduler this CTA no longer needs to hold back the next kernel's CTAs.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

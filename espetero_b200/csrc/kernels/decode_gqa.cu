@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   const int g = lane >> 2, t = lane & 3;
   const esp_attn_params& p = a.p;
   const int kvh = blockIdx.x % p.Hkv;
+  pdl_wait();  // launched with programmatic serialization: only the launch itself overlaps the previous kernel
   const esp_attn_tile tile = a.tiles[blockIdx.x / p.Hkv];
   const esp_attn_tree tree = a.trees[tile.tree];
   const int G = a.G;
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
 
   // The streaming part is over: let a dependent grid (the combine kernel) be scheduled while
   // this one merges and drains; it still waits for this grid's completion before it reads.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_launch_dependents();
 
   // ---- merge the warps through shared memory (their rings are idle now)
 #pragma unroll
@@ -372,8 +373,7 @@ cudaError_t setup_one() {
 }
 template <class C>
 cudaError_t launch_one(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream) {
-  decode_gqa_kernel<C><<<dim3(unsigned(a.n_tiles) * unsigned(a.p.Hkv)), dim3(C::NW * 32), C::SMEM_BYTES, stream>>>(m, a);
-  return cudaGetLastError();
+  return launch_pdl(decode_gqa_kernel<C>, dim3(unsigned(a.n_tiles) * unsigned(a.p.Hkv)), dim3(C::NW * 32), C::SMEM_BYTES, stream, m, a);
 }
 
 // Instantiations: (HD, pool type, Q type, warps, stages). Rings are sized for two CTAs per

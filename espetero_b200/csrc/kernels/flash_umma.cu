@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tile = ts.tile;
     tree = ts.tree;
   } else {
+    pdl_wait();  // the plan is read from device memory: no head start
     tile = a.tiles[tile_i];
     tree = a.trees[tile.tree];
   }
@@ -262,6 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int j = tile.k0 + BN * b + 16 * (lane & 7);
         return (b < nbc && j < tile.k1) ? page_table[tree.table + j / bt] : -1;
       };
+      pdl_wait();  // everything above used only parameters and shared memory
       int g_cur = load_group(0), g_nxt = load_group(1);
       for (int b = 0; b < nbc; ++b) {
         if (b && (b & 3) == 0) {
@@ -290,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_alloc(&tmem_slot, TMEM_COLS);
       tmem_relinquish();
     }
+    pdl_wait();  // Q, the mask records and, later, O / the records belong to the stream's order
     int4 d = make_int4(0, 0, 0, 0);
     uint64_t am = 0;
     if (is_softmax) {
@@ -498,7 +501,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // ---- epilogue: merge the two halves of every row, then write
       if (tid == 0) cta_stamp(2);
-      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine grid may be scheduled
+      pdl_launch_dependents();  // the next grid of the stream (the combine) may be scheduled
       if (nb > 0) {
         wait_bar(&o_full, 0, kStatusMmaTimeout);
         tc_fence_after_sync();
@@ -626,9 +629,8 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
   }
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
-  if (a.q_dtype == ESP_F16) flash_umma_kernel<ESP_F16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, plan, a);
-  else flash_umma_kernel<ESP_BF16><<<grid, block, SMEM_BYTES, stream>>>(pool_map, kb_map, vb_map, plan, a);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = a.q_dtype == ESP_F16 ? launch_pdl(flash_umma_kernel<ESP_F16>, grid, block, SMEM_BYTES, stream, pool_map, kb_map, vb_map, plan, a)
+                                             : launch_pdl(flash_umma_kernel<ESP_BF16>, grid, block, SMEM_BYTES, stream, pool_map, kb_map, vb_map, plan, a);
   if (e == cudaSuccess) ++*launches;
   return e;
 }

@@ -103,6 +103,20 @@ inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
   return nsl;
 }
 
+// Launch with programmatic stream serialization: the grid may be scheduled while the previous
+// kernel of the stream drains; the kernel orders itself with griddepcontrol.wait.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+  return e == cudaSuccess ? cudaGetLastError() : e;
+}
+
 // Each launcher enqueues on `stream`, returns cudaGetLastError() of the launch and
 // adds the number of kernels it launched to *launches.
 cudaError_t launch_flash_general(const KernelArgs& a, cudaStream_t stream, uint64_t* launches);
