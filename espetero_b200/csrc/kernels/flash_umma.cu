@@ -263,7 +263,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int j = tile.k0 + BN * b + 16 * (lane & 7);
         return (b < nbc && j < tile.k1) ? page_table[tree.table + j / bt] : -1;
       };
-      pdl_wait();  // everything above used only parameters and shared memory
+      // While the previous kernel of the stream drains (programmatic dependent launch), warm L2
+      // with what the first key blocks need: the page-table lines and the tiles themselves. These
+      // are hints through L2 only; the real loads below come after the wait, so a page table or a
+      // pool the previous kernel was still writing costs nothing but a wasted hint.
+      if (inl && nbc > 0) {
+        const int b = lane >> 3, j = tile.k0 + BN * b + 16 * (lane & 7);
+        if (b < min(nbc, depth) && j < tile.k1) {
+          const int raw = ld_cg_s32(page_table + tree.table + j / bt);
+          if (raw >= 0 && raw < a.n_blocks) {
+            const int y = (raw * 2 + (is_v ? 1 : 0)) * bt + j % bt;
+            tma_prefetch_3d(&pool_map, 0, y, kvh * 2);
+            tma_prefetch_3d(&pool_map, 0, y, kvh * 2 + 1);
+          }
+        }
+      }
+      pdl_wait();  // everything above used only parameters, shared memory and hints
       int g_cur = load_group(0), g_nxt = load_group(1);
       for (int b = 0; b < nbc; ++b) {
         if (b && (b & 3) == 0) {
@@ -292,6 +307,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_alloc(&tmem_slot, TMEM_COLS);
       tmem_relinquish();
     }
+    if (is_softmax && inl)  // hint: this thread's half of its Q row (128 bytes)
+      prefetch_l2(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD + half * 64);
     pdl_wait();  // Q, the mask records and, later, O / the records belong to the stream's order
     int4 d = make_int4(0, 0, 0, 0);
     uint64_t am = 0;
