@@ -29,6 +29,7 @@ struct esp_attn_ctx {
   int* d_status = nullptr;
   unsigned long long* trace = nullptr;  // caller-owned device buffer (esp_attn_set_trace)
   int32_t trace_blocks = 0;
+  int opt_fuse_combine = 1;  // small tcgen05 passes merge their split-K records in the attention kernel (last CTA of a job)
   int opt_trace_ctas = 0;  // per-CTA stamps behind the block events (the buffer must hold 8 * n_blocks + 2 + 4 * this)
   // driver entry point for tensor maps, resolved without linking libcuda
   void* encode_tiled = nullptr;
@@ -47,6 +48,10 @@ struct esp_attn_ctx {
 };
 
 namespace {
+
+// The context's device allocation: the status word, then (64 ints further) the arrival counters
+// of fused merges.
+constexpr size_t kStatusBytes = sizeof(int) * (64 + esp::kFixupCounters);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -195,6 +200,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "validate")) return &c->opt_validate;
   if (!std::strcmp(name, "umma_kernel")) return &c->opt_umma_kernel;
   if (!std::strcmp(name, "trace_ctas")) return &c->opt_trace_ctas;
+  if (!std::strcmp(name, "fuse_combine")) return &c->opt_fuse_combine;
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   return nullptr;
 }
@@ -243,11 +249,11 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
     delete c;
     return cuda_fail(e, "tcgen05 kernel setup");
   }
-  if ((e = cudaMalloc(reinterpret_cast<void**>(&c->d_status), sizeof(int))) != cudaSuccess) {
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&c->d_status), kStatusBytes)) != cudaSuccess) {
     delete c;
     return cuda_fail(e, "cudaMalloc(status word)");
   }
-  if ((e = cudaMemset(c->d_status, 0, sizeof(int))) != cudaSuccess) {
+  if ((e = cudaMemset(c->d_status, 0, kStatusBytes)) != cudaSuccess) {
     cudaFree(c->d_status);
     delete c;
     return cuda_fail(e, "cudaMemset(status word)");
@@ -300,7 +306,7 @@ int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return cuda_fail(e, "reading the status word");
   if (st != 0) {
-    cudaMemsetAsync(c->d_status, 0, sizeof(int), s);
+    cudaMemsetAsync(c->d_status, 0, kStatusBytes, s);  // the arrival counters too: a kernel that gave up may have left some behind
     return fail(ESP_ERR_CUDA, "a kernel gave up a bounded wait (status %d: %s)", st,
                 st == esp::kStatusTmaTimeout ? "TMA load never completed" : st == esp::kStatusMmaTimeout ? "MMA never completed"
                : st == esp::kStatusPeerTimeout ? "a peer GPU never published its records" : "bad block id");
@@ -325,7 +331,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.desc = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? nullptr : a.desc;
   k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
   k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
-  k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status;
+  k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status, k.counters = c->d_status + 64;
   k.trace = c->trace, k.trace_blocks = c->trace_blocks, k.trace_ctas = c->trace ? c->opt_trace_ctas : 0;
   k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
@@ -344,6 +350,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
 
   cudaError_t e;
+  bool merged = false;  // the attention kernel merged the split-K records itself: no combine launch
   if (decode) {
     if (int rc = pool_tensor_map(c, a)) return rc;
     c->last_kernel = "decode_gqa";
@@ -361,7 +368,8 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     const bool stream_hbm = c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch);
     if (stream_hbm) {
       c->last_kernel = "flash_umma";
-      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees, stream, &c->launches);
+      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees,
+                                 c->opt_fuse_combine ? a.jobs_host : nullptr, a.n_jobs, &merged, stream, &c->launches);
     } else {
       c->last_kernel = "flash_umma_pair";
       e = esp::launch_flash_umma_pair(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
@@ -371,7 +379,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     e = esp::launch_flash_general(k, stream, &c->launches);
   }
   if (e != cudaSuccess) return cuda_fail(e, c->last_kernel);
-  if (a.n_jobs > 0) {
+  if (a.n_jobs > 0 && !merged) {
     int rows_max = c->tile_rows, parts_max = 64;
     if (a.jobs_host) {
       rows_max = 1, parts_max = 1;

@@ -131,8 +131,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     tree = a.trees[tile.tree];
   }
   const int32_t* page_table = inl ? ts.blocks : a.blocks;
-  const int bt = inl ? ts.bt : p.bt;
-  const int G = inl ? tile.pad0 : a.G, TR = inl ? tile.pad1 : a.tile_rows, HPC = BM / TR;
+  const int bt = inl ? int(ts.bt) : p.bt;
+  const int G = inl ? int(ts.G) : a.G, TR = inl ? int(ts.tile_rows) : a.tile_rows, HPC = BM / TR;
+  const int fix_parts = inl ? int(ts.fix_parts) : 0;  // > 0: the last CTA of this tile's merge job finishes the rows
   const int kvh = (int(blockIdx.y) * HPC) / G;
   const int end = tree.base + tree.M;
   const int rows_live = min(TR, end - tile.r0);
@@ -598,6 +599,83 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float4* src = reinterpret_cast<const float4*>(stage);
         float4* dst = reinterpret_cast<float4*>(rec0);
         for (int i = tid; i < BM * (HD + 2) / 4; i += kSoftmaxThreads) dst[i] = src[i];
+        if (fix_parts > 0) {
+          // Fused merge (what attention_combine does, kernels/40_attention.metal:811-864): every CTA
+          // of the job publishes its records and takes a ticket; whoever draws the last ticket
+          // merges all records in record order, so the result does not depend on who that is.
+          // Nobody waits for anybody.
+          __threadfence();
+          named_barrier(2, kSoftmaxThreads);
+          int* ticket = a.counters + int(ts.fix_job) * int(gridDim.y) + int(blockIdx.y);
+          if (tid == 0) {
+            const int prev = atomicAdd(ticket, 1);
+            red[0] = prev;
+            if (prev == fix_parts - 1) *ticket = 0;  // ready for the next pass on this stream
+          }
+          named_barrier(2, kSoftmaxThreads);
+          if (red[0] == fix_parts - 1) {
+            __threadfence();
+            // Records of the other CTAs come in through shared memory, one bulk copy each (a
+            // thread reading its own 520-byte row straight from L2 would fetch every sector four
+            // times); this CTA's own record is still in `stage`. The merge runs over the records
+            // in record order with a running maximum, so it needs no pass of its own for M.
+            float* other = stage + BM * (HD + 2);
+            constexpr uint32_t kRecBytes = BM * (HD + 2) * 4;
+            uint32_t xpar = nb > 0 ? 1 : 0;  // o_full has completed one phase if the tile had key blocks
+            float Mx = -INFINITY, L = 0.0f;
+            float acc[BH];
+#pragma unroll
+            for (int i = 0; i < BH; ++i) acc[i] = 0.0f;
+#pragma unroll 1
+            for (int s2 = 0; s2 < fix_parts; ++s2) {
+              const float* src = stage;
+              if (tile.pad0 + s2 != tile.part) {
+                named_barrier(2, kSoftmaxThreads);  // the previous record in `other` has been consumed
+                if (tid == 0) {
+                  asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
+                  mbar_arrive_expect_tx(&o_full, kRecBytes);
+                  bulk_load(other, a.parts + (size_t(tile.pad0 + s2) * p.Hkv + kvh) * TR * G * (HD + 2), kRecBytes, &o_full);
+                }
+                wait_bar(&o_full, xpar, kStatusTmaTimeout);
+                xpar ^= 1;
+                src = other;
+              }
+              const float* rp = src + srow * (HD + 2);
+              const float m_s = rp[HD];
+              if (m_s == -INFINITY) continue;  // an empty record adds nothing
+              if (m_s > Mx) {                    // rescale what has been summed so far
+                const float f = __expf(Mx - m_s);  // 0 for the first record
+                L *= f;
+#pragma unroll
+                for (int i = 0; i < BH; ++i) acc[i] *= f;
+                Mx = m_s;
+              }
+              const float w = __expf(m_s - Mx);
+              L += w * rp[HD + 1];
+#pragma unroll
+              for (int i = 0; i < BH; i += 2) {
+                const float2 o2 = *reinterpret_cast<const float2*>(rp + BH * half + i);
+                acc[i] += w * o2.x, acc[i + 1] += w * o2.y;
+              }
+            }
+            if (row_ok) {
+              const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+              for (int i = 0; i < BH; i += 8) {
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  o[k] = acc[i + k] * inv;
+                  if (gp) o[k] *= sigmoid_gate(gp[BH * half + i + k]);
+                }
+                uint4 w4;
+                w4.x = QE::pack2(o[0], o[1]), w4.y = QE::pack2(o[2], o[3]), w4.z = QE::pack2(o[4], o[5]), w4.w = QE::pack2(o[6], o[7]);
+                *reinterpret_cast<uint4*>(op + BH * half + i) = w4;
+              }
+              if (half == 0 && a.lse) a.lse[size_t(row) * p.H + head] = L > 0.0f ? Mx + __logf(L) : -INFINITY;
+            }
+          }
+        }
       }
     }
   }
@@ -626,24 +704,55 @@ cudaError_t flash_umma_setup() {
 
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
                               const esp_attn_tile* tiles_host, const esp_attn_tree* trees_host, int32_t n_trees,
-                              cudaStream_t stream, uint64_t* launches) {
+                              const esp_attn_combine* jobs_host, int32_t n_jobs, bool* merged, cudaStream_t stream,
+                              uint64_t* launches) {
+  *merged = false;
   if (a.n_tiles <= 0) return cudaSuccess;
   InlinePlan plan;
   for (int i = 0; i < kInlinePlanMax; ++i) plan.start[i].valid = 0;
-  if (tiles_host && trees_host && a.n_tiles <= kInlinePlanMax) {
-    for (int i = 0; i < a.n_tiles; ++i) {
-      const int t = tiles_host[i].tree;
-      if (t < 0 || t >= n_trees) {  // unvalidated plan: leave it to the device copies
-        for (int k = 0; k < i; ++k) plan.start[k].valid = 0;
-        break;
-      }
-      TileStart& ts = plan.start[i];
-      ts.tile = tiles_host[i];
-      ts.tile.pad0 = a.G, ts.tile.pad1 = a.tile_rows;
-      ts.tree = trees_host[t];
-      ts.blocks = a.blocks, ts.bt = a.p.bt, ts.valid = i + 1;
+  bool inl = tiles_host && trees_host && a.n_tiles <= kInlinePlanMax && a.p.bt <= 0xffff && a.G <= 0xff;
+  for (int i = 0; inl && i < a.n_tiles; ++i) {
+    const int t = tiles_host[i].tree;
+    if (t < 0 || t >= n_trees) {  // unvalidated plan: leave it to the device copies
+      inl = false;
+      break;
     }
+    TileStart& ts = plan.start[i];
+    ts.tile = tiles_host[i];
+    ts.tile.pad0 = ts.tile.pad1 = 0;
+    ts.tree = trees_host[t];
+    ts.blocks = a.blocks, ts.bt = uint16_t(a.p.bt), ts.G = uint8_t(a.G), ts.tile_rows = uint8_t(a.tile_rows);
+    ts.valid = uint16_t(i + 1), ts.fix_parts = 0, ts.fix_job = 0;
   }
+  if (!inl)
+    for (int i = 0; i < kInlinePlanMax; ++i) plan.start[i].valid = 0;
+  // Fused merge: possible when the plan is inline, every CTA's records are one contiguous range
+  // (its heads are the whole group of a kv head), every job has a counter and every split tile
+  // belongs to exactly one job.
+  const int grid_y = a.p.H / (BM / a.tile_rows);
+  bool fuse = inl && jobs_host && n_jobs > 0 && a.counters && BM / a.tile_rows == a.G && n_jobs <= kInlinePlanMax &&
+              int64_t(n_jobs) * grid_y <= kFixupCounters;
+  if (fuse) {
+    int covered = 0;
+    for (int j = 0; fuse && j < n_jobs; ++j) {
+      const esp_attn_combine& job = jobs_host[j];
+      if (job.nparts < 1 || job.nparts > 255) fuse = false;
+      int found = 0;
+      for (int i = 0; fuse && i < a.n_tiles; ++i) {
+        const esp_attn_tile& t = tiles_host[i];
+        if (t.part < job.part0 || t.part >= job.part0 + job.nparts) continue;
+        if (t.r0 != job.r0 || plan.start[i].fix_parts) fuse = false;  // a record of another row group, or claimed twice
+        plan.start[i].fix_parts = uint8_t(job.nparts), plan.start[i].fix_job = uint8_t(j), plan.start[i].tile.pad0 = job.part0;
+        ++found;
+      }
+      if (found != job.nparts) fuse = false;  // some record of the job is not written by this pass
+      covered += found;
+    }
+    if (!fuse)
+      for (int i = 0; i < a.n_tiles; ++i) plan.start[i].fix_parts = 0;
+    (void)covered;
+  }
+  *merged = fuse;
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
   const cudaError_t e = a.q_dtype == ESP_F16 ? launch_pdl(flash_umma_kernel<ESP_F16>, grid, block, SMEM_BYTES, stream, pool_map, kb_map, vb_map, plan, a)

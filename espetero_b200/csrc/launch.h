@@ -31,6 +31,7 @@ struct KernelArgs {
   const esp_attn_tile* tiles;
   const esp_attn_tree* trees;
   int* status;  // device status word of the context
+  int* counters;  // kFixupCounters zeroed ints of the context (arrival counters of fused merges), or NULL
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
   int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2
@@ -51,12 +52,17 @@ struct KernelArgs {
 // opens its timeline with one constant-cache miss and one page-table load instead of a chain of
 // parameter-line misses and two dependent global loads.
 constexpr int kInlinePlanMax = 48;
+constexpr int kFixupCounters = 4096;  // ints behind the status word of a context
 struct alignas(64) TileStart {
-  esp_attn_tile tile;  // pad0 = G, pad1 = tile_rows
+  esp_attn_tile tile;  // pad0 = first record of the tile's merge job (fused merge), pad1 unused
   esp_attn_tree tree;
   const int32_t* blocks;
-  int32_t bt;
-  int32_t valid;  // tile index + 1; 0: the record is not in use
+  uint16_t bt;
+  uint8_t G;
+  uint8_t tile_rows;
+  uint16_t valid;      // tile index + 1; 0: the record is not in use
+  uint8_t fix_parts;   // > 0: records of the tile's merge job; the CTA that finishes last merges them
+  uint8_t fix_job;     // index of that job (selects the arrival counter)
 };
 struct alignas(64) InlinePlan {
   TileStart start[kInlinePlanMax];
@@ -136,7 +142,8 @@ cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pair
 // mostly their own rows and sit in L2 (two CTAs per SM, 64-key blocks, short rings).
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
                               const esp_attn_tile* tiles_host, const esp_attn_tree* trees_host, int32_t n_trees,
-                              cudaStream_t stream, uint64_t* launches);
+                              const esp_attn_combine* jobs_host, int32_t n_jobs, bool* merged, cudaStream_t stream,
+                              uint64_t* launches);
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
 cudaError_t flash_umma_pair_setup();

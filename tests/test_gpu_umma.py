@@ -114,3 +114,42 @@ def test_tree_mask_probe_is_exact_on_tensor_cores(umma_kernel):
                 for kvh in range(Hkv):
                     assert np.all(r[kvh, :, 64] == (js % 16).sum()) and np.all(r[kvh, :, 65] == ((js // 16) % 16).sum())
                     assert np.all(r[kvh, :, 66] == (kvh + 1) * Pt) and np.all(r[kvh, :, 67] == Pt)
+
+
+@pytest.mark.parametrize("gate", [False, True], ids=["plain", "gate"])
+def test_fused_merge_matches_separate_combine(oracle_lib, gate):
+    """Small split passes of flash_umma merge their records in the attention kernel (the CTA that
+    finishes last for a job merges in record order) instead of launching attention_combine. Same
+    arithmetic (the two routes may add the records' terms in a different order): the outputs
+    must agree to one output ulp with the two-kernel route, repeat bit for bit from pass to pass
+    (the arrival counters reset themselves; no result depends on which CTA came last), and match
+    the oracle."""
+    w = wl.make_pass("fused", 77, [(1500, 16), (777, 16), (2100, 9)], 32, 4, 128, 16, wl.BF16, mask="tree", gate=gate)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    outs = {}
+    for fuse in (1, 0):
+        op = host.AttnOp.for_workload(w, 16)
+        try:
+            op.set_option("umma_kernel", 1)
+            op.set_option("fuse_combine", fuse)
+            plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 24, 16)
+            assert plan.n_parts > 0 and len(plan.tiles) <= 48
+            dp = op.upload(w, plan)
+            n0 = op.launch_count
+            seen = []
+            for _ in range(3):
+                dp.O.zero_()
+                op.forward(dp)
+                op.check_status()
+                seen.append(dp.O.cpu().numpy().view(np.uint16).copy())
+            assert np.array_equal(seen[0], seen[1]) and np.array_equal(seen[0], seen[2])
+            assert op.last_kernel == "flash_umma"
+            assert op.launch_count - n0 == (3 if fuse else 6)   # one kernel per pass when fused
+            outs[fuse] = (dp.O.cpu().numpy().view(np.uint16).copy(), dp.lse.cpu().numpy().copy())
+        finally:
+            op.close()
+    fa, fb = wl.from_bits16(outs[1][0], w.q_dtype), wl.from_bits16(outs[0][0], w.q_dtype)
+    assert np.all(np.abs(fa - fb) <= 2.0 ** -7 * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30)
+    assert np.abs(outs[1][1] - outs[0][1]).max() < 1e-5
+    util.check_output(outs[1][0], ref, w)
+    assert np.abs(outs[1][1] - lse_ref).max() < 2e-3
