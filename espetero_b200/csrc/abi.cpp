@@ -354,6 +354,13 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   if (decode) {
     if (int rc = pool_tensor_map(c, a)) return rc;
     c->last_kernel = "decode_gqa";
+    // Small passes (at most one CTA per SM: launch latencies dominate) whose split tiles name their
+    // jobs (ESP_PLAN_B200) are merged inside the kernel; on larger passes the serial merge in the
+    // last CTA of a long job costs more than the combine kernel's launch (measured on both).
+    k.jobs = a.jobs;
+    k.fuse = c->opt_fuse_combine && esp::decode_fuse_small(a.n_tiles, s.Hkv) && a.n_jobs > 0 && a.jobs &&
+             esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
+    merged = k.fuse != 0;
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
   } else if (umma) {
     if (int rc = umma_tensor_maps(c, a)) return rc;

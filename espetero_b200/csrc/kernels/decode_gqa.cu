@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   using CE = Elem16<C::CDT>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[NW][STAGES];
+  __shared__ int fix_info[4];  // fused merge: first record and record count of the tile's job, the ticket drawn
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -74,7 +75,14 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   const float sl2 = a.scale * kLog2e;
 
   uint8_t* wsm = smem + size_t(warp) * C::WARP_BYTES;
-  if (threadIdx.x == 0) tma_prefetch_desc(&pool_map);
+  const bool fused = a.fuse && tile.part >= 0;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&pool_map);
+    if (fused) {  // needed only at the very end: the load's latency hides behind the whole stream
+      const esp_attn_combine jb = a.jobs[tile.pad0 - 1];
+      fix_info[0] = jb.part0, fix_info[1] = jb.nparts;
+    }
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[warp][s], 1);
@@ -363,6 +371,72 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
         op[lane + 32 * i] = QE::from_f32(v);
       }
       if (a.lse && lane == 0) a.lse[size_t(row) * p.H + h] = l > 0.0f ? M * kLn2 + __logf(l) : -INFINITY;
+    }
+  }
+
+  // ---- fused merge (what attention_combine does, kernels/40_attention.metal:811-864): every CTA
+  // of a job publishes its records and draws a ticket; the CTA that draws the last one merges the
+  // job's records of its kv head in record order and writes the row. Nobody waits for anybody, and
+  // the result does not depend on which CTA came last.
+  if (fused) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* ticket = a.counters + size_t(tile.pad0 - 1) * p.Hkv + kvh;
+      const int prev = atomicAdd(ticket, 1);
+      if (prev == fix_info[1] - 1) *ticket = 0;  // ready for the next pass on this stream
+      fix_info[2] = prev;
+    }
+    __syncthreads();
+    if (fix_info[2] != fix_info[1] - 1) return;
+    __threadfence();
+    const int part0 = fix_info[0], n = fix_info[1];
+    const size_t stride = size_t(p.Hkv) * a.tile_rows * G * (HD + 2);
+    constexpr int DPT = HD / 32;  // this lane's dims: [DPT * lane, DPT * lane + DPT), read as float2
+    for (int hg = warp; hg < G; hg += NW) {
+      const int h = kvh * G + hg;
+      const float* base = a.parts + ((size_t(part0) * p.Hkv + kvh) * a.tile_rows * G + hg) * (HD + 2);
+      float M = -INFINITY, L = 0.0f, acc[DPT];
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) acc[i] = 0.0f;
+      for (int s0 = 0; s0 < n; s0 += 4) {
+        float2 ml[4], ov[4][DPT / 2];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // four records in flight
+          const float* rp = base + size_t(min(s0 + k, n - 1)) * stride;
+          ml[k] = __ldcg(reinterpret_cast<const float2*>(rp + HD));
+#pragma unroll
+          for (int i = 0; i < DPT / 2; ++i) ov[k][i] = __ldcg(reinterpret_cast<const float2*>(rp + DPT * lane + 2 * i));
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (s0 + k >= n || ml[k].x == -INFINITY) continue;  // past the end, or an empty record
+          if (ml[k].x > M) {                                   // rescale what has been summed so far
+            const float f = __expf(M - ml[k].x);               // 0 for the first record
+            L *= f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) acc[i] *= f;
+            M = ml[k].x;
+          }
+          const float w = __expf(ml[k].x - M);
+          L = fmaf(w, ml[k].y, L);
+#pragma unroll
+          for (int i = 0; i < DPT / 2; ++i) acc[2 * i] = fmaf(w, ov[k][i].x, acc[2 * i]), acc[2 * i + 1] = fmaf(w, ov[k][i].y, acc[2 * i + 1]);
+        }
+      }
+      const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
+      typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD + DPT * lane;
+      const float* gp = a.X ? a.X + size_t(row) * p.g_ld + size_t(h) * 2 * HD + HD + DPT * lane : nullptr;
+      uint32_t packed[DPT / 2];
+#pragma unroll
+      for (int i = 0; i < DPT / 2; ++i) {
+        float v0 = acc[2 * i] * inv_l, v1 = acc[2 * i + 1] * inv_l;
+        if (gp) v0 *= sigmoid_gate(gp[2 * i]), v1 *= sigmoid_gate(gp[2 * i + 1]);
+        packed[i] = QE::pack2(v0, v1);
+      }
+      if constexpr (DPT == 4) *reinterpret_cast<uint2*>(op) = make_uint2(packed[0], packed[1]);
+      else *reinterpret_cast<uint4*>(op) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      if (a.lse && lane == 0) a.lse[size_t(row) * p.H + h] = L > 0.0f ? M + __logf(L) : -INFINITY;
     }
   }
 }

@@ -28,6 +28,8 @@ constexpr size_t kStaticPartsFloats = size_t(ESP_ATTN_STATIC_PARTS_FLOATS);
 
 static __device__ __align__(256) float g_static_parts[kStaticPartsFloats];
 static __device__ __align__(256) int g_static_status[64] = {0};
+// Arrival counters of the in-kernel merge; every pass leaves them at zero again.
+static __device__ __align__(256) int g_static_counters[esp::kFixupCounters] = {0};
 
 // In host code the two names above are only handles of the symbols, not device addresses;
 // the addresses a kernel can use are looked up once per device and kept here.
@@ -35,6 +37,7 @@ struct DeviceSlot {
   bool ready = false;
   float* parts = nullptr;
   int* status = nullptr;
+  int* counters = nullptr;
   void* encode_tiled = nullptr;
 };
 constexpr int kMaxDevices = 64;
@@ -57,6 +60,8 @@ int setup_device(int dev) {
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(records)");
   e = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.status), g_static_status);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status)");
+  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&s.counters), g_static_counters);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(counters)");
   cudaDriverEntryPointQueryResult q{};
   e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &q);
   if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !s.encode_tiled)
@@ -134,8 +139,12 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   // Nothing in the array has to be cleared first: every record the merge reads below is
   // written in full by the attention kernel of this same call.
+  // Same choice as esp_attn_forward (identical bits): plans whose split tiles name their jobs are
+  // merged by the attention kernel itself, others by the combine kernel.
+  k.counters = slot.counters, k.jobs = a.jobs;
+  k.fuse = esp::decode_fuse_small(a.n_tiles, s.Hkv) && a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
   if ((e = esp::launch_decode_gqa(k, map, stream, &launches)) != cudaSuccess) return cuda_fail(e, "decode_gqa");
-  if (a.n_jobs > 0) {
+  if (a.n_jobs > 0 && !k.fuse) {
     esp::CombineArgs c{};
     c.parts = slot.parts, c.X = k.X, c.O = a.O, c.lse = a.lse, c.jobs = a.jobs, c.p = a.p;
     c.HD = s.HD, c.G = G, c.tile_rows = TR, c.n_jobs = a.n_jobs, c.q_dtype = s.q_dtype;

@@ -32,6 +32,8 @@ struct KernelArgs {
   const esp_attn_tree* trees;
   int* status;  // device status word of the context
   int* counters;  // kFixupCounters zeroed ints of the context (arrival counters of fused merges), or NULL
+  const esp_attn_combine* jobs;  // device copy of the combine jobs (decode kernel, fused merge)
+  int32_t fuse;                  // 1: tiles carry their job in pad0 and the last CTA of a job merges
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
   int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2
@@ -99,6 +101,35 @@ struct ExchangeArgs {
   unsigned long long* flags[ESP_ATTN_MAX_PEERS];
   int* status;
 };
+
+// Whether a pass can merge its split-K records inside the attention kernel: every tile that
+// writes a record names its job in pad0 (1 + index), lies inside that job's record range and row
+// group, every job's records are all written by this pass, and (job, kv head) pairs fit the counters.
+inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_attn_combine* jobs, int32_t n_jobs, int32_t Hkv) {
+  if (!tiles || !jobs || n_jobs <= 0 || int64_t(n_jobs) * Hkv > kFixupCounters) return false;
+  // Records of a job are consecutive and, in a planner's output, written by consecutive tiles in
+  // record order: check exactly that (anything else takes the two-kernel route).
+  int64_t records = 0, claimed = 0;
+  for (int32_t j = 0; j < n_jobs; ++j) {
+    if (jobs[j].nparts < 1) return false;
+    records += jobs[j].nparts;
+  }
+  int32_t prev_job = 0, prev_part = -1;
+  for (int32_t i = 0; i < n_tiles; ++i) {
+    const esp_attn_tile& t = tiles[i];
+    if (t.part < 0) continue;
+    if (t.pad0 < 1 || t.pad0 > n_jobs) return false;
+    const esp_attn_combine& jb = jobs[t.pad0 - 1];
+    if (t.part < jb.part0 || t.part >= jb.part0 + jb.nparts || t.r0 != jb.r0) return false;
+    if (t.pad0 == prev_job ? t.part != prev_part + 1 : t.part != jb.part0) return false;
+    prev_job = t.pad0, prev_part = t.part;
+    ++claimed;
+  }
+  return claimed == records;
+}
+
+// Decode passes small enough for the in-kernel merge to pay: at most one CTA per SM of a B200.
+inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv) { return int64_t(n_tiles) * Hkv <= 148; }
 
 // Record slices per head for the combine kernel: about a quarter of the job's records per slice,
 // at least one warp per head, at most one CTA (256 threads) per head.

@@ -18,6 +18,7 @@ struct Emitter {
   int32_t tiles_cap;
   esp_attn_combine* jobs;
   int32_t jobs_cap;
+  bool tag_jobs = false;  // ESP_PLAN_B200: a split tile carries 1 + the index of its combine job in pad0
   int32_t nt = 0, nj = 0, np = 0;
   void tile(const esp_attn_tile& t) {
     if (tiles && nt < tiles_cap) tiles[nt] = t;
@@ -40,7 +41,7 @@ struct Emitter {
     int32_t used = 0;
     for (int32_t k = 0; k < t.P; k += step, ++used) {
       const int32_t k1 = std::min(t.P, k + step);
-      tile({ti, t.base + r, k, k1, np++, k1 >= t.P ? 1 : 0, 0, 0});
+      tile({ti, t.base + r, k, k1, np++, k1 >= t.P ? 1 : 0, tag_jobs ? nj + 1 : 0, 0});
     }
     job({t.base + r, rows_in_job, part0, used});
   }
@@ -86,6 +87,7 @@ extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_
       for (int32_t r = 0; r < t.M; r += TR) E.group(ti, t, r, std::min(mode == ESP_PLAN_G4 ? 8 : TR, t.M - r), ns);
     }
   } else {
+    E.tag_jobs = true;
     // One chunk size for the pass: total (row group x key) work spread over the CTA slots.
     int64_t work = 0, n_groups = 0;
     for (int32_t i = 0; i < n_trees; ++i) {

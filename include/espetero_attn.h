@@ -76,7 +76,10 @@ typedef struct esp_attn_tile {
   int32_t k1;
   int32_t part; /* -1: write O; else index of the partial record */
   int32_t last; /* also scan the batch keys */
-  int32_t pad0;
+  int32_t pad0; /* 0 (the reference leaves it unused), or 1 + index of the combine job that merges this
+                   tile's record: set by the ESP_PLAN_B200 planner; when every split tile of a pass
+                   carries it, the attention kernel merges the records itself (the CTA that
+                   finishes a job last does it, in record order) and no combine kernel is launched */
   int32_t pad1;
 } esp_attn_tile;
 

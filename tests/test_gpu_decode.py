@@ -148,3 +148,45 @@ def test_fail_pass_injection_and_validation():
         op.check_status()
     finally:
         op.close()
+
+
+@pytest.mark.parametrize("shape", [(32, 4, 128, None, False), (32, 8, 256, wl.E4M3, False), (16, 4, 128, None, True),
+                                   (8, 8, 128, None, False)], ids=["hd128", "hd256-fp8", "gate", "g1"])
+def test_decode_fused_merge_matches_combine_kernel(oracle_lib, shape):
+    """ESP_PLAN_B200 tiles name their combine job: the decode kernel then merges the records itself
+    (the CTA that finishes a job last, in record order) and no combine kernel is launched. With
+    the option off the same plan takes the two-kernel route; both must match the oracle, agree with
+    each other to an output ulp, and the fused route must repeat bit for bit."""
+    H, Hkv, HD, kvdt, gate = shape
+    w = wl.make_pass("fused_dec", 11, [(9000, 1), (70, 1), (3333, 1), (64, 1), (20000, 1), (5, 1)], H, Hkv, HD, 16, wl.BF16, kvdt,
+                     gate=gate)
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    outs = {}
+    for fuse in (1, 0):
+        op = host.AttnOp.for_workload(w, 8)
+        try:
+            op.set_option("fuse_combine", fuse)
+            plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 128, 8)  # at most 128 CTAs: a small pass
+            assert plan.n_parts > 4 and len(plan.jobs) >= 2
+            assert all(int(t["pad0"]) >= 1 for t in plan.tiles if t["part"] >= 0)
+            dp = op.upload(w, plan)
+            n0 = op.launch_count
+            seen = []
+            for _ in range(3):
+                dp.O.zero_()
+                dp.lse.zero_()
+                op.forward(dp)
+                op.check_status()
+                seen.append((dp.O.cpu().numpy().view(np.uint16).copy(), dp.lse.cpu().numpy().copy()))
+            assert op.last_kernel == "decode_gqa"
+            assert op.launch_count - n0 == (3 if fuse else 6)
+            assert all(np.array_equal(seen[0][0], s[0]) and np.array_equal(seen[0][1], s[1]) for s in seen[1:])
+            outs[fuse] = seen[0]
+        finally:
+            op.close()
+    util.check_output(outs[1][0], ref, w, ref_abs=ref_abs)   # the 5-key row needs the P-rounding allowance
+    util.check_output(outs[0][0], ref, w, ref_abs=ref_abs)
+    assert np.abs(outs[1][1] - lse_ref).max() < 2e-3
+    fa, fb = wl.from_bits16(outs[1][0], w.q_dtype), wl.from_bits16(outs[0][0], w.q_dtype)
+    assert np.all(np.abs(fa - fb) <= 2.0 ** -7 * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30)
+    assert np.abs(outs[1][1] - outs[0][1]).max() < 1e-5
