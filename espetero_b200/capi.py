@@ -70,7 +70,7 @@ class Args(C.Structure):
 
 class Exchange(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phases", C.c_int32), ("wait_ms", C.c_int32), ("epoch", C.c_uint64),
-                ("records", C.c_void_p * 8), ("flags", C.c_void_p * 8)]
+                ("records", C.c_void_p * 8)]
 
 
 assert C.sizeof(Params) == 32 and C.sizeof(Tree) == 16 and C.sizeof(Tile) == 32 and C.sizeof(Combine) == 16
@@ -92,8 +92,7 @@ PROTOTYPES = {
                                          C.POINTER(Params), C.c_void_p, C.c_int32]),
     "esp_attn_reduce_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Params), C.c_void_p, C.c_int32, C.c_void_p,
                                         C.c_int32]),
-    "esp_attn_exchange_floats": (C.c_size_t, [C.POINTER(Shape), C.c_int32, C.c_int32]),
-    "esp_attn_exchange_flags": (C.c_size_t, [C.POINTER(Shape), C.c_int32, C.c_int32, C.c_int32]),
+    "esp_attn_exchange_bytes": (C.c_size_t, [C.POINTER(Shape), C.c_int32, C.c_int32]),
     "esp_attn_exchange_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Params),
                                           C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(Exchange)]),
     "esp_p2p_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_char_p]),

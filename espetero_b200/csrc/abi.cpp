@@ -412,15 +412,11 @@ int esp_attn_reduce_parts(esp_attn_ctx* c, void* stream, const float* parts, con
   return combine_impl(c, stream, parts, nullptr, nullptr, nullptr, p, jobs, n_jobs, c->tile_rows, 64, parts_out, out_part0);
 }
 
-size_t esp_attn_exchange_floats(const esp_attn_shape* s, int32_t n_jobs, int32_t world) {
+size_t esp_attn_exchange_bytes(const esp_attn_shape* s, int32_t n_jobs, int32_t world) {
   if (!s || n_jobs <= 0 || world <= 0 || s->Hkv <= 0 || s->H <= 0) return 0;
   const int TR = s->tile_rows > 0 ? s->tile_rows : 8;
-  return size_t(2) * size_t(world) * size_t(n_jobs) * size_t(s->Hkv) * size_t(TR) * size_t(s->H / s->Hkv) * size_t(s->HD + 2);
-}
-
-size_t esp_attn_exchange_flags(const esp_attn_shape* s, int32_t n_jobs, int32_t rows_max, int32_t world) {
-  if (!s || n_jobs <= 0 || world <= 0 || rows_max <= 0) return 0;
-  return size_t(world) * size_t(n_jobs) * size_t(rows_max) * size_t(s->H);
+  // two epochs x world ranks x records, 8 bytes per record element
+  return size_t(2) * size_t(world) * size_t(n_jobs) * size_t(s->Hkv) * size_t(TR) * size_t(s->H / s->Hkv) * size_t(s->HD + 2) * 8;
 }
 
 int esp_attn_exchange_parts(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
@@ -431,12 +427,12 @@ int esp_attn_exchange_parts(esp_attn_ctx* c, void* stream, const float* parts, c
   const esp_attn_exchange& x = *xp;
   if (x.world < 1 || x.world > ESP_ATTN_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
     return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: rank %d of world %d", x.rank, x.world);
-  if (x.phases < 1 || x.phases > 3 || x.wait_ms < 0 || x.epoch == 0)
+  if (x.phases < 1 || x.phases > 3 || x.wait_ms < 0 || uint32_t(x.epoch) == 0)
     return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: phases %d, wait_ms %d, epoch %llu", x.phases, x.wait_ms,
                 (unsigned long long)x.epoch);
   for (int q = 0; q < x.world; ++q)
-    if (!x.records[q] || !x.flags[q] || (reinterpret_cast<uintptr_t>(x.records[q]) & 7) || (reinterpret_cast<uintptr_t>(x.flags[q]) & 7))
-      return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: exchange buffer or flag array of rank %d is null or not 8-byte aligned", q);
+    if (!x.records[q] || (reinterpret_cast<uintptr_t>(x.records[q]) & 7))
+      return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: exchange buffer of rank %d is null or not 8-byte aligned", q);
   if (!parts || !jobs || ((x.phases & 2) && !O)) return fail(ESP_ERR_INVALID, "esp_attn_exchange_parts: null parts / O / jobs");
   if (int rc = check_params(c, *p)) return rc;
   const esp_attn_shape& s = c->shape;
@@ -447,8 +443,9 @@ int esp_attn_exchange_parts(esp_attn_ctx* c, void* stream, const float* parts, c
   k.c.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
   k.c.n_slices = esp::combine_slices(s.HD, parts_max < 1 ? 1 : parts_max);
   k.rank = x.rank, k.world = x.world, k.phases = x.phases, k.wait_ms = x.wait_ms ? uint32_t(x.wait_ms) : 2000u, k.epoch = x.epoch;
-  for (int q = 0; q < x.world; ++q) k.records[q] = x.records[q], k.flags[q] = reinterpret_cast<unsigned long long*>(x.flags[q]);
+  for (int q = 0; q < x.world; ++q) k.records[q] = static_cast<uint2*>(x.records[q]);
   k.status = c->d_status;
+  k.trace = c->trace_blocks >= 1 ? c->trace : nullptr;
   // Every CTA may wait for its peers: the grid has to be resident at once (2 CTAs of 256 threads per SM at least).
   if (esp::exchange_grid_ctas(k.c) > 296)
     return fail(ESP_ERR_UNSUPPORTED, "esp_attn_exchange_parts: %lld CTAs cannot be resident at once; gather the records with a collective and call esp_attn_combine_parts",

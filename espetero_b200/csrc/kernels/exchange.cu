@@ -4,13 +4,14 @@
 // (kernels/40_attention.metal:811-864). With one long sequence cut by KV range over several
 // GPUs that merge has two levels; this kernel does both and the exchange between them:
 //   step 1  merge this rank's records of a (job, row, head) into one unnormalised record
-//   step 2  store it into slot `rank` of every rank's exchange buffer (plain stores through
-//           peer mappings: NVLink), fence, publish flag (job, row, head) of this rank on every peer
-//   step 3  wait until all ranks' flags of this CTA's heads carry the epoch, then merge the
-//           `world` records in rank order from the local exchange buffer and finish the row.
-// A CTA waits only for the CTAs that serve the same heads on the other GPUs; nothing waits on
+//   step 2  store it into slot `rank` of every rank's exchange buffer through peer mappings
+//           (NVLink) as 8-byte words {value, tag}: the tag is the call's epoch, so every word
+//           says by itself whether it has arrived - no fence, no separate flag, one hop
+//   step 3  read the `world` records from the local exchange buffer, polling each word until it
+//           carries the tag, merge them in rank order and finish the row.
+// A thread waits only for words that the same head's CTA on another GPU stores; nothing waits on
 // another CTA of its own GPU, and the whole grid is resident, so the wait cannot starve the
-// publisher. The wait is bounded by a timer: on expiry the CTA writes the status word and returns
+// sender. The wait is bounded by a timer: on expiry the CTA writes the status word and returns
 // without touching O.
 #include "merge.cuh"
 #include "../launch.h"
@@ -18,99 +19,105 @@
 namespace esp {
 namespace {
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+// One 8-byte word {value bits, tag}: a single store / load, so the pair is never torn.
+__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-// Records in the exchange buffer are written by other GPUs: read them past L1.
-__device__ __forceinline__ float2 ld_cg2(const float* p) {
-  float2 v;
-  asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+  uint2 w;
+  asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+  return w;
 }
 
 template <int QDT>
 __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const ExchangeArgs x) {
   __shared__ MergeScratch scratch;
-  __shared__ int all_here;
   const CombineArgs& a = x.c;
   const esp_attn_params& p = a.p;
   const int HD = a.HD, G = a.G, TR = a.tile_rows, H = p.H;
   const int tpd = HD / 4, tph = tpd * a.n_slices, hpb = kCombineThreads / tph;
   const int job_i = blockIdx.x / a.rows_max, r = blockIdx.x % a.rows_max;
-  const int h0 = blockIdx.y * hpb, h = h0 + threadIdx.x / tph;
+  const int h = blockIdx.y * hpb + threadIdx.x / tph;
   const bool live_head = h < H;
   const int d4 = threadIdx.x % tpd, kvh = live_head ? h / G : 0, hg = live_head ? h % G : 0;
   const size_t stride = size_t(p.Hkv) * TR * G * (HD + 2);              // one record slot of all (kv head, row, head)
   const size_t rec_off = ((size_t(kvh) * TR + size_t(r)) * G + hg) * (HD + 2);
-  const size_t rank_floats = size_t(a.n_jobs) * stride;                   // one rank's records in a buffer
-  const size_t epoch_off = size_t(x.epoch & 1) * size_t(x.world) * rank_floats;
-  const size_t flags_per_rank = size_t(a.n_jobs) * a.rows_max * H;
-  const size_t flag0 = (size_t(job_i) * a.rows_max + r) * H;             // + head
+  const size_t rank_words = size_t(a.n_jobs) * stride;                    // one rank's records in a buffer
+  const size_t epoch_off = size_t(x.epoch & 1) * size_t(x.world) * rank_words;
+  const uint32_t tag = uint32_t(x.epoch);
 
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const bool tracing = x.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+  if (tracing) x.trace[0] = global_timer_ns();  // CTA running (the attention kernel may still be draining)
+  pdl_wait();
+  if (tracing) x.trace[1] = global_timer_ns();  // the local records are complete
   const esp_attn_combine job = a.jobs[job_i];
   const bool live = live_head && r < job.rows;
 
   if (x.phases & 1) {
     const Merged m = merge_records(a.parts + size_t(job.part0) * stride + rec_off, live ? job.nparts : 0, stride, HD, a.n_slices, scratch);
     if (m.owner && live) {
-      const size_t off = epoch_off + size_t(x.rank) * rank_floats + size_t(job_i) * stride + rec_off;
-      for (int q = 0; q < x.world; ++q) store_record(x.records[q] + off, m, HD, d4);
-    }
-    __syncthreads();  // all record stores of the CTA are ordered before the fence below
-    if (threadIdx.x < hpb * x.world) {
-      const int q = threadIdx.x / hpb, hh = h0 + threadIdx.x % hpb;
-      if (hh < H) {
-        __threadfence_system();
-        st_release_sys(x.flags[q] + size_t(x.rank) * flags_per_rank + flag0 + hh, x.epoch);
+      const size_t off = epoch_off + size_t(x.rank) * rank_words + size_t(job_i) * stride + rec_off;
+      for (int q = 0; q < x.world; ++q) {
+        uint2* dst = x.records[q] + off;
+        st_word(dst + 4 * d4, m.acc.x, tag), st_word(dst + 4 * d4 + 1, m.acc.y, tag);
+        st_word(dst + 4 * d4 + 2, m.acc.z, tag), st_word(dst + 4 * d4 + 3, m.acc.w, tag);
+        if (d4 == 0) st_word(dst + HD, m.M, tag), st_word(dst + HD + 1, m.L, tag);
       }
     }
+    if (tracing) x.trace[2] = global_timer_ns();  // merged and on its way to the peers
   }
 
   if (x.phases & 2) {
-    if (threadIdx.x == 0) all_here = 1;
-    __syncthreads();
-    if (threadIdx.x < hpb * x.world) {
-      const int q = threadIdx.x / hpb, hh = h0 + threadIdx.x % hpb;
-      if (hh < H) {
-        const unsigned long long* f = x.flags[x.rank] + size_t(q) * flags_per_rank + flag0 + hh;
-        const uint64_t t0 = global_timer_ns();
-        const uint64_t limit = uint64_t(x.wait_ms) * 1000000ull;
-        bool ok = ld_acquire_sys(f) >= x.epoch;
-        while (!ok) {
-          __nanosleep(64);
-          ok = ld_acquire_sys(f) >= x.epoch;
-          if (!ok && global_timer_ns() - t0 > limit) break;
+    // Second level: `world` records in rank order, one thread per 4 dims. Every word is polled
+    // until it carries this call's tag (or the time runs out).
+    const bool owner = live && (threadIdx.x % tph) / tpd == 0;
+    bool ok = true;
+    Merged m;
+    m.acc = make_float4(0.f, 0.f, 0.f, 0.f), m.M = -INFINITY, m.L = 0.0f, m.owner = true;
+    if (owner) {
+      const uint2* rec0 = x.records[x.rank] + epoch_off + size_t(job_i) * stride + rec_off;
+      const uint64_t t0 = global_timer_ns();
+      const uint64_t limit = uint64_t(x.wait_ms) * 1000000ull;
+      for (int q = 0; ok && q < x.world; ++q) {
+        const uint2* rec = rec0 + size_t(q) * rank_words;
+        uint2 w[6];
+        for (;;) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) w[i] = ld_word(rec + 4 * d4 + i);
+          w[4] = ld_word(rec + HD), w[5] = ld_word(rec + HD + 1);
+          bool all = true;
+#pragma unroll
+          for (int i = 0; i < 6; ++i) all = all && w[i].y == tag;
+          if (all) break;
+          if (global_timer_ns() - t0 > limit) {
+            ok = false;
+            break;
+          }
+          __nanosleep(32);
         }
-        if (!ok) all_here = 0;
+        if (!ok) break;
+        const float m_q = __uint_as_float(w[4].x);
+        if (m_q == -INFINITY) continue;  // an empty record adds nothing
+        if (m_q > m.M) {                  // rescale what has been summed so far
+          const float f = __expf(m.M - m_q);  // 0 for the first record
+          m.L *= f, m.acc.x *= f, m.acc.y *= f, m.acc.z *= f, m.acc.w *= f;
+          m.M = m_q;
+        }
+        const float wq = __expf(m_q - m.M);
+        m.L += wq * __uint_as_float(w[5].x);
+        m.acc.x += wq * __uint_as_float(w[0].x), m.acc.y += wq * __uint_as_float(w[1].x);
+        m.acc.z += wq * __uint_as_float(w[2].x), m.acc.w += wq * __uint_as_float(w[3].x);
       }
     }
-    __syncthreads();
-    if (!all_here) {
+    if (tracing) x.trace[3] = global_timer_ns();  // every rank's records are here
+    // Nobody writes O unless every thread of the CTA has all its words.
+    if (!__syncthreads_and(ok)) {
       if (threadIdx.x == 0) atomicCAS(x.status, kStatusOk, kStatusPeerTimeout);
       return;
     }
-    if (!live || (threadIdx.x % tph) / tpd != 0) return;
-    // Second level: `world` records in rank order, one thread per 4 dims (at most 8 records).
-    const float* rec0 = x.records[x.rank] + epoch_off + size_t(job_i) * stride + rec_off;
-    float M = -INFINITY;
-    for (int q = 0; q < x.world; ++q) M = fmaxf(M, ld_cg2(rec0 + size_t(q) * rank_floats + HD).x);
-    Merged m;
-    m.acc = make_float4(0.f, 0.f, 0.f, 0.f), m.M = M, m.L = 0.0f, m.owner = true;
-    for (int q = 0; q < x.world; ++q) {
-      const float* rec = rec0 + size_t(q) * rank_floats;
-      const float2 ml = ld_cg2(rec + HD);
-      const float w = (ml.x == -INFINITY) ? 0.0f : __expf(ml.x - M);
-      const float2 o01 = ld_cg2(rec + 4 * d4), o23 = ld_cg2(rec + 4 * d4 + 2);
-      m.L += w * ml.y;
-      m.acc.x += w * o01.x, m.acc.y += w * o01.y, m.acc.z += w * o23.x, m.acc.w += w * o23.y;
-    }
+    if (!owner) return;
     finish_row<QDT>(m, a.X, a.O, a.lse, p, HD, job.r0 + r, h, d4);
+    if (tracing) x.trace[4] = global_timer_ns();
   }
 }
 

@@ -97,9 +97,9 @@ struct ExchangeArgs {
   int32_t phases;
   uint32_t wait_ms;
   unsigned long long epoch;
-  float* records[ESP_ATTN_MAX_PEERS];
-  unsigned long long* flags[ESP_ATTN_MAX_PEERS];
+  uint2* records[ESP_ATTN_MAX_PEERS];  // exchange buffers: 8-byte words {value, tag}
   int* status;
+  unsigned long long* trace;  // optional: CTA (0, 0) stores %globaltimer at 5 points (esp_attn_set_trace buffer, slots 0-4)
 };
 
 // Whether a pass can merge its split-K records inside the attention kernel: every tile that

@@ -292,12 +292,12 @@ def force_partial_records(plan: Plan, trees: np.ndarray) -> Plan:
 
 
 class PeerExchange:
-    """The exchange buffers of esp_attn_exchange_parts: this rank's records + flags (esp_p2p_alloc)
-    and the peers' mapped into this process (esp_p2p_open), handles carried by torch.distributed.
+    """The exchange buffers of esp_attn_exchange_parts: this rank's buffer (esp_p2p_alloc) and the
+    peers' mapped into this process (esp_p2p_open), handles carried by torch.distributed.
 
-    PeerExchange(op, n_jobs, rows_max, group=...) is the multi-process form (one process per GPU).
-    PeerExchange.emulated(op, n_jobs, rows_max, world) keeps `world` buffer sets on ONE GPU in one
-    process, for tests that run the ranks' phases one after another.
+    PeerExchange(op, n_jobs, group=...) is the multi-process form (one process per GPU).
+    PeerExchange.emulated(op, n_jobs, world) keeps `world` buffers on ONE GPU in one process, for
+    tests that run the ranks' phases one after another.
     The caller bumps `epoch` (next_epoch()) once per exchange, on every rank alike."""
 
     def __init__(self, op: AttnOp, n_jobs: int, rows_max: int = 1, group=None):
@@ -305,43 +305,31 @@ class PeerExchange:
         self.lib, self.op = op.lib, op
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.epoch = 0
-        self._own, self._opened = [], []
-        rec_bytes, flag_bytes = self._sizes(op, n_jobs, rows_max, self.world)
-        rec, hr = self._alloc(rec_bytes)
-        flg, hf = self._alloc(flag_bytes)
-        mine = torch.tensor(list(hr + hf), dtype=torch.uint8, device=op.device)
+        self._own, self._opened, self._desc = [], [], {}
+        rec, handle = self._alloc(self._size(op, n_jobs, self.world))
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=op.device)
         every = torch.empty(self.world * mine.numel(), dtype=torch.uint8, device=op.device)
         dist.all_gather_into_tensor(every, mine, group=group)
         every = bytes(every.cpu().numpy().tobytes())
-        self.records, self.flags = [], []
-        for q in range(self.world):
-            if q == self.rank:
-                self.records.append(rec), self.flags.append(flg)
-                continue
-            h = every[q * 128:(q + 1) * 128]
-            self.records.append(self._open(h[:64])), self.flags.append(self._open(h[64:]))
+        self.records = [rec if q == self.rank else self._open(every[q * 64:(q + 1) * 64]) for q in range(self.world)]
         dist.barrier(group)  # every rank has mapped every buffer before anyone writes
 
     @classmethod
     def emulated(cls, op: AttnOp, n_jobs: int, rows_max: int, world: int):
         self = cls.__new__(cls)
         self.lib, self.op, self.rank, self.world, self.epoch = op.lib, op, 0, world, 0
-        self._own, self._opened = [], []
-        rec_bytes, flag_bytes = cls._sizes(op, n_jobs, rows_max, world)
-        self.sets = []
-        for _ in range(world):
-            self.sets.append((self._alloc(rec_bytes)[0], self._alloc(flag_bytes)[0]))
-        self.records, self.flags = None, None
+        self._own, self._opened, self._desc = [], [], {}
+        nbytes = cls._size(op, n_jobs, world)
+        self.sets = [self._alloc(nbytes)[0] for _ in range(world)]
+        self.records = None
         return self
 
     @staticmethod
-    def _sizes(op, n_jobs, rows_max, world):
-        lib = op.lib
-        nf = lib.esp_attn_exchange_floats(C.byref(op.shape), n_jobs, world)
-        ng = lib.esp_attn_exchange_flags(C.byref(op.shape), n_jobs, rows_max, world)
-        if nf == 0 or ng == 0:
-            raise ValueError("exchange sizes: bad n_jobs / rows_max / world")
-        return 4 * nf, 8 * ng
+    def _size(op, n_jobs, world):
+        n = op.lib.esp_attn_exchange_bytes(C.byref(op.shape), n_jobs, world)
+        if n == 0:
+            raise ValueError("exchange size: bad n_jobs / world")
+        return n
 
     def _alloc(self, nbytes):
         ptr, h = C.c_void_p(), C.create_string_buffer(64)
@@ -360,19 +348,13 @@ class PeerExchange:
         return self.epoch
 
     def descriptor(self, rank: int, phases: int = 3, wait_ms: int = 0) -> capi.Exchange:
-        cache = self.__dict__.setdefault("_desc", {})
-        x = cache.get((rank, phases, wait_ms))
-        if x is not None:  # only the epoch changes between calls
-            x.epoch = self.epoch
-            return x
-        x = cache[(rank, phases, wait_ms)] = capi.Exchange()
-        x.rank, x.world, x.phases, x.wait_ms, x.epoch = rank, self.world, phases, wait_ms, self.epoch
-        if self.records is None:  # emulated ranks: rank r's own buffers are set r; all are local
-            for q in range(self.world):
-                x.records[q], x.flags[q] = self.sets[q]
-        else:
-            for q in range(self.world):
-                x.records[q], x.flags[q] = self.records[q], self.flags[q]
+        x = self._desc.get((rank, phases, wait_ms))
+        if x is None:  # only the epoch changes between calls
+            x = self._desc[(rank, phases, wait_ms)] = capi.Exchange()
+            x.rank, x.world, x.phases, x.wait_ms = rank, self.world, phases, wait_ms
+            for q in range(self.world):  # emulated ranks: rank q's own buffer is set q; all are local
+                x.records[q] = self.sets[q] if self.records is None else self.records[q]
+        x.epoch = self.epoch
         return x
 
     def close(self):

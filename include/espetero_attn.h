@@ -230,17 +230,19 @@ int esp_attn_reduce_parts(esp_attn_ctx* ctx, void* stream, const float* parts, c
  * sequence and has written partial records for them (esp_attn_forward with records-only tiles).
  * esp_attn_exchange_parts then, in one launch per rank:
  *   1. merges the rank's records of each job into one unnormalised record [O | M | L];
- *   2. stores that record into slot `rank` of EVERY rank's exchange buffer with plain stores
- *      through peer mappings (NVLink), then publishes a per-CTA flag (release, system scope);
- *   3. waits (bounded) until the same CTA of every rank has published, and merges the `world`
- *      records in rank order: all ranks produce identical bits, O and lse are final.
- * The buffers come from esp_p2p_alloc on each rank and are opened on the others with
+ *   2. stores that record into slot `rank` of EVERY rank's exchange buffer through peer mappings
+ *      (NVLink) as 8-byte words {value, tag = epoch}: each word tells by itself whether it has
+ *      arrived, so there is no fence and no separate flag between the data and its consumer;
+ *   3. reads the `world` records from its own buffer, polling (bounded) until every word carries
+ *      the tag, merges them in rank order: all ranks produce identical bits, O and lse are final.
+ * The buffers come from esp_p2p_alloc on each rank (zero-filled) and are opened on the others with
  * esp_p2p_open (the caller carries the 64-byte handles between processes). `epoch` must be the
- * same on all ranks for a call and larger by one for the next call on the same buffers; the
- * buffers hold two epochs, so a rank may run at most one call ahead of the slowest.
+ * same on all ranks for a call and larger by one for the next call on the same buffers (its low
+ * 32 bits are the tag; 0 is never used); the buffers hold two epochs, so a rank may run at most
+ * one call ahead of the slowest.
  * The grid must fit on the GPU at once (jobs * rows * head groups <= 296 CTAs), else
  * ESP_ERR_UNSUPPORTED: gather with a library collective and call esp_attn_combine_parts.
- * If a peer never publishes, the kernel gives up after wait_ms, writes nothing to O and
+ * If a peer never delivers, the kernel gives up after wait_ms, writes nothing to O and
  * esp_attn_check_status reports it; the context stays usable. */
 #define ESP_ATTN_MAX_PEERS 8
 typedef struct esp_attn_exchange {
@@ -250,13 +252,11 @@ typedef struct esp_attn_exchange {
                         test run several emulated ranks one after another on one GPU) */
   int32_t wait_ms;   /* bound of the wait in step 3; 0 = 2000 */
   uint64_t epoch;    /* >= 1 */
-  float* records[ESP_ATTN_MAX_PEERS];    /* rank q's exchange buffer as mapped in this process (own included) */
-  uint64_t* flags[ESP_ATTN_MAX_PEERS];   /* rank q's flag array as mapped in this process; zeroed at allocation */
+  void* records[ESP_ATTN_MAX_PEERS];    /* rank q's exchange buffer as mapped in this process (own included) */
 } esp_attn_exchange;
 
-/* Sizes of one rank's exchange buffer (floats) and flag array (uint64) for a context's shape. */
-size_t esp_attn_exchange_floats(const esp_attn_shape* shape, int32_t n_jobs, int32_t world);
-size_t esp_attn_exchange_flags(const esp_attn_shape* shape, int32_t n_jobs, int32_t rows_max, int32_t world);
+/* Bytes of one rank's exchange buffer for a context's shape. */
+size_t esp_attn_exchange_bytes(const esp_attn_shape* shape, int32_t n_jobs, int32_t world);
 
 /* rows_max: most rows of any job (1 for decode). jobs are device-resident, as for esp_attn_combine_parts;
  * parts_max: most records of any job (sizes the merge's parallelism; 64 if unknown). */
