@@ -64,13 +64,21 @@ def measured_peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def build_workload(name: str, rank: int, small: bool = False):
-    from espetero_b200 import workloads as wl
+def build_workload(name: str, rank: int, small: bool = False, world: int = 1):
+    from espetero_b200 import shard, workloads as wl
     seed_shift = 1000 * rank
     if name == "c1":
         return wl.config_c1(0xE5B201 + seed_shift)
     if name == "c2":
-        return wl.config_c2(0xE5B202 + seed_shift, n_seqs=4 if small else 32, hi=4096 if small else 32768)
+        n, hi = (4, 4096) if small else (32, 32768)
+        if world == 1:
+            return wl.config_c2(0xE5B202, n_seqs=n, hi=hi)
+        # The box serves world x 32 sequences: every rank's draw of the configuration, spread over
+        # the GPUs by total context length (longest first onto the least loaded GPU), as a
+        # scheduler that batches by KV footprint would. Whole sequences move; nothing is exchanged.
+        lens = np.concatenate([wl.c2_context_lengths(0xE5B202 + 1000 * r, n, 512, hi) for r in range(world)])
+        mine = shard.lpt_partition(lens, world)[rank]
+        return wl.config_c2(0xE5B202 + seed_shift, lens=lens[mine])
     if name == "c4":
         return wl.config_c4(0xE5B204 + seed_shift, n_seqs=2 if small else 16, prefix=512 if small else 4096)
     if name == "c5":
@@ -268,7 +276,7 @@ def main():
     groups = args.groups or {"c4": 148, "c5": 148 * 2}.get(args.workload, 148 * 2 * 8)
     xch = None
     if not split_kv:
-        w = build_workload(args.workload, rank, args.small)
+        w = build_workload(args.workload, rank, args.small, world)
         op = host.AttnOp.for_workload(w, tile_rows, local)
         plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
         dp = op.upload(w, plan)
@@ -277,7 +285,9 @@ def main():
         a_attn = layers.args(n_jobs=0)  # attention kernel alone (no combine), for the per-kernel roofline figure
         step = lambda: op.forward(dp, layers.next(a_full))
         step_attn = lambda: op.forward(dp, layers.next(a_attn))
-        sharding, scaling = "sequences per rank, no collective", "weak"
+        sharding = "sequences per rank, no collective" + (
+            "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
+        scaling = "weak"
     else:
         # One long sequence, keys split over the ranks on page boundaries: records for the local
         # keys -> one reduced record per rank -> NCCL all-gather -> every rank merges the world's

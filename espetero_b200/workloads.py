@@ -228,10 +228,15 @@ def config_c1(seed: int = 0xE5B201) -> Workload:
     return make_pass("c1_single_decode", seed, [(1024, 1)], 8, 2, 128, 16, F16)
 
 
-def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 32768) -> Workload:
-    """Batched paged decode: 32 sequences, context ~ U[512, 32768], H32/Hkv4/HD128 bf16, 16-token pages."""
-    rng = np.random.default_rng(seed ^ 0x5EED)
-    lens = rng.integers(lo, hi + 1, size=n_seqs)
+def c2_context_lengths(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 32768) -> np.ndarray:
+    """The context lengths config_c2 draws for `seed`."""
+    return np.random.default_rng(seed ^ 0x5EED).integers(lo, hi + 1, size=n_seqs)
+
+
+def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 32768, lens=None) -> Workload:
+    """Batched paged decode: 32 sequences, context ~ U[512, 32768], H32/Hkv4/HD128 bf16, 16-token pages.
+    `lens` overrides the drawn lengths (a rank's share of a batch partitioned over several GPUs)."""
+    lens = c2_context_lengths(seed, n_seqs, lo, hi) if lens is None else np.asarray(lens)
     w = make_pass("c2_batched_decode", seed, [(int(p), 1) for p in lens], 32, 4, 128, 16, BF16)
     w.extra["ctx_lens"] = lens
     return w
