@@ -136,8 +136,10 @@ int esp_attn_abi_version(void);
  * Names: "attn_gqa" (1: single-row trees take the decode kernel; default 1),
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
  * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
- * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "validate" (1:
- * check host mirrors before launching; default 1), "fail_pass"
+ * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "fuse_combine"
+ * (1: small passes whose split tiles name their combine job in pad0 merge their records inside
+ * the attention kernel and launch no combine kernel; default 1), "trace_ctas" (see
+ * esp_attn_set_trace), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531). */
