@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libespetero_attn.so")
+# ESPETERO_ATTN_LIB selects another build of the same library (A/B timing of two builds).
+LIB_PATH = os.environ.get("ESPETERO_ATTN_LIB") or os.path.join(_HERE, "lib", "libespetero_attn.so")
 
 ESP_OK = 0
 ESP_ERR_INVALID, ESP_ERR_UNSUPPORTED, ESP_ERR_CUDA, ESP_ERR_CAPACITY, ESP_ERR_INJECTED, ESP_ERR_NO_DEVICE = -1, -2, -3, -4, -5, -6

@@ -209,7 +209,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
                         const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
-                        float* out_parts = nullptr, int32_t out_part0 = 0);
+                        float* out_parts = nullptr, int32_t out_part0 = 0, const esp_attn_combine* jobs_host = nullptr);
 
 extern "C" {
 
@@ -335,6 +335,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.trace = c->trace, k.trace_blocks = c->trace_blocks, k.trace_ctas = c->trace ? c->opt_trace_ctas : 0;
   k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
+  k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
 
   // Kernel choice, as forest.h:2864-2868: single-row trees with G <= 8 take the decode kernel.
   bool single = c->G <= 8 && a.trees_host != nullptr && a.tiles_host != nullptr;
@@ -395,7 +396,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
         parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
       }
     }
-    return combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max);
+    return combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max, nullptr, 0, a.jobs_host);
   }
   return ESP_OK;
 }
@@ -502,7 +503,7 @@ int esp_p2p_free(void* ptr) {
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
                         const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
-                        float* out_parts, int32_t out_part0) {
+                        float* out_parts, int32_t out_part0, const esp_attn_combine* jobs_host) {
   if (!c || !p) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
   if (n_jobs <= 0) return ESP_OK;
   if (!parts || (!O && !out_parts) || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
@@ -515,6 +516,10 @@ static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const
   k.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
   k.n_slices = esp::combine_slices(s.HD, parts_max);
   k.out_parts = out_parts, k.out_part0 = out_part0;
+  if (jobs_host && n_jobs <= esp::kInlineJobsMax) {
+    k.n_inline = n_jobs;
+    for (int i = 0; i < n_jobs; ++i) k.inline_jobs[i] = jobs_host[i];
+  }
   const cudaError_t e = esp::launch_combine(k, static_cast<cudaStream_t>(stream), &c->launches);
   if (e != cudaSuccess) return cuda_fail(e, "attention_combine");
   return ESP_OK;

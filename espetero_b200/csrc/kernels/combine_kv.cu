@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
   // with programmatic dependent launch this grid may start early and waits here for them.
   pdl_wait();
   pdl_launch_dependents();  // short CTAs: the next pass's grid may queue up behind them right away
-  const esp_attn_combine job = a.jobs[job_i];
+  const esp_attn_combine job = a.n_inline ? a.inline_jobs[job_i] : a.jobs[job_i];
   if (r >= job.rows) return;
   const bool live = h < p.H;  // the last CTA of a row may reach past the heads
   const int d4 = threadIdx.x % tpd, kvh = live ? h / G : 0, hg = live ? h % G : 0;

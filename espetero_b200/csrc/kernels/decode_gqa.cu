@@ -67,7 +67,28 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   const int g = lane >> 2, t = lane & 3;
   const esp_attn_params& p = a.p;
   const int kvh = blockIdx.x % p.Hkv;
-  pdl_wait();  // launched with programmatic serialization: only the launch itself overlaps the previous kernel
+  // Launched with programmatic serialization: while the previous kernel of the stream drains,
+  // warm L2 with what this CTA reads first - its plan records, page-table entries and each warp's
+  // first key blocks. Hints and L1-bypassing reads only, every index checked: stale or
+  // half-written metadata can cost a wasted hint, never a result.
+  if (lane < STAGES - 1 && a.n_trees > 0 && a.n_block_entries > 0) {
+    const int4* tp = reinterpret_cast<const int4*>(a.tiles + blockIdx.x / p.Hkv);
+    const int4 t0 = __ldcg(tp);  // tree, r0, k0, k1
+    if (t0.x >= 0 && t0.x < a.n_trees && p.bt > 0) {
+      const int4 tr = __ldcg(reinterpret_cast<const int4*>(a.trees + t0.x));  // base, P, table, M
+      const int j0 = t0.z + 16 * (warp + lane * NW);
+      const long long idx = (long long)tr.z + j0 / p.bt;
+      if (t0.z >= 0 && j0 < t0.w && tr.z >= 0 && idx < a.n_block_entries) {
+        const int b = __ldcg(a.blocks + idx);
+        if (b >= 0 && b < a.n_blocks) {
+          const int y = b * 2 * p.bt + j0 % p.bt;
+          tma_prefetch_3d(&pool_map, 0, y, kvh * C::NCH);
+          tma_prefetch_3d(&pool_map, 0, y + p.bt, kvh * C::NCH);
+        }
+      }
+    }
+  }
+  pdl_wait();
   const esp_attn_tile tile = a.tiles[blockIdx.x / p.Hkv];
   const esp_attn_tree tree = a.trees[tile.tree];
   const int G = a.G;

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const Exchang
   if (tracing) x.trace[0] = global_timer_ns();  // CTA running (the attention kernel may still be draining)
   pdl_wait();
   if (tracing) x.trace[1] = global_timer_ns();  // the local records are complete
-  const esp_attn_combine job = a.jobs[job_i];
+  const esp_attn_combine job = a.n_inline ? a.inline_jobs[job_i] : a.jobs[job_i];
   const bool live = live_head && r < job.rows;
 
   if (x.phases & 1) {

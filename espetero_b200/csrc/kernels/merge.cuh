@@ -4,9 +4,8 @@
 // threads (4 dims each) times n_slices record slices: slice k takes the records k, k + n_slices,
 // ... so that many record loads are in flight at once (a single sequential walk over 64 records is
 // latency-bound); passes with few records per job use fewer slices and put more heads in a CTA.
-// The maximum M is found first by all threads of the head, so every slice weighs its records with
-// the final e^(m_s - M); the slices' sums are then added in slice order through shared memory: no
-// atomics, the result does not depend on scheduling. A record is HD + 2 floats long, so records
+// Every slice folds its records into a running (M, L, acc); the slices' results are then folded in
+// slice order through shared memory: no atomics, the result does not depend on scheduling. A record is HD + 2 floats long, so records
 // are only 8-byte aligned: float2 accesses.
 #pragma once
 
@@ -17,8 +16,7 @@ namespace esp {
 constexpr int kCombineThreads = 256;
 
 struct MergeScratch {
-  float m[kCombineThreads / 32];
-  float acc[kCombineThreads][5];
+  float acc[kCombineThreads][6];  // per thread: its slice's 4 dims, L and M
 };
 
 struct Merged {
@@ -33,54 +31,66 @@ __device__ __forceinline__ float4 ld_rec4(const float* p) {
 }
 
 // rec0: record 0 of this thread's (row, head); records `stride` floats apart. Every thread of the
-// CTA must call this (it synchronises the CTA twice), heads past H included (give them n = 0).
+// CTA must call this (it synchronises the CTA once), heads past H included (give them n = 0).
+// One pass: a slice loads up to eight of its records at once (one round trip to L2 for most
+// passes), folds them into a running (M, L, acc) with the batch's maximum, and the slices are
+// folded the same way in slice order by the threads of slice 0.
 __device__ __forceinline__ Merged merge_records(const float* rec0, int n, size_t stride, int HD, int nsl, MergeScratch& sh) {
   const int tpd = HD / 4, tph = tpd * nsl;
   const int tid = threadIdx.x, hb = tid / tph, sl = (tid % tph) / tpd, d4 = tid % tpd;
-  float M = -INFINITY;
-  for (int s = tid % tph; s < n; s += tph) M = fmaxf(M, rec0[size_t(s) * stride + HD]);
-#pragma unroll
-  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-  if ((tid & 31) == 0) sh.m[tid >> 5] = M;
-  __syncthreads();
-  M = -INFINITY;
-  for (int w = hb * (tph / 32); w < (hb + 1) * (tph / 32); ++w) M = fmaxf(M, sh.m[w]);
-  float L = 0.0f;
+  float M = -INFINITY, L = 0.0f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int s = sl;
-  for (; s + 3 * nsl < n; s += 4 * nsl) {
-    float m4[4], l4[4];
-    float4 o4[4];
+  for (int s = sl; s < n; s += 8 * nsl) {
+    float2 ml[8];
+    float4 o4[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float* rec = rec0 + size_t(s + i * nsl) * stride;
-      m4[i] = rec[HD], l4[i] = rec[HD + 1];
-      o4[i] = ld_rec4(rec + 4 * d4);
+    for (int i = 0; i < 8; ++i) {
+      const int idx = s + i * nsl;
+      ml[i] = make_float2(-INFINITY, 0.0f);
+      o4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (idx < n) {
+        const float* rec = rec0 + size_t(idx) * stride;
+        ml[i] = *reinterpret_cast<const float2*>(rec + HD);
+        o4[i] = ld_rec4(rec + 4 * d4);
+      }
+    }
+    float bm = ml[0].x;
+#pragma unroll
+    for (int i = 1; i < 8; ++i) bm = fmaxf(bm, ml[i].x);
+    if (bm > M) {  // rescale what has been summed so far (factor 0 the first time)
+      const float f = __expf(M - bm);
+      L *= f, acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+      M = bm;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float w = (m4[i] == -INFINITY) ? 0.0f : __expf(m4[i] - M);
-      L += w * l4[i];
+    for (int i = 0; i < 8; ++i) {
+      const float w = (ml[i].x == -INFINITY) ? 0.0f : __expf(ml[i].x - M);
+      L += w * ml[i].y;
       acc.x += w * o4[i].x, acc.y += w * o4[i].y, acc.z += w * o4[i].z, acc.w += w * o4[i].w;
     }
   }
-  for (; s < n; s += nsl) {
-    const float* rec = rec0 + size_t(s) * stride;
-    const float w = (rec[HD] == -INFINITY) ? 0.0f : __expf(rec[HD] - M);
-    const float4 o = ld_rec4(rec + 4 * d4);
-    L += w * rec[HD + 1];
-    acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
-  }
-  float* mine = sh.acc[tid];
-  mine[0] = acc.x, mine[1] = acc.y, mine[2] = acc.z, mine[3] = acc.w, mine[4] = L;
-  __syncthreads();
   Merged out;
   out.owner = sl == 0;
-  if (out.owner) {
-    for (int k = 1; k < nsl; ++k) {  // fixed order
-      const float* q = sh.acc[hb * tph + k * tpd + d4];
-      acc.x += q[0], acc.y += q[1], acc.z += q[2], acc.w += q[3], L += q[4];
+  if (nsl > 1) {
+    float* mine = sh.acc[tid];
+    mine[0] = acc.x, mine[1] = acc.y, mine[2] = acc.z, mine[3] = acc.w, mine[4] = L, mine[5] = M;
+    __syncthreads();
+    if (out.owner) {
+      for (int k = 1; k < nsl; ++k) {  // fixed order
+        const float* q = sh.acc[hb * tph + k * tpd + d4];
+        const float mk = q[5];
+        if (mk == -INFINITY) continue;
+        if (mk > M) {
+          const float f = __expf(M - mk);
+          L *= f, acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+          M = mk;
+        }
+        const float w = __expf(mk - M);
+        acc.x += w * q[0], acc.y += w * q[1], acc.z += w * q[2], acc.w += w * q[3], L += w * q[4];
+      }
     }
+  } else {
+    __syncthreads();  // callers rely on one CTA-wide barrier inside
   }
   out.acc = acc, out.M = M, out.L = L;
   return out;

@@ -137,6 +137,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   k.O = a.O, k.lse = a.lse, k.parts = slot.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = slot.status;
   k.p = a.p, k.HD = s.HD, k.G = G, k.tile_rows = TR, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
+  k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   // Nothing in the array has to be cleared first: every record the merge reads below is
   // written in full by the attention kernel of this same call.
   // Same choice as esp_attn_forward (identical bits): plans whose split tiles name their jobs are
@@ -156,6 +157,10 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
       for (int i = 0; i < a.n_jobs; ++i) parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
     }
     c.n_slices = esp::combine_slices(s.HD, parts_max);
+    if (a.jobs_host && a.n_jobs <= esp::kInlineJobsMax) {
+      c.n_inline = a.n_jobs;
+      for (int i = 0; i < a.n_jobs; ++i) c.inline_jobs[i] = a.jobs_host[i];
+    }
     if ((e = esp::launch_combine(c, stream, &launches)) != cudaSuccess) return cuda_fail(e, "attention_combine");
   }
   return ESP_OK;

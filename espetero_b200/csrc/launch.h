@@ -45,6 +45,8 @@ struct KernelArgs {
   int32_t q_dtype;
   int32_t kv_dtype;
   int32_t n_blocks;
+  int32_t n_trees;          // bounds for the speculative reads ahead of the dependency wait
+  int32_t n_block_entries;
   float scale;
 };
 
@@ -71,6 +73,7 @@ struct alignas(64) InlinePlan {
 };
 static_assert(sizeof(TileStart) == 64, "one constant-cache line per tile");
 
+constexpr int kInlineJobsMax = 8;  // one 128-byte constant line: more lines cost a miss per job and SM, which measured slower than the global load
 struct CombineArgs {
   const float* parts;
   const float* X;
@@ -87,6 +90,8 @@ struct CombineArgs {
   int32_t n_slices;  // record slices per head: a power of two, 32 <= (HD / 4) * n_slices <= 256
   float* out_parts;  // reduce mode: job j's merged record goes to record out_part0 + j here; else NULL
   int32_t out_part0;
+  int32_t n_inline;  // > 0: the jobs also travel in the parameters (no dependent load before the records)
+  esp_attn_combine inline_jobs[kInlineJobsMax];
 };
 
 // The peer exchange kernel: a merge whose result goes through every rank's exchange buffer.
@@ -131,12 +136,13 @@ inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_
 // Decode passes small enough for the in-kernel merge to pay: at most one CTA per SM of a B200.
 inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv) { return int64_t(n_tiles) * Hkv <= 148; }
 
-// Record slices per head for the combine kernel: about a quarter of the job's records per slice,
-// at least one warp per head, at most one CTA (256 threads) per head.
+// Record slices per head for the combine kernel: a slice folds up to eight records per round trip
+// to L2, so eight records per slice at most where the CTA allows it; at least one warp per head, at
+// most one CTA (256 threads) per head.
 inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
-  const int tpd = HD / 4;
-  int nsl = 256 / tpd;
-  while (nsl > 1 && nsl * 2 > parts_max && tpd * (nsl / 2) >= 32) nsl /= 2;
+  const int tpd = HD / 4, max_nsl = 256 / tpd;
+  int nsl = 1;
+  while (nsl < max_nsl && (nsl * 8 < parts_max || tpd * nsl < 32)) nsl *= 2;
   return nsl;
 }
 
