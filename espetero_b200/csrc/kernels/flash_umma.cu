@@ -55,6 +55,7 @@ constexpr uint32_t COL_S = 0, COL_O = 256;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 constexpr int kSoftmaxThreads = 2 * BM;     // warps 0-3: half A (keys 0-63 of a block), 4-7: half B
+constexpr int kHintBlocks = 3;               // key blocks per CTA hinted into L2 ahead of the dependency wait (64 KB each; 8 measured slower)
 constexpr int kMmaWarp = 8;                 // MMA issue (one thread), owns tensor memory
 constexpr int kTmaWarpK = 9;                // TMA producer of K tiles (lanes 0-7, one 16-key page each)
 constexpr int kTmaWarpV = 10;               // TMA producer of V tiles
@@ -269,8 +270,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       // are hints through L2 only; the real loads below come after the wait, so a page table or a
       // pool the previous kernel was still writing costs nothing but a wasted hint.
       if (inl && nbc > 0) {
-        const int b = lane >> 3, j = tile.k0 + BN * b + 16 * (lane & 7);
-        if (b < min(nbc, depth) && j < tile.k1) {
+#pragma unroll 1
+        for (int b = lane >> 3; b < min(nbc, kHintBlocks); b += 4) {
+          const int j = tile.k0 + BN * b + 16 * (lane & 7);
+          if (j >= tile.k1) break;
           const int raw = ld_cg_s32(page_table + tree.table + j / bt);
           if (raw >= 0 && raw < a.n_blocks) {
             const int y = (raw * 2 + (is_v ? 1 : 0)) * bt + j % bt;
