@@ -69,6 +69,12 @@ class Args(C.Structure):
                 ("p", Params)]
 
 
+class PrepParams(C.Structure):
+    _fields_ = [("H", C.c_int32), ("Hkv", C.c_int32), ("ld", C.c_int32), ("q_off", C.c_int32), ("q_stride", C.c_int32),
+                ("k_off", C.c_int32), ("v_off", C.c_int32), ("q_ld", C.c_int32), ("kv_ld", C.c_int32), ("rot_half", C.c_int32),
+                ("eps", C.c_float), ("qscale", C.c_float), ("bt", C.c_int32), ("reserved", C.c_int32), ("kv_base", C.c_uint64)]
+
+
 class Exchange(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phases", C.c_int32), ("wait_ms", C.c_int32), ("epoch", C.c_uint64),
                 ("records", C.c_void_p * 8)]
@@ -100,6 +106,7 @@ PROTOTYPES = {
     "esp_p2p_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "esp_p2p_close": (C.c_int, [C.c_void_p]),
     "esp_p2p_free": (C.c_int, [C.c_void_p]),
+    "esp_attn_prep": (C.c_int, [C.c_void_p] * 14 + [C.c_int32, C.POINTER(PrepParams)]),
     "esp_kv_save": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                               C.POINTER(Params)]),
     "esp_kv_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(Params), C.c_uint64,

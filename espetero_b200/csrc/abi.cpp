@@ -1,6 +1,7 @@
 // C-ABI entry points of the attention path: context, options, host-side validation,
 // kernel selection and launches. Mirrors the attention() / kv_save() / kv_cow_copy()
 // dispatch code of the reference (src/model/impl/forest.h:2855-2947, :1438-1449).
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -526,6 +527,41 @@ static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const
 }
 
 extern "C" {
+
+int esp_attn_prep(esp_attn_ctx* c, void* stream, const float* X, const float* q_norm_w, const float* k_norm_w, const int32_t* pos,
+                  const float* inv_freq, const int32_t* rope_sel, void* Q, void* Kb, void* Vb, const int32_t* ktab, void* kv,
+                  const float* kv_scales, int32_t rows, const esp_attn_prep_params* pp) {
+  if (!c || !pp) return fail(ESP_ERR_INVALID, "esp_attn_prep: null argument");
+  if (rows <= 0) return ESP_OK;
+  const esp_attn_shape& s = c->shape;
+  const esp_attn_prep_params& p = *pp;
+  if (!esp::attn_prep_supports(s.HD)) return fail(ESP_ERR_UNSUPPORTED, "esp_attn_prep: head dim %d (128 or 256)", s.HD);
+  if (!X || !q_norm_w || !k_norm_w || !pos || !inv_freq || !rope_sel || !Q || !Kb || !Vb)
+    return fail(ESP_ERR_INVALID, "esp_attn_prep: null input / output pointer");
+  if (p.H != s.H || p.Hkv != s.Hkv) return fail(ESP_ERR_INVALID, "esp_attn_prep: H=%d Hkv=%d do not match the context", p.H, p.Hkv);
+  const int npt = s.HD / 32;
+  if (p.rot_half < npt || p.rot_half > s.HD / 2 || (p.rot_half & (p.rot_half - 1)))
+    return fail(ESP_ERR_INVALID, "esp_attn_prep: rot_half=%d (a power of two in [%d, %d])", p.rot_half, npt, s.HD / 2);
+  if (p.ld % 4 || p.q_off % 4 || p.q_stride % 4 || p.k_off % 4 || p.v_off % 4 || p.q_stride < s.HD || p.q_off < 0 || p.k_off < 0 || p.v_off < 0)
+    return fail(ESP_ERR_INVALID, "esp_attn_prep: X columns must be multiples of 4 floats (ld=%d q_off=%d q_stride=%d k_off=%d v_off=%d)", p.ld,
+                p.q_off, p.q_stride, p.k_off, p.v_off);
+  const int64_t need = std::max<int64_t>({int64_t(p.q_off) + int64_t(s.H - 1) * p.q_stride + s.HD, int64_t(p.k_off) + int64_t(s.Hkv) * s.HD,
+                                          int64_t(p.v_off) + int64_t(s.Hkv) * s.HD});
+  if (p.ld < need) return fail(ESP_ERR_INVALID, "esp_attn_prep: ld=%d but the heads reach column %lld", p.ld, (long long)need);
+  if (p.q_ld < s.H * s.HD || p.kv_ld < s.Hkv * s.HD || p.q_ld % 8 || p.kv_ld % 8)
+    return fail(ESP_ERR_INVALID, "esp_attn_prep: q_ld=%d kv_ld=%d", p.q_ld, p.kv_ld);
+  if (!(p.eps >= 0.0f) || !(p.qscale > 0.0f)) return fail(ESP_ERR_INVALID, "esp_attn_prep: eps / qscale");
+  const bool fp8 = s.kv_dtype == ESP_E4M3;
+  if (ktab) {
+    if (!kv || p.bt <= 0) return fail(ESP_ERR_INVALID, "esp_attn_prep: ktab given but no pool / bt");
+    if (fp8 && !kv_scales) return fail(ESP_ERR_INVALID, "esp_attn_prep: E4M3 pool needs kv_scales");
+    if (p.kv_base % 8) return fail(ESP_ERR_INVALID, "esp_attn_prep: kv_base must be a multiple of 8 elements");
+  }
+  esp::PrepArgs a{X, q_norm_w, k_norm_w, pos, inv_freq, rope_sel, Q, Kb, Vb, ktab, kv, kv_scales, rows, p};
+  const cudaError_t e = esp::launch_attn_prep(a, s.HD, s.q_dtype, fp8 && ktab, static_cast<cudaStream_t>(stream), &c->launches);
+  if (e != cudaSuccess) return cuda_fail(e, "attn_prep");
+  return ESP_OK;
+}
 
 int esp_kv_save(esp_attn_ctx* c, void* stream, const void* Kb, const void* Vb, void* kv, const float* kv_scales,
                 const esp_kv_save_entry* entries, int32_t n, const esp_attn_params* p) {

@@ -1,0 +1,166 @@
+// attn_prep for sm_100a: the step that feeds the attention pass.
+//
+// Reference: kernels/40_attention.metal:23-102 (256-dim heads, gate interleaved with the query
+// heads, 64 rotated dims, K / V of saved rows written into the paged pool in the same kernel) and
+// its generic twin q3m_attn_prep, kernels/82_qwen3_omni.metal:40-88 (full rotary, scale folded into
+// the queries). One warp per (row, head); heads [0, H) are queries, [H, H + Hkv) a key head together
+// with its value head. A lane owns HD / 32 consecutive dims, so the rotary partner (d +- rot_half)
+// lives in lane ^ (rot_half / (HD / 32)): one shuffle per element.
+//
+// HBM-bound: per row it reads (H + 2 Hkv) * HD floats of X and writes as many 16-bit elements
+// (plus the pool rows): 16-byte loads and 8- or 16-byte stores, every byte touched once.
+#include "common.cuh"
+#include "../launch.h"
+
+namespace esp {
+namespace {
+
+constexpr int kPrepWarps = 4;
+
+template <int HD, int QDT, bool FP8_POOL>
+__global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepArgs a) {
+  using QE = Elem16<QDT>;
+  constexpr int NPT = HD / 32;
+  const esp_attn_prep_params& p = a.p;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * kPrepWarps + warp;
+  const size_t row = blockIdx.x;
+  if (head >= p.H + p.Hkv) return;
+  const bool is_q = head < p.H;
+  const int h = is_q ? head : head - p.H;
+  pdl_wait();  // X is the previous kernel's output
+  const float* src = a.X + row * p.ld + (is_q ? p.q_off + size_t(h) * p.q_stride : p.k_off + size_t(h) * HD) + lane * NPT;
+  const float* nw = (is_q ? a.qn_w : a.kn_w) + lane * NPT;
+
+  float x[NPT], wv[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; i += 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + i);
+    const float4 w = *reinterpret_cast<const float4*>(nw + i);
+    x[i] = v.x, x[i + 1] = v.y, x[i + 2] = v.z, x[i + 3] = v.w;
+    wv[i] = w.x, wv[i + 1] = w.y, wv[i + 2] = w.z, wv[i + 3] = w.w;
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) x[i] = x[i] * inv * wv[i];
+
+  // Rotary embedding: dims [0, 2 * rot_half) in pairs (d, d + rot_half); M-RoPE picks the position
+  // component per frequency.
+  const int4 pr = reinterpret_cast<const int4*>(a.pos)[row];
+  const int partner_xor = p.rot_half / NPT;       // lanes apart
+  const bool rotates = lane < 2 * partner_xor;    // this lane's dims lie below 2 * rot_half
+  const bool low = lane < partner_xor;
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, x[i], partner_xor);
+    if (rotates) {
+      const int f = (lane * NPT + i) & (p.rot_half - 1);
+      const int sl = a.rope_sel[f];
+      const float position = float(sl == 0 ? pr.x : (sl == 1 ? pr.y : pr.z));
+      float sn, c;
+      sincosf(position * a.inv_freq[f], &sn, &c);
+      x[i] = low ? (x[i] * c - partner * sn) : (x[i] * c + partner * sn);
+    }
+  }
+
+  uint32_t packed[NPT / 2];
+  if (is_q) {
+#pragma unroll
+    for (int i = 0; i < NPT; i += 2) packed[i / 2] = QE::pack2(x[i] * p.qscale, x[i + 1] * p.qscale);
+    typename QE::T* q = static_cast<typename QE::T*>(a.Q) + row * p.q_ld + size_t(h) * HD + lane * NPT;
+    if constexpr (NPT == 4) *reinterpret_cast<uint2*>(q) = make_uint2(packed[0], packed[1]);
+    else *reinterpret_cast<uint4*>(q) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    return;
+  }
+
+  // key head: K as computed, V as it is
+  uint32_t vpacked[NPT / 2];
+  const float* vsrc = a.X + row * p.ld + p.v_off + size_t(h) * HD + lane * NPT;
+#pragma unroll
+  for (int i = 0; i < NPT; i += 4) {
+    const float4 v = *reinterpret_cast<const float4*>(vsrc + i);
+    vpacked[i / 2] = QE::pack2(v.x, v.y);
+    vpacked[i / 2 + 1] = QE::pack2(v.z, v.w);
+  }
+#pragma unroll
+  for (int i = 0; i < NPT; i += 2) packed[i / 2] = QE::pack2(x[i], x[i + 1]);
+  const size_t col = size_t(h) * HD + lane * NPT;
+  typename QE::T* ko = static_cast<typename QE::T*>(a.Kb) + row * p.kv_ld + col;
+  typename QE::T* vo = static_cast<typename QE::T*>(a.Vb) + row * p.kv_ld + col;
+  if constexpr (NPT == 4) {
+    *reinterpret_cast<uint2*>(ko) = make_uint2(packed[0], packed[1]);
+    *reinterpret_cast<uint2*>(vo) = make_uint2(vpacked[0], vpacked[1]);
+  } else {
+    *reinterpret_cast<uint4*>(ko) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    *reinterpret_cast<uint4*>(vo) = make_uint4(vpacked[0], vpacked[1], vpacked[2], vpacked[3]);
+  }
+
+  // kv_save folded in: the same (rounded) values into the row's pool entries; a row saved into two
+  // slots has two.
+  if (a.ktab) {
+    const int4 t = reinterpret_cast<const int4*>(a.ktab)[row];
+    const size_t blk = size_t(p.bt) * p.kv_ld;
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const int b = w ? t.z : t.x, ps = w ? t.w : t.y;
+      if (b < 0) continue;
+      const size_t dst = p.kv_base + size_t(b) * 2 * blk + size_t(ps) * p.kv_ld + col;
+      if constexpr (!FP8_POOL) {
+        typename QE::T* dk = static_cast<typename QE::T*>(a.kv) + dst;
+        if constexpr (NPT == 4) {
+          *reinterpret_cast<uint2*>(dk) = make_uint2(packed[0], packed[1]);
+          *reinterpret_cast<uint2*>(dk + blk) = make_uint2(vpacked[0], vpacked[1]);
+        } else {
+          *reinterpret_cast<uint4*>(dk) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(dk + blk) = make_uint4(vpacked[0], vpacked[1], vpacked[2], vpacked[3]);
+        }
+      } else {
+        // E4M3 pool: the rounded 16-bit value divided by the block's scale (division, as
+        // esp_kv_save does, so that prep + save and prep with ktab give the same codes)
+        const float sk = a.kv_scales[(size_t(b) * 2) * p.Hkv + h], sv = a.kv_scales[(size_t(b) * 2 + 1) * p.Hkv + h];
+        uint8_t ck[NPT], cv[NPT];
+#pragma unroll
+        for (int i = 0; i < NPT / 2; ++i) {
+          const float2 kf = QE::unpack2(packed[i]), vf = QE::unpack2(vpacked[i]);
+          ck[2 * i] = f32_to_e4m3(__fdiv_rn(kf.x, sk)), ck[2 * i + 1] = f32_to_e4m3(__fdiv_rn(kf.y, sk));
+          cv[2 * i] = f32_to_e4m3(__fdiv_rn(vf.x, sv)), cv[2 * i + 1] = f32_to_e4m3(__fdiv_rn(vf.y, sv));
+        }
+        uint8_t* dk = static_cast<uint8_t*>(a.kv) + dst;
+        if constexpr (NPT == 4) {
+          *reinterpret_cast<uint32_t*>(dk) = *reinterpret_cast<const uint32_t*>(ck);
+          *reinterpret_cast<uint32_t*>(dk + blk) = *reinterpret_cast<const uint32_t*>(cv);
+        } else {
+          *reinterpret_cast<uint2*>(dk) = *reinterpret_cast<const uint2*>(ck);
+          *reinterpret_cast<uint2*>(dk + blk) = *reinterpret_cast<const uint2*>(cv);
+        }
+      }
+    }
+  }
+}
+
+template <int HD, int QDT>
+cudaError_t launch_hd(const PrepArgs& a, bool fp8, dim3 grid, cudaStream_t stream) {
+  return fp8 ? launch_pdl(attn_prep_kernel<HD, QDT, true>, grid, dim3(kPrepWarps * 32), 0, stream, a)
+             : launch_pdl(attn_prep_kernel<HD, QDT, false>, grid, dim3(kPrepWarps * 32), 0, stream, a);
+}
+
+}  // namespace
+
+bool attn_prep_supports(int32_t HD) { return HD == 128 || HD == 256; }
+
+cudaError_t launch_attn_prep(const PrepArgs& a, int32_t HD, int32_t q_dtype, bool fp8_pool, cudaStream_t stream, uint64_t* launches) {
+  if (a.rows <= 0) return cudaSuccess;
+  const dim3 grid(unsigned(a.rows), unsigned((a.p.H + a.p.Hkv + kPrepWarps - 1) / kPrepWarps));
+  cudaError_t e;
+  if (HD == 128) e = q_dtype == ESP_F16 ? launch_hd<128, ESP_F16>(a, fp8_pool, grid, stream) : launch_hd<128, ESP_BF16>(a, fp8_pool, grid, stream);
+  else e = q_dtype == ESP_F16 ? launch_hd<256, ESP_F16>(a, fp8_pool, grid, stream) : launch_hd<256, ESP_BF16>(a, fp8_pool, grid, stream);
+  if (e == cudaSuccess) ++*launches;
+  return e;
+}
+
+}  // namespace esp

@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&pool_map);
     if (fused) {  // needed only at the very end: the load's latency hides behind the whole stream
-      const esp_attn_combine jb = a.jobs[tile.pad0 - 1];
+      const esp_attn_combine jb = a.jobs[tile.pad1 - 1];
       fix_info[0] = jb.part0, fix_info[1] = jb.nparts;
     }
   }
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-      int* ticket = a.counters + size_t(tile.pad0 - 1) * p.Hkv + kvh;
+      int* ticket = a.counters + size_t(tile.pad1 - 1) * p.Hkv + kvh;
       const int prev = atomicAdd(ticket, 1);
       if (prev == fix_info[1] - 1) *ticket = 0;  // ready for the next pass on this stream
       fix_info[2] = prev;

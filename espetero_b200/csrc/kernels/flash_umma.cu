@@ -632,12 +632,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll 1
             for (int s2 = 0; s2 < fix_parts; ++s2) {
               const float* src = stage;
-              if (tile.pad0 + s2 != tile.part) {
+              if (tile.pad1 + s2 != tile.part) {
                 named_barrier(2, kSoftmaxThreads);  // the previous record in `other` has been consumed
                 if (tid == 0) {
                   asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
                   mbar_arrive_expect_tx(&o_full, kRecBytes);
-                  bulk_load(other, a.parts + (size_t(tile.pad0 + s2) * p.Hkv + kvh) * TR * G * (HD + 2), kRecBytes, &o_full);
+                  bulk_load(other, a.parts + (size_t(tile.pad1 + s2) * p.Hkv + kvh) * TR * G * (HD + 2), kRecBytes, &o_full);
                 }
                 wait_bar(&o_full, xpar, kStatusTmaTimeout);
                 xpar ^= 1;
@@ -745,7 +745,7 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
         const esp_attn_tile& t = tiles_host[i];
         if (t.part < job.part0 || t.part >= job.part0 + job.nparts) continue;
         if (t.r0 != job.r0 || plan.start[i].fix_parts) fuse = false;  // a record of another row group, or claimed twice
-        plan.start[i].fix_parts = uint8_t(job.nparts), plan.start[i].fix_job = uint8_t(j), plan.start[i].tile.pad0 = job.part0;
+        plan.start[i].fix_parts = uint8_t(job.nparts), plan.start[i].fix_job = uint8_t(j), plan.start[i].tile.pad1 = job.part0;
         ++found;
       }
       if (found != job.nparts) fuse = false;  // some record of the job is not written by this pass

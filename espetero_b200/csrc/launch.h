@@ -33,7 +33,7 @@ struct KernelArgs {
   int* status;  // device status word of the context
   int* counters;  // kFixupCounters zeroed ints of the context (arrival counters of fused merges), or NULL
   const esp_attn_combine* jobs;  // device copy of the combine jobs (decode kernel, fused merge)
-  int32_t fuse;                  // 1: tiles carry their job in pad0 and the last CTA of a job merges
+  int32_t fuse;                  // 1: tiles carry their job in pad1 and the last CTA of a job merges
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
   int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2
@@ -58,7 +58,7 @@ struct KernelArgs {
 constexpr int kInlinePlanMax = 48;
 constexpr int kFixupCounters = 4096;  // ints behind the status word of a context
 struct alignas(64) TileStart {
-  esp_attn_tile tile;  // pad0 = first record of the tile's merge job (fused merge), pad1 unused
+  esp_attn_tile tile;  // pad1 = first record of the tile's merge job (fused merge)
   esp_attn_tree tree;
   const int32_t* blocks;
   uint16_t bt;
@@ -108,7 +108,7 @@ struct ExchangeArgs {
 };
 
 // Whether a pass can merge its split-K records inside the attention kernel: every tile that
-// writes a record names its job in pad0 (1 + index), lies inside that job's record range and row
+// writes a record names its job in pad1 (1 + index), lies inside that job's record range and row
 // group, every job's records are all written by this pass, and (job, kv head) pairs fit the counters.
 inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_attn_combine* jobs, int32_t n_jobs, int32_t Hkv) {
   if (!tiles || !jobs || n_jobs <= 0 || int64_t(n_jobs) * Hkv > kFixupCounters) return false;
@@ -123,11 +123,11 @@ inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_
   for (int32_t i = 0; i < n_tiles; ++i) {
     const esp_attn_tile& t = tiles[i];
     if (t.part < 0) continue;
-    if (t.pad0 < 1 || t.pad0 > n_jobs) return false;
-    const esp_attn_combine& jb = jobs[t.pad0 - 1];
+    if (t.pad1 < 1 || t.pad1 > n_jobs) return false;
+    const esp_attn_combine& jb = jobs[t.pad1 - 1];
     if (t.part < jb.part0 || t.part >= jb.part0 + jb.nparts || t.r0 != jb.r0) return false;
-    if (t.pad0 == prev_job ? t.part != prev_part + 1 : t.part != jb.part0) return false;
-    prev_job = t.pad0, prev_part = t.part;
+    if (t.pad1 == prev_job ? t.part != prev_part + 1 : t.part != jb.part0) return false;
+    prev_job = t.pad1, prev_part = t.part;
     ++claimed;
   }
   return claimed == records;
@@ -145,6 +145,24 @@ inline int32_t combine_slices(int32_t HD, int32_t parts_max) {
   while (nsl < max_nsl && (nsl * 8 < parts_max || tpd * nsl < 32)) nsl *= 2;
   return nsl;
 }
+
+// attn_prep (kernels/40_attention.metal:23-102): bindings of the reference dispatch (forest.h:2951-2977).
+struct PrepArgs {
+  const float* X;
+  const float* qn_w;
+  const float* kn_w;
+  const int32_t* pos;       // int4 per row
+  const float* inv_freq;
+  const int32_t* rope_sel;
+  void* Q;
+  void* Kb;
+  void* Vb;
+  const int32_t* ktab;      // int4 per row, or NULL
+  void* kv;
+  const float* kv_scales;
+  int32_t rows;
+  esp_attn_prep_params p;
+};
 
 // Launch with programmatic stream serialization: the grid may be scheduled while the previous
 // kernel of the stream drains; the kernel orders itself with griddepcontrol.wait.
@@ -165,6 +183,8 @@ inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, 
 cudaError_t launch_flash_general(const KernelArgs& a, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& pool_map, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_combine(const CombineArgs& a, cudaStream_t stream, uint64_t* launches);
+bool attn_prep_supports(int32_t HD);
+cudaError_t launch_attn_prep(const PrepArgs& a, int32_t HD, int32_t q_dtype, bool fp8_pool, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_exchange(const ExchangeArgs& x, cudaStream_t stream, uint64_t* launches);
 int64_t exchange_grid_ctas(const CombineArgs& a);
 cudaError_t launch_kv_save(const void* Kb, const void* Vb, void* kv, const float* kv_scales, const esp_kv_save_entry* entries,

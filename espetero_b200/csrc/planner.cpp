@@ -18,7 +18,7 @@ struct Emitter {
   int32_t tiles_cap;
   esp_attn_combine* jobs;
   int32_t jobs_cap;
-  bool tag_jobs = false;  // ESP_PLAN_B200: a split tile carries 1 + the index of its combine job in pad0
+  bool tag_jobs = false;  // ESP_PLAN_B200: a split tile carries 1 + the index of its combine job in pad1
   int32_t nt = 0, nj = 0, np = 0;
   void tile(const esp_attn_tile& t) {
     if (tiles && nt < tiles_cap) tiles[nt] = t;
@@ -41,7 +41,7 @@ struct Emitter {
     int32_t used = 0;
     for (int32_t k = 0; k < t.P; k += step, ++used) {
       const int32_t k1 = std::min(t.P, k + step);
-      tile({ti, t.base + r, k, k1, np++, k1 >= t.P ? 1 : 0, tag_jobs ? nj + 1 : 0, 0});
+      tile({ti, t.base + r, k, k1, np++, k1 >= t.P ? 1 : 0, 0, tag_jobs ? nj + 1 : 0});
     }
     job({t.base + r, rows_in_job, part0, used});
   }

@@ -226,6 +226,15 @@ class AttnOp:
         capi.check(self.lib.esp_attn_exchange_parts(self.ctx, C.c_void_p(s), _ptr(parts), _ptr(dp.X), _ptr(dp.O), _ptr(dp.lse),
                                                     C.byref(p), _ptr(jobs_dev), n_jobs, rows_max, parts_max, C.byref(x)))
 
+    def attn_prep(self, X, qn_w, kn_w, pos, inv_freq, rope_sel, Q, Kb, Vb, pp: "capi.PrepParams", ktab=None, kv=None,
+                  kv_scales=None, stream: int | None = None):
+        """esp_attn_prep on device tensors: RMSNorm + rotary + cast of the fused projection X into Q / Kb / Vb
+        (and, with ktab, into the paged pool)."""
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        capi.check(self.lib.esp_attn_prep(self.ctx, C.c_void_p(s), _ptr(X), _ptr(qn_w), _ptr(kn_w), _ptr(pos), _ptr(inv_freq),
+                                          _ptr(rope_sel), _ptr(Q), _ptr(Kb), _ptr(Vb), _ptr(ktab), _ptr(kv), _ptr(kv_scales),
+                                          X.shape[0], C.byref(pp)))
+
     def kv_save(self, dp: DevicePass, entries: np.ndarray, stream: int | None = None):
         s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
         e = _dev(np.ascontiguousarray(entries, dtype=KVSAVE_DT), self.device)

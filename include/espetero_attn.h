@@ -76,11 +76,11 @@ typedef struct esp_attn_tile {
   int32_t k1;
   int32_t part; /* -1: write O; else index of the partial record */
   int32_t last; /* also scan the batch keys */
-  int32_t pad0; /* 0 (the reference leaves it unused), or 1 + index of the combine job that merges this
-                   tile's record: set by the ESP_PLAN_B200 planner; when every split tile of a pass
-                   carries it, the attention kernel merges the records itself (the CTA that
-                   finishes a job last does it, in record order) and no combine kernel is launched */
-  int32_t pad1;
+  int32_t pad0; /* first batch key to scan in the reference's sliding-window plans (gemma.h:89-94); 0 otherwise */
+  int32_t pad1; /* 0 (unused in the reference), or 1 + index of the combine job that merges this tile's
+                   record: set by the ESP_PLAN_B200 planner; when every split tile of a pass carries
+                   it, small passes merge the records inside the attention kernel (the CTA that
+                   finishes a job last does it, in record order) and launch no combine kernel */
 } esp_attn_tile;
 
 typedef struct esp_attn_combine {
@@ -137,7 +137,7 @@ int esp_attn_abi_version(void);
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
  * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
  * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "fuse_combine"
- * (1: small passes whose split tiles name their combine job in pad0 merge their records inside
+ * (1: small passes whose split tiles name their combine job in pad1 merge their records inside
  * the attention kernel and launch no combine kernel; default 1), "trace_ctas" (see
  * esp_attn_set_trace), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
@@ -274,6 +274,41 @@ int esp_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[ESP_P2P_HANDLE_
 int esp_p2p_open(const unsigned char handle[ESP_P2P_HANDLE_BYTES], void** ptr);
 int esp_p2p_close(void* ptr);
 int esp_p2p_free(void* ptr);
+
+/* ---- attn_prep: the step right before the attention pass (kernels/40_attention.metal:23-102, host
+ * dispatch src/model/impl/forest.h:2951-2977; generic head dim q3m_attn_prep,
+ * kernels/82_qwen3_omni.metal:40-88). Per (row, head) of the fused projection X (fp32):
+ * RMSNorm over the head (x * rsqrt(mean x^2 + eps) * weight), rotary embedding of the pairs
+ * (d, d + rot_half) for d < rot_half at angle pos[sel[d]] * inv_freq[d] (M-RoPE: pos is an int4 per
+ * row - temporal, height, width, unused - and sel[d] in {0, 1, 2} picks the component), queries times
+ * qscale, cast to the context's q_dtype into Q / Kb; values are cast into Vb unchanged. With `ktab`
+ * (int4 per row: block, pos, block2, pos2; -1 = none) the row's K / V are also written into the paged
+ * pool (kv_save folded in; E4M3 pools quantise the rounded 16-bit value with the block's scale, exactly
+ * as esp_kv_save would).
+ * Layouts: the 256-dim reference kernel reads query head h at X + h * 2 * HD (the gate follows each
+ * head: q_stride = 2 * HD), rotates 64 dims (rot_half = 32) and leaves the scale to the attention
+ * kernel (qscale = 1); the generic kernel has q_stride = HD, rot_half = HD / 2 and folds the scale. */
+typedef struct esp_attn_prep_params {
+  int32_t H;
+  int32_t Hkv;
+  int32_t ld;       /* row stride of X in floats */
+  int32_t q_off;    /* column of query head 0 */
+  int32_t q_stride; /* floats between consecutive query heads: HD, or 2 * HD with interleaved gates */
+  int32_t k_off;    /* column of key head 0 (heads HD apart) */
+  int32_t v_off;    /* column of value head 0 (heads HD apart) */
+  int32_t q_ld;     /* Q row stride in elements */
+  int32_t kv_ld;    /* Kb / Vb row stride and pool row width in elements */
+  int32_t rot_half; /* frequencies: dims [0, 2 * rot_half) rotate, the rest pass through; a power of two, <= HD / 2 */
+  float eps;
+  float qscale;
+  int32_t bt;       /* tokens per KV block (ktab) */
+  int32_t reserved;
+  uint64_t kv_base; /* element offset of the layer's region in the pool (ktab) */
+} esp_attn_prep_params;
+
+int esp_attn_prep(esp_attn_ctx* ctx, void* stream, const float* X, const float* q_norm_w, const float* k_norm_w,
+                  const int32_t* pos, const float* inv_freq, const int32_t* rope_sel, void* Q, void* Kb, void* Vb,
+                  const int32_t* ktab, void* kv, const float* kv_scales, int32_t rows, const esp_attn_prep_params* p);
 
 /* kv_save (40_attention.metal:875-889; forest.h:2935-2947). With an ESP_E4M3
  * pool the rows are quantised with the destination block's scale from kv_scales. */

@@ -169,6 +169,25 @@ def kv_save(w, kv, entries):
                        C.c_void_p(_p(w.kv_scales)), C.c_void_p(entries.ctypes.data), len(entries), C.byref(p), w.HD, w.q_dtype, w.kv_dtype)
 
 
+class PrepParams(C.Structure):
+    _fields_ = [("H", C.c_int32), ("Hkv", C.c_int32), ("ld", C.c_int32), ("q_off", C.c_int32), ("q_stride", C.c_int32),
+                ("k_off", C.c_int32), ("v_off", C.c_int32), ("q_ld", C.c_int32), ("kv_ld", C.c_int32), ("rot_half", C.c_int32),
+                ("eps", C.c_float), ("qscale", C.c_float), ("bt", C.c_int32), ("reserved", C.c_int32), ("kv_base", C.c_uint64)]
+
+
+def attn_prep_f64(X, qn_w, kn_w, pos, inv_freq, sel, rows, HD, pp: PrepParams):
+    """attn_prep in double (40_attention.metal:23-102 / 82_qwen3_omni.metal:40-88): returns Q64, K64, V64."""
+    Q = np.zeros((rows, pp.q_ld), dtype=np.float64)
+    K = np.zeros((rows, pp.kv_ld), dtype=np.float64)
+    V = np.zeros((rows, pp.kv_ld), dtype=np.float64)
+    X, qn_w, kn_w, inv_freq = (np.ascontiguousarray(a, dtype=np.float32) for a in (X, qn_w, kn_w, inv_freq))
+    pos, sel = np.ascontiguousarray(pos, dtype=np.int32), np.ascontiguousarray(sel, dtype=np.int32)
+    load().orc_attn_prep_f64(C.c_void_p(X.ctypes.data), C.c_void_p(qn_w.ctypes.data), C.c_void_p(kn_w.ctypes.data),
+                             C.c_void_p(pos.ctypes.data), C.c_void_p(inv_freq.ctypes.data), C.c_void_p(sel.ctypes.data),
+                             C.c_void_p(Q.ctypes.data), C.c_void_p(K.ctypes.data), C.c_void_p(V.ctypes.data), rows, HD, C.byref(pp))
+    return Q, K, V
+
+
 def kv_copy_blocks(w, kv, pairs, region_elems, n_layers):
     p = Params(w.H, w.Hkv, w.q_ld, w.kv_ld, w.g_ld, w.bt, w.kv_base)
     pairs = np.ascontiguousarray(pairs, dtype=np.int32)

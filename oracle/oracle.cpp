@@ -653,6 +653,52 @@ int orc_kv_save(const void* Kb, const void* Vb, void* kv, const float* kv_scales
   return 0;
 }
 
+// attn_prep (kernels/40_attention.metal:23-102; generic head dim kernels/82_qwen3_omni.metal:40-88),
+// restated per (row, head) in double: RMSNorm over the head, rotary embedding of the pairs
+// (d, d + rot_half) at angle pos[sel[d]] * inv_freq[d] (the product in fp32, as the kernels form it),
+// queries times qscale. Q64 / K64 / V64 hold the unrounded results, row-major with strides q_ld / kv_ld;
+// rounding to the 16-bit output type is the caller's.
+struct PrepParams {
+  int32_t H, Hkv, ld, q_off, q_stride, k_off, v_off, q_ld, kv_ld, rot_half;
+  float eps, qscale;
+  int32_t bt, reserved;
+  uint64_t kv_base;
+};
+int orc_attn_prep_f64(const float* X, const float* qn_w, const float* kn_w, const int32_t* pos, const float* inv_freq,
+                      const int32_t* sel, double* Q64, double* K64, double* V64, int32_t rows, int32_t HD, const PrepParams* pp) {
+  const PrepParams& p = *pp;
+  std::vector<double> x(HD);
+  for (int64_t row = 0; row < rows; ++row) {
+    for (int head = 0; head < p.H + p.Hkv; ++head) {
+      const bool is_q = head < p.H;
+      const int h = is_q ? head : head - p.H;
+      const float* src = X + row * p.ld + (is_q ? p.q_off + int64_t(h) * p.q_stride : p.k_off + int64_t(h) * HD);
+      const float* nw = is_q ? qn_w : kn_w;
+      double ss = 0.0;
+      for (int d = 0; d < HD; ++d) ss += double(src[d]) * double(src[d]);
+      const double inv = 1.0 / std::sqrt(ss / double(HD) + double(p.eps));
+      for (int d = 0; d < HD; ++d) x[d] = double(src[d]) * inv * double(nw[d]);
+      for (int d = 0; d < p.rot_half; ++d) {
+        const int sl = sel[d];
+        const float position = float(sl == 0 ? pos[4 * row] : (sl == 1 ? pos[4 * row + 1] : pos[4 * row + 2]));
+        const float ang = position * inv_freq[d];
+        const double c = std::cos(double(ang)), sn = std::sin(double(ang));
+        const double lo = x[d], hi = x[d + p.rot_half];
+        x[d] = lo * c - hi * sn;
+        x[d + p.rot_half] = hi * c + lo * sn;
+      }
+      double* out = is_q ? Q64 + row * p.q_ld + int64_t(h) * HD : K64 + row * p.kv_ld + int64_t(h) * HD;
+      const double scale = is_q ? double(p.qscale) : 1.0;
+      for (int d = 0; d < HD; ++d) out[d] = x[d] * scale;
+      if (!is_q) {
+        const float* v = X + row * p.ld + p.v_off + int64_t(h) * HD;
+        for (int d = 0; d < HD; ++d) V64[row * p.kv_ld + int64_t(h) * HD + d] = double(v[d]);
+      }
+    }
+  }
+  return 0;
+}
+
 // kv_copy_blocks (kernels/40_attention.metal:894-905).
 int orc_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pairs, const Params* pp, uint64_t region_elems,
                        int32_t n_layers, int32_t elem_bytes) {

@@ -168,7 +168,7 @@ def test_decode_fused_merge_matches_combine_kernel(oracle_lib, shape):
             op.set_option("fuse_combine", fuse)
             plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 128, 8)  # at most 128 CTAs: a small pass
             assert plan.n_parts > 4 and len(plan.jobs) >= 2
-            assert all(int(t["pad0"]) >= 1 for t in plan.tiles if t["part"] >= 0)
+            assert all(int(t["pad1"]) >= 1 for t in plan.tiles if t["part"] >= 0)
             dp = op.upload(w, plan)
             n0 = op.launch_count
             seen = []

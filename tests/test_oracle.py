@@ -130,3 +130,37 @@ def test_kv_save_and_copy(oracle_lib):
     x = wl.bf16_bits_to_f32(w8.Kb).reshape(16, 2, 128)
     want = wl.e4m3_encode(x / w8.kv_scales[1, 0][None, :, None])
     assert np.array_equal(pool8[1, 0] & 0x7F, want & 0x7F)
+
+
+def test_attn_prep_oracle_against_numpy(oracle_lib):
+    """The C restatement of attn_prep (40_attention.metal:23-102) against the same formulas written
+    with numpy arrays: RMSNorm, rotary pairs (d, d + rot_half) with the M-RoPE component per frequency."""
+    import oracle
+    rng = np.random.default_rng(3)
+    H, Hkv, HD, rot_half, rows = 4, 2, 128, 32, 5
+    q_stride, k_off = 2 * HD, 2 * H * HD
+    v_off = k_off + Hkv * HD
+    ld = v_off + Hkv * HD
+    X = rng.standard_normal((rows, ld)).astype(np.float32)
+    qn, kn = rng.uniform(0.5, 1.5, HD).astype(np.float32), rng.uniform(0.5, 1.5, HD).astype(np.float32)
+    inv_freq = (10000.0 ** (-np.arange(rot_half) / rot_half)).astype(np.float32)
+    sel = (np.arange(rot_half) % 3).astype(np.int32)
+    pos = rng.integers(0, 5000, size=(rows, 4)).astype(np.int32)
+    pp = oracle.PrepParams(H, Hkv, ld, 0, q_stride, k_off, v_off, H * HD, Hkv * HD, rot_half, 1e-5, 0.25, 16, 0, 0)
+    Q, K, V = oracle.attn_prep_f64(X, qn, kn, pos, inv_freq, sel, rows, HD, pp)
+
+    def head(x, w, r):
+        x = x.astype(np.float64)
+        y = x / np.sqrt((x * x).mean() + np.float64(np.float32(1e-5))) * w
+        ang = (pos[r, sel].astype(np.float32) * inv_freq).astype(np.float64)   # fp32 product, as the kernels form it
+        lo, hi = y[:rot_half].copy(), y[rot_half:2 * rot_half].copy()
+        y[:rot_half] = lo * np.cos(ang) - hi * np.sin(ang)
+        y[rot_half:2 * rot_half] = hi * np.cos(ang) + lo * np.sin(ang)
+        return y
+
+    for r in range(rows):
+        for h in range(H):
+            np.testing.assert_allclose(Q[r, h * HD:(h + 1) * HD], 0.25 * head(X[r, h * q_stride: h * q_stride + HD], qn, r), rtol=1e-12, atol=1e-12)
+        for h in range(Hkv):
+            np.testing.assert_allclose(K[r, h * HD:(h + 1) * HD], head(X[r, k_off + h * HD: k_off + (h + 1) * HD], kn, r), rtol=1e-12, atol=1e-12)
+    np.testing.assert_array_equal(V, X[:, v_off: v_off + Hkv * HD].astype(np.float64))
