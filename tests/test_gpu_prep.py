@@ -72,8 +72,12 @@ def test_prep_matches_oracle(oracle_lib, layout, q_dtype):
     Q, Kb, Vb, _ = _run(c)
     for got_bits, ref, name in ((Q, Q64, "Q"), (Kb, K64, "K")):
         got = wl.from_bits16(got_bits, q_dtype).astype(np.float64)
-        # fp32 arithmetic, then one rounding to 16 bits: within 0.51 output ulp + 2e-6 relative of the double result
-        allow = 0.51 * _ulp16(ref, q_dtype) + 2e-6 * np.abs(ref) + 1e-9
+        # fp32 arithmetic, then one rounding to 16 bits: within 0.51 output ulp of the double result, plus the
+        # fp32 error of the head's arithmetic, which is relative to the head's largest element (a rotation
+        # can cancel two large terms into a small one)
+        head_max = np.abs(ref).reshape(ref.shape[0], -1, c["HD"]).max(axis=2, keepdims=True)
+        head_max = np.broadcast_to(head_max, (ref.shape[0], head_max.shape[1], c["HD"])).reshape(ref.shape)
+        allow = 0.51 * _ulp16(ref, q_dtype) + 2e-6 * head_max + 1e-9
         err = np.abs(got - ref)
         assert (err <= allow).all(), f"{name}: {int((err > allow).sum())} elements off, worst {err.max():.3e}"
     # values are a plain cast: bit-exact
