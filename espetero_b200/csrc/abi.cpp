@@ -557,7 +557,15 @@ int esp_attn_prep(esp_attn_ctx* c, void* stream, const float* X, const float* q_
     if (fp8 && !kv_scales) return fail(ESP_ERR_INVALID, "esp_attn_prep: E4M3 pool needs kv_scales");
     if (p.kv_base % 8) return fail(ESP_ERR_INVALID, "esp_attn_prep: kv_base must be a multiple of 8 elements");
   }
-  esp::PrepArgs a{X, q_norm_w, k_norm_w, pos, inv_freq, rope_sel, Q, Kb, Vb, ktab, kv, kv_scales, rows, p};
+  // Heads per warp: as many as keep about four CTAs per SM in the grid (the rotation's sines and
+  // cosines are formed once per warp), between 1 (decode: few rows) and 16.
+  const int heads = s.H + s.Hkv;
+  const int64_t want_ctas = 148 * 4;
+  const int q4 = (heads + 3) / 4;  // heads per warp if one CTA took the whole row
+  const int cap = int(std::clamp<int64_t>(int64_t(rows) * q4 / want_ctas, 1, 16));
+  const int per_row = (q4 + cap - 1) / cap;   // CTAs per row
+  const int hpw = (q4 + per_row - 1) / per_row;  // spread evenly over them
+  esp::PrepArgs a{X, q_norm_w, k_norm_w, pos, inv_freq, rope_sel, Q, Kb, Vb, ktab, kv, kv_scales, rows, hpw, p};
   const cudaError_t e = esp::launch_attn_prep(a, s.HD, s.q_dtype, fp8 && ktab, static_cast<cudaStream_t>(stream), &c->launches);
   if (e != cudaSuccess) return cuda_fail(e, "attn_prep");
   return ESP_OK;

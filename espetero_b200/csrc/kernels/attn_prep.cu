@@ -23,22 +23,64 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepAr
   constexpr int NPT = HD / 32;
   const esp_attn_prep_params& p = a.p;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * kPrepWarps + warp;
   const size_t row = blockIdx.x;
-  if (head >= p.H + p.Hkv) return;
+  const int head_first = (blockIdx.y * kPrepWarps + warp) * a.heads_per_warp;
+  const int head_end = min(head_first + a.heads_per_warp, p.H + p.Hkv);
+  pdl_wait();  // X is the previous kernel's output
+
+  // The rotation depends on the row and the frequency only, not on the head or on which half of a
+  // pair a dim is: the CTA forms the rot_half sines and cosines of its row once (sincosf of a large
+  // angle costs far more than the rest of a head's arithmetic) and every lane picks its own.
+  __shared__ float cs_s[128], sn_s[128];
+  for (int f = threadIdx.x; f < p.rot_half; f += kPrepWarps * 32) {
+    const int4 pr = reinterpret_cast<const int4*>(a.pos)[row];
+    const int sl = a.rope_sel[f];
+    const float position = float(sl == 0 ? pr.x : (sl == 1 ? pr.y : pr.z));
+    sincosf(position * a.inv_freq[f], &sn_s[f], &cs_s[f]);
+  }
+  __syncthreads();
+  if (head_first >= head_end) return;
+  const int partner_xor = p.rot_half / NPT;     // lanes apart
+  const bool rotates = lane < 2 * partner_xor;  // this lane's dims lie below 2 * rot_half
+  const bool low = lane < partner_xor;
+  float cs[NPT], sn[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    cs[i] = 1.0f, sn[i] = 0.0f;
+    if (rotates) {
+      const int f = (lane * NPT + i) & (p.rot_half - 1);
+      cs[i] = cs_s[f];
+      sn[i] = low ? -sn_s[f] : sn_s[f];  // x' = x c - partner s below rot_half, x c + partner s above
+    }
+  }
+
+  // The next head's elements are requested before this head's arithmetic starts: two loads in
+  // flight per warp keep enough bytes on the way to hide the memory latency with 128-dim heads.
+  auto src_of = [&](int head) {
+    const bool q = head < p.H;
+    const int hh = q ? head : head - p.H;
+    return a.X + row * p.ld + (q ? p.q_off + size_t(hh) * p.q_stride : p.k_off + size_t(hh) * HD) + lane * NPT;
+  };
+  float4 nxt[NPT / 4];
+#pragma unroll
+  for (int i = 0; i < NPT / 4; ++i) nxt[i] = reinterpret_cast<const float4*>(src_of(head_first))[i];
+
+  for (int head = head_first; head < head_end; ++head) {
   const bool is_q = head < p.H;
   const int h = is_q ? head : head - p.H;
-  pdl_wait();  // X is the previous kernel's output
-  const float* src = a.X + row * p.ld + (is_q ? p.q_off + size_t(h) * p.q_stride : p.k_off + size_t(h) * HD) + lane * NPT;
   const float* nw = (is_q ? a.qn_w : a.kn_w) + lane * NPT;
 
   float x[NPT], wv[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; i += 4) {
-    const float4 v = *reinterpret_cast<const float4*>(src + i);
+    const float4 v = nxt[i / 4];
     const float4 w = *reinterpret_cast<const float4*>(nw + i);
     x[i] = v.x, x[i + 1] = v.y, x[i + 2] = v.z, x[i + 3] = v.w;
     wv[i] = w.x, wv[i + 1] = w.y, wv[i + 2] = w.z, wv[i + 3] = w.w;
+  }
+  if (head + 1 < head_end) {
+#pragma unroll
+    for (int i = 0; i < NPT / 4; ++i) nxt[i] = reinterpret_cast<const float4*>(src_of(head + 1))[i];
   }
   float ss = 0.0f;
 #pragma unroll
@@ -49,23 +91,11 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepAr
 #pragma unroll
   for (int i = 0; i < NPT; ++i) x[i] = x[i] * inv * wv[i];
 
-  // Rotary embedding: dims [0, 2 * rot_half) in pairs (d, d + rot_half); M-RoPE picks the position
-  // component per frequency.
-  const int4 pr = reinterpret_cast<const int4*>(a.pos)[row];
-  const int partner_xor = p.rot_half / NPT;       // lanes apart
-  const bool rotates = lane < 2 * partner_xor;    // this lane's dims lie below 2 * rot_half
-  const bool low = lane < partner_xor;
+  // Rotary embedding: dims [0, 2 * rot_half) in pairs (d, d + rot_half).
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const float partner = __shfl_xor_sync(0xffffffffu, x[i], partner_xor);
-    if (rotates) {
-      const int f = (lane * NPT + i) & (p.rot_half - 1);
-      const int sl = a.rope_sel[f];
-      const float position = float(sl == 0 ? pr.x : (sl == 1 ? pr.y : pr.z));
-      float sn, c;
-      sincosf(position * a.inv_freq[f], &sn, &c);
-      x[i] = low ? (x[i] * c - partner * sn) : (x[i] * c + partner * sn);
-    }
+    x[i] = x[i] * cs[i] + partner * sn[i];  // lanes that do not rotate hold c = 1, s = 0
   }
 
   uint32_t packed[NPT / 2];
@@ -75,7 +105,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepAr
     typename QE::T* q = static_cast<typename QE::T*>(a.Q) + row * p.q_ld + size_t(h) * HD + lane * NPT;
     if constexpr (NPT == 4) *reinterpret_cast<uint2*>(q) = make_uint2(packed[0], packed[1]);
     else *reinterpret_cast<uint4*>(q) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    return;
+    continue;
   }
 
   // key head: K as computed, V as it is
@@ -141,6 +171,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepAr
       }
     }
   }
+  }  // heads of this warp
 }
 
 template <int HD, int QDT>
@@ -155,7 +186,8 @@ bool attn_prep_supports(int32_t HD) { return HD == 128 || HD == 256; }
 
 cudaError_t launch_attn_prep(const PrepArgs& a, int32_t HD, int32_t q_dtype, bool fp8_pool, cudaStream_t stream, uint64_t* launches) {
   if (a.rows <= 0) return cudaSuccess;
-  const dim3 grid(unsigned(a.rows), unsigned((a.p.H + a.p.Hkv + kPrepWarps - 1) / kPrepWarps));
+  const int per_cta = kPrepWarps * a.heads_per_warp;
+  const dim3 grid(unsigned(a.rows), unsigned((a.p.H + a.p.Hkv + per_cta - 1) / per_cta));
   cudaError_t e;
   if (HD == 128) e = q_dtype == ESP_F16 ? launch_hd<128, ESP_F16>(a, fp8_pool, grid, stream) : launch_hd<128, ESP_BF16>(a, fp8_pool, grid, stream);
   else e = q_dtype == ESP_F16 ? launch_hd<256, ESP_F16>(a, fp8_pool, grid, stream) : launch_hd<256, ESP_BF16>(a, fp8_pool, grid, stream);

@@ -161,6 +161,7 @@ struct PrepArgs {
   void* kv;
   const float* kv_scales;
   int32_t rows;
+  int32_t heads_per_warp;   // a warp forms its row's rotation once and reuses it for this many heads
   esp_attn_prep_params p;
 };
 
