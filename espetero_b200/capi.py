@@ -106,6 +106,10 @@ PROTOTYPES = {
     "esp_p2p_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "esp_p2p_close": (C.c_int, [C.c_void_p]),
     "esp_p2p_free": (C.c_int, [C.c_void_p]),
+    "esp_kv_slot_save": (C.c_int, [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                   C.c_uint64, C.c_uint64]),
+    "esp_kv_slot_load": (C.c_int, [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int32),
+                                   C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "esp_attn_prep": (C.c_int, [C.c_void_p] * 14 + [C.c_int32, C.POINTER(PrepParams)]),
     "esp_kv_save": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                               C.POINTER(Params)]),

@@ -275,6 +275,24 @@ int esp_p2p_open(const unsigned char handle[ESP_P2P_HANDLE_BYTES], void** ptr);
 int esp_p2p_close(void* ptr);
 int esp_p2p_free(void* ptr);
 
+/* ---- Checkpoint files of a sequence's KV blocks in the reference's layout (slot_save / slot_load,
+ * src/model/model.mm:604-740): a 120-byte header (magic 0x554b5043, version 4) and the blocks
+ * layer-major - for every layer the blocks of the sequence's list in order, block_bytes each (K rows, then
+ * V rows). The sections of other subsystems (linear-layer state, MTP rows, n-gram state, index blocks,
+ * rings) are written with zero counts; esp_kv_slot_load refuses files that carry them
+ * (ESP_ERR_UNSUPPORTED) and, like the reference, files whose geometry or size does not match
+ * (ESP_ERR_INVALID). region_bytes = bytes between the layer regions of the pool; a block's bytes sit at
+ * layer * region_bytes + block * block_bytes. Both calls allocate staging buffers (up to 64 MB on the
+ * device and pinned on the host), synchronise the stream, and free them before they return.
+ * Load takes ceil(len / bt) blocks from `pool` (ESP_ERR_CAPACITY "KV cache full" if it has fewer,
+ * leaving it unchanged) and reports them in blocks_out. */
+typedef struct esp_kv_pool esp_kv_pool;
+int esp_kv_slot_save(const char* path, void* stream, const void* kv, const int32_t* blocks_host, int32_t len, int32_t next_pos,
+                     int32_t bt, int32_t n_layers, uint64_t region_bytes, uint64_t block_bytes);
+int esp_kv_slot_load(const char* path, void* stream, void* kv, esp_kv_pool* pool, int32_t* blocks_out, int32_t blocks_cap,
+                     int32_t* n_blocks, int32_t* len, int32_t* next_pos, int32_t bt, int32_t n_layers, uint64_t region_bytes,
+                     uint64_t block_bytes);
+
 /* ---- attn_prep: the step right before the attention pass (kernels/40_attention.metal:23-102, host
  * dispatch src/model/impl/forest.h:2951-2977; generic head dim q3m_attn_prep,
  * kernels/82_qwen3_omni.metal:40-88). Per (row, head) of the fused projection X (fp32):
@@ -328,7 +346,7 @@ int esp_kv_copy_blocks(esp_attn_ctx* ctx, void* stream, void* kv, const int32_t*
 /* Refcounted block pool: KVPool::ref / free_list with kv_alloc / kv_retain / kv_release
  * (src/model/impl/model.h:387-411, :722-737; set-up forest.h:51-62: block 0 is handed out
  * first). esp_kv_alloc fails with ESP_ERR_CAPACITY ("KV cache full") when no block is free. */
-typedef struct esp_kv_pool esp_kv_pool;
+/* esp_kv_pool: declared above, with the checkpoint functions. */
 int esp_kv_pool_create(esp_kv_pool** out, int32_t n_blocks, int32_t bt);
 int esp_kv_pool_destroy(esp_kv_pool* pool);
 int32_t esp_kv_free_count(const esp_kv_pool* pool);
