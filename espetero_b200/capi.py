@@ -91,6 +91,9 @@ PROTOTYPES = {
     "esp_attn_abi_version": (C.c_int, []),
     "esp_attn_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "esp_attn_get_option": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int)]),
+    "esp_attn_plan_window": (C.c_int, [C.POINTER(Tree), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                       C.POINTER(Tile), C.c_int32, C.POINTER(Combine), C.c_int32, C.POINTER(C.c_int32),
+                                       C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "esp_attn_plan": (C.c_int, [C.POINTER(Tree), C.c_int32, C.c_int32, C.POINTER(PlanOpts), C.POINTER(Tile), C.c_int32,
                                 C.POINTER(Combine), C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "esp_attn_parts_floats": (C.c_size_t, [C.POINTER(Shape), C.c_int32]),

@@ -103,6 +103,9 @@ int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
   if ((s.flags & ESP_ATTN_FLAG_GATE) && !a.X) return fail(ESP_ERR_INVALID, "forward: gate flag set but X is null");
   if ((s.flags & ESP_ATTN_FLAG_ANC_MASK) ? !a.anc_mask : !a.desc) return fail(ESP_ERR_INVALID, "forward: the row mask (desc or anc_mask) is null");
   if (a.n_jobs > 0 && (!a.jobs || !a.parts)) return fail(ESP_ERR_INVALID, "forward: combine jobs need jobs and parts");
+  if (a.window < 0 || a.ring < 0) return fail(ESP_ERR_INVALID, "forward: window=%d ring=%d", a.window, a.ring);
+  if (a.window > 0 && !a.pos) return fail(ESP_ERR_INVALID, "forward: a sliding window needs the rows' positions (pos)");
+  if (a.bidi && (s.flags & ESP_ATTN_FLAG_ANC_MASK)) return fail(ESP_ERR_UNSUPPORTED, "forward: bidi uses desc.w and cannot be combined with ancestor masks");
   if (!c->opt_validate || !a.trees_host || !a.tiles_host) return ESP_OK;
   bool any_cached = false;
   for (int i = 0; i < a.n_trees; ++i) {
@@ -111,12 +114,15 @@ int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
     if (int64_t(t.base) + t.M > a.n_rows) return fail(ESP_ERR_INVALID, "tree %d: rows [%d, %d) beyond the pass's %d rows", i, t.base, t.base + t.M, a.n_rows);
     if (t.P > 0) {
       any_cached = true;
-      if (int64_t(t.table) + (t.P + s.bt - 1) / s.bt > a.n_block_entries)
+      if (a.ring > 0) {
+        if (int64_t(t.table) + a.ring > a.n_blocks) return fail(ESP_ERR_INVALID, "tree %d: ring [%d, +%d) beyond the %d blocks of the region", i, t.table, a.ring, a.n_blocks);
+      } else if (int64_t(t.table) + (t.P + s.bt - 1) / s.bt > a.n_block_entries) {
         return fail(ESP_ERR_INVALID, "tree %d: block list [%d, +%d) beyond the %d entries of blocks", i, t.table, (t.P + s.bt - 1) / s.bt, a.n_block_entries);
+      }
     }
     if ((s.flags & ESP_ATTN_FLAG_ANC_MASK) && t.M > 64) return fail(ESP_ERR_UNSUPPORTED, "tree %d: %d rows with a 64-bit ancestor mask", i, t.M);
   }
-  if (any_cached && (!a.kv || !a.blocks || a.n_blocks <= 0)) return fail(ESP_ERR_INVALID, "forward: cached keys but no pool / block table");
+  if (any_cached && (!a.kv || (!a.blocks && a.ring <= 0) || a.n_blocks <= 0)) return fail(ESP_ERR_INVALID, "forward: cached keys but no pool / block table");
   for (int i = 0; i < a.n_tiles; ++i) {
     const esp_attn_tile& t = a.tiles_host[i];
     if (t.tree < 0 || t.tree >= a.n_trees) return fail(ESP_ERR_INVALID, "tile %d: tree %d of %d", i, t.tree, a.n_trees);
@@ -337,16 +343,18 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
+  k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
+  const bool windowed = a.window > 0 || a.ring > 0 || a.bidi != 0;  // the generic kernel's layer options (80_gemma.metal)
 
   // Kernel choice, as forest.h:2864-2868: single-row trees with G <= 8 take the decode kernel.
   bool single = c->G <= 8 && a.trees_host != nullptr && a.tiles_host != nullptr;
   for (int i = 0; single && i < a.n_trees; ++i) single = a.trees_host[i].M == 1;
   bool decode = single && c->opt_attn_gqa && esp::decode_gqa_supports(s.HD, c->G, s.bt, s.q_dtype, s.kv_dtype) && a.kv != nullptr && a.n_blocks > 0 &&
                 (size_t(a.p.kv_ld) * elem_bytes(s.kv_dtype)) % 128 == 0 && (a.p.kv_base * elem_bytes(s.kv_dtype)) % 128 == 0;
-  for (int i = 0; decode && i < a.n_tiles; ++i) decode = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+  // (a tile may start at any key: sliding-window plans begin at the row's first visible key)
 
   // Multi-row tiles: the tcgen05 kernel when the shape fits it (128 (row, head) pairs per CTA).
-  bool umma = !decode && c->opt_attn_umma && a.tiles_host != nullptr &&
+  bool umma = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr &&
               esp::flash_umma_supports(s.HD, c->G, c->tile_rows, s.bt, s.q_dtype, s.kv_dtype) && a.p.kv_ld % 64 == 0 &&
               a.p.kv_base % 64 == 0;
   for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;

@@ -71,14 +71,14 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   // warm L2 with what this CTA reads first - its plan records, page-table entries and each warp's
   // first key blocks. Hints and L1-bypassing reads only, every index checked: stale or
   // half-written metadata can cost a wasted hint, never a result.
-  if (lane < STAGES - 1 && a.n_trees > 0 && a.n_block_entries > 0) {
+  if (lane < STAGES - 1 && a.n_trees > 0 && a.n_block_entries > 0 && a.blocks != nullptr) {
     const int4* tp = reinterpret_cast<const int4*>(a.tiles + blockIdx.x / p.Hkv);
     const int4 t0 = __ldcg(tp);  // tree, r0, k0, k1
     if (t0.x >= 0 && t0.x < a.n_trees && p.bt > 0) {
       const int4 tr = __ldcg(reinterpret_cast<const int4*>(a.trees + t0.x));  // base, P, table, M
-      const int j0 = t0.z + 16 * (warp + lane * NW);
+      const int j0 = (t0.z & ~15) + 16 * (warp + lane * NW);
       const long long idx = (long long)tr.z + j0 / p.bt;
-      if (t0.z >= 0 && j0 < t0.w && tr.z >= 0 && idx < a.n_block_entries) {
+      if (a.ring == 0 && t0.z >= 0 && j0 < t0.w && tr.z >= 0 && idx < a.n_block_entries) {
         const int b = __ldcg(a.blocks + idx);
         if (b >= 0 && b < a.n_blocks) {
           const int y = b * 2 * p.bt + j0 % p.bt;
@@ -136,7 +136,11 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   }
 
   // ---- this warp's 16-key blocks: warp, warp + NW, ... of the tile's cached range
-  const int nblk = (tile.k1 - tile.k0 + 15) >> 4;
+  // A tile may start at any key (a sliding-window plan begins at the row's first visible key): the
+  // 16-key blocks are cut from the 16-aligned key below it, and the first block masks what lies
+  // before k0 the way the last one masks what lies past k1.
+  const int kbase = tile.k0 & ~15;
+  const int nblk = tile.k1 > tile.k0 ? (tile.k1 - kbase + 15) >> 4 : 0;
   const int n_it = nblk > warp ? (nblk - warp + NW - 1) / NW : 0;
 
   // Lane L of a window keeps the metadata of iteration win + L (page-table lookups are
@@ -145,8 +149,9 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   int use_win = -32;
   float use_ks = 1.0f, use_vs = 1.0f;
   auto block_of_it = [&](int it, int& j0) {
-    j0 = tile.k0 + 16 * (warp + it * NW);
-    return a.blocks[tree.table + j0 / p.bt];
+    j0 = kbase + 16 * (warp + it * NW);
+    // ring layers (kernels/80_gemma.metal:429) keep a sequence's blocks in place: no page table
+    return a.ring > 0 ? tree.table + (j0 / p.bt) % a.ring : a.blocks[tree.table + j0 / p.bt];
   };
   auto issue = [&](int it) {
     if (it - iss_win >= 32) {
@@ -203,7 +208,9 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     }
     const uint8_t* kt = wsm + slot * C::STAGE_BYTES;
     uint8_t* vt = wsm + slot * C::STAGE_BYTES + C::TILE_BYTES;
-    const int n_valid = min(16, tile.k1 - (tile.k0 + 16 * (warp + it * NW)));
+    const int jb = kbase + 16 * (warp + it * NW);  // first key of this block
+    const int n_valid = min(16, tile.k1 - jb);
+    const int n_skip = tile.k0 - jb;               // > 0 only in the tile's first block
     if (n_valid < 16) {
       // Tail block: rows past the range hold other keys (or stale bytes); V must be zero
       // there (0 * NaN), K is masked by selection below.
@@ -243,8 +250,8 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     // lane: s[0] = (key g, head 2t), s[1] = (key g, head 2t+1), s[2], s[3] = key g + 8
     const float sc = sl2 * kscale;
     float s0 = (sa[0] + sb[0]) * sc, s1 = (sa[1] + sb[1]) * sc, s2 = (sa[2] + sb[2]) * sc, s3 = (sa[3] + sb[3]) * sc;
-    if (g >= n_valid) s0 = s1 = -INFINITY;
-    if (g + 8 >= n_valid) s2 = s3 = -INFINITY;
+    if (g >= n_valid || g < n_skip) s0 = s1 = -INFINITY;
+    if (g + 8 >= n_valid || g + 8 < n_skip) s2 = s3 = -INFINITY;
 
     // ---- online softmax per head over the 16 keys (key lanes: xor 4, 8, 16)
     float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);

@@ -71,6 +71,12 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
     __syncwarp();
     const float* q = qs[warp];
 
+    // Sliding-window layers (kernels/80_gemma.metal:123-142, :284-285): a key `window` or more
+    // positions behind the query is masked; cached key j sits at position j, a batch key at its row's.
+    const int qpos = a.window > 0 ? a.pos[4 * size_t(row)] : 0;
+    auto block_of = [&](int j) {  // ring layers keep a sequence's blocks in place: table + (j / bt) % ring
+      return a.ring > 0 ? size_t(tree.table + (j / p.bt) % a.ring) : size_t(a.blocks[tree.table + j / p.bt]);
+    };
     float m_run = -INFINITY, l_run = 0.0f;
     float acc[DPL];
 #pragma unroll
@@ -104,8 +110,8 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
     for (int j0 = tile.k0; j0 < tile.k1; j0 += 32) {
       const int j = j0 + lane;
       float s = -INFINITY;
-      if (j < tile.k1) {
-        const size_t b = size_t(a.blocks[tree.table + j / p.bt]);
+      if (j < tile.k1 && (a.window <= 0 || qpos - j < a.window)) {
+        const size_t b = block_of(j);
         const size_t off = p.kv_base + (b * 2) * blk_elems + size_t(j % p.bt) * p.kv_ld + size_t(kvh) * HD;
         float dot = 0.0f;
         if constexpr (KVDT == ESP_E4M3) {
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
       }
       softmax_pv(s, [&](int jj, float pj) {
         const int jk = j0 + jj;
-        const size_t b = size_t(a.blocks[tree.table + jk / p.bt]);
+        const size_t b = block_of(jk);
         const size_t off = p.kv_base + (b * 2 + 1) * blk_elems + size_t(jk % p.bt) * p.kv_ld + size_t(kvh) * HD + lane * DPL;
         if constexpr (KVDT == ESP_E4M3) {
           const float w = pj * a.kv_scales[(b * 2 + 1) * p.Hkv + kvh];
@@ -148,12 +154,14 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
       } else {
         d = reinterpret_cast<const int4*>(a.desc)[row];
         k_last = min(tree.M - 1, max(rr, d.z - 1));
+        if (a.bidi) k_last = min(tree.M - 1, max(k_last, d.w - 1));  // an image's rows see the whole image
       }
       for (int j0 = 0; j0 <= k_last; j0 += 32) {
         const int j = j0 + lane;
         bool vis = j <= k_last;
         if (a.anc_mask) vis = vis && ((am >> j) & 1ull);
-        else vis = vis && ((j < d.z) || (j >= d.x && j <= rr));
+        else vis = vis && ((j < d.z) || (j >= d.x && (j <= rr || (a.bidi && j < d.w))));
+        if (a.window > 0 && vis) vis = qpos - a.pos[4 * size_t(tree.base + j)] < a.window;
         float s = -INFINITY;
         if (vis) {
           const uint4* src =

@@ -97,8 +97,8 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   int max_part = -1;
   for (int i = 0; i < a.n_tiles; ++i) {
     const esp_attn_tile& t = a.tiles_host[i];
-    if (t.tree < 0 || t.tree >= a.n_trees || t.k0 < 0 || t.k0 > t.k1 || t.k1 > a.trees_host[t.tree].P || t.k0 % esp::kDecodeKeyBlock)
-      return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: tile %d is malformed or does not start on a 16-key boundary", i);
+    if (t.tree < 0 || t.tree >= a.n_trees || t.k0 < 0 || t.k0 > t.k1 || t.k1 > a.trees_host[t.tree].P)
+      return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: tile %d is malformed", i);
     max_part = t.part > max_part ? t.part : max_part;
   }
   const size_t need = size_t(max_part + 1) * size_t(s.Hkv) * size_t(TR) * size_t(G) * size_t(s.HD + 2);
@@ -138,6 +138,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   k.p = a.p, k.HD = s.HD, k.G = G, k.tile_rows = TR, k.n_tiles = a.n_tiles;
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
+  k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
   // Nothing in the array has to be cleared first: every record the merge reads below is
   // written in full by the attention kernel of this same call.
   // Same choice as esp_attn_forward (identical bits): plans whose split tiles name their jobs are

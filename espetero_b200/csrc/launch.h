@@ -48,6 +48,11 @@ struct KernelArgs {
   int32_t n_trees;          // bounds for the speculative reads ahead of the dependency wait
   int32_t n_block_entries;
   float scale;
+  // sliding-window layers (kernels/80_gemma.metal:123-142)
+  const int32_t* pos;  // int4 per row, x = position (needed when window > 0)
+  int32_t window;      // > 0: keys `window` or more positions behind the query are masked
+  int32_t ring;        // > 0: cached key j lives in block table + (j / bt) % ring (no page table)
+  int32_t bidi;        // rows of an image also see the image's later rows (desc.w)
 };
 
 // Small plans travel in the kernel's parameter space (constant bank), one 64-byte line per tile

@@ -6,6 +6,7 @@
 // ESP_PLAN_B200 emits the same records with one chunk size for the whole pass, chosen so
 // that (kv head, tile) CTAs of near-equal length fill `groups` CTA slots.
 #include <algorithm>
+#include <climits>
 #include <cstdint>
 
 #include "../../include/espetero_attn.h"
@@ -124,6 +125,66 @@ extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_
   *n_parts = E.np;
   if ((tiles && E.nt > tiles_cap) || (jobs && E.nj > jobs_cap))
     return esp::fail(ESP_ERR_CAPACITY, "esp_attn_plan: needs %d tiles and %d jobs", E.nt, E.nj);
+  return ESP_OK;
+}
+
+// The generic planner with its window branch (src/model/impl/gemma.h:77-116). Budget and tile height
+// as in ESP_PLAN_G4; per row group the cached range starts at the first key a row of the group can
+// see, and the first batch key worth scanning travels in pad0.
+extern "C" int esp_attn_plan_window(const esp_attn_tree* trees, int32_t n_trees, int32_t groups, int32_t split, int32_t rows,
+                                    int32_t window, const int32_t* pos, esp_attn_tile* tiles, int32_t tiles_cap,
+                                    esp_attn_combine* jobs, int32_t jobs_cap, int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts,
+                                    int32_t* plan_rows) {
+  if ((!trees && n_trees > 0) || n_trees < 0 || groups <= 0 || rows <= 0 || window < 0 || !n_tiles || !n_jobs || !n_parts || !plan_rows)
+    return esp::fail(ESP_ERR_INVALID, "esp_attn_plan_window: null or negative argument");
+  if (window > 0 && !pos) return esp::fail(ESP_ERR_INVALID, "esp_attn_plan_window: a window needs the rows' positions");
+  for (int32_t i = 0; i < n_trees; ++i)
+    if (trees[i].P < 0 || trees[i].M < 0 || trees[i].base < 0)
+      return esp::fail(ESP_ERR_INVALID, "esp_attn_plan_window: tree %d has a negative field", i);
+  int64_t row_groups = 0;
+  for (int32_t i = 0; i < n_trees; ++i) row_groups += (trees[i].M + 7) / 8;
+  const int32_t budget = int32_t(std::max<int64_t>(1, 256 / std::max<int64_t>(1, int64_t(groups) * row_groups)));
+  const int32_t TR = budget == 1 ? rows : 8;
+  int32_t nt = 0, nj = 0, np = 0;
+  auto put_tile = [&](const esp_attn_tile& t) {
+    if (tiles && nt < tiles_cap) tiles[nt] = t;
+    ++nt;
+  };
+  for (int32_t ti = 0; ti < n_trees; ++ti) {
+    const esp_attn_tree& t = trees[ti];
+    for (int32_t r = 0; r < t.M; r += TR) {
+      int32_t first_key = 0, first_batch = 0;
+      if (window > 0) {
+        int32_t lowest = INT32_MAX;  // the earliest query position of the group decides what is still visible
+        for (int32_t i = r; i < std::min(t.M, r + TR); ++i) lowest = std::min(lowest, pos[4 * size_t(t.base + i)]);
+        const int64_t start = int64_t(lowest) - window + 1;
+        first_key = int32_t(std::clamp<int64_t>(start, 0, t.P));
+        first_batch = int32_t(std::max<int64_t>(0, start - t.P));
+      }
+      const int32_t span = t.P - first_key;
+      int32_t pieces = 1;
+      if (split > 0 && budget > 1 && span >= 64) {
+        const int32_t chunk = std::max(32, std::min(split, (ceil_div(span, budget) + 31) / 32 * 32));
+        pieces = std::min({ceil_div(span, chunk), budget, 64});
+      }
+      if (pieces == 1) {
+        put_tile({ti, t.base + r, first_key, t.P, -1, 1, first_batch, 0});
+        continue;
+      }
+      const int32_t step = (ceil_div(span, pieces) + 31) / 32 * 32;
+      const int32_t part0 = np;
+      int32_t used = 0;
+      for (int32_t k = first_key; k < t.P; k += step, ++used) {
+        const int32_t k1 = std::min(t.P, k + step);
+        put_tile({ti, t.base + r, k, k1, np++, k1 >= t.P ? 1 : 0, first_batch, 0});
+      }
+      if (jobs && nj < jobs_cap) jobs[nj] = {t.base + r, std::min(8, t.M - r), part0, used};
+      ++nj;
+    }
+  }
+  *n_tiles = nt, *n_jobs = nj, *n_parts = np, *plan_rows = TR;
+  if ((tiles && nt > tiles_cap) || (jobs && nj > jobs_cap))
+    return esp::fail(ESP_ERR_CAPACITY, "esp_attn_plan_window: needs %d tiles and %d jobs", nt, nj);
   return ESP_OK;
 }
 

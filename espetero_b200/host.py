@@ -42,6 +42,24 @@ def plan_tiles(trees: np.ndarray, Hkv: int, mode: int = capi.ESP_PLAN_REFERENCE,
     return Plan(tiles[:nt.value], jobs[:nj.value], np_.value, tile_rows)
 
 
+def plan_window(trees: np.ndarray, groups: int, split: int = 512, rows: int = 8, window: int = 0, pos=None) -> Plan:
+    """esp_attn_plan_window: the generic planner with its sliding-window branch (gemma.h:77-116)."""
+    lib = capi.load()
+    trees = np.ascontiguousarray(trees, dtype=TREE_DT)
+    pos = None if pos is None else np.ascontiguousarray(pos, dtype=np.int32)
+    pp = None if pos is None else C.c_void_p(pos.ctypes.data)
+    nt, nj, np_, pr = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+    tp = trees.ctypes.data_as(C.POINTER(capi.Tree))
+    capi.check(lib.esp_attn_plan_window(tp, len(trees), groups, split, rows, window, pp, None, 0, None, 0, C.byref(nt), C.byref(nj),
+                                        C.byref(np_), C.byref(pr)))
+    tiles = np.zeros(max(1, nt.value), dtype=TILE_DT)
+    jobs = np.zeros(max(1, nj.value), dtype=COMBINE_DT)
+    capi.check(lib.esp_attn_plan_window(tp, len(trees), groups, split, rows, window, pp, tiles.ctypes.data_as(C.POINTER(capi.Tile)),
+                                        len(tiles), jobs.ctypes.data_as(C.POINTER(capi.Combine)), len(jobs), C.byref(nt), C.byref(nj),
+                                        C.byref(np_), C.byref(pr)))
+    return Plan(tiles[:nt.value], jobs[:nj.value], np_.value, pr.value)
+
+
 def _dev(arr: np.ndarray | None, device, pin: bool = False):
     if arr is None:
         return None
@@ -74,6 +92,8 @@ class DevicePass:
         self.anc_mask = _dev(w.anc_mask, device)
         self.X = _dev(w.X, device)
         self.trees = _dev(w.trees, device)
+        self.win = w.extra.get("window") if isinstance(getattr(w, "extra", None), dict) else None
+        self.pos = _dev(self.win["pos"], device) if self.win else None
         self.O = torch.zeros((w.n_rows, w.q_ld), dtype=torch.int16, device=device)
         self.lse = torch.zeros((w.n_rows, w.H), dtype=torch.float32, device=device)
         self.tiles = self.jobs = self.parts = None
@@ -192,6 +212,8 @@ class AttnOp:
         a.jobs_host = plan.jobs.ctypes.data if len(plan.jobs) else None
         a.n_tiles, a.n_trees, a.n_jobs, a.n_rows = len(plan.tiles), len(w.trees), len(plan.jobs), w.n_rows
         a.n_blocks, a.n_block_entries, a.n_parts = w.n_blocks, len(w.blocks), plan.n_parts
+        if dp.win:
+            a.pos, a.window, a.ring, a.bidi = _ptr(dp.pos), dp.win["window"], dp.win["ring"], dp.win["bidi"]
         a.p = self.params(w)
         return a
 

@@ -222,6 +222,29 @@ def make_pass(name: str, seed: int, trees_PM, H: int, Hkv: int, HD: int, bt: int
                     anc, X, trees, 0, extra)
 
 
+def make_window_pass(name: str, seed: int, trees_PM, H: int, Hkv: int, HD: int, bt: int, q_dtype: int, window: int,
+                     ring: int = 0, images=None, scale: float = 1.0, kv_dtype: int | None = None) -> Workload:
+    """A pass of a sliding-window layer of the generic kernel (kernels/80_gemma.metal:123-142): causal
+    rows at positions P, P + 1, ... behind P cached keys, keys `window` or more positions back masked.
+    ring > 0: a tree's cached keys live in its own ring of `ring` blocks (key j in block
+    table + (j / bt) % ring), no page table. images = {tree: (first row, end row)}: those rows carry
+    desc.w = end and, with bidi, see the whole image. The parameters travel in extra["window"]."""
+    n_trees = len(trees_PM)
+    w = make_pass(name, seed, trees_PM, H, Hkv, HD, bt, q_dtype, kv_dtype, scale=scale, spare_blocks=3 + n_trees * max(ring, 0))
+    pos = np.zeros((w.n_rows, 4), dtype=np.int32)
+    for i, (P, M) in enumerate(trees_PM):
+        b0 = int(w.trees[i]["base"])
+        pos[b0:b0 + M, 0] = P + np.arange(M)
+        pos[b0:b0 + M, 1:3] = pos[b0:b0 + M, 0:1]
+        if ring > 0:
+            w.trees[i]["table"] = i * ring
+        if images and i in images:
+            a, b = images[i]
+            w.desc[b0 + a:b0 + b, 3] = b
+    w.extra["window"] = {"pos": pos, "window": int(window), "ring": int(ring), "bidi": 1 if images else 0}
+    return w
+
+
 # ----------------------------------------------------------------------------- the five configurations
 def config_c1(seed: int = 0xE5B201) -> Workload:
     """Single-sequence paged decode: 1 query token, H8/Hkv2/HD128 fp16, 1024 cached tokens, 16-token pages."""

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define ESP_ATTN_ABI_VERSION 1
+#define ESP_ATTN_ABI_VERSION 2
 
 /* ---------------------------------------------------------------- status */
 typedef enum esp_status {
@@ -163,6 +163,15 @@ typedef struct esp_plan_opts {
   int32_t reserved[2];
 } esp_plan_opts;
 
+/* g4_plan_tiles (src/model/impl/gemma.h:77-116) bit for bit, window branch included: a sliding tile
+ * starts at the first cached key any of its rows can see (k0 = min position - window + 1, clamped) and
+ * carries the first batch key to scan in pad0. `groups` = kv heads x split groups of the grid, `rows` =
+ * rows per tile when nothing is split (8 otherwise), pos = int4 per row. plan_rows receives the tile
+ * height the plan was made for. Same capacity protocol as esp_attn_plan. */
+int esp_attn_plan_window(const esp_attn_tree* trees, int32_t n_trees, int32_t groups, int32_t split, int32_t rows,
+                         int32_t window, const int32_t* pos, esp_attn_tile* tiles, int32_t tiles_cap, esp_attn_combine* jobs,
+                         int32_t jobs_cap, int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts, int32_t* plan_rows);
+
 /* Pure host function. Writes up to tiles_cap tiles and jobs_cap combine jobs and
  * always reports the counts needed (ESP_ERR_CAPACITY if an array was too small;
  * pass NULL arrays to size them). n_parts = partial records the pass needs; the
@@ -208,6 +217,18 @@ typedef struct esp_attn_args {
   int32_t n_parts;         /* records `parts` can hold */
   int32_t reserved;
   esp_attn_params p;
+  /* Sliding-window layers of the generic attention kernel (kernels/80_gemma.metal:123-142; host
+   * src/model/impl/gemma.h:77-116). All zero / NULL for ordinary layers. */
+  const int32_t* pos;      /* int4 per row, x = the row's position; needed when window > 0 */
+  int32_t window;          /* > 0: a key `window` or more positions behind the query is masked (cached key j
+                              is at position j, a batch key at its row's position). Single-row trees rely on
+                              the plan instead, as the reference's decode kernel does: its tile starts at the
+                              row's first visible key (esp_attn_plan_window). */
+  int32_t ring;            /* > 0: cached key j of a tree lives in block tree.table + (j / bt) % ring of the
+                              layer region - the slot's ring of a sliding layer - and `blocks` is not read */
+  int32_t bidi;            /* 1: rows of an image also see the image's later rows (desc.w = end of the row's
+                              image, 0 outside images) */
+  int32_t reserved2;
 } esp_attn_args;
 
 /* Attention over the plan's tiles, then the combine jobs: the reference's

@@ -25,7 +25,8 @@ class Problem(C.Structure):
     _fields_ = [("Q", C.c_void_p), ("Kb", C.c_void_p), ("Vb", C.c_void_p), ("kv", C.c_void_p), ("kv_scales", C.c_void_p),
                 ("blocks", C.c_void_p), ("desc", C.c_void_p), ("anc_mask", C.c_void_p), ("X", C.c_void_p), ("trees", C.c_void_p),
                 ("n_trees", C.c_int32), ("HD", C.c_int32), ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32),
-                ("tile_rows", C.c_int32), ("scale", C.c_float), ("p", Params)]
+                ("tile_rows", C.c_int32), ("scale", C.c_float), ("p", Params),
+                ("pos", C.c_void_p), ("window", C.c_int32), ("ring", C.c_int32), ("bidi", C.c_int32), ("pad", C.c_int32)]
 
 
 _lib = None
@@ -81,6 +82,9 @@ def problem(w, tile_rows: int = 8) -> Problem:
     pb.anc_mask = _p(w.anc_mask) if (w.flags & 2) else None
     pb.n_trees, pb.HD, pb.q_dtype, pb.kv_dtype, pb.tile_rows, pb.scale = len(w.trees), w.HD, w.q_dtype, w.kv_dtype, tile_rows, w.scale
     pb.p = Params(w.H, w.Hkv, w.q_ld, w.kv_ld, w.g_ld, w.bt, w.kv_base)
+    win = w.extra.get("window") if hasattr(w, "extra") else None
+    if win:
+        pb.pos, pb.window, pb.ring, pb.bidi = _p(win["pos"]), win["window"], win["ring"], win["bidi"]
     return pb
 
 
@@ -148,17 +152,19 @@ def plan_tiles(trees, Hkv, split=512, groups=256, min_chunk=32, tile_rows=8):
     return tiles[:nt.value], jobs[:nj.value], npart.value
 
 
-def g4_plan_tiles(trees, groups, split=512, rows=8):
+def g4_plan_tiles(trees, groups, split=512, rows=8, window=0, pos=None):
     from espetero_b200.workloads import COMBINE_DT, TILE_DT
     lib = load()
     trees = np.ascontiguousarray(trees)
+    pos = None if pos is None else np.ascontiguousarray(pos, dtype=np.int32)
     nt, nj, npart, pr = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
-    lib.orc_g4_plan_tiles(C.c_void_p(trees.ctypes.data), len(trees), groups, split, rows, None, None, C.byref(nt), C.byref(nj),
-                          C.byref(npart), C.byref(pr))
+    lib.orc_g4_plan_tiles(C.c_void_p(trees.ctypes.data), len(trees), groups, split, rows, window, C.c_void_p(_p(pos)), None, None,
+                          C.byref(nt), C.byref(nj), C.byref(npart), C.byref(pr))
     tiles = np.zeros(max(1, nt.value), dtype=TILE_DT)
     jobs = np.zeros(max(1, nj.value), dtype=COMBINE_DT)
-    lib.orc_g4_plan_tiles(C.c_void_p(trees.ctypes.data), len(trees), groups, split, rows, C.c_void_p(tiles.ctypes.data),
-                          C.c_void_p(jobs.ctypes.data), C.byref(nt), C.byref(nj), C.byref(npart), C.byref(pr))
+    lib.orc_g4_plan_tiles(C.c_void_p(trees.ctypes.data), len(trees), groups, split, rows, window, C.c_void_p(_p(pos)),
+                          C.c_void_p(tiles.ctypes.data), C.c_void_p(jobs.ctypes.data), C.byref(nt), C.byref(nj), C.byref(npart),
+                          C.byref(pr))
     return tiles[:nt.value], jobs[:nj.value], npart.value, pr.value
 
 

@@ -182,6 +182,12 @@ struct Problem {
   int32_t tile_rows;
   float scale;
   Params p;
+  // Sliding-window layers of the generic kernel (kernels/80_gemma.metal:123-142): pos = int4 per row
+  // (x = position), window > 0 masks keys `window` or more positions behind the query, ring > 0
+  // reads cached key j from block table + (j / bt) % ring instead of the page table, bidi lets the
+  // rows of an image see the image's later rows (desc.w = end of the row's image, 0 outside).
+  const int32_t* pos;
+  int32_t window, ring, bidi, pad;
 };
 
 struct KeyRef {  // one visible key of a row
@@ -192,7 +198,16 @@ struct KeyRef {  // one visible key of a row
 inline bool batch_visible(const Problem& pb, int row, int rr, int j) {
   if (pb.anc_mask) return j < 64 && ((pb.anc_mask[row] >> j) & 1ull);
   const int32_t* d = pb.desc + 4 * size_t(row);
-  return (j < d[2]) || (j >= d[0] && j <= rr);
+  return (j < d[2]) || (j >= d[0] && (j <= rr || (pb.bidi && j < d[3])));  // 80_gemma.metal:284
+}
+
+// The window test of 80_gemma.metal:285: a key at position kpos is visible from a query at qpos
+// iff qpos - kpos < window (cached key j sits at position j, a batch key at its row's position).
+inline bool in_window(const Problem& pb, const Tree& t, int row, bool cached, int j) {
+  if (pb.window <= 0) return true;
+  const int qpos = pb.pos[4 * size_t(row)];
+  const int kpos = cached ? j : pb.pos[4 * size_t(t.base + j)];
+  return qpos - kpos < pb.window;
 }
 
 // One K (which 0) or V (1) row of a key, as raw codes (float) plus its scale: cached
@@ -208,7 +223,7 @@ inline void load_key_row(const Problem& pb, const Tree& t, bool cached, int j, i
     else for (int d = 0; d < HD; ++d) out[d] = bf16_to_f32(src[d]);
     return;
   }
-  const uint64_t b = uint64_t(pb.blocks[t.table + j / p.bt]);
+  const uint64_t b = pb.ring > 0 ? uint64_t(t.table + (j / p.bt) % pb.ring) : uint64_t(pb.blocks[t.table + j / p.bt]);  // 80_gemma.metal:250
   const uint64_t off = p.kv_base + (b * 2 + uint64_t(which)) * uint64_t(p.bt) * p.kv_ld + uint64_t(j % p.bt) * p.kv_ld + uint64_t(kvh) * HD;
   if (pb.kv_dtype == ORC_E4M3) {
     *scale = pb.kv_scales[(b * 2 + which) * p.Hkv + kvh];
@@ -300,9 +315,10 @@ int orc_attention_f64(const Problem* pbp, const int32_t* rows, int32_t n_rows, d
         q[size_t(g) * HD + d] = double(load16(pb.Q, size_t(row) * p.q_ld + size_t(kvh * G + g) * HD + d, pb.q_dtype));
     std::vector<KeyRef> keys;
     keys.reserve(size_t(t.P) + t.M);
-    for (int j = 0; j < t.P; ++j) keys.push_back({true, j});
+    for (int j = 0; j < t.P; ++j)
+      if (in_window(pb, t, row, true, j)) keys.push_back({true, j});
     for (int j = 0; j < t.M; ++j)
-      if (batch_visible(pb, row, rr, j)) keys.push_back({false, j});
+      if (batch_visible(pb, row, rr, j) && in_window(pb, t, row, false, j)) keys.push_back({false, j});
     const size_t nk = keys.size();
     std::vector<double> s(size_t(G) * nk);
     std::vector<double> mx(G, -std::numeric_limits<double>::infinity());
@@ -759,8 +775,11 @@ int orc_plan_tiles(const Tree* trees, int32_t n_trees, int32_t Hkv, int32_t spli
 
 // g4_plan_tiles with window = 0 (src/model/impl/gemma.h:77-116): min_chunk fixed
 // at 32, tiles of `rows` rows only when nothing is split (budget == 1), else 8.
-int orc_g4_plan_tiles(const Tree* trees, int32_t n_trees, int32_t groups, int32_t split, int32_t rows, Tile* tiles,
-                      Combine* jobs, int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts, int32_t* plan_rows) {
+// g4_plan_tiles (src/model/impl/gemma.h:77-116) with its window branch: a sliding tile starts at the
+// first key any of its rows can see (k0) and records the first batch key to scan (b0, in pad0).
+int orc_g4_plan_tiles(const Tree* trees, int32_t n_trees, int32_t groups, int32_t split, int32_t rows, int32_t window,
+                      const int32_t* pos, Tile* tiles, Combine* jobs, int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts,
+                      int32_t* plan_rows) {
   int total = 0;
   for (int i = 0; i < n_trees; ++i) total += (trees[i].M + 7) / 8;
   const int budget = std::max(1, 256 / std::max(1, groups * total));
@@ -769,14 +788,21 @@ int orc_g4_plan_tiles(const Tree* trees, int32_t n_trees, int32_t groups, int32_
   for (int ti = 0; ti < n_trees; ++ti) {
     const Tree& t = trees[ti];
     for (int r = 0; r < t.M; r += TR) {
-      const int span = t.P;
+      int k0 = 0, b0 = 0;
+      if (window > 0) {
+        int minpos = std::numeric_limits<int32_t>::max();
+        for (int i = r; i < std::min(t.M, r + TR); ++i) minpos = std::min(minpos, pos[4 * (t.base + i)]);
+        k0 = std::clamp(minpos - window + 1, 0, t.P);
+        b0 = std::max(0, minpos - window + 1 - t.P);
+      }
+      const int span = t.P - k0;
       int ns = 1;
       if (split > 0 && budget > 1 && span >= 64) {
         const int chunk = std::max(32, std::min(split, ((span + budget - 1) / budget + 31) / 32 * 32));
         ns = std::min({(span + chunk - 1) / chunk, budget, 64});
       }
       if (ns == 1) {
-        if (tiles) tiles[nt] = Tile{ti, t.base + r, 0, t.P, -1, 1, 0, 0};
+        if (tiles) tiles[nt] = Tile{ti, t.base + r, k0, t.P, -1, 1, b0, 0};
         ++nt;
         continue;
       }
@@ -784,9 +810,9 @@ int orc_g4_plan_tiles(const Tree* trees, int32_t n_trees, int32_t groups, int32_
       const int step = (per + 31) / 32 * 32;
       const int part0 = np;
       int used = 0;
-      for (int k = 0; k < t.P; k += step, ++used) {
+      for (int k = k0; k < t.P; k += step, ++used) {
         const int k1 = std::min(t.P, k + step);
-        if (tiles) tiles[nt] = Tile{ti, t.base + r, k, k1, np, k1 >= t.P ? 1 : 0, 0, 0};
+        if (tiles) tiles[nt] = Tile{ti, t.base + r, k, k1, np, k1 >= t.P ? 1 : 0, b0, 0};
         ++nt;
         ++np;
       }

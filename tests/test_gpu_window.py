@@ -1,0 +1,109 @@
+"""Sliding-window layers of the generic attention kernel (kernels/80_gemma.metal:123-142, :250, :284-285;
+planner src/model/impl/gemma.h:77-116) through the C ABI against the float64 oracle: window masks on cached
+and batch keys, ring addressing of the cached keys, bidirectional image rows, and single-row (decode)
+passes whose window lives in the plan (tiles start at the first visible key, at any alignment)."""
+import numpy as np
+import pytest
+import torch
+
+from espetero_b200 import capi, host, workloads as wl
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(w, plan, options=None):
+    op = host.AttnOp.for_workload(w, plan.tile_rows)
+    try:
+        for k, v in (options or {}).items():
+            op.set_option(k, v)
+        dp = op.upload(w, plan)
+        op.forward(dp)
+        op.check_status()
+        torch.cuda.synchronize()
+        return dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy(), op.last_kernel
+    finally:
+        op.close()
+
+
+def _check(oracle_lib, w, plan, expect_kernel, options=None):
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    O, lse, kernel = _run(w, plan, options)
+    assert kernel == expect_kernel
+    util.check_output(O, ref, w, ref_abs=ref_abs, what=w.name)
+    fin = np.isfinite(lse_ref)
+    assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
+    return O
+
+
+@pytest.mark.parametrize("HD", [128, 256])
+@pytest.mark.parametrize("window", [64, 1000])
+def test_window_masks_multi_row(oracle_lib, HD, window):
+    """Chunked prefill / verify rows behind a cached prefix: the window cuts into the prefix for the late
+    rows and into the batch keys for the early ones."""
+    w = wl.make_window_pass("win", 21, [(700, 40), (30, 90), (0, 17)], 8, 2, HD, 16, wl.BF16, window, scale=HD ** -0.5)
+    win = w.extra["window"]
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=window, pos=win["pos"])
+    assert any(int(t["k0"]) % 16 for t in plan.tiles) or window >= 1000
+    _check(oracle_lib, w, plan, "flash_general")
+    # the mask alone (no help from the plan): full-range tiles give the same answer
+    full = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=0, pos=None)
+    _check(oracle_lib, w, full, "flash_general")
+
+
+def test_window_changes_the_result(oracle_lib):
+    """The same inputs with and without the window differ (the test above would pass on a kernel that
+    ignores the window only if the oracle did too)."""
+    w = wl.make_window_pass("win2", 22, [(600, 24)], 8, 2, 128, 16, wl.BF16, 50, scale=128 ** -0.5)
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=0, rows=8, window=0, pos=None)
+    O_win = _check(oracle_lib, w, plan, "flash_general")
+    w.extra.pop("window")
+    O_all = _check(oracle_lib, w, plan, "flash_general")
+    assert not np.array_equal(O_win, O_all)
+
+
+def test_ring_addressing_and_bidi_images(oracle_lib):
+    """Cached keys in per-sequence rings (no page table) and image rows that see their whole image."""
+    bt, ring = 16, 12
+    w = wl.make_window_pass("ring", 23, [(150, 30), (100, 12)], 8, 2, 256, bt, wl.F16, 96, ring=ring, images={0: (5, 21)},
+                            scale=256 ** -0.5)
+    w.blocks[:] = -1                                   # the page table must not be read
+    win = w.extra["window"]
+    assert win["bidi"] == 1 and win["ring"] == ring
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=96, pos=win["pos"])
+    _check(oracle_lib, w, plan, "flash_general")
+
+
+@pytest.mark.parametrize("kvdt", [None, wl.E4M3], ids=["bf16", "fp8"])
+@pytest.mark.parametrize("ring", [0, 80])
+def test_window_decode_plan_starts_at_any_key(oracle_lib, kvdt, ring):
+    """Single-row trees: the decode kernel applies no window mask, the plan starts each tile at the
+    row's first visible key - here at every alignment modulo 16 - and splits the rest."""
+    Ps = [1000 + i for i in range(17)] + [30, 1023, 1024, 1025, 5]
+    window = 1024 if ring else 777
+    bt = 16
+    if ring:                                            # a ring must hold the window
+        assert ring * bt >= window + bt
+    w = wl.make_window_pass("windec", 24, [(P, 1) for P in Ps], 32, 4, 128, bt, wl.BF16, window, ring=ring, scale=128 ** -0.5,
+                            kv_dtype=kvdt)
+    win = w.extra["window"]
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=256, rows=8, window=window, pos=win["pos"])
+    starts = {int(t["k0"]) % 16 for t in plan.tiles}
+    assert len(starts) >= 12
+    assert plan.n_parts > 0
+    _check(oracle_lib, w, plan, "decode_gqa")
+
+
+def test_window_needs_positions():
+    w = wl.make_window_pass("winv", 25, [(100, 4)], 8, 2, 128, 16, wl.BF16, 32)
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=0, rows=8, window=32, pos=w.extra["window"]["pos"])
+    op = host.AttnOp.for_workload(w, plan.tile_rows)
+    try:
+        dp = op.upload(w, plan)
+        a = op.make_args(dp)
+        a.pos = None
+        with pytest.raises(capi.EspError) as e:
+            op.forward(dp, a)
+        assert e.value.code == capi.ESP_ERR_INVALID
+    finally:
+        op.close()

@@ -136,3 +136,33 @@ def test_plan_errors():
     tiles = (capi.Tile * 4)()
     rc = lib.esp_attn_plan(trees.ctypes.data_as(C.POINTER(capi.Tree)), 1, 2, C.byref(opts), tiles, 4, None, 0, C.byref(nt), C.byref(nj), C.byref(np_))
     assert rc == capi.ESP_ERR_CAPACITY and nt.value == 32
+
+
+def test_window_planner_matches_restatement(oracle_lib):
+    """esp_attn_plan_window against the restatement of g4_plan_tiles with its window branch
+    (src/model/impl/gemma.h:77-116): same tiles (k0 at the first visible key, first batch key in pad0),
+    jobs and tile height, bit for bit, for split and unsplit budgets."""
+    from espetero_b200 import host
+    rng = np.random.default_rng(9)
+    for case in range(40):
+        n_trees = int(rng.integers(1, 6))
+        trees = np.zeros(n_trees, dtype=TREE_DT)
+        base = tab = 0
+        for i in range(n_trees):
+            P, M = int(rng.integers(0, 5000)), int(rng.integers(1, 40))
+            trees[i] = (base, P, tab, M)
+            base += M
+            tab += (P + 15) // 16
+        pos = np.zeros((base, 4), dtype=np.int32)
+        for t in trees:
+            b0, P, M = int(t["base"]), int(t["P"]), int(t["M"])
+            pos[b0:b0 + M, 0] = P + np.sort(rng.integers(0, M, size=M))     # tree rows: repeated depths
+        window = int(rng.choice([0, 1, 17, 512, 1024, 100000]))
+        groups = int(rng.choice([1, 2, 8, 32]))
+        split = int(rng.choice([0, 256, 512]))
+        rows = int(rng.choice([8, 16]))
+        plan = host.plan_window(trees, groups, split, rows, window, pos)
+        tiles, jobs, n_parts, plan_rows = oracle_lib.g4_plan_tiles(trees, groups, split, rows, window, pos)
+        assert plan.tile_rows == plan_rows and plan.n_parts == n_parts
+        assert plan.tiles.tobytes() == tiles.tobytes(), case
+        assert plan.jobs.tobytes() == jobs.tobytes(), case
