@@ -66,7 +66,8 @@ class Args(C.Structure):
                 ("tiles_host", C.c_void_p), ("trees_host", C.c_void_p), ("jobs_host", C.c_void_p),
                 ("n_tiles", C.c_int32), ("n_trees", C.c_int32), ("n_jobs", C.c_int32), ("n_rows", C.c_int32),
                 ("n_blocks", C.c_int32), ("n_block_entries", C.c_int32), ("n_parts", C.c_int32), ("reserved", C.c_int32),
-                ("p", Params)]
+                ("p", Params), ("pos", C.c_void_p), ("window", C.c_int32), ("ring", C.c_int32), ("bidi", C.c_int32),
+                ("reserved2", C.c_int32)]
 
 
 class PrepParams(C.Structure):

@@ -66,3 +66,23 @@ def test_host_op_refuses_to_run_on_cpu():
     from espetero_b200 import host
     with pytest.raises(RuntimeError, match="no CPU implementation"):
         host.AttnOp(8, 2, 128, 16, capi.ESP_F16, capi.ESP_F16, 0.1)
+
+
+def test_ctypes_structs_have_the_headers_layout(tmp_path):
+    """sizeof of every struct the header declares, as gcc sees it, against the ctypes mirrors (a field
+    missing from a mirror would otherwise be accepted silently as a Python attribute)."""
+    import ctypes as C
+    import subprocess
+    pairs = {"esp_attn_params": capi.Params, "esp_attn_tree": capi.Tree, "esp_attn_tile": capi.Tile, "esp_attn_combine": capi.Combine,
+             "esp_kv_save_entry": capi.KVSaveEntry, "esp_attn_shape": capi.Shape, "esp_plan_opts": capi.PlanOpts,
+             "esp_attn_args": capi.Args, "esp_attn_exchange": capi.Exchange, "esp_attn_prep_params": capi.PrepParams,
+             "esp_tree_spec": capi.TreeSpec}
+    src = tmp_path / "sizes.c"
+    body = "".join(f'  printf("{n} %zu\\n", sizeof({n}));\n' for n in pairs)
+    src.write_text(f'#include <stdio.h>\n#include "espetero_attn.h"\nint main(void) {{\n{body}  return 0;\n}}\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c99", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    sizes = dict(line.split() for line in out.strip().splitlines())
+    for name, mirror in pairs.items():
+        assert int(sizes[name]) == C.sizeof(mirror), name
