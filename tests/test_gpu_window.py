@@ -80,7 +80,7 @@ def test_window_decode_plan_starts_at_any_key(oracle_lib, kvdt, ring):
     """Single-row trees: the decode kernel applies no window mask, the plan starts each tile at the
     row's first visible key - here at every alignment modulo 16 - and splits the rest."""
     Ps = [1000 + i for i in range(17)] + [30, 1023, 1024, 1025, 5]
-    window = 1024 if ring else 777
+    window = 777
     bt = 16
     if ring:                                            # a ring must hold the window
         assert ring * bt >= window + bt
