@@ -27,7 +27,32 @@ CASES = {
     "verify_tree16": lambda: wl.make_pass("g_c4", 0xA4, [(256, 16), (100, 16)], 16, 2, 128, 16, wl.BF16, mask="tree"),
     "prefill_causal": lambda: wl.make_pass("g_c3", 0xA3, [(0, 150), (0, 129)], 8, 2, 128, 16, wl.BF16),
     "forest_gate_f16": lambda: wl.make_pass("g_forest", 0xA6, [(40, 20), (0, 9)], 8, 2, 128, 16, wl.F16, mask="forest", gate=True),
+    "window_ring_bidi": lambda: wl.make_window_pass("g_win", 0xA7, [(300, 24), (90, 10)], 8, 2, 256, 16, wl.BF16, 128, ring=24,
+                                                    images={0: (4, 15)}, scale=1.0 / 16),
 }
+
+
+def prep_case():
+    """Inputs of the attn_prep fixture: the gate-interleaved 256-dim layout of kernels/40_attention.metal:23-102."""
+    rng = np.random.default_rng(0xA8)
+    H, Hkv, HD, rot_half, rows = 4, 2, 256, 32, 6
+    k_off = 2 * H * HD
+    v_off = k_off + Hkv * HD
+    ld = v_off + Hkv * HD
+    X = rng.standard_normal((rows, ld)).astype(np.float32)
+    qn, kn = rng.uniform(0.5, 1.5, HD).astype(np.float32), rng.uniform(0.5, 1.5, HD).astype(np.float32)
+    inv_freq = (1e6 ** (-np.arange(rot_half) / rot_half)).astype(np.float32)
+    sel = (np.arange(rot_half) * 3 // rot_half).astype(np.int32)
+    pos = rng.integers(0, 100000, size=(rows, 4)).astype(np.int32)
+    pp = oracle.PrepParams(H, Hkv, ld, 0, 2 * HD, k_off, v_off, H * HD, Hkv * HD, rot_half, 1e-6, 1.0, 16, 0, 0)
+    return dict(H=H, Hkv=Hkv, HD=HD, rows=rows, X=X, qn_w=qn, kn_w=kn, inv_freq=inv_freq, sel=sel, pos=pos, pp=pp)
+
+
+def build_prep():
+    c = prep_case()
+    Q, K, V = oracle.attn_prep_f64(c["X"], c["qn_w"], c["kn_w"], c["pos"], c["inv_freq"], c["sel"], c["rows"], c["HD"], c["pp"])
+    digest = np.array([float(np.abs(c["X"]).sum()), float(c["pos"].sum())])
+    return dict(Q=Q, K=K, V=V, input_digest=digest)
 
 
 def build(name):
@@ -46,3 +71,5 @@ if __name__ == "__main__":
     for name in CASES:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **build(name))
         print("wrote", name)
+    np.savez_compressed(os.path.join(HERE, "attn_prep_gated256.npz"), **build_prep())
+    print("wrote attn_prep_gated256")

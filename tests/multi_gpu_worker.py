@@ -68,10 +68,36 @@ def main():
     op.check_status()
     util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w)
     dist.barrier()
+    # A rank that sits a step out (decided on the host: it simply does not launch): the others'
+    # wait runs out after 100 ms, they leave O alone and report it; the silent rank reports nothing.
+    # The next step, with every rank back, is correct again on the same buffers and contexts.
+    xch.next_epoch()
+    silent = world - 1
+    dp.O.fill_(0x3C00)
+    op.forward(dp)
+    if rank != silent:
+        op.exchange_parts(dp, dp.parts, jobs_dev, len(jobs), xch, parts_max=n_parts, wait_ms=100)
+        try:
+            op.check_status()
+            raise AssertionError("the wait for a silent peer did not report")
+        except capi.EspError as e:
+            assert "never published" in str(e), str(e)
+        assert bool((dp.O == 0x3C00).all()), "O was written although a peer was missing"
+    else:
+        op.check_status()
+    torch.cuda.synchronize()
+    dist.barrier()   # the ranks learn of each other on the host before the next launch
+    xch.next_epoch()
+    dp.O.zero_()
+    op.forward(dp)
+    op.exchange_parts(dp, dp.parts, jobs_dev, len(jobs), xch, parts_max=n_parts)
+    op.check_status()
+    util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w)
+    dist.barrier()
     xch.close()
     op.close()
     if rank == 0:
-        print(f"MULTI_GPU_OK world={world} fp8={fp8} launches>0", flush=True)
+        print(f"MULTI_GPU_OK world={world} fp8={fp8} silent-peer step reported and recovered", flush=True)
     dist.destroy_process_group()
 
 
