@@ -54,40 +54,59 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepAr
     }
   }
 
-  // The next head's elements are requested before this head's arithmetic starts: two loads in
-  // flight per warp keep enough bytes on the way to hide the memory latency with 128-dim heads.
+  // The elements of the next PF heads are requested before this head's arithmetic starts: about
+  // 2 KB in flight per warp hide the memory latency at the occupancy the registers allow.
+  constexpr int PF = NPT == 4 ? 4 : 1;
   auto src_of = [&](int head) {
     const bool q = head < p.H;
     const int hh = q ? head : head - p.H;
     return a.X + row * p.ld + (q ? p.q_off + size_t(hh) * p.q_stride : p.k_off + size_t(hh) * HD) + lane * NPT;
   };
-  float4 nxt[NPT / 4];
+  float4 nxt[PF][NPT / 4];
 #pragma unroll
-  for (int i = 0; i < NPT / 4; ++i) nxt[i] = reinterpret_cast<const float4*>(src_of(head_first))[i];
+  for (int k = 0; k < PF; ++k)
+    if (head_first + k < head_end) {
+#pragma unroll
+      for (int i = 0; i < NPT / 4; ++i) nxt[k][i] = reinterpret_cast<const float4*>(src_of(head_first + k))[i];
+    }
+
+  // The norm weights are the same for every query head (and for every key head): in registers, once.
+  float wq[NPT], wk[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; i += 4) {
+    const float4 a4 = *reinterpret_cast<const float4*>(a.qn_w + lane * NPT + i);
+    const float4 b4 = *reinterpret_cast<const float4*>(a.kn_w + lane * NPT + i);
+    wq[i] = a4.x, wq[i + 1] = a4.y, wq[i + 2] = a4.z, wq[i + 3] = a4.w;
+    wk[i] = b4.x, wk[i + 1] = b4.y, wk[i + 2] = b4.z, wk[i + 3] = b4.w;
+  }
 
   for (int head = head_first; head < head_end; ++head) {
   const bool is_q = head < p.H;
   const int h = is_q ? head : head - p.H;
-  const float* nw = (is_q ? a.qn_w : a.kn_w) + lane * NPT;
 
   float x[NPT], wv[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; i += 4) {
-    const float4 v = nxt[i / 4];
-    const float4 w = *reinterpret_cast<const float4*>(nw + i);
+    const float4 v = nxt[0][i / 4];
     x[i] = v.x, x[i + 1] = v.y, x[i + 2] = v.z, x[i + 3] = v.w;
-    wv[i] = w.x, wv[i + 1] = w.y, wv[i + 2] = w.z, wv[i + 3] = w.w;
   }
-  if (head + 1 < head_end) {
 #pragma unroll
-    for (int i = 0; i < NPT / 4; ++i) nxt[i] = reinterpret_cast<const float4*>(src_of(head + 1))[i];
+  for (int i = 0; i < NPT; ++i) wv[i] = is_q ? wq[i] : wk[i];
+#pragma unroll
+  for (int k = 0; k + 1 < PF; ++k) {
+#pragma unroll
+    for (int i = 0; i < NPT / 4; ++i) nxt[k][i] = nxt[k + 1][i];
+  }
+  if (head + PF < head_end) {
+#pragma unroll
+    for (int i = 0; i < NPT / 4; ++i) nxt[PF - 1][i] = reinterpret_cast<const float4*>(src_of(head + PF))[i];
   }
   float ss = 0.0f;
 #pragma unroll
   for (int i = 0; i < NPT; ++i) ss = fmaf(x[i], x[i], ss);
 #pragma unroll
   for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float inv = 1.0f / sqrtf(ss / float(HD) + p.eps);
+  const float inv = rsqrtf(fmaf(ss, 1.0f / float(HD), p.eps));  // the reference's rsqrt (40_attention.metal:64)
 #pragma unroll
   for (int i = 0; i < NPT; ++i) x[i] = x[i] * inv * wv[i];
 
