@@ -382,7 +382,8 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
       cached += t.k1 - t.k0;
       if (t.last) batch += a.trees_host[t.tree].M;
     }
-    const bool stream_hbm = c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch);
+    // 256-dim heads run on flash_umma_pair only (one CTA per SM there: its tiles take the whole SM).
+    const bool stream_hbm = s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch));
     if (stream_hbm) {
       c->last_kernel = "flash_umma";
       e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees,

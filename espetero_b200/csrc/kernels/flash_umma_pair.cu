@@ -40,20 +40,22 @@ namespace {
 
 constexpr int BM = 128;  // (row, head) pairs per CTA
 constexpr int BN = 64;   // keys per block
-constexpr int HD = 128;  // head dim of this kernel
-constexpr int Q_BYTES = BM * HD * 2;        // [2 halves of 64 dims][128 rows][128 B]
-constexpr int KV_TILE = BN * HD * 2;        // [2 halves][64 rows][128 B]
-constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim halves of the Q tile
+// The head dim is a template parameter (128: two CTAs per SM; 256: the whole SM for one CTA). Tiles
+// are stored as HD / 64 chunks of 64 dims, each [rows][128 B] with the 128-byte swizzle.
+constexpr int q_bytes(int hd) { return BM * hd * 2; }
+constexpr int kv_tile(int hd) { return BN * hd * 2; }
+constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim chunks of the Q tile
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
 // Ring depths come in two flavours: (3, 2) lets two CTAs share an SM (passes whose keys sit in L2:
 // prefill), (6, 6) takes the whole SM for one CTA and keeps ~160 KB of K/V in flight (passes
 // that stream their keys from HBM: verify over a long cached prefix).
 constexpr int kMaxStages = 6;
-constexpr int tiles_bytes(int ks, int vs) { return Q_BYTES + (ks + vs) * KV_TILE; }
-constexpr int smem_bytes(int ks, int vs) { return tiles_bytes(ks, vs) + 384; }  // + mbarriers; no static shared memory
-constexpr uint32_t TMEM_COLS = 256;
+constexpr int tiles_bytes(int hd, int ks, int vs) { return q_bytes(hd) + (ks + vs) * kv_tile(hd); }
+constexpr int smem_bytes(int hd, int ks, int vs) { return tiles_bytes(hd, ks, vs) + 384; }  // + mbarriers; no static shared memory
 // Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
-// S buffer as 16-bit pairs, once the thread holds its scores in registers), O: 128 fp32 columns.
+// S buffer as 16-bit pairs, once the thread holds its scores in registers), O: HD fp32 columns
+// (allocations are powers of two: 256 columns for 128-dim heads, 512 for 256-dim heads).
+constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 constexpr uint32_t COL_S = 0, COL_O = 128;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -80,8 +82,8 @@ struct Shared {
 };
 static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
 
-template <int QDT, int KS, int VS>
-__global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ? 2 : 1)
+template <int QDT, int HD, int KS, int VS>
+__global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 1024) ? 2 : 1)
     flash_umma_pair_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
@@ -89,7 +91,10 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
   // o_full: last P.V done
-  constexpr int TILES_BYTES = tiles_bytes(KS, VS);
+  constexpr int NCH = HD / 64;  // 64-dim chunks of a row
+  constexpr int Q_BYTES = q_bytes(HD), KV_TILE = kv_tile(HD);
+  constexpr uint32_t TMEM_COLS = tmem_cols(HD);
+  constexpr int TILES_BYTES = tiles_bytes(HD, KS, VS);
   Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
   uint64_t* k_full = sh.k_full;
   uint64_t* k_empty = sh.k_empty;
@@ -162,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
     // Q row of this thread into the K-major swizzled tile
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD);
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
+    for (int c = 0; c < NCH; ++c)
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         *reinterpret_cast<uint4*>(q_sm + c * HALF_Q + tid * 128 + ((i ^ (tid & 7)) << 4)) = src[c * 8 + i];
@@ -275,9 +280,9 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
         } else {
           const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
           const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
-          mbar_arrive_expect_tx(&full[stage], 4096);
-          tma_load_3d(dst, m, &full[stage], 0, y, kvh * 2);
-          tma_load_3d(dst + HALF_KV, m, &full[stage], 0, y, kvh * 2 + 1);
+          mbar_arrive_expect_tx(&full[stage], 2048 * NCH);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c);
         }
         if (lane == 0) stamp(b, is_v ? 7 : 6);
         cur = nxt;
@@ -425,9 +430,9 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
         // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
         const int vst = b % VS;
         wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
-        const int n = (BN - n_valid) * 16;  // 16-byte chunks: 2 halves x 8 per row
+        const int n = (BN - n_valid) * 8 * NCH;  // 16-byte pieces: NCH chunks x 8 per row
         for (int i = tid; i < n; i += BM) {
-          const int r = n_valid + i / 16, c = i % 16;
+          const int r = n_valid + i / (8 * NCH), c = i % (8 * NCH);
           *reinterpret_cast<uint4*>(v_sm + vst * KV_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
@@ -500,25 +505,37 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(KS, VS) <= 114 * 1024) ?
 
 }  // namespace
 
-template <int QDT, int KS, int VS>
+template <int QDT, int HD, int KS, int VS>
 cudaError_t setup_variant() {
-  return cudaFuncSetAttribute(flash_umma_pair_kernel<QDT, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(KS, VS));
+  return cudaFuncSetAttribute(flash_umma_pair_kernel<QDT, HD, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(HD, KS, VS));
 }
 
 cudaError_t flash_umma_pair_setup() {
-  const cudaError_t e = setup_variant<ESP_F16, 3, 2>();
-  if (e != cudaSuccess) return e;
-  return setup_variant<ESP_BF16, 3, 2>();
+  cudaError_t e = setup_variant<ESP_F16, 128, 3, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 128, 3, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 2, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 2, 2>();
+  return e;
 }
 
+// 128-dim heads: rings of 3 K and 2 V tiles, two CTAs per SM. 256-dim heads (the head dim of
+// kernels/40_attention.metal's flash_attention): a 64 KB Q tile, rings of 2 + 2 tiles of 32 KB, 384
+// tensor-memory columns: one CTA per SM.
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
-  constexpr int smem = smem_bytes(3, 2);
-  if (a.q_dtype == ESP_F16) flash_umma_pair_kernel<ESP_F16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
-  else flash_umma_pair_kernel<ESP_BF16, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  const bool f16 = a.q_dtype == ESP_F16;
+  if (a.HD == 128) {
+    constexpr int smem = smem_bytes(128, 3, 2);
+    if (f16) flash_umma_pair_kernel<ESP_F16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_pair_kernel<ESP_BF16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  } else {
+    constexpr int smem = smem_bytes(256, 2, 2);
+    if (f16) flash_umma_pair_kernel<ESP_F16, 256, 2, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_pair_kernel<ESP_BF16, 256, 2, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  }
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

@@ -210,8 +210,8 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
 cudaError_t flash_umma_pair_setup();
-// Shapes the tcgen05 kernel covers: HD 128, 16-bit pool of the pass's type, tiles of 16..128 rows
-// whose 128 / tile_rows heads belong to one kv head.
+// Shapes the tcgen05 kernels cover: HD 128 (both kernels) or 256 (flash_umma_pair), 16-bit pool of the
+// pass's type, tiles of 16..128 rows whose 128 / tile_rows heads belong to one kv head.
 bool flash_umma_supports(int32_t HD, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype);
 cudaError_t flash_umma_setup();
 

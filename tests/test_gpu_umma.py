@@ -153,3 +153,24 @@ def test_fused_merge_matches_separate_combine(oracle_lib, gate):
     assert np.abs(outs[1][1] - outs[0][1]).max() < 1e-5
     util.check_output(outs[1][0], ref, w)
     assert np.abs(outs[1][1] - lse_ref).max() < 2e-3
+
+
+@pytest.mark.parametrize("case", ["prefill", "verify", "chunked_gate_f16", "forest"])
+def test_hd256_on_tensor_cores(oracle_lib, case):
+    """256-dim heads (the head dim of the reference's flash_attention, kernels/40_attention.metal:156)
+    on the tcgen05 kernel: one CTA per SM, four 64-dim chunks per row, a 256-column accumulator."""
+    if case == "prefill":
+        w, tr = wl.make_pass("hd256_prefill", 91, [(0, 300), (0, 77)], 8, 2, 256, 16, wl.BF16), 128
+    elif case == "verify":
+        w, tr = wl.make_pass("hd256_verify", 92, [(1000, 16), (333, 16), (64, 9)], 32, 4, 256, 16, wl.BF16, mask="tree"), 16
+    elif case == "chunked_gate_f16":
+        w, tr = wl.make_pass("hd256_chunk", 93, [(500, 200)], 8, 2, 256, 16, wl.F16, gate=True), 128
+    else:
+        w, tr = wl.make_pass("hd256_forest", 94, [(70, 40), (0, 33)], 8, 2, 256, 16, wl.BF16, mask="forest"), 32
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    for groups in (8, 592):                                  # unsplit, and split with records + merge
+        O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=tr, split=1 << 20, groups=groups)
+        assert kernel == "flash_umma_pair"
+        util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}")
+        fin = np.isfinite(lse_ref)
+        assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
