@@ -260,6 +260,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
+    ap.add_argument("--fuse", type=int, default=-1, help="option fuse_combine of the library (0 off, 1 small passes, 2 always); -1: its default")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -288,6 +289,8 @@ def main():
     if not split_kv:
         w = build_workload(args.workload, rank, args.small, world)
         op = host.AttnOp.for_workload(w, tile_rows, local)
+        if args.fuse >= 0:
+            op.set_option("fuse_combine", args.fuse)
         plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
         dp = op.upload(w, plan)
         layers = LayerCycle(op, dp, w)

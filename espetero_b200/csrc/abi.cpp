@@ -368,8 +368,10 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     // jobs (ESP_PLAN_B200) are merged inside the kernel; on larger passes the serial merge in the
     // last CTA of a long job costs more than the combine kernel's launch (measured on both).
     k.jobs = a.jobs;
-    k.fuse = c->opt_fuse_combine && esp::decode_fuse_small(a.n_tiles, s.Hkv) && a.n_jobs > 0 && a.jobs &&
-             esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
+    // (option 2 merges in the kernel whatever the size; the records of a kv head's G heads must be a
+    // multiple of 16 bytes for the bulk copies: G even)
+    k.fuse = c->opt_fuse_combine && (c->opt_fuse_combine == 2 || esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs)) && c->G % 2 == 0 &&
+             a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
     merged = k.fuse != 0;
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
   } else if (umma) {

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[NW][STAGES];
   __shared__ int fix_info[4];  // fused merge: first record and record count of the tile's job, the ticket drawn
+  __shared__ uint64_t fix_bar;  // fused merge: completion of the records' bulk copies
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   const bool fused = a.fuse && tile.part >= 0;
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&pool_map);
+    mbar_init(&fix_bar, 1);  // made visible by the fence and barrier below
     if (fused) {  // needed only at the very end: the load's latency hides behind the whole stream
       const esp_attn_combine jb = a.jobs[tile.pad1 - 1];
       fix_info[0] = jb.part0, fix_info[1] = jb.nparts;
@@ -418,53 +420,72 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     __syncthreads();
     if (fix_info[2] != fix_info[1] - 1) return;
     __threadfence();
+    // The job's records of this kv head come into shared memory by bulk copies (the rings are idle):
+    // the G records of a part are contiguous, as many parts per round as fit. Then every thread folds
+    // its 4-dim items over the parts in record order with a running maximum.
     const int part0 = fix_info[0], n = fix_info[1];
-    const size_t stride = size_t(p.Hkv) * a.tile_rows * G * (HD + 2);
-    constexpr int DPT = HD / 32;  // this lane's dims: [DPT * lane, DPT * lane + DPT), read as float2
-    for (int hg = warp; hg < G; hg += NW) {
-      const int h = kvh * G + hg;
-      const float* base = a.parts + ((size_t(part0) * p.Hkv + kvh) * a.tile_rows * G + hg) * (HD + 2);
-      float M = -INFINITY, L = 0.0f, acc[DPT];
+    const size_t part_stride = size_t(p.Hkv) * a.tile_rows * G * (HD + 2);
+    const uint32_t rec_bytes = uint32_t(G) * (HD + 2) * 4;
+    const float* base = a.parts + (size_t(part0) * p.Hkv + kvh) * a.tile_rows * G * (HD + 2);
+    float* stage = reinterpret_cast<float*>(smem);
+    const int per_round = max(1, min(n, int((NW * C::WARP_BYTES) / rec_bytes)));
+    constexpr int MAXI = HD / 64;              // items per thread at most: G * HD / 4 items over 128 threads
+    const int n_items = G * HD / 4;
+    float st_m[MAXI], st_l[MAXI];
+    float4 st_acc[MAXI];
 #pragma unroll
-      for (int i = 0; i < DPT; ++i) acc[i] = 0.0f;
-      for (int s0 = 0; s0 < n; s0 += 4) {
-        float2 ml[4], ov[4][DPT / 2];
+    for (int k = 0; k < MAXI; ++k) st_m[k] = -INFINITY, st_l[k] = 0.0f, st_acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint32_t par = 0;
+    for (int s0 = 0; s0 < n; s0 += per_round) {
+      const int cnt = min(per_round, n - s0);
+      __syncthreads();  // the previous round's records have been consumed
+      if (threadIdx.x == 0) {
+        asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
+        mbar_arrive_expect_tx(&fix_bar, uint32_t(cnt) * rec_bytes);
+        for (int s = 0; s < cnt; ++s)
+          bulk_load(reinterpret_cast<uint8_t*>(stage) + size_t(s) * rec_bytes, base + size_t(s0 + s) * part_stride, rec_bytes, &fix_bar);
+      }
+      if (!mbar_wait(&fix_bar, par)) {
+        if (threadIdx.x == 0) atomicExch(a.status, kStatusTmaTimeout);
+        return;
+      }
+      par ^= 1;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // four records in flight
-          const float* rp = base + size_t(min(s0 + k, n - 1)) * stride;
-          ml[k] = __ldcg(reinterpret_cast<const float2*>(rp + HD));
-#pragma unroll
-          for (int i = 0; i < DPT / 2; ++i) ov[k][i] = __ldcg(reinterpret_cast<const float2*>(rp + DPT * lane + 2 * i));
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (s0 + k >= n || ml[k].x == -INFINITY) continue;  // past the end, or an empty record
-          if (ml[k].x > M) {                                   // rescale what has been summed so far
-            const float f = __expf(M - ml[k].x);               // 0 for the first record
-            L *= f;
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) acc[i] *= f;
-            M = ml[k].x;
+      for (int k = 0; k < MAXI; ++k) {
+        const int item = threadIdx.x + k * (NW * 32);
+        if (item >= n_items) break;
+        const int hg = item / (HD / 4), c4 = item % (HD / 4);
+        const float* rec = stage + size_t(hg) * (HD + 2);
+        for (int s = 0; s < cnt; ++s, rec += size_t(G) * (HD + 2)) {
+          const float m_s = rec[HD];
+          if (m_s == -INFINITY) continue;          // an empty record adds nothing
+          if (m_s > st_m[k]) {                      // rescale what has been summed so far (factor 0 the first time)
+            const float f = __expf(st_m[k] - m_s);
+            st_l[k] *= f, st_acc[k].x *= f, st_acc[k].y *= f, st_acc[k].z *= f, st_acc[k].w *= f;
+            st_m[k] = m_s;
           }
-          const float w = __expf(ml[k].x - M);
-          L = fmaf(w, ml[k].y, L);
-#pragma unroll
-          for (int i = 0; i < DPT / 2; ++i) acc[2 * i] = fmaf(w, ov[k][i].x, acc[2 * i]), acc[2 * i + 1] = fmaf(w, ov[k][i].y, acc[2 * i + 1]);
+          const float w = __expf(m_s - st_m[k]);
+          const float2 o01 = *reinterpret_cast<const float2*>(rec + 4 * c4), o23 = *reinterpret_cast<const float2*>(rec + 4 * c4 + 2);
+          st_l[k] = fmaf(w, rec[HD + 1], st_l[k]);
+          st_acc[k].x = fmaf(w, o01.x, st_acc[k].x), st_acc[k].y = fmaf(w, o01.y, st_acc[k].y);
+          st_acc[k].z = fmaf(w, o23.x, st_acc[k].z), st_acc[k].w = fmaf(w, o23.y, st_acc[k].w);
         }
       }
-      const float inv_l = L > 0.0f ? 1.0f / L : 0.0f;
-      typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD + DPT * lane;
-      const float* gp = a.X ? a.X + size_t(row) * p.g_ld + size_t(h) * 2 * HD + HD + DPT * lane : nullptr;
-      uint32_t packed[DPT / 2];
+    }
 #pragma unroll
-      for (int i = 0; i < DPT / 2; ++i) {
-        float v0 = acc[2 * i] * inv_l, v1 = acc[2 * i + 1] * inv_l;
-        if (gp) v0 *= sigmoid_gate(gp[2 * i]), v1 *= sigmoid_gate(gp[2 * i + 1]);
-        packed[i] = QE::pack2(v0, v1);
+    for (int k = 0; k < MAXI; ++k) {
+      const int item = threadIdx.x + k * (NW * 32);
+      if (item >= n_items) break;
+      const int hg = item / (HD / 4), c4 = item % (HD / 4), h = kvh * G + hg;
+      const float inv_l = st_l[k] > 0.0f ? 1.0f / st_l[k] : 0.0f;
+      float v[4] = {st_acc[k].x * inv_l, st_acc[k].y * inv_l, st_acc[k].z * inv_l, st_acc[k].w * inv_l};
+      if (a.X) {
+        const float4 gt = *reinterpret_cast<const float4*>(a.X + size_t(row) * p.g_ld + size_t(h) * 2 * HD + HD + 4 * c4);
+        v[0] *= sigmoid_gate(gt.x), v[1] *= sigmoid_gate(gt.y), v[2] *= sigmoid_gate(gt.z), v[3] *= sigmoid_gate(gt.w);
       }
-      if constexpr (DPT == 4) *reinterpret_cast<uint2*>(op) = make_uint2(packed[0], packed[1]);
-      else *reinterpret_cast<uint4*>(op) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      if (a.lse && lane == 0) a.lse[size_t(row) * p.H + h] = L > 0.0f ? M + __logf(L) : -INFINITY;
+      *reinterpret_cast<uint2*>(static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD + 4 * c4) =
+          make_uint2(QE::pack2(v[0], v[1]), QE::pack2(v[2], v[3]));
+      if (a.lse && c4 == 0) a.lse[size_t(row) * p.H + h] = st_l[k] > 0.0f ? st_m[k] + __logf(st_l[k]) : -INFINITY;
     }
   }
 }

@@ -138,8 +138,14 @@ inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_
   return claimed == records;
 }
 
-// Decode passes small enough for the in-kernel merge to pay: at most one CTA per SM of a B200.
-inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv) { return int64_t(n_tiles) * Hkv <= 148; }
+// Decode passes for which the in-kernel merge pays: small ones (at most one CTA per SM of a B200:
+// launch latencies dominate), and passes with many jobs, whose merges happen while other CTAs still
+// stream (measured on the batched decode: -1.8 us per step). A pass with a few long jobs that all end
+// together (one 131072-token sequence: 8 merges of 37 records) is faster with the combine kernel's
+// parallelism (+7 us when merged in the kernel).
+inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv, int32_t n_jobs) {
+  return int64_t(n_tiles) * Hkv <= 148 || int64_t(n_jobs) * Hkv >= 32;
+}
 
 // Record slices per head for the combine kernel: a slice folds up to eight records per round trip
 // to L2, so eight records per slice at most where the CTA allows it; at least one warp per head, at
