@@ -364,9 +364,8 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   if (decode) {
     if (int rc = pool_tensor_map(c, a)) return rc;
     c->last_kernel = "decode_gqa";
-    // Small passes (at most one CTA per SM: launch latencies dominate) whose split tiles name their
-    // jobs (ESP_PLAN_B200) are merged inside the kernel; on larger passes the serial merge in the
-    // last CTA of a long job costs more than the combine kernel's launch (measured on both).
+    // Plans whose split tiles name their jobs (ESP_PLAN_B200) can be merged inside the kernel; whether
+    // that pays depends on the pass (decode_fuse_small: small passes and passes with many jobs).
     k.jobs = a.jobs;
     // (option 2 merges in the kernel whatever the size; the records of a kv head's G heads must be a
     // multiple of 16 bytes for the bulk copies: G even)
