@@ -67,7 +67,7 @@ class Args(C.Structure):
                 ("n_tiles", C.c_int32), ("n_trees", C.c_int32), ("n_jobs", C.c_int32), ("n_rows", C.c_int32),
                 ("n_blocks", C.c_int32), ("n_block_entries", C.c_int32), ("n_parts", C.c_int32), ("reserved", C.c_int32),
                 ("p", Params), ("pos", C.c_void_p), ("window", C.c_int32), ("ring", C.c_int32), ("bidi", C.c_int32),
-                ("reserved2", C.c_int32)]
+                ("reserved2", C.c_int32), ("dequant_scratch", C.c_void_p), ("dequant_scratch_bytes", C.c_uint64)]
 
 
 class PrepParams(C.Structure):
@@ -98,6 +98,7 @@ PROTOTYPES = {
     "esp_attn_plan": (C.c_int, [C.POINTER(Tree), C.c_int32, C.c_int32, C.POINTER(PlanOpts), C.POINTER(Tile), C.c_int32,
                                 C.POINTER(Combine), C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "esp_attn_parts_floats": (C.c_size_t, [C.POINTER(Shape), C.c_int32]),
+    "esp_attn_dequant_scratch_bytes": (C.c_size_t, [C.POINTER(Shape), C.c_int32]),
     "esp_attn_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Args)]),
     "esp_attn_combine_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.POINTER(Params), C.c_void_p, C.c_int32]),

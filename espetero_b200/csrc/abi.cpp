@@ -354,10 +354,28 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   // (a tile may start at any key: sliding-window plans begin at the row's first visible key)
 
   // Multi-row tiles: the tcgen05 kernel when the shape fits it (128 (row, head) pairs per CTA).
-  bool umma = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr &&
-              esp::flash_umma_supports(s.HD, c->G, c->tile_rows, s.bt, s.q_dtype, s.kv_dtype) && a.p.kv_ld % 64 == 0 &&
-              a.p.kv_base % 64 == 0;
+  // Over an E4M3 pool they need the caller's scratch: the blocks of the pass are widened to the
+  // 16-bit type first (one more pass over the keys, still far faster than the CUDA-core kernel).
+  const bool fp8_pool = s.kv_dtype == ESP_E4M3;
+  const size_t widened_pool_bytes = size_t(std::max(a.n_block_entries, 0)) * 2 * size_t(a.p.bt) * size_t(a.p.kv_ld) * 2;
+  const bool widen = fp8_pool && a.dequant_scratch != nullptr && a.n_block_entries > 0 && a.kv != nullptr && a.blocks != nullptr &&
+                     a.dequant_scratch_bytes >= widened_pool_bytes + ((size_t(a.n_block_entries) * 4 + 127) / 128) * 128 &&
+                     (reinterpret_cast<uintptr_t>(a.dequant_scratch) & 127) == 0 && a.p.kv_ld % 8 == 0 && a.p.kv_base % 8 == 0;
+  bool umma = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen) &&
+              esp::flash_umma_supports(s.HD, c->G, c->tile_rows, s.bt, s.q_dtype, fp8_pool ? s.q_dtype : s.kv_dtype) &&
+              a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+  esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
+  if (umma && fp8_pool) {
+    int32_t* identity = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.dequant_scratch) + widened_pool_bytes);
+    const cudaError_t de = esp::launch_kv_dequant(a.kv, a.kv_scales, a.blocks, a.n_block_entries, a.dequant_scratch, identity, a.p, s.HD,
+                                                  a.n_blocks, s.q_dtype, stream, &c->launches);
+    if (de != cudaSuccess) return cuda_fail(de, "kv_dequant");
+    widened.kv = a.dequant_scratch, widened.blocks = identity, widened.kv_scales = nullptr;
+    widened.n_blocks = a.n_block_entries, widened.p.kv_base = 0;
+    k.kv = widened.kv, k.blocks = widened.blocks, k.kv_scales = nullptr, k.kv_dtype = s.q_dtype;
+    k.n_blocks = widened.n_blocks, k.p.kv_base = 0;
+  }
 
   cudaError_t e;
   bool merged = false;  // the attention kernel merged the split-K records itself: no combine launch
@@ -374,7 +392,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     merged = k.fuse != 0;
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
   } else if (umma) {
-    if (int rc = umma_tensor_maps(c, a)) return rc;
+    if (int rc = umma_tensor_maps(c, widened)) return rc;
     // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
     // from HBM, the pass's own rows sit in L2), unless the "umma_kernel" option forces one.
     int64_t cached = 0, batch = 0;
@@ -422,6 +440,13 @@ int esp_attn_reduce_parts(esp_attn_ctx* c, void* stream, const float* parts, con
                           int32_t n_jobs, float* parts_out, int32_t out_part0) {
   if (!c || !parts_out || out_part0 < 0) return fail(ESP_ERR_INVALID, "esp_attn_reduce_parts: null or negative argument");
   return combine_impl(c, stream, parts, nullptr, nullptr, nullptr, p, jobs, n_jobs, c->tile_rows, 64, parts_out, out_part0);
+}
+
+size_t esp_attn_dequant_scratch_bytes(const esp_attn_shape* s, int32_t n_block_entries) {
+  if (!s || n_block_entries <= 0 || s->bt <= 0 || s->Hkv <= 0) return 0;
+  // the widened blocks (16-bit, K rows + V rows each) and an identity block table behind them, 128-byte granules
+  const size_t pool = size_t(n_block_entries) * 2 * size_t(s->bt) * size_t(s->Hkv) * size_t(s->HD) * 2;
+  return pool + ((size_t(n_block_entries) * 4 + 127) / 128) * 128;
 }
 
 size_t esp_attn_exchange_bytes(const esp_attn_shape* s, int32_t n_jobs, int32_t world) {

@@ -87,6 +87,34 @@ __global__ void kv_save_kernel_e4m3(const uint4* Kb, const uint4* Vb, uint8_t* k
   }
 }
 
+// One thread widens 8 codes: grid (8-element chunks of a block's K + V rows / 256, entries).
+template <int QDT>
+__global__ void kv_dequant_kernel(const uint8_t* kv, const float* kv_scales, const int32_t* blocks, uint4* out, int32_t* identity,
+                                  const esp_attn_params p, int HD, int n_blocks) {
+  using QE = Elem16<QDT>;
+  const int e = blockIdx.y;
+  const size_t row_chunks = size_t(p.kv_ld) / 8, half_chunks = size_t(p.bt) * row_chunks;  // K rows, then V rows
+  const size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c == 0) identity[e] = e;
+  if (c >= 2 * half_chunks) return;
+  const int b = blocks[e];
+  if (b < 0 || b >= n_blocks) return;  // an entry no tile reads (validated plans never name it)
+  const int which = c >= half_chunks;
+  const int col = int(c % row_chunks) * 8, kvh = col / HD;
+  const float sc = kv_scales[(size_t(b) * 2 + which) * p.Hkv + kvh];
+  const uint2 codes = *reinterpret_cast<const uint2*>(kv + p.kv_base + size_t(b) * 2 * half_chunks * 8 + c * 8);
+  const uint32_t w[2] = {codes.x, codes.y};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t pair = (w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+    const uint32_t h2 = e4m3x2_to_f16x2(uint16_t(pair));  // exact
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    o[i] = QE::pack2(f.x * sc, f.y * sc);
+  }
+  out[size_t(e) * 2 * half_chunks + c] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // grid (chunks of a block pair, pairs, layers); 16 bytes per thread.
 __global__ void kv_copy_blocks_kernel(uint4* kv, const int2* pairs, size_t blk2_chunks, size_t region_chunks) {
   const size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -137,6 +165,21 @@ cudaError_t launch_kv_save(const void* Kb, const void* Vb, void* kv, const float
     kv_save_kernel16<<<grid, block, 0, stream>>>(static_cast<const uint4*>(Kb), static_cast<const uint4*>(Vb),
                                                  static_cast<uint4*>(kv), entries, p);
   }
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) ++*launches;
+  return e;
+}
+
+cudaError_t launch_kv_dequant(const void* kv, const float* kv_scales, const int32_t* blocks, int32_t n_entries, void* out,
+                              int32_t* identity, const esp_attn_params& p, int32_t HD, int32_t n_blocks, int32_t q_dtype,
+                              cudaStream_t stream, uint64_t* launches) {
+  if (n_entries <= 0) return cudaSuccess;
+  const size_t chunks = 2 * size_t(p.bt) * size_t(p.kv_ld) / 8;
+  const dim3 grid(unsigned((chunks + 255) / 256), unsigned(n_entries));
+  if (q_dtype == ESP_F16)
+    kv_dequant_kernel<ESP_F16><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(kv), kv_scales, blocks, static_cast<uint4*>(out), identity, p, HD, n_blocks);
+  else
+    kv_dequant_kernel<ESP_BF16><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(kv), kv_scales, blocks, static_cast<uint4*>(out), identity, p, HD, n_blocks);
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

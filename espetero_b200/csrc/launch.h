@@ -202,6 +202,11 @@ int64_t exchange_grid_ctas(const CombineArgs& a);
 cudaError_t launch_kv_save(const void* Kb, const void* Vb, void* kv, const float* kv_scales, const esp_kv_save_entry* entries,
                            int32_t n, const esp_attn_params& p, int32_t HD, int32_t q_dtype, int32_t kv_dtype,
                            cudaStream_t stream, uint64_t* launches);
+// Widens the E4M3 blocks named by blocks[0 .. n_entries) of a layer region to the 16-bit type
+// (code * scale) into a compact pool: entry e becomes block e of `out`; `identity` receives 0 .. n_entries-1.
+cudaError_t launch_kv_dequant(const void* kv, const float* kv_scales, const int32_t* blocks, int32_t n_entries, void* out,
+                              int32_t* identity, const esp_attn_params& p, int32_t HD, int32_t n_blocks, int32_t q_dtype,
+                              cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pairs, const esp_attn_params& p,
                                   uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
                                   uint64_t* launches);

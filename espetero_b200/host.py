@@ -193,6 +193,10 @@ class AttnOp:
 
     def upload(self, w: Workload, plan: Plan | None = None) -> DevicePass:
         dp = DevicePass(w, self.device)
+        if w.kv_dtype == E4M3 and bool((w.trees["M"] > 1).any()):
+            # multi-row passes over an E4M3 pool: scratch for the widened blocks (tensor-core kernels)
+            n = int(self.lib.esp_attn_dequant_scratch_bytes(C.byref(self.shape), len(w.blocks)))
+            dp.scratch = torch.empty(max(n, 128), dtype=torch.uint8, device=self.device)
         if plan is not None:
             dp.set_plan(plan, self.parts_floats(plan.n_parts))
         return dp
@@ -212,6 +216,8 @@ class AttnOp:
         a.jobs_host = plan.jobs.ctypes.data if len(plan.jobs) else None
         a.n_tiles, a.n_trees, a.n_jobs, a.n_rows = len(plan.tiles), len(w.trees), len(plan.jobs), w.n_rows
         a.n_blocks, a.n_block_entries, a.n_parts = w.n_blocks, len(w.blocks), plan.n_parts
+        if getattr(dp, "scratch", None) is not None:
+            a.dequant_scratch, a.dequant_scratch_bytes = dp.scratch.data_ptr(), dp.scratch.numel()
         if dp.win:
             a.pos, a.window, a.ring, a.bidi = _ptr(dp.pos), dp.win["window"], dp.win["ring"], dp.win["bidi"]
         a.p = self.params(w)

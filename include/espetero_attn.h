@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define ESP_ATTN_ABI_VERSION 2
+#define ESP_ATTN_ABI_VERSION 3
 
 /* ---------------------------------------------------------------- status */
 typedef enum esp_status {
@@ -229,7 +229,18 @@ typedef struct esp_attn_args {
   int32_t bidi;            /* 1: rows of an image also see the image's later rows (desc.w = end of the row's
                               image, 0 outside images) */
   int32_t reserved2;
+  /* Optional scratch for multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys): with
+   * it the pass first widens the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into
+   * the scratch and runs the tensor-core kernels on that copy; without it (NULL) such passes run on
+   * the general kernel. Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
+  void* dequant_scratch;
+  uint64_t dequant_scratch_bytes;
 } esp_attn_args;
+
+/* Bytes of dequant_scratch for a pass whose block table has n_block_entries entries (pool rows of
+ * kv_ld = Hkv * HD elements; wider rows need n_block_entries * 4 * bt * kv_ld + 4 * n_block_entries
+ * rounded up to 128). */
+size_t esp_attn_dequant_scratch_bytes(const esp_attn_shape* shape, int32_t n_block_entries);
 
 /* Attention over the plan's tiles, then the combine jobs: the reference's
  * attention() lambda. stream is a cudaStream_t. */
