@@ -126,7 +126,8 @@ typedef struct esp_attn_ctx esp_attn_ctx;
 
 /* Create / destroy a context on `device`. Creation resolves the driver entry
  * point used to build tensor maps and raises the kernels' shared-memory limits;
- * it allocates one 4-byte device status word, freed by destroy. */
+ * it allocates one small device block (the status word and 4096 arrival counters of the in-kernel
+ * merge, 16.6 KB), freed by destroy. */
 int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape);
 int esp_attn_destroy(esp_attn_ctx* ctx);
 const char* esp_attn_last_error(void);
@@ -137,8 +138,9 @@ int esp_attn_abi_version(void);
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
  * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
  * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "fuse_combine"
- * (1: small passes whose split tiles name their combine job in pad1 merge their records inside
- * the attention kernel and launch no combine kernel; default 1), "trace_ctas" (see
+ * (passes whose split tiles name their combine job in pad1 can merge their records inside the
+ * attention kernel and launch no combine kernel: 0 never, 1 where it measured faster - small passes
+ * and decode passes with many jobs -, 2 whenever possible; default 1), "trace_ctas" (see
  * esp_attn_set_trace), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
