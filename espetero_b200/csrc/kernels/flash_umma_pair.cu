@@ -59,6 +59,9 @@ constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 constexpr uint32_t COL_S = 0, COL_O = 128;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
+// The n lowest bits set (n <= 0: none, n >= 64: all).
+__device__ __forceinline__ uint64_t low_bits64(int n) { return n <= 0 ? 0ull : (n >= 64 ? ~0ull : ((1ull << n) - 1ull)); }
+
 struct PageRef {  // where one 16-key page of a key block comes from
   int raw;        // block id as loaded from the page table (pool), or first row (Kb / Vb)
   int off;        // row inside the block (pool)
@@ -369,15 +372,19 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       if (tid == 0) stamp(b, 1);
       float mx = -INFINITY;
       if (need_mask) {
-        // diagonal, tail and tree blocks: visibility per (row, key)
+        // diagonal, tail and tree blocks: the visibility of this row's 64 columns as one bit mask
+        // (a few integer operations), then one select per score
+        uint64_t vm = low_bits64(n_valid);
+        if (!cached) {
+          if (use_anc) vm &= am >> (j0 & 63);  // one block, j0 = 0
+          else vm &= low_bits64(d.z - j0) | (low_bits64(rr - j0 + 1) & ~low_bits64(d.x - j0));  // j < d.z || d.x <= j <= rr
+        }
+        const uint32_t vw[2] = {uint32_t(vm), uint32_t(vm >> 32)};
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            const int col = 32 * h + c, j = j0 + col;
-            bool vis = col < n_valid;
-            if (!cached) vis = vis && (use_anc ? ((am >> (j & 63)) & 1ull) != 0 : ((j < d.z) || (j >= d.x && j <= rr)));
-            const float s = vis ? __uint_as_float(sr[h][c]) : -INFINITY;
+            const float s = ((vw[h] >> c) & 1u) ? __uint_as_float(sr[h][c]) : -INFINITY;
             sr[h][c] = __float_as_uint(s);
             mx = fmaxf(mx, s);
           }
