@@ -191,3 +191,26 @@ def test_decode_fused_merge_matches_combine_kernel(oracle_lib, shape):
     fa, fb = wl.from_bits16(outs[1][0], w.q_dtype), wl.from_bits16(outs[0][0], w.q_dtype)
     assert np.all(np.abs(fa - fb) <= 2.0 ** -7 * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30)
     assert np.abs(outs[1][1] - outs[0][1]).max() < 1e-5
+
+
+def test_in_kernel_merge_is_deterministic():
+    """A batched decode whose many jobs are merged inside the kernel by whichever CTA finishes a job
+    last: forty passes must give the same bits (no result may depend on that order) with one launch each."""
+    import torch
+    w = wl.config_c2(n_seqs=16, hi=8192)
+    op = host.AttnOp.for_workload(w, 8)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 2368, 8)
+        assert len(plan.jobs) * w.Hkv >= 32
+        dp = op.upload(w, plan)
+        op.forward(dp)
+        ref_O, ref_lse = dp.O.clone(), dp.lse.clone()
+        n0 = op.launch_count
+        for _ in range(40):
+            dp.O.zero_()
+            op.forward(dp)
+            assert torch.equal(dp.O, ref_O) and torch.equal(dp.lse, ref_lse)
+        op.check_status()
+        assert op.launch_count - n0 == 40 and op.last_kernel == "decode_gqa"
+    finally:
+        op.close()
