@@ -18,7 +18,7 @@ namespace {
 constexpr int kPrepWarps = 4;
 
 template <int HD, int QDT, bool FP8_POOL>
-__global__ void __launch_bounds__(kPrepWarps * 32) attn_prep_kernel(const PrepArgs a) {
+__global__ void __launch_bounds__(kPrepWarps * 32, HD == 128 ? 10 : 8) attn_prep_kernel(const PrepArgs a) {
   using QE = Elem16<QDT>;
   constexpr int NPT = HD / 32;
   const esp_attn_prep_params& p = a.p;
