@@ -107,14 +107,20 @@ PROTOTYPES = {
     "esp_attn_exchange_bytes": (C.c_size_t, [C.POINTER(Shape), C.c_int32, C.c_int32]),
     "esp_attn_exchange_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Params),
                                           C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(Exchange)]),
+    "esp_shard_lpt": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "esp_attn_split_kv_ranges": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "esp_attn_plan_split_kv": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32),
+                                         C.POINTER(C.c_int32)]),
+    "esp_attn_world_merge_jobs": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
     "esp_p2p_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_char_p]),
     "esp_p2p_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "esp_p2p_close": (C.c_int, [C.c_void_p]),
     "esp_p2p_free": (C.c_int, [C.c_void_p]),
     "esp_kv_slot_save": (C.c_int, [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
-                                   C.c_uint64, C.c_uint64]),
+                                   C.c_uint64, C.c_uint64, C.c_void_p, C.c_int32, C.c_uint64]),
     "esp_kv_slot_load": (C.c_int, [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int32),
-                                   C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
+                                   C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64,
+                                   C.c_void_p, C.c_int32, C.c_uint64]),
     "esp_attn_prep": (C.c_int, [C.c_void_p] * 14 + [C.c_int32, C.POINTER(PrepParams)]),
     "esp_kv_save": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                               C.POINTER(Params)]),
@@ -136,6 +142,7 @@ PROTOTYPES = {
                                        C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "esp_forest_anc_masks": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "esp_attn_decode_static": (C.c_int, [C.POINTER(Shape), C.c_void_p, C.POINTER(Args)]),
+    "esp_attn_decode_static_status": (C.c_int, [C.c_void_p]),
     "esp_attn_set_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "esp_attn_stamp": (C.c_int, [C.c_void_p, C.c_void_p]),
     "esp_attn_last_kernel": (C.c_char_p, [C.c_void_p]),

@@ -89,11 +89,12 @@ int check_params(const esp_attn_ctx* c, const esp_attn_params& p) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+}  // namespace
+
 // The checks run_forest makes before it encodes a pass (forest.h:2136-2280), on the host
-// mirrors of the plan. Nothing is launched when one fails.
-int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
-  const esp_attn_shape& s = c->shape;
-  const int TR = c->tile_rows;
+// mirrors of the plan. Nothing is launched when one fails. `deep` = also walk the mirrors
+// (the "validate" option of a context).
+int esp::validate_pass(const esp_attn_shape& s, int TR, bool deep, const esp_attn_args& a) {
   if (a.n_tiles < 0 || a.n_trees < 0 || a.n_jobs < 0 || a.n_rows < 0) return fail(ESP_ERR_INVALID, "forward: negative count");
   if (a.n_tiles == 0) return ESP_OK;
   if (!a.Q || !a.Kb || !a.Vb || !a.O || !a.tiles || !a.trees) return fail(ESP_ERR_INVALID, "forward: null Q/Kb/Vb/O/tiles/trees");
@@ -106,7 +107,7 @@ int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
   if (a.window < 0 || a.ring < 0) return fail(ESP_ERR_INVALID, "forward: window=%d ring=%d", a.window, a.ring);
   if (a.window > 0 && !a.pos) return fail(ESP_ERR_INVALID, "forward: a sliding window needs the rows' positions (pos)");
   if (a.bidi && (s.flags & ESP_ATTN_FLAG_ANC_MASK)) return fail(ESP_ERR_UNSUPPORTED, "forward: bidi uses desc.w and cannot be combined with ancestor masks");
-  if (!c->opt_validate || !a.trees_host || !a.tiles_host) return ESP_OK;
+  if (!deep || !a.trees_host || !a.tiles_host) return ESP_OK;
   bool any_cached = false;
   for (int i = 0; i < a.n_trees; ++i) {
     const esp_attn_tree& t = a.trees_host[i];
@@ -140,6 +141,10 @@ int validate(const esp_attn_ctx* c, const esp_attn_args& a) {
     }
   return ESP_OK;
 }
+
+namespace {
+
+int validate(const esp_attn_ctx* c, const esp_attn_args& a) { return esp::validate_pass(c->shape, c->tile_rows, c->opt_validate != 0, a); }
 
 // Tensor map of one layer region of the pool, as the decode kernel reads it:
 // [128-byte line][rows][lines per row], box [line, 16 rows, lines of one head].
@@ -279,6 +284,10 @@ int esp_attn_destroy(esp_attn_ctx* c) {
 
 int esp_attn_set_option(esp_attn_ctx* c, const char* name, int value) {
   if (!c || !name) return fail(ESP_ERR_INVALID, "esp_attn_set_option: null argument");
+  // attn_vec (src/model/impl/model.h:590): the reference's alternative decode schedule, off there by
+  // default; it is not rebuilt here - the one decode kernel serves every single-row pass.
+  if (!std::strcmp(name, "attn_vec"))
+    return value == 0 ? ESP_OK : fail(ESP_ERR_UNSUPPORTED, "esp_attn_set_option: attn_vec is not built; single-row trees always take the attn_gqa kernel");
   int* slot = option_slot(c, name);
   if (!slot) return fail(ESP_ERR_INVALID, "esp_attn_set_option: unknown option '%s'", name);
   *slot = value;

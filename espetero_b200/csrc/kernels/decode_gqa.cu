@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[NW][STAGES];
   __shared__ int fix_info[4];  // fused merge: first record and record count of the tile's job, the ticket drawn
+  __shared__ int gave_up;      // a warp's bounded wait ran out: the CTA writes an empty result and leaves its rings alone
   __shared__ uint64_t fix_bar;  // fused merge: completion of the records' bulk copies
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
   const bool fused = a.fuse && tile.part >= 0;
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&pool_map);
+    gave_up = 0;
     mbar_init(&fix_bar, 1);  // made visible by the fence and barrier below
     if (fused) {  // needed only at the very end: the load's latency hides behind the whole stream
       const esp_attn_combine jb = a.jobs[tile.pad1 - 1];
@@ -204,8 +206,13 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
       kscale = __shfl_sync(0xffffffffu, use_ks, it - use_win);
       vscale = __shfl_sync(0xffffffffu, use_vs, it - use_win);
     }
-    if (!mbar_wait(&full_bar[warp][slot], (it / STAGES) & 1)) {
-      if (lane == 0) atomicExch(a.status, kStatusTmaTimeout);
+    // One verdict for the whole warp (each lane reads its own timer: without the vote lanes could
+    // disagree at the limit and the warp-wide shuffles / MMAs below would run with lanes missing).
+    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[warp][slot], (it / STAGES) & 1))) {
+      if (lane == 0) {
+        atomicExch(a.status, kStatusTmaTimeout);
+        gave_up = 1;
+      }
       break;
     }
     const uint8_t* kt = wsm + slot * C::STAGE_BYTES;
@@ -323,6 +330,24 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     l1 += __shfl_xor_sync(0xffffffffu, l1, off);
   }
   __syncthreads();
+  if (gave_up) {
+    // A load never landed (the status word says so): loads may still be in flight into the rings, so
+    // they are not reused as scratch. The CTA writes an empty record (m = -inf, l = 0: it weighs
+    // nothing in a merge) or a zero row, and takes no part in a fused merge.
+    for (int hg = warp; hg < G; hg += NW) {
+      const int h = kvh * G + hg;
+      if (tile.part >= 0) {
+        float* rec = a.parts + ((size_t(tile.part) * p.Hkv + kvh) * a.tile_rows * G + hg) * (HD + 2);
+        for (int i = lane; i < HD; i += 32) rec[i] = 0.0f;
+        if (lane == 0) rec[HD] = -INFINITY, rec[HD + 1] = 0.0f;
+      } else {
+        typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(h) * HD;
+        for (int i = lane; i < HD; i += 32) op[i] = QE::from_f32(0.0f);
+        if (a.lse && lane == 0) a.lse[size_t(row) * p.H + h] = -INFINITY;
+      }
+    }
+    return;
+  }
   {
     float* osm = reinterpret_cast<float*>(wsm);
     float* msm = osm + 8 * OLD;
@@ -445,7 +470,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
         for (int s = 0; s < cnt; ++s)
           bulk_load(reinterpret_cast<uint8_t*>(stage) + size_t(s) * rec_bytes, base + size_t(s0 + s) * part_stride, rec_bytes, &fix_bar);
       }
-      if (!mbar_wait(&fix_bar, par)) {
+      if (!__syncthreads_and(mbar_wait(&fix_bar, par))) {  // one verdict for the CTA: nobody is left behind at a barrier
         if (threadIdx.x == 0) atomicExch(a.status, kStatusTmaTimeout);
         return;
       }

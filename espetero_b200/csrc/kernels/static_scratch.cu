@@ -16,6 +16,11 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <atomic>
+#include <climits>
+#include <mutex>
+
 #include "../host_util.h"
 #include "../launch.h"
 
@@ -34,7 +39,7 @@ static __device__ __align__(256) int g_static_counters[esp::kFixupCounters] = {0
 // In host code the two names above are only handles of the symbols, not device addresses;
 // the addresses a kernel can use are looked up once per device and kept here.
 struct DeviceSlot {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   float* parts = nullptr;
   int* status = nullptr;
   int* counters = nullptr;
@@ -67,8 +72,17 @@ int setup_device(int dev) {
   if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !s.encode_tiled)
     return esp::fail(ESP_ERR_CUDA, "esp_attn_decode_static: cuTensorMapEncodeTiled not available from the driver");
   if ((e = esp::decode_gqa_setup()) != cudaSuccess) return cuda_fail(e, "decode kernel setup");
-  s.ready = true;
+  s.ready.store(true, std::memory_order_release);
   return ESP_OK;
+}
+
+// Host threads may race to make the first call on a device: the set-up runs once, under a lock.
+std::mutex g_setup_lock;
+int ensure_device(int dev) {
+  if (g_slots[dev].ready.load(std::memory_order_acquire)) return ESP_OK;
+  std::lock_guard<std::mutex> hold(g_setup_lock);
+  if (g_slots[dev].ready.load(std::memory_order_relaxed)) return ESP_OK;
+  return setup_device(dev);
 }
 
 }  // namespace
@@ -92,16 +106,20 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   if (a.p.H != s.H || a.p.Hkv != s.Hkv || a.p.bt != s.bt || a.p.q_ld < s.H * s.HD || a.p.kv_ld < s.Hkv * s.HD ||
       (size_t(a.p.kv_ld) * esz) % 128 || (a.p.kv_base * esz) % 128)
     return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: params do not match the shape");
+  if (a.n_jobs > 0 && !a.jobs_host)
+    return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: combine jobs need their host copy (jobs_host): the records they name cannot be checked against the built-in array otherwise");
   for (int i = 0; i < a.n_trees; ++i)
     if (a.trees_host[i].M != 1) return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: tree %d has %d rows (decode only)", i, a.trees_host[i].M);
-  int max_part = -1;
-  for (int i = 0; i < a.n_tiles; ++i) {
-    const esp_attn_tile& t = a.tiles_host[i];
-    if (t.tree < 0 || t.tree >= a.n_trees || t.k0 < 0 || t.k0 > t.k1 || t.k1 > a.trees_host[t.tree].P)
-      return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: tile %d is malformed", i);
-    max_part = t.part > max_part ? t.part : max_part;
+  // Records the pass touches: the largest one a tile writes or a combine job reads.
+  int64_t top_part = 0;
+  for (int i = 0; i < a.n_tiles; ++i) top_part = std::max<int64_t>(top_part, int64_t(a.tiles_host[i].part) + 1);
+  for (int i = 0; i < a.n_jobs; ++i) {
+    const esp_attn_combine& j = a.jobs_host[i];
+    if (j.part0 < 0 || j.nparts < 1) return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: job %d: records [%d, +%d)", i, j.part0, j.nparts);
+    top_part = std::max<int64_t>(top_part, int64_t(j.part0) + j.nparts);
   }
-  const size_t need = size_t(max_part + 1) * size_t(s.Hkv) * size_t(TR) * size_t(G) * size_t(s.HD + 2);
+  const size_t rec_floats = size_t(s.Hkv) * size_t(TR) * size_t(G) * size_t(s.HD + 2);
+  const size_t need = size_t(top_part) * rec_floats;
   if (need > kStaticPartsFloats)
     return esp::fail(ESP_ERR_CAPACITY, "esp_attn_decode_static: the pass needs %zu floats of records, the built-in array holds %zu; use esp_attn_forward with a caller-owned parts buffer",
                      need, kStaticPartsFloats);
@@ -110,9 +128,21 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
   if (dev < 0 || dev >= kMaxDevices) return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: device index %d", dev);
-  if (!g_slots[dev].ready)
-    if (int rc = setup_device(dev)) return rc;
+  if (int rc = ensure_device(dev)) return rc;
   const DeviceSlot& slot = g_slots[dev];
+
+  // The same host checks esp_attn_forward makes (trees, tiles and jobs against the row, block-table
+  // and record counts), with the built-in array standing in for the caller's parts buffer.
+  {
+    esp_attn_args chk = a;
+    chk.parts = slot.parts;
+    chk.n_parts = int32_t(std::min<size_t>(kStaticPartsFloats / rec_floats, size_t(INT32_MAX)));
+    chk.anc_mask = nullptr;
+    esp_attn_shape cs = s;
+    cs.flags &= ~ESP_ATTN_FLAG_ANC_MASK;  // single-row trees have no batch keys to mask: desc is what the kernel gets
+    if (!a.desc) chk.desc = reinterpret_cast<const int32_t*>(a.Q);  // never dereferenced by the decode kernel; only its presence is checked
+    if (int rc = esp::validate_pass(cs, TR, true, chk)) return rc;
+  }
 
   CUtensorMap map;
   {
@@ -165,4 +195,26 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
     if ((e = esp::launch_combine(c, stream, &launches)) != cudaSuccess) return cuda_fail(e, "attention_combine");
   }
   return ESP_OK;
+}
+
+// Reads and clears the status word of the current device's built-in arrays: a bounded wait of the
+// decode kernel that ran out (a TMA or bulk copy that never landed) leaves a code there, and the
+// output of that pass is then not to be trusted. Also zeroes the merge's arrival counters, which a
+// kernel that gave up may have left half counted. Synchronises the stream; allocates nothing.
+extern "C" int esp_attn_decode_static_status(void* stream_v) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static_status: device index %d", dev);
+  if (!g_slots[dev].ready.load(std::memory_order_acquire)) return ESP_OK;  // nothing has run here yet
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int st = 0;
+  e = cudaMemcpyFromSymbolAsync(&st, g_static_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the status word");
+  if (st == 0) return ESP_OK;
+  cudaMemsetAsync(g_slots[dev].status, 0, sizeof(int) * 64, stream);
+  cudaMemsetAsync(g_slots[dev].counters, 0, sizeof(int) * esp::kFixupCounters, stream);
+  return esp::fail(ESP_ERR_CUDA, "esp_attn_decode_static: a kernel gave up a bounded wait (status %d: %s); the outputs of passes since the last check are not valid",
+                   st, st == esp::kStatusTmaTimeout ? "a TMA or bulk copy never completed" : "unexpected code");
 }

@@ -176,6 +176,12 @@ struct PrepArgs {
   esp_attn_prep_params p;
 };
 
+// Host-side checks of a pass before anything is launched (the checks run_forest makes,
+// src/model/impl/forest.h:2136-2280): pointers, alignment, and - with `deep` - every tree, tile and
+// combine job of the host mirrors against the row, block-table and record counts of `a`.
+// Returns ESP_OK or a negative esp_status with the message set.
+int validate_pass(const esp_attn_shape& s, int tile_rows, bool deep, const esp_attn_args& a);
+
 // Launch with programmatic stream serialization: the grid may be scheduled while the previous
 // kernel of the stream drains; the kernel orders itself with griddepcontrol.wait.
 template <typename... Params, typename... Args>

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define ESP_ATTN_ABI_VERSION 3
+#define ESP_ATTN_ABI_VERSION 4
 
 /* ---------------------------------------------------------------- status */
 typedef enum esp_status {
@@ -300,6 +300,24 @@ int esp_attn_exchange_parts(esp_attn_ctx* ctx, void* stream, const float* parts,
                             const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int32_t rows_max,
                             int32_t parts_max, const esp_attn_exchange* x);
 
+/* ---- Planning of the multi-GPU layer (pure host functions; no counterpart in the reference).
+ * esp_shard_lpt: sequences -> ranks by longest-processing-time greedy on their context lengths
+ * (longest first, ties by index, onto the least loaded rank, ties to the lowest): rank_of[i] = rank of
+ * sequence i. Whole sequences move; nothing is exchanged on the data path.
+ * esp_attn_split_kv_ranges: key range [lo[r], hi[r]) of each rank for one sequence of P keys, cut on
+ * page boundaries with the pages spread as evenly as possible.
+ * esp_attn_plan_split_kv: turns a rank's plan over its local keys (esp_attn_plan) into the
+ * records-only plan esp_attn_exchange_parts / esp_attn_reduce_parts expect: every tile writes a
+ * record, only the last rank keeps `last`, job tags are cleared, and one reduce job per row group
+ * names the rank's records (tiles rewritten in place; jobs_cap protocol as esp_attn_plan).
+ * esp_attn_world_merge_jobs: the job that merges the ranks' reduced records, gathered rank-major. */
+int esp_shard_lpt(const int64_t* lengths, int32_t n, int32_t world, int32_t* rank_of);
+int esp_attn_split_kv_ranges(int32_t P, int32_t world, int32_t bt, int32_t* lo, int32_t* hi);
+int esp_attn_plan_split_kv(esp_attn_tile* tiles, int32_t n_tiles, int32_t is_last_rank, esp_attn_combine* jobs, int32_t jobs_cap,
+                           int32_t* n_jobs, int32_t* n_parts);
+int esp_attn_world_merge_jobs(int32_t n_groups, int32_t world, int32_t rows, esp_attn_combine* jobs, int32_t jobs_cap,
+                              int32_t* n_jobs);
+
 /* Device memory another process of the same box can map: cudaMalloc + zero fill + an IPC handle
  * (64 bytes, opaque). esp_p2p_open maps a peer's allocation into this process (peer access is
  * enabled on first use); esp_p2p_close unmaps it; esp_p2p_free releases an own allocation. */
@@ -319,13 +337,22 @@ int esp_p2p_free(void* ptr);
  * layer * region_bytes + block * block_bytes. Both calls allocate staging buffers (up to 64 MB on the
  * device and pinned on the host), synchronise the stream, and free them before they return.
  * Load takes ceil(len / bt) blocks from `pool` (ESP_ERR_CAPACITY "KV cache full" if it has fewer,
- * leaving it unchanged) and reports them in blocks_out. */
+ * leaving it unchanged) and reports them in blocks_out.
+ * ESP_E4M3 pools (an extension; the reference has no FP8 KV cache): pass the scale table of layer 0
+ * in kv_scales ([n_blocks][2][Hkv] fp32 per layer, the layers' tables scales_region_floats apart) and
+ * Hkv. The file then carries, behind the blocks, the 2 * Hkv scales of every block of the list for
+ * every layer, and says so in the header word the reference leaves at zero (`pad` = scale bytes per
+ * block and layer); load restores them into the rows of the blocks it allocated, so the sequence
+ * decodes with its own scales whatever used those blocks before. With kv_scales == NULL (16-bit
+ * pools) the file is the reference's, byte for byte; a file written with scales is refused by a pool
+ * without them and the other way round (ESP_ERR_INVALID). */
 typedef struct esp_kv_pool esp_kv_pool;
 int esp_kv_slot_save(const char* path, void* stream, const void* kv, const int32_t* blocks_host, int32_t len, int32_t next_pos,
-                     int32_t bt, int32_t n_layers, uint64_t region_bytes, uint64_t block_bytes);
+                     int32_t bt, int32_t n_layers, uint64_t region_bytes, uint64_t block_bytes, const float* kv_scales,
+                     int32_t Hkv, uint64_t scales_region_floats);
 int esp_kv_slot_load(const char* path, void* stream, void* kv, esp_kv_pool* pool, int32_t* blocks_out, int32_t blocks_cap,
                      int32_t* n_blocks, int32_t* len, int32_t* next_pos, int32_t bt, int32_t n_layers, uint64_t region_bytes,
-                     uint64_t block_bytes);
+                     uint64_t block_bytes, float* kv_scales, int32_t Hkv, uint64_t scales_region_floats);
 
 /* ---- attn_prep: the step right before the attention pass (kernels/40_attention.metal:23-102, host
  * dispatch src/model/impl/forest.h:2951-2977; generic head dim q3m_attn_prep,
@@ -449,21 +476,29 @@ int esp_forest_anc_masks(const int32_t* parents, int32_t n, uint64_t* masks);
  * the library's device image - every GPU that loads the library holds it until the
  * process exits. args->parts and args->n_parts are ignored; inputs, outputs and the plan
  * (device and host copies) are passed as for esp_attn_forward. Limits and rules:
- *  - a pass whose records need more than the array holds
- *    ((largest part + 1) * Hkv * tile_rows * G * (HD + 2) floats) is refused with
- *    ESP_ERR_CAPACITY; shapes the decode kernel does not cover, multi-row trees and tiles
- *    that do not start on a 16-key boundary are refused with ESP_ERR_UNSUPPORTED /
- *    ESP_ERR_INVALID. Nothing is launched in either case.
+ *  - a pass whose records need more than the array holds (the largest record a tile writes or a
+ *    combine job reads, + 1, times Hkv * tile_rows * G * (HD + 2) floats) is refused with
+ *    ESP_ERR_CAPACITY; shapes the decode kernel does not cover and multi-row trees are refused
+ *    with ESP_ERR_UNSUPPORTED; a plan that fails the host checks of esp_attn_forward (trees, tiles
+ *    and jobs against the row, block-table and record counts; the host copies tiles_host,
+ *    trees_host and - with combine jobs - jobs_host are required) with ESP_ERR_INVALID. Nothing
+ *    is launched in any of these cases. A tile may start at any key.
  *  - the call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
  *  - the first call on each device (with that device current) looks up the array's device
  *    address and raises the kernels' shared-memory limit; make that call before any stream
- *    capture begins.
+ *    capture begins. Host threads that race to make it are serialised by a lock.
  *  - all calls on a GPU share the one array, which keeps the previous call's records:
  *    nothing in it needs clearing (each call overwrites every record it later reads), but
  *    two calls that overlap on the GPU (different streams, or different threads) race on
- *    it - serialise them on one stream. */
+ *    it - serialise them on one stream.
+ *  - failures on the device: the kernels' waits are bounded; one that runs out leaves a code in a
+ *    status word next to the array and the pass's output is not valid.
+ *    esp_attn_decode_static_status(stream) reads and clears that word for the current device
+ *    (ESP_OK, or ESP_ERR_CUDA with the reason); it synchronises the stream and allocates nothing,
+ *    so call it at a checkpoint, not per pass. */
 #define ESP_ATTN_STATIC_PARTS_FLOATS (4u << 20)
 int esp_attn_decode_static(const esp_attn_shape* shape, void* stream, const esp_attn_args* args);
+int esp_attn_decode_static_status(void* stream);
 
 /* Name of the attention kernel the last esp_attn_forward on this context
  * launched ("decode_gqa", "flash_umma", "flash_umma_pair", "flash_general"), for tests and traces. */

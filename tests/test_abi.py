@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} is declared in the header but not exported"
         assert n in capi.PROTOTYPES, f"{n} has no ctypes prototype"
-    assert lib.esp_attn_abi_version() == 3
+    assert lib.esp_attn_abi_version() == 4
 
 
 def test_record_layouts():

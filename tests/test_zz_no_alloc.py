@@ -36,10 +36,21 @@ def _both(w, seed_note):
         args.parts = None                                 # no caller buffer for the records
         args.n_parts = 0
         stream = torch.cuda.current_stream().cuda_stream
-        mem_before = torch.cuda.memory_allocated()
+        # One call first (on a device's first call the library looks up its array's address), then the
+        # measured one: free device memory as the driver reports it (cudaMemGetInfo sees every
+        # allocation of the process, the library's own included; torch's counter would only see torch's).
         capi.check(lib.esp_attn_decode_static(C.byref(op.shape), C.c_void_p(stream), C.byref(args)))
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == mem_before
+        dp.O.zero_()
+        dp.lse.zero_()
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        torch_before = torch.cuda.memory_allocated()
+        capi.check(lib.esp_attn_decode_static(C.byref(op.shape), C.c_void_p(stream), C.byref(args)))
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+        assert torch.cuda.memory_allocated() == torch_before
+        capi.check(lib.esp_attn_decode_static_status(C.c_void_p(stream)))   # no bounded wait ran out
         return want_O, want_lse, dp.O.cpu().numpy(), dp.lse.cpu().numpy()
     finally:
         op.close()
@@ -83,5 +94,41 @@ def test_static_records_capacity_and_shape_limits():
         args = op.make_args(dp)
         rc = lib.esp_attn_decode_static(C.byref(op.shape), C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(args))
         assert rc == capi.ESP_ERR_UNSUPPORTED
+    finally:
+        op.close()
+
+
+def test_static_records_refuse_jobs_beyond_the_array():
+    """A combine job that names records past the built-in array, a job list without its host copy and
+    a tree whose block list runs past the table are refused before anything is launched."""
+    lib = capi.load()
+    w = wl.make_pass("noalloc_jobs", 9005, [(1024, 1), (512, 1)], 32, 4, 128, 16, wl.BF16)
+    op = host.AttnOp.for_workload(w)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv)
+        assert len(plan.jobs) > 0
+        dp = op.upload(w, plan)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rec = w.Hkv * 8 * w.G * (w.HD + 2)
+        # (i) a job whose records end past the array
+        args = op.make_args(dp)
+        jobs = (capi.Combine * len(plan.jobs)).from_buffer_copy(C.string_at(args.jobs_host, C.sizeof(capi.Combine) * len(plan.jobs)))
+        jobs[0].part0 = (4 << 20) // rec - 1
+        jobs[0].nparts = 4
+        args.jobs_host = C.cast(jobs, C.c_void_p)
+        assert lib.esp_attn_decode_static(C.byref(op.shape), stream, C.byref(args)) == capi.ESP_ERR_CAPACITY
+        # (ii) jobs without the host copy: the bound cannot be proved
+        args = op.make_args(dp)
+        args.jobs_host = None
+        assert lib.esp_attn_decode_static(C.byref(op.shape), stream, C.byref(args)) == capi.ESP_ERR_INVALID
+        assert b"jobs_host" in lib.esp_attn_last_error()
+        # (iii) a block table shorter than the trees need
+        args = op.make_args(dp)
+        args.n_block_entries = 3
+        assert lib.esp_attn_decode_static(C.byref(op.shape), stream, C.byref(args)) == capi.ESP_ERR_INVALID
+        # the well-formed call still runs afterwards
+        args = op.make_args(dp)
+        capi.check(lib.esp_attn_decode_static(C.byref(op.shape), stream, C.byref(args)))
+        torch.cuda.synchronize()
     finally:
         op.close()
