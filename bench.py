@@ -3,14 +3,22 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
 
-One step = one pass of the hot path (esp_attn_forward: attention kernel + combine) over one
-batch of seeded synthetic input with the shapes of the benchmark configuration. The default
-workload is the batched paged decode (32 sequences per GPU, context ~ U[512, 32768],
-H32/Hkv4/HD128 bf16, 16-token pages scattered by a seeded page table); the metric is the
-HBM bandwidth the pass achieves = algorithmic K/V bytes / time. With N > 1 (torchrun, one
-process per GPU) every rank runs its own batch: the path shards by sequence, there is no
-collective on the data path ("scaling": "weak"). The split-KV workload (c5) is the one path
-with an exchange step: ranks all-gather their partial records (NCCL) and combine locally.
+One step = one pass of the hot path (esp_attn_forward: attention kernel + merge of the split-K
+records) over one batch of seeded synthetic input with the shapes of the benchmark configuration.
+The default workload is the batched paged decode (32 sequences per GPU, context ~ U[512, 32768],
+H32/Hkv4/HD128 bf16, 16-token pages scattered by a seeded page table); the metric is the HBM
+bandwidth the pass achieves = algorithmic K/V bytes / time. With N > 1 (torchrun, one process per
+GPU) every rank runs its own batch: the path shards by sequence, there is no collective on the data
+path ("scaling": "weak"). The default run at N > 1 also times, and reports inside the same JSON
+line, the two strong-scaling cases: the one 32-sequence batch spread over the N GPUs by context
+length ("c2_strong") and the long-context decode with its keys split over the GPUs by range
+("split_kv"). That last one is the only path with an exchange step: one kernel per rank reduces its
+records, stores the result into every rank's buffer over NVLink peer mappings and finishes the
+merge (esp_attn_exchange_parts); `--exchange nccl` gathers the reduced records with a library
+all-gather instead, which is also the fallback when peer mappings cannot be set up.
+
+At N = 1 the pass's output is also compared with the float64 oracle after the timed region
+("parity" in the line; `--no-check` skips it).
 
 `--impl reference` times the CPU restatement of the reference's kernels (oracle/) on the
 host cores instead; the reference itself is Metal-only and cannot run on this box.
@@ -182,13 +190,30 @@ def time_cpu(name: str, repeats: int = 1):
     return w.kv_bytes_read() / best / 1e9, threads, sample, best
 
 
+def l2_note(w) -> str:
+    """How the keys of a pass are kept out of L2 between timed steps (see LayerCycle)."""
+    n = layer_regions(w)
+    if n == 1:
+        return "inputs larger than L2"
+    return (f"{n} layer regions of the pool read in turn ({n * w.kv_bytes_read() / 1e6:.0f} MB per cycle, "
+            f"L2 is 126 MB): a pass reads keys last touched {n - 1} passes ago; no flush kernels")
+
+
+def workload_config(w):
+    """The `config` object of a JSON line: what the workload is, identical on the GPU arm and on the
+    reference arm (what each arm ran it with is reported beside it, in `plan` / `cpu_baseline`)."""
+    return {"workload": w.name, "sequences_per_gpu": len(w.trees), "H": w.H, "Hkv": w.Hkv, "HD": w.HD, "page": w.bt,
+            "kv_bytes_per_gpu": w.kv_bytes_read(), "l2": l2_note(w)}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return  # the CPU arm runs on rank 0 alone
     steps = max(1, args.steps)
+    W = max(0, args.warmup)
     vals = []
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(W):
         time_cpu(args.workload)
     t_all = 0.0
     for _ in range(steps):
@@ -196,26 +221,34 @@ def run_reference_arm(args):
         vals.append(v)
         t_all += dt
     value = float(np.mean(vals))
+    w = _CPU_CASES[args.workload][0]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t_all / steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": _CPU_CASES[args.workload][0].name, "note": "CPU restatement of the reference's Metal kernels (oracle/), fp32, std::thread"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "warmup": W, "ms_per_step": 1e3 * t_all / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if w.kv_elem_bytes == 2 else "e4m3->f16", "data": "synthetic",
+        "config": workload_config(w),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "what": "CPU restatement of the reference's Metal kernels (oracle/), fp32, std::thread, rank 0's host cores"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel on each bench workload, from the
-# ncu captures summarised under profiles/ (decode_gqa_c2_batched_decode.md, decode_gqa_c5_long_fp8_decode.md,
-# flash_umma_c4_tree_verify.md, flash_umma_pair_c3_causal_prefill.md). A capture cannot run inside a
-# timed run, so the figure is carried here; it holds for the default sizes of the workload only.
-# The prefill workload was captured on a smaller case only and is tensor-bound: no figure.
+# DRAM bytes (read + write) of one launch of the dominant kernel on each bench workload, from one ncu
+# capture per workload (a capture cannot run inside a timed run, so the figure is carried here; it holds
+# for the default sizes of the workload only). The prefill workload was captured on a smaller case
+# only and is tensor-bound: no figure.
 NCU_TRAFFIC_BYTES = {"c2": 1.12084e9 + 12.20e6, "c5": 537.83e6 + 4.29e6, "c4": 136.96e6 + 4.32e6}
 
 
 L2_BYTES = 126e6
+
+
+def layer_regions(w) -> int:
+    """Layer regions the pool of a workload is given: one if its K/V bytes evict themselves from L2
+    (>= 2 x L2), else as many copies as make one cycle at least 4 x L2 long."""
+    nbytes = max(1, w.kv_bytes_read())
+    return 1 if nbytes >= 2 * L2_BYTES else min(64, int(-(-4 * L2_BYTES // nbytes)))
 
 
 class LayerCycle:
@@ -227,8 +260,7 @@ class LayerCycle:
 
     def __init__(self, op, dp, w):
         self.op, self.dp, self.w = op, dp, w
-        nbytes = max(1, w.kv_bytes_read())
-        self.n = 1 if nbytes >= 2 * L2_BYTES else min(64, int(-(-4 * L2_BYTES // nbytes)))
+        self.n = layer_regions(w)
         self.region = dp.replicate_layers(self.n)
         self.i = 0
 
@@ -244,188 +276,236 @@ class LayerCycle:
         return a
 
     def describe(self):
-        if self.n == 1:
-            return "inputs larger than L2"
-        return (f"{self.n} layer regions of the pool read in turn ({self.n * self.w.kv_bytes_read() / 1e6:.0f} MB per cycle, "
-                f"L2 is 126 MB): a pass reads keys last touched {self.n - 1} passes ago; no flush kernels")
+        return l2_note(self.w)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
-    ap.add_argument("--fuse", type=int, default=-1, help="option fuse_combine of the library (0 off, 1 small passes, 2 always); -1: its default")
-    ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        return run_reference_arm(args)
+def default_groups(name: str) -> int:
+    """CTA target of the planner per workload: one wave for the short passes, 8 waves of 2 CTAs per SM otherwise."""
+    return {"c4": 148, "c5": 148 * 2}.get(name, 148 * 2 * 8)
 
-    import torch
-    import torch.distributed as dist
-    from espetero_b200 import capi, host, workloads as wl
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    W = max(3, args.warmup)
+def bench_plan(name: str, w, groups: int = 0):
+    """The plan the bench runs a workload with (the full-size parity tests use the same one)."""
+    from espetero_b200 import capi, host
+    tile_rows = TILE_ROWS[name]
+    return host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups or default_groups(name), tile_rows)
 
-    from espetero_b200 import shard
-    tile_rows = TILE_ROWS[args.workload]
-    split_kv = args.workload == "c5" and world > 1
-    groups = args.groups or {"c4": 148, "c5": 148 * 2}.get(args.workload, 148 * 2 * 8)
-    xch = None
-    if not split_kv:
-        w = build_workload(args.workload, rank, args.small, world)
-        op = host.AttnOp.for_workload(w, tile_rows, local)
-        if args.fuse >= 0:
-            op.set_option("fuse_combine", args.fuse)
-        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tile_rows)
-        dp = op.upload(w, plan)
-        layers = LayerCycle(op, dp, w)
-        a_full = layers.args()
-        a_attn = layers.args(n_jobs=0)  # attention kernel alone (no combine), for the per-kernel roofline figure
-        step = lambda: op.forward(dp, layers.next(a_full))
-        step_attn = lambda: op.forward(dp, layers.next(a_attn))
-        sharding = "sequences per rank, no collective" + (
-            "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
-        scaling = "weak"
-    else:
-        # One long sequence, keys split over the ranks on page boundaries: records for the local
-        # keys -> one reduced record per rank -> NCCL all-gather -> every rank merges the world's
-        # records in rank order. Total work is fixed: strong scaling.
-        ctx_all = 8192 if args.small else 131072
-        lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
-        w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
-        op = host.AttnOp.for_workload(w, tile_rows, local)
-        base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, args.groups or 148 * 2, tile_rows)
-        tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
-        plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, tile_rows)
-        dp = op.upload(w, plan)
-        for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
-            dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
-        layers = LayerCycle(op, dp, w)
-        a_attn = layers.args()
-        a_full = a_attn
-        red_dev = host._dev(red_jobs, dev)
-        merge_dev = host._dev(shard.world_merge_jobs(1, world), dev)
-        rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
-        rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)
 
-        # Preferred: one kernel per rank reduces, stores the record into every rank's buffer over
-        # NVLink peer mappings and merges (esp_attn_exchange_parts). If the peer mappings cannot be
-        # set up on this box (all ranks decide together), the records go through an NCCL all-gather.
-        if args.exchange == "p2p":
-            try:
-                xch = host.PeerExchange(op, n_jobs=1, rows_max=1)
-                ok = 1
-            except Exception as e:  # noqa: BLE001 - reported below, then the NCCL path is used
-                print(f"[rank {rank}] peer exchange unavailable: {e}", file=sys.stderr, flush=True)
-                ok = 0
-            flag = torch.tensor([ok], dtype=torch.int32, device=dev)
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-            if int(flag.item()) == 0:
-                xch = None
+def parity_rows(name: str, w):
+    """Rows compared with the float64 oracle: all of them, except for the prefill workload, whose
+    full float64 result is ~1e13 flop: there the first and last 16 rows of every sequence plus 256
+    seeded rows, all heads."""
+    if name != "c3":
+        return None
+    rows = set()
+    for t in w.trees:
+        b, M = int(t["base"]), int(t["M"])
+        rows.update(range(b, b + min(16, M)))
+        rows.update(range(b + max(0, M - 16), b + M))
+    rng = np.random.default_rng(0xC3)
+    rows.update(int(r) for r in rng.integers(0, w.n_rows, size=256))
+    return np.array(sorted(rows), dtype=np.int32)
 
-        if xch is not None:
-            def step():
-                xch.next_epoch()
-                op.forward(dp, layers.next(a_attn))
-                op.exchange_parts(dp, dp.parts, red_dev, len(red_jobs), xch, parts_max=n_parts)
-            sharding = "KV range per rank; one kernel per rank merges, exchanges records over NVLink peer stores and finishes"
-        else:
-            def step():
-                op.forward(dp, layers.next(a_attn))
-                op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
-                dist.all_gather_into_tensor(rec_world, rec_local)
-                op.combine(dp, rec_world, merge_dev, 1)
-            sharding = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank"
-        step_attn = lambda: op.forward(dp, layers.next(a_attn))
-        scaling = "strong"
-    bytes_step = w.kv_bytes_read()
-    stream = torch.cuda.current_stream(dev)
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
 
-    def timed(fn, n, tail=None):
+def parity_report(name: str, w, O_bits, lse):
+    """max |O - float64 oracle| over the checked rows, and how it sits against the stated tolerance
+    (2e-3; 1e-2 over an E4M3 pool) plus half an ulp of the 16-bit output and, for rows with a handful
+    of keys, the bound on rounding P to 16 bits before P.V (u * sum_j p_j |v_j|)."""
+    import oracle
+    from espetero_b200 import workloads as wl
+    rows = parity_rows(name, w)
+    ref, lse_ref, ref_abs = oracle.attention_f64(w, rows=rows, with_abs=True)
+    got = wl.from_bits16(O_bits if rows is None else O_bits[rows], w.q_dtype).astype(np.float64)
+    got_lse = lse if rows is None else lse[rows]
+    tol = 1e-2 if w.kv_dtype == wl.E4M3 else 2e-3
+    mant = 10 if w.q_dtype == wl.F16 else 7
+    half_ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(ref), 2.0 ** -14))) - mant - 1)
+    u_p = 2.0 ** -12 if (w.q_dtype == wl.F16 or w.kv_dtype == wl.E4M3) else 2.0 ** -9
+    err = np.abs(got - ref)
+    allow = tol + half_ulp + u_p * ref_abs
+    fin = np.isfinite(lse_ref)
+    lse_err = float(np.abs(got_lse[fin] - lse_ref[fin]).max()) if fin.any() else 0.0
+    return {"max_abs_err": float(err.max()), "tol": tol, "rows_checked": int(len(ref)), "elements": int(err.size),
+            "beyond_plain_tol": int((err > tol).sum()), "beyond_allowance": int((err > allow).sum()),
+            "allowance": "tol + half an ulp of the 16-bit output + 2^-9 (bf16; 2^-12 fp16) x sum_j p_j|v_j| for rounding P",
+            "lse_max_abs_err": lse_err, "ok": bool((err <= allow).all() and lse_err < 2e-3),
+            "oracle": "float64 direct softmax on the stored values (oracle/)"}
+
+
+class Bench:
+    """Process-wide state of one bench run (one rank)."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.args = torch, dist, args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def timed(self, fn, n, tail=None, solo=False):
         """Seconds for n calls of fn: CUDA events on the launching stream, barrier + synchronize on both sides.
-        tail() runs before the closing event (it makes the launching stream wait for work on other streams)."""
-        barrier()
+        tail() runs before the closing event (it makes the launching stream wait for work on other streams).
+        solo: this rank measures alone (no barrier with the others)."""
+        torch = self.torch
+        sync = (lambda: torch.cuda.synchronize(self.dev)) if solo else self.barrier
+        sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        e0.record(self.stream)
         for _ in range(n):
             fn()
         if tail is not None:
             tail()
-        e1.record(stream)
-        barrier()
+        e1.record(self.stream)
+        sync()
         return e0.elapsed_time(e1) / 1e3
 
-    # ---- device-resident throughput (value)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    for _ in range(W):
-        step()
-    op.check_status()
-    n0 = op.launch_count
-    t_total = timed(step, args.steps)
-    launches = op.launch_count - n0
-    # ---- attention kernel alone (roofline of the dominant kernel)
-    for _ in range(3):
-        step_attn()
-    t_attn = timed(step_attn, args.steps) / args.steps
-    # nvidia-smi samples every 100 ms: keep the same kernels running (untimed) until it has seen the
-    # GPU under this load for about half a second, on every rank alike
-    # (a fixed number of steps derived from rank 0's timing, so that ranks which exchange records
-    # inside a step all run the same count)
-    hold = torch.tensor([min(20000, int(0.6 / max(t_total / args.steps, 1e-6)) + 1)], dtype=torch.int64, device=dev)
-    if world > 1:
-        dist.broadcast(hold, src=0)
-    for _ in range(int(hold.item())):
-        step()
-    torch.cuda.synchronize(dev)
-    clocks = sampler.stop() if rank == 0 else None
-    op.check_status()
+    def reduce_max_sum(self, times, total):
+        """max over ranks of each time, sum over ranks of `total`."""
+        torch = self.torch
+        tt = torch.tensor(list(times), dtype=torch.float64, device=self.dev)
+        bb = torch.tensor([float(total)], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(tt, op=self.dist.ReduceOp.MAX)
+            self.dist.all_reduce(bb, op=self.dist.ReduceOp.SUM)
+        return [float(x) for x in tt.cpu()], float(bb.cpu()[0])
 
-    # ---- end to end through the C ABI from host buffers: the step's inputs (Q, Kb, Vb and the
-    # plan tables) come from pinned host memory, the result goes back; the KV pool is device state.
+
+class Run:
+    """One workload set up on this rank: step() = the whole pass, step_attn() = the attention kernel alone."""
+    xch = None
+    split_kv = False
+
+
+def setup_sequences(B: Bench, name: str, w, scaling: str, sharding: str) -> Run:
+    """Sequences are whole units of work: this rank's batch, its own pool and plan, no exchange."""
+    from espetero_b200 import host
+    args = B.args
+    r = Run()
+    r.name, r.w, r.scaling, r.sharding = name, w, scaling, sharding
+    r.op = host.AttnOp.for_workload(w, TILE_ROWS[name], B.local)
+    if args.fuse >= 0:
+        r.op.set_option("fuse_combine", args.fuse)
+    r.plan = bench_plan(name, w, args.groups)
+    r.dp = r.op.upload(w, r.plan)
+    r.layers = LayerCycle(r.op, r.dp, w)
+    r.a_full = r.layers.args()
+    r.a_attn = r.layers.args(n_jobs=0)  # attention kernel alone (records only, no merge), for the per-kernel roofline figure
+    r.step = lambda: r.op.forward(r.dp, r.layers.next(r.a_full))
+    r.step_attn = lambda: r.op.forward(r.dp, r.layers.next(r.a_attn))
+    return r
+
+
+def setup_split_kv(B: Bench, small: bool) -> Run:
+    """One long sequence, keys split over the ranks on page boundaries: records for the local keys ->
+    one kernel per rank reduces them, stores the reduced record into every rank's buffer over NVLink
+    peer mappings and merges the world's records in rank order (or: reduce -> NCCL all-gather ->
+    merge). Total work is fixed: strong scaling."""
+    from espetero_b200 import capi, host, shard, workloads as wl
+    torch, dist, args = B.torch, B.dist, B.args
+    rank, world, dev = B.rank, B.world, B.dev
+    r = Run()
+    r.name, r.split_kv, r.scaling = "c5", True, "strong"
+    ctx_all = 8192 if small else 131072
+    lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
+    w = r.w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
+    op = r.op = host.AttnOp.for_workload(w, TILE_ROWS["c5"], B.local)
+    base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, args.groups or 148 * 2, TILE_ROWS["c5"])
+    tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
+    r.plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, TILE_ROWS["c5"])
+    dp = r.dp = op.upload(w, r.plan)
+    for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
+        dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
+    layers = r.layers = LayerCycle(op, dp, w)
+    r.a_attn = layers.args()
+    r.a_full = r.a_attn
+    red_dev = host._dev(red_jobs, dev)
+    merge_dev = host._dev(shard.world_merge_jobs(1, world), dev)
+    rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
+    rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)
+    xch = None
+    if args.exchange == "p2p":
+        try:
+            xch = host.PeerExchange(op, n_jobs=1, rows_max=1)
+            ok = 1
+        except Exception as e:  # noqa: BLE001 - reported below, then the NCCL path is used
+            print(f"[rank {rank}] peer exchange unavailable: {e}", file=sys.stderr, flush=True)
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # all ranks decide together
+        if int(flag.item()) == 0:
+            xch = None
+    r.xch = xch
+    if xch is not None:
+        def step():
+            xch.next_epoch()
+            op.forward(dp, layers.next(r.a_attn))
+            op.exchange_parts(dp, dp.parts, red_dev, len(red_jobs), xch, parts_max=n_parts)
+        r.sharding = "KV range per rank; one kernel per rank merges, exchanges records over NVLink peer stores and finishes"
+    else:
+        def step():
+            op.forward(dp, layers.next(r.a_attn))
+            op.reduce_parts(dp, dp.parts, red_dev, len(red_jobs), rec_local, 0)
+            dist.all_gather_into_tensor(rec_world, rec_local)
+            op.combine(dp, rec_world, merge_dev, 1)
+        r.sharding = "KV range per rank; reduced records all-gathered (NCCL), merged on every rank"
+    r.step = step
+    r.step_attn = lambda: op.forward(dp, layers.next(r.a_attn))
+    return r
+
+
+def time_run(B: Bench, r: Run, steps: int, W: int, solo: bool = False):
+    """(seconds per step of the whole pass, of the attention kernel alone, launches per step)."""
+    for _ in range(W):
+        r.step()
+    r.op.check_status()
+    n0 = r.op.launch_count
+    t_total = B.timed(r.step, steps, solo=solo)
+    launches = r.op.launch_count - n0
+    for _ in range(3):
+        r.step_attn()
+    t_attn = B.timed(r.step_attn, steps, solo=solo) / steps
+    return t_total / steps, t_attn, launches
+
+
+def time_e2e(B: Bench, r: Run, steps: int, t_step: float):
+    """End to end through the C ABI from host buffers: the step's inputs (Q, Kb, Vb and the plan
+    tables) come from pinned host memory, the result goes back; the KV pool is device state."""
+    from espetero_b200 import host
+    torch = B.torch
+    op, dp, layers, stream, dev = r.op, r.dp, r.layers, B.stream, B.dev
     arena = host.StepArena(dp)
     a_e2e = arena.patch(op.make_args(dp))
     h_out = torch.empty_like(dp.O, device="cpu").pin_memory()
     h2d = arena.nbytes
     d2h = h_out.numel() * h_out.element_size()
-
-    if split_kv:
-        a_attn.Q, a_attn.Kb, a_attn.Vb = a_e2e.Q, a_e2e.Kb, a_e2e.Vb  # the step reads its inputs from the arena
-        a_attn.tiles, a_attn.trees, a_attn.blocks = a_e2e.tiles, a_e2e.trees, a_e2e.blocks
-
+    if r.split_kv:
+        a = r.a_attn  # the step reads its inputs from the arena
+        a.Q, a.Kb, a.Vb, a.tiles, a.trees, a.blocks = a_e2e.Q, a_e2e.Kb, a_e2e.Vb, a_e2e.tiles, a_e2e.trees, a_e2e.blocks
     e2e_tail = None
     # Passes of a few microseconds are bound by the host's calls, not by the GPU: pipelining them over
     # three streams only adds calls, so they keep the plain sequence on one stream.
-    sequential = split_kv or t_total / args.steps < 25e-6
-    if sequential:
+    if r.split_kv or t_step < 25e-6:
         def step_e2e():
             arena.upload()
-            if split_kv:
-                step()
+            if r.split_kv:
+                r.step()
             else:
                 op.forward(dp, layers.next(a_e2e))
             h_out.copy_(dp.O, non_blocking=True)
-        e2e_note = "Q/Kb/Vb + plan tables in one arena copied from pinned host memory, O back to the host; the KV pool is resident device state"
+        note = "Q/Kb/Vb + plan tables in one arena copied from pinned host memory, O back to the host; the KV pool is resident device state"
     else:
         # Every step copies its own inputs up and its own result down; the steps are pipelined over two
         # sets of buffers and three streams, so the copies of step i + 1 cross PCIe while step i computes
@@ -465,24 +545,146 @@ def main():
         def e2e_tail():
             for ev in fetched:
                 stream.wait_event(ev)
-        e2e_note = ("Q/Kb/Vb + plan tables in one arena copied from pinned host memory, O back to the host, every step; two buffer sets, "
-                    "copies of step i+1 overlap the kernels of step i; the KV pool is resident device state")
+        note = ("Q/Kb/Vb + plan tables in one arena copied from pinned host memory, O back to the host, every step; two buffer sets, "
+                "copies of step i+1 overlap the kernels of step i; the KV pool is resident device state")
     for _ in range(3):
         step_e2e()
-    t_e2e = timed(step_e2e, args.steps, e2e_tail)
+    return B.timed(step_e2e, steps, e2e_tail) / steps, h2d, d2h, note
+
+
+def close_run(r: Run):
+    if r.xch is not None:
+        r.xch.close()
+    r.op.close()
+
+
+def strong_scaling_legs(B: Bench, steps: int):
+    """At N > 1: the two fixed-total-work cases, each with the one-GPU time measured by rank 0 alone in
+    the same run (the other ranks wait), so that the line carries its own efficiency."""
+    from espetero_b200 import shard, workloads as wl
+    torch = B.torch
+    out = {}
+    # ---- the one 32-sequence batch of the configuration, spread over the GPUs by context length
+    lens = wl.c2_context_lengths(0xE5B202, 32, 512, 32768)
+    mine = shard.lpt_partition(lens, B.world)[B.rank]
+    w = wl.config_c2(0xE5B202 + 1000 * B.rank, lens=lens[mine] if len(mine) else lens[:1])
+    r = setup_sequences(B, "c2", w, "strong", "the 32 sequences spread by total context length (LPT), no collective")
+    t_step, t_attn, _ = time_run(B, r, steps, 3)
+    (t_step, t_attn), bytes_all = B.reduce_max_sum([t_step, t_attn], w.kv_bytes_read() if len(mine) else 0)
+    close_run(r)
+    t1 = 0.0
+    if B.rank == 0:
+        w1 = wl.config_c2(0xE5B202)
+        r1 = setup_sequences(B, "c2", w1, "strong", "one GPU")
+        t1, _, _ = time_run(B, r1, steps, 3, solo=True)
+        close_run(r1)
+    B.barrier()
+    if B.rank == 0:
+        out["c2_strong"] = {"workload": "c2_batched_decode: ONE batch of 32 sequences over all GPUs", "scaling": "strong",
+                            "sequences_per_gpu": len(mine), "value": bytes_all / t_step / 1e9, "unit": UNIT,
+                            "us_per_step": 1e6 * t_step, "us_attention_kernel": 1e6 * t_attn, "us_per_step_one_gpu": 1e6 * t1,
+                            "speedup_vs_n1": t1 / t_step, "efficiency_vs_n1": t1 / t_step / B.world}
+    # ---- one 131072-token sequence, keys split over the GPUs by range
+    r = setup_split_kv(B, small=False)
+    t_step, t_attn, launches = time_run(B, r, steps, 3)
+    (t_step, t_attn), bytes_all = B.reduce_max_sum([t_step, t_attn], r.w.kv_bytes_read())
+    route = "p2p" if r.xch is not None else "nccl"
+    close_run(r)
+    t1 = 0.0
+    if B.rank == 0:
+        w1 = wl.config_c5()
+        r1 = setup_sequences(B, "c5", w1, "strong", "one GPU")
+        t1, _, _ = time_run(B, r1, steps, 3, solo=True)
+        close_run(r1)
+    B.barrier()
+    if B.rank == 0:
+        out["split_kv"] = {"workload": "c5_long_fp8_decode: one 131072-token sequence, keys split over the GPUs by range",
+                           "scaling": "strong", "exchange": route, "value": bytes_all / t_step / 1e9, "unit": UNIT,
+                           "us_per_step": 1e6 * t_step, "us_attention_kernel": 1e6 * t_attn,
+                           "us_exchange": 1e6 * (t_step - t_attn), "launches_per_step": launches // max(1, steps),
+                           "us_per_step_one_gpu": 1e6 * t1, "speedup_vs_n1": t1 / t_step, "efficiency_vs_n1": t1 / t_step / B.world}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
+    ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
+    ap.add_argument("--fuse", type=int, default=-1, help="option fuse_combine of the library (0 off, 1 small passes, 2 always); -1: its default")
+    ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    B = Bench(args)
+    torch, dist = B.torch, B.dist
+    from espetero_b200 import workloads as wl
+    rank, world, dev = B.rank, B.world, B.dev
+    W = max(3, args.warmup)
+
+    if args.workload == "c5" and world > 1:
+        r = setup_split_kv(B, args.small)
+    else:
+        w = build_workload(args.workload, rank, args.small, world)
+        sharding = "sequences per rank, no collective" + (
+            "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
+        r = setup_sequences(B, args.workload, w, "weak", sharding)
+    w, op, plan = r.w, r.op, r.plan
+    bytes_step = w.kv_bytes_read()
+
+    # ---- device-resident throughput (value) and the attention kernel alone (roofline of the dominant kernel)
+    sampler = ClockSampler(B.local)
+    if rank == 0:
+        sampler.start()
+    t_step, t_attn, launches = time_run(B, r, args.steps, W)
+    # nvidia-smi samples every 100 ms: keep the same kernels running (untimed) until it has seen the
+    # GPU under this load for about half a second, on every rank alike
+    # (a fixed number of steps derived from rank 0's timing, so that ranks which exchange records
+    # inside a step all run the same count)
+    hold = torch.tensor([min(20000, int(0.6 / max(t_step, 1e-6)) + 1)], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.broadcast(hold, src=0)
+    for _ in range(int(hold.item())):
+        r.step()
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop() if rank == 0 else None
+    op.check_status()
+
+    t_e2e, h2d, d2h, e2e_note = time_e2e(B, r, args.steps, t_step)
+
+    # ---- parity of exactly this pass (plan, options, sizes) with the float64 oracle, off the timed region
+    parity = None
+    if world == 1 and not args.no_check:
+        r.dp.O.zero_()
+        r.dp.lse.zero_()
+        a = r.layers.args()
+        a.p.kv_base = w.kv_base  # the first layer region holds the workload's own pool
+        op.forward(r.dp, a)
+        op.check_status()
+        torch.cuda.synchronize(dev)
+        parity = parity_report(args.workload, w, r.dp.O.cpu().numpy().view(np.uint16), r.dp.lse.cpu().numpy())
 
     # ---- aggregate over ranks: max time, summed bytes
-    tt = torch.tensor([t_total, t_attn, t_e2e], dtype=torch.float64, device=dev)
-    bb = torch.tensor([float(bytes_step)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dist.all_reduce(bb, op=dist.ReduceOp.SUM)
-    t_total, t_attn_max, t_e2e = [float(x) for x in tt.cpu()]
-    bytes_all = float(bb.cpu()[0])
+    (t_step, t_attn_max, t_e2e), bytes_all = B.reduce_max_sum([t_step, t_attn, t_e2e], bytes_step)
+    kernel_name = op.last_kernel
+    scaling, sharding, split_kv = r.scaling, r.sharding, r.split_kv
+    close_run(r)
+
+    extra = {}
+    if world > 1 and args.workload == "c2" and not (args.no_strong or args.small):
+        extra = strong_scaling_legs(B, min(args.steps, 50))
 
     if rank == 0:
         hbm_peak, tf_peak, which = measured_peaks()
-        value = bytes_all * args.steps / t_total / 1e9
+        value = bytes_all / t_step / 1e9
         achieved = bytes_step / t_attn / 1e9
         flops = attention_flops(w)
         traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv) else None
@@ -493,33 +695,37 @@ def main():
             tensor["frac_of_sustained"] = tensor["tflops"] / measured_peaks.sustained_tflops
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": W,
-            "ms_per_step": 1e3 * t_total / args.steps, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "ms_per_step": 1e3 * t_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16" if w.kv_dtype != wl.E4M3 else "e4m3->f16", "data": "synthetic",
-            "config": {"workload": w.name, "sequences_per_gpu": len(w.trees), "H": w.H, "Hkv": w.Hkv, "HD": w.HD, "page": w.bt,
-                       "kv_bytes_per_gpu": bytes_step, "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": op.last_kernel,
-                       "l2": layers.describe(),
-                       "sharding": sharding},
+            "config": workload_config(w),
+            "plan": {"planner": "ESP_PLAN_B200", "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": kernel_name,
+                     "sharding": sharding},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": traffic, "peak_source": which, "kernel": op.last_kernel, "ms_per_launch": 1e3 * t_attn},
-            "e2e": {"value": bytes_all * args.steps / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                         "traffic": traffic, "peak_source": which, "kernel": kernel_name, "ms_per_launch": 1e3 * t_attn,
+                         "launch": "the attention kernel alone: the same plan launched without its combine jobs (records only)",
+                         "step_frac": bytes_step / t_step / 1e9 / hbm_peak if world == 1 else bytes_all / world / t_step / 1e9 / hbm_peak,
+                         "step": "the whole pass (attention kernel + merge of the split-K records), as in `value`"},
+            "e2e": {"value": bytes_all / t_e2e / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": e2e_note},
             "gpu_launches": int(launches), "clocks": clocks, "tensor": tensor,
         }
         if args.workload == "c3":  # the prefill configuration is bound by the tensor cores, not by HBM
             line["metric"], line["unit"] = "prefill_attn_tflops", "TFLOP/s"
-            line["value"] = flops * world * args.steps / t_total / 1e12
+            line["value"] = flops * world / t_step / 1e12
+            sm = (clocks or {}).get("sm_mhz")
             line["roofline"] = {"bound": "tensor", "achieved": tensor["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
-                                "frac": tensor["frac"], "traffic": traffic, "peak_source": which, "kernel": op.last_kernel,
-                                "ms_per_launch": 1e3 * t_attn}
-            line["e2e"]["value"] = flops * world * args.steps / t_e2e / 1e12
+                                "frac": tensor["frac"], "traffic": traffic, "peak_source": which, "kernel": kernel_name,
+                                "ms_per_launch": 1e3 * t_attn, "step_frac": flops / t_step / 1e12 / tf_peak,
+                                "ms_x_sm_mhz": (1e3 * t_attn * sm) if sm else None}
+            line["e2e"]["value"] = flops * world / t_e2e / 1e12
             line["e2e"]["unit"] = "TFLOP/s"
+        if parity is not None:
+            line["parity"] = parity
+        line.update(extra)
         if world == 1 and not args.no_cpu:
             v, threads, sample, dt = time_cpu(args.workload)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
         print(json.dumps(line), flush=True)
-    if xch is not None:
-        xch.close()
-    op.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -143,6 +143,7 @@ PROTOTYPES = {
     "esp_forest_anc_masks": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "esp_attn_decode_static": (C.c_int, [C.POINTER(Shape), C.c_void_p, C.POINTER(Args)]),
     "esp_attn_decode_static_status": (C.c_int, [C.c_void_p]),
+    "esp_attn_finite_check": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int32, C.c_float, C.c_void_p]),
     "esp_attn_set_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "esp_attn_stamp": (C.c_int, [C.c_void_p, C.c_void_p]),
     "esp_attn_last_kernel": (C.c_char_p, [C.c_void_p]),

@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "host_util.h"
 #include "launch.h"
@@ -31,6 +32,8 @@ struct esp_attn_ctx {
   unsigned long long* trace = nullptr;  // caller-owned device buffer (esp_attn_set_trace)
   int32_t trace_blocks = 0;
   int opt_fuse_combine = 1;  // small tcgen05 passes merge their split-K records in the attention kernel (last CTA of a job)
+  bool finite_armed = false;  // a pass has been checked since the record was last read
+  int opt_check_finite = 0;  // scan O for NaN / Inf after every pass (ESPETERO_CHECK_FINITE of the reference)
   int opt_trace_ctas = 0;  // per-CTA stamps behind the block events (the buffer must hold 8 * n_blocks + 2 + 4 * this)
   // driver entry point for tensor maps, resolved without linking libcuda
   void* encode_tiled = nullptr;
@@ -46,6 +49,17 @@ struct esp_attn_ctx {
   const void* umap_vb = nullptr;
   uint64_t umap_base = 0;
   int32_t umap_blocks = 0, umap_rows = 0, umap_ld = 0;
+  // Re-planning of reference-shaped multi-row passes (8-row tiles) for the tensor-core kernels: the new
+  // tiles and jobs are built on the host and travel through a small ring of pinned staging slots into
+  // device slots of the context (see replan_pass).
+  int opt_replan = 1;
+  uint8_t* replan_dev = nullptr;
+  uint8_t* replan_host = nullptr;
+  cudaEvent_t replan_done[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool replan_used[4] = {false, false, false, false};
+  int replan_next = 0;
+  std::vector<esp_attn_tile> rp_tiles;
+  std::vector<esp_attn_combine> rp_jobs;
 };
 
 namespace {
@@ -53,6 +67,7 @@ namespace {
 // The context's device allocation: the status word, then (64 ints further) the arrival counters
 // of fused merges.
 constexpr size_t kStatusBytes = sizeof(int) * (64 + esp::kFixupCounters);
+constexpr int kFiniteRecAt = 16;  // ints 16..19 of the status header: the finite-check record of the last pass
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -66,7 +81,7 @@ int elem_bytes(int dt) { return dt == ESP_E4M3 ? 1 : 2; }
 
 int check_shape(const esp_attn_shape& s) {
   if (s.H <= 0 || s.Hkv <= 0 || s.H % s.Hkv != 0) return fail(ESP_ERR_INVALID, "shape: H=%d must be a positive multiple of Hkv=%d", s.H, s.Hkv);
-  if (s.HD != 64 && s.HD != 128 && s.HD != 256) return fail(ESP_ERR_UNSUPPORTED, "shape: head dim %d (64, 128 or 256)", s.HD);
+  if (s.HD != 64 && s.HD != 128 && s.HD != 256 && s.HD != 512) return fail(ESP_ERR_UNSUPPORTED, "shape: head dim %d (64, 128, 256 or 512)", s.HD);
   if (s.bt <= 0) return fail(ESP_ERR_INVALID, "shape: bt=%d", s.bt);
   if (s.q_dtype != ESP_F16 && s.q_dtype != ESP_BF16) return fail(ESP_ERR_UNSUPPORTED, "shape: q_dtype %d (fp16 or bf16)", s.q_dtype);
   if (s.kv_dtype != s.q_dtype && s.kv_dtype != ESP_E4M3)
@@ -206,6 +221,46 @@ int umma_tensor_maps(esp_attn_ctx* c, const esp_attn_args& a) {
   return ESP_OK;
 }
 
+constexpr int kReplanSlots = 4;
+constexpr int kReplanTiles = 8192, kReplanJobs = 8192;
+constexpr size_t kReplanSlotBytes = size_t(kReplanTiles) * sizeof(esp_attn_tile) + size_t(kReplanJobs) * sizeof(esp_attn_combine);
+
+// Does the plan compute plain full attention for every row of every tree - each 8-row group of each
+// tree covered once, over the whole cached range [0, P) (in one tile, or in split tiles that tile the
+// range in order and are all merged by one job of this pass), batch keys scanned by the tile that
+// ends at P? That is what the reference's planners emit (plan_tiles, src/model/impl/forest.h:1378-1433);
+// such a pass may be re-planned freely: only O and lse are its results.
+bool full_attention_plan(const esp_attn_args& a, int TR) {
+  if (!a.tiles_host || !a.trees_host || (a.n_jobs > 0 && !a.jobs_host)) return false;
+  int ti = 0, ji = 0;
+  for (int t = 0; t < a.n_trees; ++t) {
+    const esp_attn_tree& tr = a.trees_host[t];
+    for (int r = 0; r < tr.M; r += TR) {
+      if (ti >= a.n_tiles) return false;
+      const esp_attn_tile& first = a.tiles_host[ti];
+      if (first.tree != t || first.r0 != tr.base + r || first.pad0 != 0 || first.k0 != 0) return false;
+      if (first.part < 0) {
+        if (first.k1 != tr.P || !first.last) return false;
+        ++ti;
+        continue;
+      }
+      if (ji >= a.n_jobs) return false;
+      const esp_attn_combine& job = a.jobs_host[ji++];
+      if (job.r0 != tr.base + r || job.rows != std::min(TR, tr.M - r) || job.part0 != first.part || job.nparts < 1) return false;
+      int k = 0;
+      for (int s2 = 0; s2 < job.nparts; ++s2, ++ti) {
+        if (ti >= a.n_tiles) return false;
+        const esp_attn_tile& x = a.tiles_host[ti];
+        if (x.tree != t || x.r0 != tr.base + r || x.part != job.part0 + s2 || x.k0 != k || x.k1 <= x.k0 || x.pad0 != 0) return false;
+        if ((x.last != 0) != (x.k1 == tr.P)) return false;
+        k = x.k1;
+      }
+      if (k != tr.P) return false;
+    }
+  }
+  return ti == a.n_tiles && ji == a.n_jobs;
+}
+
 int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "attn_gqa")) return &c->opt_attn_gqa;
   if (!std::strcmp(name, "attn_umma")) return &c->opt_attn_umma;
@@ -214,6 +269,8 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "trace_ctas")) return &c->opt_trace_ctas;
   if (!std::strcmp(name, "fuse_combine")) return &c->opt_fuse_combine;
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
+  if (!std::strcmp(name, "check_finite")) return &c->opt_check_finite;
+  if (!std::strcmp(name, "replan")) return &c->opt_replan;
   return nullptr;
 }
 
@@ -221,7 +278,8 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
                         const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
-                        float* out_parts = nullptr, int32_t out_part0 = 0, const esp_attn_combine* jobs_host = nullptr);
+                        float* out_parts = nullptr, int32_t out_part0 = 0, const esp_attn_combine* jobs_host = nullptr,
+                        int tile_rows = 0);
 
 extern "C" {
 
@@ -247,6 +305,7 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
   c->tile_rows = shape->tile_rows > 0 ? shape->tile_rows : 8;
   c->shape.tile_rows = c->tile_rows;
   if (const char* env = std::getenv("ESPETERO_FAIL_PASS")) c->fail_every = std::atoi(env);
+  if (const char* env = std::getenv("ESPETERO_CHECK_FINITE")) c->opt_check_finite = (*env && std::strcmp(env, "0") && std::strcmp(env, "off")) ? 1 : 0;
   cudaDriverEntryPointQueryResult qres{};
   e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &c->encode_tiled, cudaEnableDefault, &qres);
   if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !c->encode_tiled) {
@@ -270,6 +329,14 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
     delete c;
     return cuda_fail(e, "cudaMemset(status word)");
   }
+  // slots for re-planned passes (1.5 MB on the device, as much pinned on the host)
+  e = cudaMalloc(reinterpret_cast<void**>(&c->replan_dev), kReplanSlots * kReplanSlotBytes);
+  if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&c->replan_host), kReplanSlots * kReplanSlotBytes);
+  for (int i = 0; e == cudaSuccess && i < kReplanSlots; ++i) e = cudaEventCreateWithFlags(&c->replan_done[i], cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    esp_attn_destroy(c);
+    return cuda_fail(e, "esp_attn_create: plan staging slots");
+  }
   *out = c;
   return ESP_OK;
 }
@@ -277,6 +344,10 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
 int esp_attn_destroy(esp_attn_ctx* c) {
   if (!c) return ESP_OK;
   cudaSetDevice(c->device);
+  for (int i = 0; i < kReplanSlots; ++i)
+    if (c->replan_done[i]) cudaEventDestroy(c->replan_done[i]);
+  if (c->replan_dev) cudaFree(c->replan_dev);
+  if (c->replan_host) cudaFreeHost(c->replan_host);
   if (c->d_status) cudaFree(c->d_status);
   delete c;
   return ESP_OK;
@@ -316,11 +387,20 @@ uint64_t esp_attn_launch_count(const esp_attn_ctx* c) { return c ? c->launches :
 // and clears it. Synchronises the stream: meant for tests and post-mortems, not the hot path.
 int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
   if (!c) return fail(ESP_ERR_INVALID, "esp_attn_check_status: null context");
-  int st = 0;
+  int hdr[kFiniteRecAt + 4] = {0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyAsync(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, s);
+  cudaError_t e = cudaMemcpyAsync(hdr, c->d_status, sizeof(hdr), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return cuda_fail(e, "reading the status word");
+  const int st = hdr[0];
+  if (st == 0 && c->finite_armed && uint32_t(hdr[kFiniteRecAt]) != 0) {
+    // the record of the last checked pass (site "attn_out" of the reference's detector)
+    const uint32_t hits = uint32_t(hdr[kFiniteRecAt]), idx = uint32_t(hdr[kFiniteRecAt + 1]), cols = uint32_t(c->shape.H * c->shape.HD);
+    float val;
+    std::memcpy(&val, &hdr[kFiniteRecAt + 3], 4);
+    cudaMemsetAsync(c->d_status + kFiniteRecAt, 0, 4 * sizeof(int), s);
+    return fail(ESP_ERR_CUDA, "attn_out: %u non-finite elements, first at row %u, column %u (value %g)", hits, idx / cols, idx % cols, double(val));
+  }
   if (st != 0) {
     cudaMemsetAsync(c->d_status, 0, kStatusBytes, s);  // the arrival counters too: a kernel that gave up may have left some behind
     return fail(ESP_ERR_CUDA, "a kernel gave up a bounded wait (status %d: %s)", st,
@@ -330,9 +410,75 @@ int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
   return ESP_OK;
 }
 
+// A reference-shaped multi-row pass (tiles of 8 rows, forest.h:1378-1433) would have to run on the
+// CUDA-core kernel: the tcgen05 kernels want 128 (row, head) pairs per CTA. When the plan is plain full
+// attention (full_attention_plan) only O and lse are results of the pass, so the pass is planned again
+// here for the tensor-core kernels - 128-row tiles for passes over their own rows (prefill), tiles of
+// 128 / G rows with the G heads of a kv head for passes over a cached prefix (verify) - and the new
+// tiles and jobs replace the caller's for this call. Records go to the caller's `parts` in the new
+// tiles' layout (the split is chosen so that they fit). Returns false when the pass stays as it is.
+static bool replan_pass(esp_attn_ctx* c, esp_attn_args& a, int& TR, cudaStream_t stream, int* rc) {
+  *rc = ESP_OK;
+  const esp_attn_shape& s = c->shape;
+  int64_t cached = 0, batch = 0;
+  for (int i = 0; i < a.n_trees; ++i) cached += int64_t(a.trees_host[i].P) * a.trees_host[i].M, batch += int64_t(a.trees_host[i].M) * a.trees_host[i].M / 2;
+  const bool stream_hbm = s.HD == 128 && cached > 2 * batch;
+  int hpc = 1;
+  if (stream_hbm)
+    for (int h = 8; h >= 1; h >>= 1)
+      if (h <= c->G && c->G % h == 0) {
+        hpc = h;
+        break;
+      }
+  const int new_TR = 128 / hpc;
+  if (!esp::flash_umma_supports(s.HD, c->G, new_TR, s.bt, s.q_dtype, s.kv_dtype)) return false;
+  esp_plan_opts o{};
+  o.mode = ESP_PLAN_B200, o.min_chunk = 32, o.tile_rows = new_TR, o.max_parts = 64;
+  o.groups = stream_hbm ? 148 : 148 * 2 * 8;
+  o.split = (a.parts && a.n_parts > 0) ? (1 << 20) : 0;
+  int32_t nt = 0, nj = 0, np = 0;
+  c->rp_tiles.resize(kReplanTiles), c->rp_jobs.resize(kReplanJobs);
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    const int prc = esp_attn_plan(a.trees_host, a.n_trees, s.Hkv, &o, c->rp_tiles.data(), kReplanTiles, c->rp_jobs.data(), kReplanJobs, &nt, &nj, &np);
+    if (prc != ESP_OK) return false;  // more tiles than the slots hold: the pass stays on the general kernel
+    // the records must fit the caller's buffer: n_parts records of 8 rows there, np records of new_TR rows here
+    if (int64_t(np) * new_TR <= int64_t(a.n_parts) * TR) break;
+    if (attempt == 1) return false;
+    o.split = 0;
+  }
+  // a free staging slot (its previous pass has run)
+  const int slot = c->replan_next;
+  c->replan_next = (slot + 1) % kReplanSlots;
+  if (c->replan_used[slot]) {
+    const cudaError_t e = cudaEventSynchronize(c->replan_done[slot]);
+    if (e != cudaSuccess) {
+      *rc = cuda_fail(e, "waiting for a plan staging slot");
+      return false;
+    }
+  }
+  uint8_t* h = c->replan_host + size_t(slot) * kReplanSlotBytes;
+  uint8_t* d = c->replan_dev + size_t(slot) * kReplanSlotBytes;
+  const size_t tiles_bytes = size_t(nt) * sizeof(esp_attn_tile), jobs_at = size_t(kReplanTiles) * sizeof(esp_attn_tile);
+  std::memcpy(h, c->rp_tiles.data(), tiles_bytes);
+  std::memcpy(h + jobs_at, c->rp_jobs.data(), size_t(nj) * sizeof(esp_attn_combine));
+  cudaError_t e = cudaMemcpyAsync(d, h, tiles_bytes, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess && nj > 0) e = cudaMemcpyAsync(d + jobs_at, h + jobs_at, size_t(nj) * sizeof(esp_attn_combine), cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) {
+    *rc = cuda_fail(e, "uploading the re-planned tiles");
+    return false;
+  }
+  c->replan_used[slot] = true;
+  a.tiles = reinterpret_cast<const esp_attn_tile*>(d), a.tiles_host = c->rp_tiles.data(), a.n_tiles = nt;
+  a.jobs = nj > 0 ? reinterpret_cast<const esp_attn_combine*>(d + jobs_at) : nullptr, a.jobs_host = nj > 0 ? c->rp_jobs.data() : nullptr, a.n_jobs = nj;
+  a.n_parts = int32_t(int64_t(a.n_parts) * TR / new_TR);
+  TR = new_TR;
+  *rc = slot + 1;  // the caller records the slot's event once the pass is enqueued
+  return true;
+}
+
 int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   if (!c || !ap) return fail(ESP_ERR_INVALID, "esp_attn_forward: null argument");
-  const esp_attn_args& a = *ap;
+  esp_attn_args a = *ap;  // the pass as it runs: re-planning may replace tiles and jobs
   const esp_attn_shape& s = c->shape;
   if (int rc = check_params(c, a.p)) return rc;
   if (int rc = validate(c, a)) return rc;
@@ -341,18 +487,8 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     return fail(ESP_ERR_INJECTED, "attention pass failed: injected (ESPETERO_FAIL_PASS)");
   if (a.n_tiles == 0) return ESP_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int TR = c->tile_rows;
 
-  esp::KernelArgs k{};
-  k.Q = a.Q, k.Kb = a.Kb, k.Vb = a.Vb, k.kv = a.kv, k.kv_scales = a.kv_scales, k.blocks = a.blocks;
-  k.desc = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? nullptr : a.desc;
-  k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
-  k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
-  k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status, k.counters = c->d_status + 64;
-  k.trace = c->trace, k.trace_blocks = c->trace_blocks, k.trace_ctas = c->trace ? c->opt_trace_ctas : 0;
-  k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_tiles = a.n_tiles;
-  k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
-  k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
-  k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
   const bool windowed = a.window > 0 || a.ring > 0 || a.bidi != 0;  // the generic kernel's layer options (80_gemma.metal)
 
   // Kernel choice, as forest.h:2864-2868: single-row trees with G <= 8 take the decode kernel.
@@ -370,10 +506,30 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   const bool widen = fp8_pool && a.dequant_scratch != nullptr && a.n_block_entries > 0 && a.kv != nullptr && a.blocks != nullptr &&
                      a.dequant_scratch_bytes >= widened_pool_bytes + ((size_t(a.n_block_entries) * 4 + 127) / 128) * 128 &&
                      (reinterpret_cast<uintptr_t>(a.dequant_scratch) & 127) == 0 && a.p.kv_ld % 8 == 0 && a.p.kv_base % 8 == 0;
-  bool umma = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen) &&
-              esp::flash_umma_supports(s.HD, c->G, c->tile_rows, s.bt, s.q_dtype, fp8_pool ? s.q_dtype : s.kv_dtype) &&
-              a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
+  const bool umma_ok = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen) &&
+                       a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
+  // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.
+  int replan_slot = -1;
+  if (umma_ok && TR == 8 && c->opt_replan && !single && full_attention_plan(a, TR)) {
+    int rrc = ESP_OK;
+    if (replan_pass(c, a, TR, stream, &rrc)) replan_slot = rrc - 1;
+    else if (rrc != ESP_OK) return rrc;
+  }
+  bool umma = umma_ok && esp::flash_umma_supports(s.HD, c->G, TR, s.bt, s.q_dtype, fp8_pool ? s.q_dtype : s.kv_dtype);
   for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+
+  esp::KernelArgs k{};
+  k.Q = a.Q, k.Kb = a.Kb, k.Vb = a.Vb, k.kv = a.kv, k.kv_scales = a.kv_scales, k.blocks = a.blocks;
+  k.desc = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? nullptr : a.desc;
+  k.anc_mask = (s.flags & ESP_ATTN_FLAG_ANC_MASK) ? a.anc_mask : nullptr;
+  k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? a.X : nullptr;
+  k.O = a.O, k.lse = a.lse, k.parts = a.parts, k.tiles = a.tiles, k.trees = a.trees, k.status = c->d_status, k.counters = c->d_status + 64;
+  k.trace = c->trace, k.trace_blocks = c->trace_blocks, k.trace_ctas = c->trace ? c->opt_trace_ctas : 0;
+  k.p = a.p, k.HD = s.HD, k.G = c->G, k.tile_rows = TR, k.n_tiles = a.n_tiles;
+  k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
+  k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
+  k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
+
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {
     int32_t* identity = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.dequant_scratch) + widened_pool_bytes);
@@ -426,7 +582,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   }
   if (e != cudaSuccess) return cuda_fail(e, c->last_kernel);
   if (a.n_jobs > 0 && !merged) {
-    int rows_max = c->tile_rows, parts_max = 64;
+    int rows_max = TR, parts_max = 64;
     if (a.jobs_host) {
       rows_max = 1, parts_max = 1;
       for (int i = 0; i < a.n_jobs; ++i) {
@@ -434,8 +590,31 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
         parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
       }
     }
-    return combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max, nullptr, 0, a.jobs_host);
+    if (int rc = combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max, nullptr, 0, a.jobs_host, TR)) return rc;
   }
+  if (replan_slot >= 0) cudaEventRecord(c->replan_done[replan_slot], stream);  // the slot's tiles and jobs have been read
+  if (c->opt_check_finite && a.n_rows > 0) {
+    const cudaError_t fe = esp::launch_finite_check(a.O, uint32_t(a.n_rows), uint32_t(s.H * s.HD), uint64_t(a.p.q_ld),
+                                                    s.q_dtype == ESP_F16 ? ESP_FINITE_F16 : ESP_FINITE_BF16, 0x7F800000u,
+                                                    reinterpret_cast<uint32_t*>(c->d_status + kFiniteRecAt), stream, &c->launches);
+    if (fe != cudaSuccess) return cuda_fail(fe, "finite_check");
+    c->finite_armed = true;
+  }
+  return ESP_OK;
+}
+
+int esp_attn_finite_check(void* stream, const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int32_t dtype, float threshold,
+                          esp_finite_rec* rec) {
+  if (!x || !rec || ld < cols) return fail(ESP_ERR_INVALID, "esp_attn_finite_check: null pointer or ld < cols");
+  if (dtype != ESP_FINITE_F32 && dtype != ESP_FINITE_F16 && dtype != ESP_FINITE_BF16) return fail(ESP_ERR_INVALID, "esp_attn_finite_check: dtype %d", dtype);
+  if (uint64_t(rows) * cols >= 0xFFFFFFFFull) return fail(ESP_ERR_UNSUPPORTED, "esp_attn_finite_check: more than 2^32 - 1 elements");
+  if (rows == 0 || cols == 0) return ESP_OK;
+  uint32_t thr_bits;
+  std::memcpy(&thr_bits, &threshold, 4);
+  thr_bits &= 0x7FFFFFFFu;
+  if (thr_bits > 0x7F800000u) thr_bits = 0x7F800000u;  // a NaN threshold: only NaN and Inf offend
+  const cudaError_t e = esp::launch_finite_check(x, rows, cols, ld, dtype, thr_bits, reinterpret_cast<uint32_t*>(rec), static_cast<cudaStream_t>(stream), nullptr);
+  if (e != cudaSuccess) return cuda_fail(e, "finite_check");
   return ESP_OK;
 }
 
@@ -548,7 +727,7 @@ int esp_p2p_free(void* ptr) {
 
 static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const float* X, void* O, float* lse,
                         const esp_attn_params* p, const esp_attn_combine* jobs, int32_t n_jobs, int rows_max, int parts_max,
-                        float* out_parts, int32_t out_part0, const esp_attn_combine* jobs_host) {
+                        float* out_parts, int32_t out_part0, const esp_attn_combine* jobs_host, int tile_rows) {
   if (!c || !p) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null argument");
   if (n_jobs <= 0) return ESP_OK;
   if (!parts || (!O && !out_parts) || !jobs) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: null parts / O / jobs");
@@ -557,8 +736,9 @@ static int combine_impl(esp_attn_ctx* c, void* stream, const float* parts, const
   if ((s.flags & ESP_ATTN_FLAG_GATE) && !X) return fail(ESP_ERR_INVALID, "esp_attn_combine_parts: gate flag set but X is null");
   esp::CombineArgs k{};
   k.parts = parts, k.X = (s.flags & ESP_ATTN_FLAG_GATE) ? X : nullptr, k.O = O, k.lse = lse, k.jobs = jobs, k.p = *p;
-  k.HD = s.HD, k.G = c->G, k.tile_rows = c->tile_rows, k.n_jobs = n_jobs, k.q_dtype = s.q_dtype;
-  k.rows_max = rows_max < 1 ? 1 : (rows_max > c->tile_rows ? c->tile_rows : rows_max);
+  const int TR = tile_rows > 0 ? tile_rows : c->tile_rows;  // a re-planned pass merges records of its own tile height
+  k.HD = s.HD, k.G = c->G, k.tile_rows = TR, k.n_jobs = n_jobs, k.q_dtype = s.q_dtype;
+  k.rows_max = rows_max < 1 ? 1 : (rows_max > TR ? TR : rows_max);
   k.n_slices = esp::combine_slices(s.HD, parts_max);
   k.out_parts = out_parts, k.out_part0 = out_part0;
   if (jobs_host && n_jobs <= esp::kInlineJobsMax) {

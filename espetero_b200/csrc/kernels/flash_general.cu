@@ -74,8 +74,14 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
     // Sliding-window layers (kernels/80_gemma.metal:123-142, :284-285): a key `window` or more
     // positions behind the query is masked; cached key j sits at position j, a batch key at its row's.
     const int qpos = a.window > 0 ? a.pos[4 * size_t(row)] : 0;
-    auto block_of = [&](int j) {  // ring layers keep a sequence's blocks in place: table + (j / bt) % ring
-      return a.ring > 0 ? size_t(tree.table + (j / p.bt) % a.ring) : size_t(a.blocks[tree.table + j / p.bt]);
+    // Block of cached key j (ring layers keep a sequence's blocks in place: table + (j / bt) % ring).
+    // The table's contents live on the device and no host check sees them: an id outside the region is
+    // recorded in the status word and the key is skipped instead of read.
+    auto block_of = [&](int j, bool& ok) {
+      const int b = a.ring > 0 ? tree.table + (j / p.bt) % a.ring : a.blocks[tree.table + j / p.bt];
+      ok = b >= 0 && b < a.n_blocks;
+      if (!ok) atomicExch(a.status, kStatusBadBlock);
+      return size_t(ok ? b : 0);
     };
     float m_run = -INFINITY, l_run = 0.0f;
     float acc[DPL];
@@ -110,8 +116,9 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
     for (int j0 = tile.k0; j0 < tile.k1; j0 += 32) {
       const int j = j0 + lane;
       float s = -INFINITY;
-      if (j < tile.k1 && (a.window <= 0 || qpos - j < a.window)) {
-        const size_t b = block_of(j);
+      bool b_ok = false;
+      const size_t b = (j < tile.k1 && (a.window <= 0 || qpos - j < a.window)) ? block_of(j, b_ok) : 0;
+      if (b_ok) {
         const size_t off = p.kv_base + (b * 2) * blk_elems + size_t(j % p.bt) * p.kv_ld + size_t(kvh) * HD;
         float dot = 0.0f;
         if constexpr (KVDT == ESP_E4M3) {
@@ -128,7 +135,8 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
       }
       softmax_pv(s, [&](int jj, float pj) {
         const int jk = j0 + jj;
-        const size_t b = block_of(jk);
+        bool v_ok;
+        const size_t b = block_of(jk, v_ok);  // valid: its score was finite
         const size_t off = p.kv_base + (b * 2 + 1) * blk_elems + size_t(jk % p.bt) * p.kv_ld + size_t(kvh) * HD + lane * DPL;
         if constexpr (KVDT == ESP_E4M3) {
           const float w = pj * a.kv_scales[(b * 2 + 1) * p.Hkv + kvh];
@@ -219,6 +227,7 @@ cudaError_t launch_flash_general(const KernelArgs& a, cudaStream_t stream, uint6
   if (a.HD == 128) e = a.q_dtype == ESP_F16 ? launch_typed<128, ESP_F16>(a, stream) : launch_typed<128, ESP_BF16>(a, stream);
   else if (a.HD == 256) e = a.q_dtype == ESP_F16 ? launch_typed<256, ESP_F16>(a, stream) : launch_typed<256, ESP_BF16>(a, stream);
   else if (a.HD == 64) e = a.q_dtype == ESP_F16 ? launch_typed<64, ESP_F16>(a, stream) : launch_typed<64, ESP_BF16>(a, stream);
+  else if (a.HD == 512) e = a.q_dtype == ESP_F16 ? launch_typed<512, ESP_F16>(a, stream) : launch_typed<512, ESP_BF16>(a, stream);
   if (e == cudaSuccess) ++*launches;
   return e;
 }

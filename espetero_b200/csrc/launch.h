@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 #include "../../include/espetero_attn.h"
 
 namespace esp {
@@ -216,6 +218,10 @@ cudaError_t launch_kv_dequant(const void* kv, const float* kv_scales, const int3
 cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pairs, const esp_attn_params& p,
                                   uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
                                   uint64_t* launches);
+
+// finite_check over rows x cols elements (row stride ld, in elements) into the 4-word record `rec`.
+cudaError_t launch_finite_check(const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int dtype, uint32_t thr_bits, uint32_t* rec,
+                                cudaStream_t stream, uint64_t* launches);
 
 // Two tcgen05 kernels with the same contract: flash_umma streams a long cached prefix from HBM
 // (one CTA per SM, 128-key blocks, deep K/V rings); flash_umma_pair is for passes whose keys are

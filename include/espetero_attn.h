@@ -127,7 +127,8 @@ typedef struct esp_attn_ctx esp_attn_ctx;
 /* Create / destroy a context on `device`. Creation resolves the driver entry
  * point used to build tensor maps and raises the kernels' shared-memory limits;
  * it allocates one small device block (the status word and 4096 arrival counters of the in-kernel
- * merge, 16.6 KB), freed by destroy. */
+ * merge, 16.6 KB) and the staging slots of re-planned passes (1.5 MB on the device, as much pinned on
+ * the host), all freed by destroy. */
 int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape);
 int esp_attn_destroy(esp_attn_ctx* ctx);
 const char* esp_attn_last_error(void);
@@ -136,6 +137,8 @@ int esp_attn_abi_version(void);
 /* Runtime options, as NativeModel::set_option(name, int) (src/model/model.mm:936-1004).
  * Names: "attn_gqa" (1: single-row trees take the decode kernel; default 1),
  * "attn_umma" (1: multi-row tiles take the tcgen05 kernel when the shape allows;
+ * default 1), "replan" (1: a context with tile_rows 8 plans plain full-attention passes again for the
+ * tcgen05 kernels instead of running their 8-row tiles on the CUDA-core kernel - see esp_attn_forward;
  * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
  * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "fuse_combine"
  * (passes whose split tiles name their combine job in pad1 can merge their records inside the
@@ -144,7 +147,10 @@ int esp_attn_abi_version(void);
  * esp_attn_set_trace), "validate" (1: check host mirrors before launching; default 1), "fail_pass"
  * (N > 0: every Nth pass of 64 rows or more fails with ESP_ERR_INJECTED before anything
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
- * reference's host-side fault injection, forest.h:2521-2531). */
+ * reference's host-side fault injection, forest.h:2521-2531), "check_finite" (1: scan every pass's
+ * output for NaN / Inf, see esp_attn_finite_check; initialised from ESPETERO_CHECK_FINITE; default 0),
+ * "attn_vec" (the reference's alternative decode schedule, src/model/impl/model.h:590, off there by
+ * default and not built here: 0 is accepted, anything else answers ESP_ERR_UNSUPPORTED). */
 int esp_attn_set_option(esp_attn_ctx* ctx, const char* name, int value);
 int esp_attn_get_option(const esp_attn_ctx* ctx, const char* name, int* value);
 
@@ -245,7 +251,16 @@ typedef struct esp_attn_args {
 size_t esp_attn_dequant_scratch_bytes(const esp_attn_shape* shape, int32_t n_block_entries);
 
 /* Attention over the plan's tiles, then the combine jobs: the reference's
- * attention() lambda. stream is a cudaStream_t. */
+ * attention() lambda. stream is a cudaStream_t.
+ * Contexts with tile_rows 8 (the reference's tile height, forest.h:1378-1433): the tensor-core kernels
+ * need 128 (row, head) pairs per CTA, which 8-row tiles do not give. When a multi-row pass's plan is
+ * plain full attention - every 8-row group of every tree covered once over [0, P), split tiles merged
+ * by the pass's own jobs: what plan_tiles emits - only O and lse are its results, and the pass is
+ * planned again inside this call for those kernels (tiles of 128 rows, or of 128 / G rows x G heads
+ * over a cached prefix); the new tiles travel through pinned staging slots the context owns. The
+ * caller's tiles / jobs are only read; `parts` is then scratch in the new tiles' layout and its
+ * contents after the call are unspecified. Any other plan (records without jobs, sliding-window
+ * plans, hand-made tilings) runs as given. Option "replan" = 0 switches this off. */
 int esp_attn_forward(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args);
 
 /* Only the merge step (attention_combine): used after records of other GPUs
@@ -499,6 +514,26 @@ int esp_forest_anc_masks(const int32_t* parents, int32_t n, uint64_t* masks);
 #define ESP_ATTN_STATIC_PARTS_FLOATS (4u << 20)
 int esp_attn_decode_static(const esp_attn_shape* shape, void* stream, const esp_attn_args* args);
 int esp_attn_decode_static_status(void* stream);
+
+/* ---- NaN / Inf / outlier detector, for debugging: the reference's finite_check
+ * (src/model/impl/finite_check.h:4-18, kernels/05_finite_check.metal; the attention output is its site
+ * "attn_out", src/model/impl/forest.h:4019-4047). Scans rows x cols elements of x (row stride ld, in
+ * elements) and fills the caller's device record: hits = offending elements, idx = the smallest
+ * offending index (row * cols + col; 0xFFFFFFFF if none), done = blocks finished, val = that element's
+ * value as fp32 bits. An element offends when its |x| bits are >= those of `threshold` (NaN and Inf
+ * always; pass INFINITY for only those). Two small launches on the stream; nothing is allocated.
+ * With the context option "check_finite" = 1 esp_attn_forward runs this check over the pass's O rows
+ * into a record of the context and esp_attn_check_status reports the first offender (ESP_ERR_CUDA,
+ * "attn_out: ..."); off by default: nothing is launched and the bits are the same. */
+typedef struct esp_finite_rec {
+  uint32_t hits;
+  uint32_t idx;
+  uint32_t done;
+  uint32_t val;
+} esp_finite_rec;
+enum { ESP_FINITE_F32 = 0, ESP_FINITE_F16 = 1, ESP_FINITE_BF16 = 2 };
+int esp_attn_finite_check(void* stream, const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int32_t dtype, float threshold,
+                          esp_finite_rec* rec_device);
 
 /* Name of the attention kernel the last esp_attn_forward on this context
  * launched ("decode_gqa", "flash_umma", "flash_umma_pair", "flash_general"), for tests and traces. */

@@ -21,6 +21,9 @@
 //   orc_plan_tiles      plan_tiles, src/model/impl/forest.h:1378-1433
 //   orc_g4_plan_tiles   g4_plan_tiles (no window), src/model/impl/gemma.h:77-116
 //   orc_round_e4m3 / orc_e4m3_*  ds4_round_e4m3, ds4_e4m3x2, kernels/80_dsv4.metal:22-33, :58-60
+#if defined(__linux__)
+#include <sched.h>
+#endif
 #include <algorithm>
 #include <atomic>
 #include <cmath>
@@ -511,8 +514,10 @@ int orc_decode_gqa_f32(const Problem* pbp, const Tile* tiles, int32_t n_tiles, v
     const int row = tile.r0;
     const int n_slot = tile.k1 - tile.k0;
     const int n_keys = n_slot + (tile.last ? 1 : 0);
-    std::vector<float> q(size_t(G) * HD), kt(size_t(8) * HD), vt(size_t(8) * HD);
-    std::vector<float> acc(size_t(KP) * G * HD, 0.0f), m_s(size_t(KP) * G, -INFINITY), l_s(size_t(KP) * G, 0.0f);
+    // scratch of the worker thread, reused by every unit it takes (no allocation in the work loop)
+    static thread_local std::vector<float> q, kt, vt, acc, m_s, l_s, out;
+    q.resize(size_t(G) * HD), kt.resize(size_t(8) * HD), vt.resize(size_t(8) * HD), out.resize(size_t(HD));
+    acc.assign(size_t(KP) * G * HD, 0.0f), m_s.assign(size_t(KP) * G, -INFINITY), l_s.assign(size_t(KP) * G, 0.0f);
     for (int hg = 0; hg < G; ++hg)
       for (int d = 0; d < HD; ++d)
         q[size_t(hg) * HD + d] = load16(pb.Q, size_t(row) * p.q_ld + size_t(kvh * G + hg) * HD + d, pb.q_dtype);
@@ -571,7 +576,6 @@ int orc_decode_gqa_f32(const Problem* pbp, const Tile* tiles, int32_t n_tiles, v
           }
         }
       }
-    std::vector<float> out(HD);
     for (int hg = 0; hg < G; ++hg) {
       const int h = kvh * G + hg;
       float M = m_s[hg];
@@ -827,6 +831,15 @@ int orc_g4_plan_tiles(const Tree* trees, int32_t n_trees, int32_t groups, int32_
   return 0;
 }
 
-int orc_hw_threads(void) { return int(std::max(1u, std::thread::hardware_concurrency())); }
+// Host threads this process may run on: the affinity mask (a container's share of the box), not the
+// machine's core count.
+int orc_hw_threads(void) {
+#if defined(__linux__)
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  if (sched_getaffinity(0, sizeof(set), &set) == 0 && CPU_COUNT(&set) > 0) return CPU_COUNT(&set);
+#endif
+  return int(std::max(1u, std::thread::hardware_concurrency()));
+}
 
 }  // extern "C"

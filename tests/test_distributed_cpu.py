@@ -77,3 +77,35 @@ def test_two_gloo_ranks_split_kv_and_sequences():
     for rank, err, same, lse_err, share in res:
         assert err <= 2e-3 + 2.0 ** -9 and same and lse_err < 2e-3
     assert sorted(res[0][4] + res[1][4]) == list(range(6))
+
+
+def test_c_abi_sharding_planners_match_a_python_restatement():
+    """esp_shard_lpt / esp_attn_split_kv_ranges / esp_attn_plan_split_kv against the rules stated in
+    the header, restated here in a few lines of Python, on random inputs."""
+    rng = np.random.default_rng(7)
+    for _ in range(50):
+        n, world = int(rng.integers(0, 40)), int(rng.integers(1, 9))
+        lens = rng.integers(1, 40000, size=n)
+        order = sorted(range(n), key=lambda i: (-int(lens[i]), i))
+        load, want = [0] * world, [[] for _ in range(world)]
+        for i in order:
+            r = min(range(world), key=lambda k: (load[k], k))
+            want[r].append(i)
+            load[r] += int(lens[i])
+        assert shard.lpt_partition(lens, world) == [sorted(x) for x in want]
+        P, bt = int(rng.integers(0, 200000)), int(rng.choice([16, 32, 64]))
+        pages = (P + bt - 1) // bt
+        cuts = [(pages * r) // world for r in range(world + 1)]
+        assert shard.split_kv_range(P, world, bt) == [(min(P, cuts[r] * bt), min(P, cuts[r + 1] * bt)) for r in range(world)]
+    # records-only plan: two row groups, one split in three (tagged for a fused merge), one unsplit
+    tiles = np.zeros(4, dtype=wl.TILE_DT)
+    tiles[0] = (0, 0, 0, 64, 0, 0, 0, 1)
+    tiles[1] = (0, 0, 64, 128, 1, 0, 0, 1)
+    tiles[2] = (0, 0, 128, 150, 2, 1, 0, 1)
+    tiles[3] = (1, 1, 0, 40, -1, 1, 0, 0)
+    for last in (False, True):
+        t, jobs, n_parts = shard.local_decode_plan(tiles, is_last_rank=last)
+        assert n_parts == 4 and list(t["part"]) == [0, 1, 2, 3] and not t["pad1"].any()
+        assert list(t["last"]) == ([0, 0, 1, 1] if last else [0, 0, 0, 0])
+        assert [tuple(j) for j in jobs] == [(0, 1, 0, 3), (1, 1, 3, 1)]
+    assert [tuple(j) for j in shard.world_merge_jobs(1, 4)] == [(0, 1, 0, 4)]

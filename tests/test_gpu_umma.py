@@ -5,6 +5,7 @@ accumulators) with the float64 oracle, through the C ABI; every case runs on bot
 and integer-exact mask probes."""
 import numpy as np
 import pytest
+import torch
 
 from espetero_b200 import capi, host, workloads as wl
 from tests import util
@@ -209,3 +210,74 @@ def test_e4m3_pool_on_tensor_cores_through_scratch(oracle_lib, case):
             util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=f"{w.name}/general")
         finally:
             op.close()
+
+
+@pytest.mark.parametrize("case", ["prefill", "verify", "chunked", "ragged"])
+def test_reference_shaped_plans_reach_the_tensor_cores(oracle_lib, case):
+    """A drop-in caller plans the reference's way: a context with 8-row tiles and plan_tiles
+    (src/model/impl/forest.h:1378-1433). Such a plan is plain full attention, so the library plans the
+    pass again for the tcgen05 kernels; it must not fall onto the CUDA-core kernel, and O / lse must be
+    the same results (against the float64 oracle, and against the general kernel on the caller's own plan)."""
+    if case == "prefill":
+        w = wl.config_c3(n_seqs=2, rows=1024)               # M = 1024, HD 128: 256 unsplit 8-row tiles
+        expect = "flash_umma_pair"
+    elif case == "verify":
+        w = wl.config_c4(n_seqs=4, prefix=2048)             # split by the reference planner: records + combine
+        expect = "flash_umma"
+    elif case == "chunked":
+        w = wl.make_pass("chunk", 501, [(900, 200), (64, 77)], 16, 4, 128, 16, wl.BF16, gate=True)
+        expect = None
+    else:
+        w = wl.make_pass("ragged", 502, [(300, 13), (0, 3), (1000, 16), (17, 9)], 32, 4, 128, 16, wl.F16, mask="forest")
+        expect = None
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    op = host.AttnOp.for_workload(w, 8)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_REFERENCE)
+        assert plan.tile_rows == 8
+        if case == "verify":
+            assert plan.n_parts > 0
+        dp = op.upload(w, plan)
+        tiles_before = dp.tiles.clone()
+        op.forward(dp)
+        op.check_status()
+        torch.cuda.synchronize()
+        assert op.last_kernel != "flash_general", "a reference-shaped plan fell onto the CUDA-core kernel"
+        if expect:
+            assert op.last_kernel == expect
+        assert torch.equal(dp.tiles, tiles_before)          # the caller's plan is read, never written
+        O, lse = dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy()
+        util.check_output(O, ref, w, ref_abs=ref_abs, what=case)
+        fin = np.isfinite(lse_ref)
+        assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
+        # several passes in a row reuse the staging slots
+        for _ in range(6):
+            op.forward(dp)
+        op.check_status()
+        torch.cuda.synchronize()
+        assert np.array_equal(dp.O.cpu().numpy().view(np.uint16), O)
+        # the same plan with re-planning off runs as given, on the general kernel
+        op.set_option("replan", 0)
+        dp.O.zero_()
+        op.forward(dp)
+        op.check_status()
+        assert op.last_kernel == "flash_general"
+        util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=case + "/general")
+    finally:
+        op.close()
+
+
+def test_records_only_plans_are_not_replanned():
+    """Tiles whose records no job of the pass merges (the first level of a multi-GPU merge) are results
+    of the pass in the caller's layout: such a plan runs as given."""
+    w = wl.config_c4(n_seqs=2, prefix=512)
+    op = host.AttnOp.for_workload(w, 8)
+    try:
+        plan = host.force_partial_records(host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_REFERENCE, split=0), w.trees)
+        plan = host.Plan(plan.tiles, np.zeros(0, dtype=wl.COMBINE_DT), plan.n_parts, 8)
+        dp = op.upload(w, plan)
+        op.forward(dp)
+        op.check_status()
+        assert op.last_kernel == "flash_general"
+    finally:
+        op.close()

@@ -58,7 +58,7 @@ def test_window_changes_the_result(oracle_lib):
     plan = host.plan_window(w.trees, groups=w.Hkv, split=0, rows=8, window=0, pos=None)
     O_win = _check(oracle_lib, w, plan, "flash_general")
     w.extra.pop("window")
-    O_all = _check(oracle_lib, w, plan, "flash_general")
+    O_all = _check(oracle_lib, w, plan, "flash_general", options={"replan": 0})  # an ordinary layer now: keep it on the same kernel
     assert not np.array_equal(O_win, O_all)
 
 
