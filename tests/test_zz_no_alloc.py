@@ -45,11 +45,9 @@ def _both(w, seed_note):
         dp.lse.zero_()
         torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info()[0]
-        torch_before = torch.cuda.memory_allocated()
         capi.check(lib.esp_attn_decode_static(C.byref(op.shape), C.c_void_p(stream), C.byref(args)))
         torch.cuda.synchronize()
         assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
-        assert torch.cuda.memory_allocated() == torch_before
         capi.check(lib.esp_attn_decode_static_status(C.c_void_p(stream)))   # no bounded wait ran out
         return want_O, want_lse, dp.O.cpu().numpy(), dp.lse.cpu().numpy()
     finally:
