@@ -398,6 +398,8 @@ def setup_sequences(B: Bench, name: str, w, scaling: str, sharding: str) -> Run:
     r.op = host.AttnOp.for_workload(w, TILE_ROWS[name], B.local)
     if args.fuse >= 0:
         r.op.set_option("fuse_combine", args.fuse)
+    for kv in args.opt:
+        r.op.set_option(kv.split("=")[0], int(kv.split("=")[1]))
     r.plan = bench_plan(name, w, args.groups)
     r.dp = r.op.upload(w, r.plan)
     r.layers = LayerCycle(r.op, r.dp, w)
@@ -449,11 +451,17 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
             xch = None
     r.xch = xch
     if xch is not None:
+        # ONE launch per rank and step: the decode kernel folds the rank's records as its CTAs finish, stores the
+        # result into every rank's buffer over NVLink peer mappings, waits for the peers' and writes the row
+        a_x = layers.args()
+        a_x.jobs, a_x.jobs_host, a_x.n_jobs = red_dev.data_ptr(), red_jobs.ctypes.data, len(red_jobs)
+        r.keep = (red_jobs, red_dev)
+
         def step():
             xch.next_epoch()
-            op.forward(dp, layers.next(r.a_attn))
-            op.exchange_parts(dp, dp.parts, red_dev, len(red_jobs), xch, parts_max=n_parts)
-        r.sharding = "KV range per rank; one kernel per rank merges, exchanges records over NVLink peer stores and finishes"
+            op.forward_exchange(dp, layers.next(a_x), xch)
+        r.a_full = a_x
+        r.sharding = "KV range per rank; one launch per rank: records, two-level fold, NVLink peer stores, wait, final fold"
     else:
         def step():
             op.forward(dp, layers.next(r.a_attn))
@@ -492,8 +500,8 @@ def time_e2e(B: Bench, r: Run, steps: int, t_step: float):
     h2d = arena.nbytes
     d2h = h_out.numel() * h_out.element_size()
     if r.split_kv:
-        a = r.a_attn  # the step reads its inputs from the arena
-        a.Q, a.Kb, a.Vb, a.tiles, a.trees, a.blocks = a_e2e.Q, a_e2e.Kb, a_e2e.Vb, a_e2e.tiles, a_e2e.trees, a_e2e.blocks
+        for a in (r.a_attn, r.a_full):  # the step reads its inputs from the arena
+            a.Q, a.Kb, a.Vb, a.tiles, a.trees, a.blocks = a_e2e.Q, a_e2e.Kb, a_e2e.Vb, a_e2e.tiles, a_e2e.trees, a_e2e.blocks
     e2e_tail = None
     # Passes of a few microseconds are bound by the host's calls, not by the GPU: pipelining them over
     # three streams only adds calls, so they keep the plain sequence on one stream.
@@ -619,6 +627,7 @@ def main():
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
     ap.add_argument("--fuse", type=int, default=-1, help="option fuse_combine of the library (0 off, 1 small passes, 2 always); -1: its default")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="set a library option (esp_attn_set_option) on the pass's context")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -112,6 +112,7 @@ PROTOTYPES = {
     "esp_attn_plan_split_kv": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32),
                                          C.POINTER(C.c_int32)]),
     "esp_attn_world_merge_jobs": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "esp_attn_forward_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Args), C.POINTER(Exchange)]),
     "esp_p2p_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_char_p]),
     "esp_p2p_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "esp_p2p_close": (C.c_int, [C.c_void_p]),

@@ -53,6 +53,7 @@ struct esp_attn_ctx {
   // tiles and jobs are built on the host and travel through a small ring of pinned staging slots into
   // device slots of the context (see replan_pass).
   int opt_replan = 1;
+  int opt_p_f16 = 0;
   uint8_t* replan_dev = nullptr;
   uint8_t* replan_host = nullptr;
   cudaEvent_t replan_done[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -271,6 +272,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   if (!std::strcmp(name, "check_finite")) return &c->opt_check_finite;
   if (!std::strcmp(name, "replan")) return &c->opt_replan;
+  if (!std::strcmp(name, "umma_p_f16")) return &c->opt_p_f16;
   return nullptr;
 }
 
@@ -476,7 +478,12 @@ static bool replan_pass(esp_attn_ctx* c, esp_attn_args& a, int& TR, cudaStream_t
   return true;
 }
 
-int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
+}  // extern "C"
+
+// xch != NULL: the pass is one rank's share of a sequence split over several GPUs and ends with the peer
+// exchange inside the decode kernel. *fused_out tells whether that happened; if not, nothing was launched
+// for the exchange and the caller takes the two-kernel route.
+static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap, const esp_attn_exchange* xch, bool* fused_out) {
   if (!c || !ap) return fail(ESP_ERR_INVALID, "esp_attn_forward: null argument");
   esp_attn_args a = *ap;  // the pass as it runs: re-planning may replace tiles and jobs
   const esp_attn_shape& s = c->shape;
@@ -529,6 +536,7 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
+  k.p_f16 = (c->opt_p_f16 && s.q_dtype == ESP_BF16) ? 1 : 0;
 
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {
@@ -555,7 +563,28 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     k.fuse = c->opt_fuse_combine && (c->opt_fuse_combine == 2 || esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs)) && c->G % 2 == 0 &&
              a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
     merged = k.fuse != 0;
+    if (xch) {
+      // the exchange rides on the fused merge of ONE job (one row group: a single long sequence)
+      if (!(c->G % 2 == 0 && a.n_jobs == 1 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv))) {
+        *fused_out = false;
+        return ESP_OK;
+      }
+      k.fuse = 1, merged = true;
+      k.x_world = xch->world, k.x_rank = xch->rank, k.x_phases = xch->phases, k.x_tag = uint32_t(xch->epoch);
+      k.x_wait_ms = xch->wait_ms ? uint32_t(xch->wait_ms) : 2000u;
+      const size_t rank_words = size_t(s.Hkv) * TR * c->G * (s.HD + 2);
+      k.x_epoch_off = (xch->epoch & 1) * uint64_t(xch->world) * rank_words;
+      for (int q = 0; q < xch->world; ++q) k.x_records[q] = static_cast<uint2*>(xch->records[q]);
+    }
     e = esp::launch_decode_gqa(k, c->pool_map, stream, &c->launches);
+    if (xch) {
+      if (e == cudaErrorCooperativeLaunchTooLarge) {  // the grid would not be resident at once: two-kernel route
+        (void)cudaGetLastError();
+        *fused_out = false;
+        return ESP_OK;
+      }
+      *fused_out = e == cudaSuccess;
+    }
   } else if (umma) {
     if (int rc = umma_tensor_maps(c, widened)) return rc;
     // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
@@ -601,6 +630,35 @@ int esp_attn_forward(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap) {
     c->finite_armed = true;
   }
   return ESP_OK;
+}
+
+extern "C" {
+
+int esp_attn_forward(esp_attn_ctx* c, void* stream, const esp_attn_args* args) { return forward_impl(c, stream, args, nullptr, nullptr); }
+
+int esp_attn_forward_exchange(esp_attn_ctx* c, void* stream, const esp_attn_args* ap, const esp_attn_exchange* xp) {
+  if (!c || !ap || !xp) return fail(ESP_ERR_INVALID, "esp_attn_forward_exchange: null argument");
+  const esp_attn_exchange& x = *xp;
+  if (x.world < 1 || x.world > ESP_ATTN_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
+    return fail(ESP_ERR_INVALID, "esp_attn_forward_exchange: rank %d of world %d", x.rank, x.world);
+  if (x.phases < 1 || x.phases > 3 || x.wait_ms < 0 || uint32_t(x.epoch) == 0)
+    return fail(ESP_ERR_INVALID, "esp_attn_forward_exchange: phases %d, wait_ms %d, epoch %llu", x.phases, x.wait_ms, (unsigned long long)x.epoch);
+  for (int q = 0; q < x.world; ++q)
+    if (!x.records[q] || (reinterpret_cast<uintptr_t>(x.records[q]) & 7))
+      return fail(ESP_ERR_INVALID, "esp_attn_forward_exchange: exchange buffer of rank %d is null or not 8-byte aligned", q);
+  if (ap->n_jobs < 1 || !ap->jobs || !ap->jobs_host) return fail(ESP_ERR_INVALID, "esp_attn_forward_exchange: the rank's reduce jobs (device and host copies) are required");
+  int parts_max = 1;
+  for (int i = 0; i < ap->n_jobs; ++i) parts_max = std::max(parts_max, ap->jobs_host[i].nparts);
+  if (x.phases == 2)  // only the second half: the records were published by an earlier launch
+    return esp_attn_exchange_parts(c, stream, ap->parts, ap->X, ap->O, ap->lse, &ap->p, ap->jobs, ap->n_jobs, 1, parts_max, xp);
+  bool fused = false;
+  if (int rc = forward_impl(c, stream, ap, xp, &fused)) return rc;
+  if (fused) return ESP_OK;
+  // two kernels: the records, then merge + exchange + merge
+  esp_attn_args rec = *ap;
+  rec.n_jobs = 0, rec.jobs = nullptr, rec.jobs_host = nullptr;
+  if (int rc = forward_impl(c, stream, &rec, nullptr, nullptr)) return rc;
+  return esp_attn_exchange_parts(c, stream, ap->parts, ap->X, ap->O, ap->lse, &ap->p, ap->jobs, ap->n_jobs, 1, parts_max, xp);
 }
 
 int esp_attn_finite_check(void* stream, const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int32_t dtype, float threshold,

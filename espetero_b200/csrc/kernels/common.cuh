@@ -120,6 +120,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
   }
 }
 
+// One 8-byte word {value bits, tag} of a peer exchange: a single store / load, so the pair is never torn.
+__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+  uint2 w;
+  asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+  return w;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA (plain per-CTA loads only)

@@ -429,74 +429,187 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     }
   }
 
-  // ---- fused merge (what attention_combine does, kernels/40_attention.metal:811-864): every CTA
-  // of a job publishes its records and draws a ticket; the CTA that draws the last one merges the
-  // job's records of its kv head in record order and writes the row. Nobody waits for anybody, and
-  // the result does not depend on which CTA came last.
+  // ---- fused merge (what attention_combine does, kernels/40_attention.metal:811-864), in two levels.
+  // The records of a job are cut into at most 8 groups of consecutive records. Every CTA publishes
+  // its record and draws a ticket of its group; the CTA that draws a group's last ticket folds the
+  // group's records of its kv head in record order into one unnormalised record, stores it over the
+  // group's first slot and draws a ticket of the job; whoever draws the job's last ticket folds the
+  // group records in group order and finishes the row. Groups that end early are folded while other
+  // CTAs still stream, so the tail holds two short folds instead of one long one. Nobody waits for
+  // anybody on this GPU, and the result does not depend on which CTAs came last.
+  // With a peer exchange (a.x_world > 0: one sequence's keys split over several GPUs) the finished
+  // record is not the row yet: it goes into slot `rank` of every rank's exchange buffer as 8-byte
+  // words {value, tag} through peer mappings (plain stores over NVLink), and the same CTA then reads
+  // the world's records of its heads from its own buffer - polling each word, bounded by a timer,
+  // until it carries the call's tag -, folds them in rank order and writes the row. It waits only for
+  // the same kv head's CTA on the OTHER GPUs; the host launches this mode only when the whole grid is
+  // resident at once, so a waiting CTA never keeps another one off an SM.
   if (fused) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int* ticket = a.counters + size_t(tile.pad1 - 1) * p.Hkv + kvh;
-      const int prev = atomicAdd(ticket, 1);
-      if (prev == fix_info[1] - 1) *ticket = 0;  // ready for the next pass on this stream
-      fix_info[2] = prev;
-    }
-    __syncthreads();
-    if (fix_info[2] != fix_info[1] - 1) return;
-    __threadfence();
-    // The job's records of this kv head come into shared memory by bulk copies (the rings are idle):
-    // the G records of a part are contiguous, as many parts per round as fit. Then every thread folds
-    // its 4-dim items over the parts in record order with a running maximum.
     const int part0 = fix_info[0], n = fix_info[1];
+    const int S = n > 8 ? (n + 7) / 8 : n;  // records per group
+    const int n_groups = (n + S - 1) / S;
+    const int grp = (tile.part - part0) / S, gsize = min(S, n - grp * S);
+    int* tickets = a.counters + (size_t(tile.pad1 - 1) * p.Hkv + kvh) * kFixupPerJob;
+    auto last_of = [&](int* ticket, int count) {  // CTA-uniform: did this CTA draw the last of `count` tickets?
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const int prev = atomicAdd(ticket, 1);
+        if (prev == count - 1) *ticket = 0;  // ready for the next pass on this stream
+        fix_info[2] = prev;
+      }
+      __syncthreads();
+      const bool last = fix_info[2] == count - 1;
+      if (last) __threadfence();
+      return last;
+    };
+    if (!last_of(tickets + 1 + grp, gsize)) return;
+
+    // Records come into shared memory by bulk copies (the rings are idle): the G records of a part are
+    // contiguous, as many parts per round as fit. Then every thread folds its 4-dim items over the
+    // parts in order with a running maximum.
     const size_t part_stride = size_t(p.Hkv) * a.tile_rows * G * (HD + 2);
     const uint32_t rec_bytes = uint32_t(G) * (HD + 2) * 4;
-    const float* base = a.parts + (size_t(part0) * p.Hkv + kvh) * a.tile_rows * G * (HD + 2);
+    float* const kvh_base = a.parts + size_t(kvh) * a.tile_rows * G * (HD + 2);  // record 0 of this kv head
     float* stage = reinterpret_cast<float*>(smem);
-    const int per_round = max(1, min(n, int((NW * C::WARP_BYTES) / rec_bytes)));
     constexpr int MAXI = HD / 64;              // items per thread at most: G * HD / 4 items over 128 threads
     const int n_items = G * HD / 4;
     float st_m[MAXI], st_l[MAXI];
     float4 st_acc[MAXI];
-#pragma unroll
-    for (int k = 0; k < MAXI; ++k) st_m[k] = -INFINITY, st_l[k] = 0.0f, st_acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     uint32_t par = 0;
-    for (int s0 = 0; s0 < n; s0 += per_round) {
-      const int cnt = min(per_round, n - s0);
-      __syncthreads();  // the previous round's records have been consumed
-      if (threadIdx.x == 0) {
-        asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
-        mbar_arrive_expect_tx(&fix_bar, uint32_t(cnt) * rec_bytes);
-        for (int s = 0; s < cnt; ++s)
-          bulk_load(reinterpret_cast<uint8_t*>(stage) + size_t(s) * rec_bytes, base + size_t(s0 + s) * part_stride, rec_bytes, &fix_bar);
+    bool alive = true;
+    // folds records first, first + step, ... (count of them) into the state
+    auto fold = [&](int first, int count, int step) {
+#pragma unroll
+      for (int k = 0; k < MAXI; ++k) st_m[k] = -INFINITY, st_l[k] = 0.0f, st_acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int per_round = max(1, min(count, int((NW * C::WARP_BYTES) / rec_bytes)));
+      for (int s0 = 0; s0 < count; s0 += per_round) {
+        const int cnt = min(per_round, count - s0);
+        __syncthreads();  // the previous round's records have been consumed
+        if (threadIdx.x == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
+          mbar_arrive_expect_tx(&fix_bar, uint32_t(cnt) * rec_bytes);
+          for (int s2 = 0; s2 < cnt; ++s2)
+            bulk_load(reinterpret_cast<uint8_t*>(stage) + size_t(s2) * rec_bytes, kvh_base + size_t(first + (s0 + s2) * step) * part_stride, rec_bytes, &fix_bar);
+        }
+        if (!__syncthreads_and(mbar_wait(&fix_bar, par))) {  // one verdict for the CTA: nobody is left behind at a barrier
+          if (threadIdx.x == 0) atomicExch(a.status, kStatusTmaTimeout);
+          alive = false;
+          return;
+        }
+        par ^= 1;
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k) {
+          const int item = threadIdx.x + k * (NW * 32);
+          if (item >= n_items) break;
+          const int hg = item / (HD / 4), c4 = item % (HD / 4);
+          const float* rec = stage + size_t(hg) * (HD + 2);
+          for (int s2 = 0; s2 < cnt; ++s2, rec += size_t(G) * (HD + 2)) {
+            const float m_s = rec[HD];
+            if (m_s == -INFINITY) continue;          // an empty record adds nothing
+            if (m_s > st_m[k]) {                      // rescale what has been summed so far (factor 0 the first time)
+              const float f = __expf(st_m[k] - m_s);
+              st_l[k] *= f, st_acc[k].x *= f, st_acc[k].y *= f, st_acc[k].z *= f, st_acc[k].w *= f;
+              st_m[k] = m_s;
+            }
+            const float w = __expf(m_s - st_m[k]);
+            const float2 o01 = *reinterpret_cast<const float2*>(rec + 4 * c4), o23 = *reinterpret_cast<const float2*>(rec + 4 * c4 + 2);
+            st_l[k] = fmaf(w, rec[HD + 1], st_l[k]);
+            st_acc[k].x = fmaf(w, o01.x, st_acc[k].x), st_acc[k].y = fmaf(w, o01.y, st_acc[k].y);
+            st_acc[k].z = fmaf(w, o23.x, st_acc[k].z), st_acc[k].w = fmaf(w, o23.y, st_acc[k].w);
+          }
+        }
       }
-      if (!__syncthreads_and(mbar_wait(&fix_bar, par))) {  // one verdict for the CTA: nobody is left behind at a barrier
-        if (threadIdx.x == 0) atomicExch(a.status, kStatusTmaTimeout);
-        return;
-      }
-      par ^= 1;
+    };
+    fold(part0 + grp * S, gsize, 1);
+    if (!alive) return;
+    if (n_groups > 1) {
+      // the group's record, unnormalised, over the group's first slot (its own records are spent)
+      float* gout = kvh_base + size_t(part0 + grp * S) * part_stride;
+      __syncthreads();  // every thread is done reading the staged records of the last round
 #pragma unroll
       for (int k = 0; k < MAXI; ++k) {
         const int item = threadIdx.x + k * (NW * 32);
         if (item >= n_items) break;
         const int hg = item / (HD / 4), c4 = item % (HD / 4);
-        const float* rec = stage + size_t(hg) * (HD + 2);
-        for (int s = 0; s < cnt; ++s, rec += size_t(G) * (HD + 2)) {
-          const float m_s = rec[HD];
-          if (m_s == -INFINITY) continue;          // an empty record adds nothing
-          if (m_s > st_m[k]) {                      // rescale what has been summed so far (factor 0 the first time)
-            const float f = __expf(st_m[k] - m_s);
-            st_l[k] *= f, st_acc[k].x *= f, st_acc[k].y *= f, st_acc[k].z *= f, st_acc[k].w *= f;
-            st_m[k] = m_s;
+        float* rec = gout + size_t(hg) * (HD + 2);
+        *reinterpret_cast<float2*>(rec + 4 * c4) = make_float2(st_acc[k].x, st_acc[k].y);
+        *reinterpret_cast<float2*>(rec + 4 * c4 + 2) = make_float2(st_acc[k].z, st_acc[k].w);
+        if (c4 == 0) *reinterpret_cast<float2*>(rec + HD) = make_float2(st_m[k], st_l[k]);
+      }
+      if (!last_of(tickets, n_groups)) return;
+      fold(part0, n_groups, S);
+      if (!alive) return;
+    }
+
+    if (a.x_world > 0) {
+      // ---- peer exchange: publish, then fold the world's records in rank order
+      const size_t rank_words = part_stride;  // one job: a rank's records in a buffer = one record slot of every (kv head, row, head)
+      const size_t kvh_off = size_t(kvh) * a.tile_rows * G * (HD + 2);
+      if (a.x_phases & 1) {
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k) {
+          const int item = threadIdx.x + k * (NW * 32);
+          if (item >= n_items) break;
+          const int hg = item / (HD / 4), c4 = item % (HD / 4);
+          const size_t off = a.x_epoch_off + size_t(a.x_rank) * rank_words + kvh_off + size_t(hg) * (HD + 2);
+          for (int q = 0; q < a.x_world; ++q) {
+            uint2* dst = a.x_records[q] + off;
+            st_word(dst + 4 * c4, st_acc[k].x, a.x_tag), st_word(dst + 4 * c4 + 1, st_acc[k].y, a.x_tag);
+            st_word(dst + 4 * c4 + 2, st_acc[k].z, a.x_tag), st_word(dst + 4 * c4 + 3, st_acc[k].w, a.x_tag);
+            if (c4 == 0) st_word(dst + HD, st_m[k], a.x_tag), st_word(dst + HD + 1, st_l[k], a.x_tag);
           }
-          const float w = __expf(m_s - st_m[k]);
-          const float2 o01 = *reinterpret_cast<const float2*>(rec + 4 * c4), o23 = *reinterpret_cast<const float2*>(rec + 4 * c4 + 2);
-          st_l[k] = fmaf(w, rec[HD + 1], st_l[k]);
-          st_acc[k].x = fmaf(w, o01.x, st_acc[k].x), st_acc[k].y = fmaf(w, o01.y, st_acc[k].y);
-          st_acc[k].z = fmaf(w, o23.x, st_acc[k].z), st_acc[k].w = fmaf(w, o23.y, st_acc[k].w);
         }
       }
+      if (!(a.x_phases & 2)) return;
+      bool ok = true;
+      const uint64_t t0 = global_timer_ns();
+      const uint64_t limit = uint64_t(a.x_wait_ms) * 1000000ull;
+#pragma unroll
+      for (int k = 0; k < MAXI; ++k) {
+        const int item = threadIdx.x + k * (NW * 32);
+        if (item >= n_items) break;
+        const int hg = item / (HD / 4), c4 = item % (HD / 4);
+        const uint2* rec0 = a.x_records[a.x_rank] + a.x_epoch_off + kvh_off + size_t(hg) * (HD + 2);
+        st_m[k] = -INFINITY, st_l[k] = 0.0f, st_acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; ok && q < a.x_world; ++q) {
+          const uint2* rec = rec0 + size_t(q) * rank_words;
+          uint2 w[6];
+          for (;;) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[i] = ld_word(rec + 4 * c4 + i);
+            w[4] = ld_word(rec + HD), w[5] = ld_word(rec + HD + 1);
+            bool all = true;
+#pragma unroll
+            for (int i = 0; i < 6; ++i) all = all && w[i].y == a.x_tag;
+            if (all) break;
+            if (global_timer_ns() - t0 > limit) {
+              ok = false;
+              break;
+            }
+            __nanosleep(32);
+          }
+          if (!ok) break;
+          const float m_q = __uint_as_float(w[4].x);
+          if (m_q == -INFINITY) continue;
+          if (m_q > st_m[k]) {
+            const float f = __expf(st_m[k] - m_q);
+            st_l[k] *= f, st_acc[k].x *= f, st_acc[k].y *= f, st_acc[k].z *= f, st_acc[k].w *= f;
+            st_m[k] = m_q;
+          }
+          const float wq = __expf(m_q - st_m[k]);
+          st_l[k] += wq * __uint_as_float(w[5].x);
+          st_acc[k].x += wq * __uint_as_float(w[0].x), st_acc[k].y += wq * __uint_as_float(w[1].x);
+          st_acc[k].z += wq * __uint_as_float(w[2].x), st_acc[k].w += wq * __uint_as_float(w[3].x);
+        }
+      }
+      // Nobody writes O unless every thread of the CTA has all its words.
+      if (!__syncthreads_and(ok)) {
+        if (threadIdx.x == 0) atomicCAS(a.status, kStatusOk, kStatusPeerTimeout);
+        return;
+      }
     }
+
 #pragma unroll
     for (int k = 0; k < MAXI; ++k) {
       const int item = threadIdx.x + k * (NW * 32);
@@ -521,6 +634,15 @@ cudaError_t setup_one() {
 }
 template <class C>
 cudaError_t launch_one(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream) {
+  if (a.x_world > 0 && (a.x_phases & 2)) {
+    // CTAs of this launch wait for CTAs of other GPUs: every CTA of the grid must hold an SM slot at once.
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_gqa_kernel<C>, C::NW * 32, C::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    if (int64_t(a.n_tiles) * a.p.Hkv > int64_t(per_sm) * sms) return cudaErrorCooperativeLaunchTooLarge;
+  }
   return launch_pdl(decode_gqa_kernel<C>, dim3(unsigned(a.n_tiles) * unsigned(a.p.Hkv)), dim3(C::NW * 32), C::SMEM_BYTES, stream, m, a);
 }
 

@@ -19,16 +19,6 @@
 namespace esp {
 namespace {
 
-// One 8-byte word {value bits, tag}: a single store / load, so the pair is never torn.
-__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t tag) {
-  asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_word(const uint2* p) {
-  uint2 w;
-  asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
-  return w;
-}
-
 template <int QDT>
 __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const ExchangeArgs x) {
   __shared__ MergeScratch scratch;

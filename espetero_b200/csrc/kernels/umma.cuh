@@ -35,6 +35,13 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_
          (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
+// The same with the A and B element types chosen separately (the descriptor has one format field each).
+__device__ __forceinline__ constexpr uint32_t umma_idesc_ab(int a_dt, int b_dt, int M, int N, int a_mn_major, int b_mn_major) {
+  const uint32_t fa = a_dt == ESP_BF16 ? 1u : 0u, fb = b_dt == ESP_BF16 ? 1u : 0u;
+  return (1u << 4) | (fa << 7) | (fb << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(N >> 3) << 17) |
+         (uint32_t(M >> 4) << 24);
+}
+
 // ---------------------------------------------------------------- MMA issue (one thread)
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {

@@ -55,6 +55,13 @@ struct KernelArgs {
   int32_t window;      // > 0: keys `window` or more positions behind the query are masked
   int32_t ring;        // > 0: cached key j lives in block table + (j / bt) % ring (no page table)
   int32_t bidi;        // rows of an image also see the image's later rows (desc.w)
+  // Peer exchange at the end of the decode kernel's fused merge (one sequence's keys split over several GPUs);
+  // x_world = 0: none. Buffers hold 8-byte words {value, tag}, laid out [epoch parity][rank][record slot].
+  int32_t x_world, x_rank, x_phases;  // phases: 1 publish, 2 wait for the world's records and finish the row, 3 both
+  uint32_t x_tag, x_wait_ms;
+  unsigned long long x_epoch_off;     // words from a buffer's start to this epoch's half
+  uint2* x_records[ESP_ATTN_MAX_PEERS];
+  int32_t p_f16;       // tcgen05 kernels: round P to fp16 before P.V whatever the pass's 16-bit type (the reference rounds P to fp16, 40_attention.metal:297)
 };
 
 // Small plans travel in the kernel's parameter space (constant bank), one 64-byte line per tile
@@ -64,6 +71,7 @@ struct KernelArgs {
 // parameter-line misses and two dependent global loads.
 constexpr int kInlinePlanMax = 48;
 constexpr int kFixupCounters = 4096;  // ints behind the status word of a context
+constexpr int kFixupPerJob = 9;       // decode kernel: per (job, kv head) one ticket of the job and up to 8 of its record groups
 struct alignas(64) TileStart {
   esp_attn_tile tile;  // pad1 = first record of the tile's merge job (fused merge)
   esp_attn_tree tree;
@@ -118,7 +126,7 @@ struct ExchangeArgs {
 // writes a record names its job in pad1 (1 + index), lies inside that job's record range and row
 // group, every job's records are all written by this pass, and (job, kv head) pairs fit the counters.
 inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_attn_combine* jobs, int32_t n_jobs, int32_t Hkv) {
-  if (!tiles || !jobs || n_jobs <= 0 || int64_t(n_jobs) * Hkv > kFixupCounters) return false;
+  if (!tiles || !jobs || n_jobs <= 0 || int64_t(n_jobs) * Hkv * kFixupPerJob > kFixupCounters) return false;
   // Records of a job are consecutive and, in a planner's output, written by consecutive tiles in
   // record order: check exactly that (anything else takes the two-kernel route).
   int64_t records = 0, claimed = 0;

@@ -44,9 +44,11 @@ int esp_attn_split_kv_ranges(int32_t P, int32_t world, int32_t bt, int32_t* lo, 
 }
 
 // A rank's plan over its local keys as "records only": every tile writes a partial record (an unsplit
-// tile gets a fresh one), the job tags of fused merges are dropped (no rank may finish a row alone),
-// only the rank holding the end of the sequence keeps `last` (the row's own key counts once), and one
-// reduce job per row group covers the rank's records of that group. tiles are rewritten in place.
+// tile gets a fresh one), only the rank holding the end of the sequence keeps `last` (the row's own key
+// counts once), and one reduce job per row group covers the rank's records of that group; every tile
+// names that job in pad1 (1 + its index), which lets esp_attn_forward_exchange merge and exchange inside
+// the attention kernel (esp_attn_forward ignores the tags of a pass without jobs). tiles are rewritten
+// in place.
 int esp_attn_plan_split_kv(esp_attn_tile* tiles, int32_t n_tiles, int32_t is_last_rank, esp_attn_combine* jobs, int32_t jobs_cap,
                            int32_t* n_jobs, int32_t* n_parts) {
   if (n_tiles < 0 || (n_tiles > 0 && !tiles) || !n_jobs || !n_parts) return esp::fail(ESP_ERR_INVALID, "esp_attn_plan_split_kv: null or negative argument");
@@ -61,6 +63,11 @@ int esp_attn_plan_split_kv(esp_attn_tile* tiles, int32_t n_tiles, int32_t is_las
     groups[{t.tree, t.r0}].push_back(t.part);
   }
   int32_t nj = 0;
+  {
+    std::map<std::pair<int32_t, int32_t>, int32_t> job_of;
+    for (auto& kv : groups) job_of[kv.first] = int32_t(job_of.size());
+    for (int32_t i = 0; i < n_tiles; ++i) tiles[i].pad1 = 1 + job_of[{tiles[i].tree, tiles[i].r0}];
+  }
   for (auto& [key, parts] : groups) {
     std::sort(parts.begin(), parts.end());
     for (size_t k = 1; k < parts.size(); ++k)

@@ -254,6 +254,14 @@ class AttnOp:
         capi.check(self.lib.esp_attn_exchange_parts(self.ctx, C.c_void_p(s), _ptr(parts), _ptr(dp.X), _ptr(dp.O), _ptr(dp.lse),
                                                     C.byref(p), _ptr(jobs_dev), n_jobs, rows_max, parts_max, C.byref(x)))
 
+    def forward_exchange(self, dp: DevicePass, args: capi.Args, xch: "PeerExchange", rank: int | None = None, phases: int = 3,
+                         wait_ms: int = 0, stream: int | None = None):
+        """esp_attn_forward_exchange: a rank's split-KV step in one launch (args carry the records-only plan
+        and its reduce job)."""
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        x = xch.descriptor(xch.rank if rank is None else rank, phases, wait_ms)
+        capi.check(self.lib.esp_attn_forward_exchange(self.ctx, C.c_void_p(s), C.byref(args), C.byref(x)))
+
     def attn_prep(self, X, qn_w, kn_w, pos, inv_freq, rope_sel, Q, Kb, Vb, pp: "capi.PrepParams", ktab=None, kv=None,
                   kv_scales=None, stream: int | None = None):
         """esp_attn_prep on device tensors: RMSNorm + rotary + cast of the fused projection X into Q / Kb / Vb

@@ -324,7 +324,8 @@ int esp_attn_exchange_parts(esp_attn_ctx* ctx, void* stream, const float* parts,
  * esp_attn_plan_split_kv: turns a rank's plan over its local keys (esp_attn_plan) into the
  * records-only plan esp_attn_exchange_parts / esp_attn_reduce_parts expect: every tile writes a
  * record, only the last rank keeps `last`, job tags are cleared, and one reduce job per row group
- * names the rank's records (tiles rewritten in place; jobs_cap protocol as esp_attn_plan).
+ * names the rank's records and is named by its tiles in pad1 (tiles rewritten in place; jobs_cap
+ * protocol as esp_attn_plan).
  * esp_attn_world_merge_jobs: the job that merges the ranks' reduced records, gathered rank-major. */
 int esp_shard_lpt(const int64_t* lengths, int32_t n, int32_t world, int32_t* rank_of);
 int esp_attn_split_kv_ranges(int32_t P, int32_t world, int32_t bt, int32_t* lo, int32_t* hi);
@@ -332,6 +333,18 @@ int esp_attn_plan_split_kv(esp_attn_tile* tiles, int32_t n_tiles, int32_t is_las
                            int32_t* n_jobs, int32_t* n_parts);
 int esp_attn_world_merge_jobs(int32_t n_groups, int32_t world, int32_t rows, esp_attn_combine* jobs, int32_t jobs_cap,
                               int32_t* n_jobs);
+
+/* The whole split-KV step of a rank in ONE launch: the decode kernel over the rank's records-only plan
+ * (args: tiles tagged by esp_attn_plan_split_kv, jobs / jobs_host = its reduce job, n_jobs = 1), whose
+ * CTAs fold the rank's records in two short levels as they finish (no CTA waits for another of its
+ * GPU); the CTA that completes a kv head's record stores it into every rank's exchange buffer over peer
+ * mappings, waits (bounded by wait_ms) for the other ranks' records of the same heads, folds them in
+ * rank order and writes O / lse. Same buffers, epochs, bits-on-every-rank guarantee and failure
+ * behaviour as esp_attn_exchange_parts. The waiting CTAs need the whole grid resident at once; a pass
+ * whose grid is larger, or that the decode kernel does not take, runs as esp_attn_forward (records only)
+ * followed by esp_attn_exchange_parts inside this call. phases = 1 publishes without waiting, phases = 2
+ * runs only the second half (both for tests that emulate several ranks on one GPU). */
+int esp_attn_forward_exchange(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args, const esp_attn_exchange* x);
 
 /* Device memory another process of the same box can map: cudaMalloc + zero fill + an IPC handle
  * (64 bytes, opaque). esp_p2p_open maps a peer's allocation into this process (peer access is

@@ -2,8 +2,8 @@
 
 Launched with torch.distributed.run (one process per GPU, NCCL, rendezvous on 127.0.0.1). Every rank
 builds the same seeded single-sequence decode workload, keeps the pages of its own key range, and
-the ranks finish it twice: with the fused peer exchange kernel (esp_attn_exchange_parts) and with
-reduce + NCCL all-gather + combine. Both must match the float64 oracle over the whole sequence,
+the ranks finish it twice: with the fused peer exchange kernel (esp_attn_exchange_parts), with the
+one-launch route (esp_attn_forward_exchange) and with reduce + NCCL all-gather + combine. Both must match the float64 oracle over the whole sequence,
 every rank must hold identical bits, and a few more epochs on the same buffers must repeat them.
 Rank 0 prints one line "MULTI_GPU_OK ..." on success."""
 import os
@@ -57,6 +57,46 @@ def main():
     dist.all_gather_into_tensor(every, mine.flatten())
     every = every.view(world, -1)
     assert bool((every == every[0]).all()), "ranks hold different outputs"
+    # the one-launch route (esp_attn_forward_exchange: records, two-level fold, peer stores, wait and final fold in
+    # the decode kernel): correct, identical on every rank, the same over several epochs, and one launch per step
+    dpf = op.upload(sub, host.Plan(tiles, jobs, n_parts, 8))
+    args_f = op.make_args(dpf)
+    fused = []
+    for _ in range(4):
+        xch.next_epoch()
+        dpf.O.zero_()
+        n0 = op.launch_count
+        op.forward_exchange(dpf, args_f, xch)
+        op.check_status()
+        assert op.launch_count - n0 == 1, "the fused exchange took the two-kernel route"
+        fused.append((dpf.O.cpu().numpy().view(np.uint16).copy(), dpf.lse.cpu().numpy().copy()))
+    for O, lse in fused[1:]:
+        assert np.array_equal(O, fused[0][0]) and np.array_equal(lse, fused[0][1]), "fused epochs differ"
+    util.check_output(fused[0][0], ref, w)
+    assert np.abs(fused[0][1] - lse_ref).max() < 2e-3
+    mine = torch.from_numpy(fused[0][0].astype(np.int32)).to(dev)
+    dist.all_gather_into_tensor(every.view(-1), mine.flatten())
+    assert bool((every.view(world, -1) == every.view(world, -1)[0]).all()), "ranks hold different outputs (fused exchange)"
+    dist.barrier()
+    # a silent peer on the one-launch route: the waiting CTAs give up after 100 ms, O stays untouched
+    xch.next_epoch()
+    dpf.O.fill_(0x3C00)
+    if rank != world - 1:
+        op.forward_exchange(dpf, args_f, xch, wait_ms=100)
+        try:
+            op.check_status()
+            raise AssertionError("the fused wait for a silent peer did not report")
+        except capi.EspError as e:
+            assert "never published" in str(e), str(e)
+        assert bool((dpf.O == 0x3C00).all()), "O was written although a peer was missing (fused exchange)"
+    torch.cuda.synchronize()
+    dist.barrier()
+    xch.next_epoch()
+    dpf.O.zero_()
+    op.forward_exchange(dpf, args_f, xch)
+    op.check_status()
+    util.check_output(dpf.O.cpu().numpy().view(np.uint16), ref, w)
+    dist.barrier()
     # the library-collective route gives the same answer within the tolerance
     rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
     rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)

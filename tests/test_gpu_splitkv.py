@@ -156,3 +156,122 @@ def test_peer_exchange_wait_runs_out(oracle_lib):
     finally:
         xch.close()
         op.close()
+
+
+def _rank_pass(op, sub, last, groups=64):
+    """A rank's records-only plan with its reduce job, uploaded: (dp, args for esp_attn_forward_exchange)."""
+    plan = host.plan_tiles(sub.trees, sub.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, 8)
+    tiles, jobs, n_parts = shard.local_decode_plan(plan.tiles, is_last_rank=last)
+    dp = op.upload(sub, host.Plan(tiles, jobs, n_parts, 8))
+    return dp, op.make_args(dp)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("fp8", [False, True], ids=["bf16", "fp8"])
+@pytest.mark.parametrize("groups", [16, 64, 296])
+def test_fused_exchange_emulated_ranks(oracle_lib, world, fp8, groups):
+    """esp_attn_forward_exchange with the ranks emulated on one GPU: every rank's ONE launch computes its
+    records, folds them in two levels inside the decode kernel and stores the result into all ranks'
+    buffers (phase 1: it does not wait); then every rank runs the second half (phase 2), whose words are
+    all there by then - no launch ever waits for a later one. All ranks must hold identical bits, equal
+    to attention over the whole sequence, for three epochs on the same buffers; and the bits must be the
+    ones the two-kernel route (esp_attn_forward + esp_attn_exchange_parts) stores in the buffers, up to
+    the order of the folds (same tolerance)."""
+    P = 7000 + 16 * world + 9
+    w = wl.make_pass("fxch", 180 + world, [(P, 1)], 32, 8, 256 if fp8 else 128, 16, wl.BF16, wl.E4M3 if fp8 else None)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    ranges = shard.split_kv_range(P, world, w.bt)
+    op = host.AttnOp.for_workload(w)
+    xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=world)
+    try:
+        passes = [_rank_pass(op, _rank_workload(w, lo, hi), r == world - 1, groups) for r, (lo, hi) in enumerate(ranges)]
+        for epoch in range(3):
+            xch.next_epoch()
+            launches0 = op.launch_count
+            for r, (dp, args) in enumerate(passes):
+                dp.O.zero_()
+                op.forward_exchange(dp, args, xch, rank=r, phases=1)
+            assert op.launch_count - launches0 == world and op.last_kernel == "decode_gqa"   # one launch per rank
+            torch.cuda.synchronize()
+            outs = []
+            for r, (dp, args) in enumerate(passes):
+                op.forward_exchange(dp, args, xch, rank=r, phases=2)
+                op.check_status()
+                outs.append((dp.O.cpu().numpy().view(np.uint16).copy(), dp.lse.cpu().numpy().copy()))
+            for O, lse in outs[1:]:
+                assert np.array_equal(O, outs[0][0]) and np.array_equal(lse, outs[0][1])
+            util.check_output(outs[0][0], ref, w)
+            assert np.abs(outs[0][1] - lse_ref).max() < 2e-3
+    finally:
+        xch.close()
+        op.close()
+
+
+def test_fused_exchange_one_rank_one_launch_and_many_parts(oracle_lib):
+    """world = 1, phases = 3: one launch publishes to itself, reads its own words and writes the row. Also with
+    a plan of 64 records (8 groups of 8 in the two-level fold) and with few records (a single level)."""
+    w = wl.make_pass("fxch1", 191, [(9000, 1)], 32, 8, 128, 16, wl.BF16, None)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    op = host.AttnOp.for_workload(w)
+    xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=1)
+    try:
+        for groups in (8, 40, 296, 512):
+            dp, args = _rank_pass(op, w, True, groups)
+            for _ in range(2):
+                xch.next_epoch()
+                dp.O.zero_()
+                n0 = op.launch_count
+                op.forward_exchange(dp, args, xch, rank=0, phases=3)
+                op.check_status()
+                torch.cuda.synchronize()
+                resident = len(dp.plan.tiles) * w.Hkv <= 2 * 148        # the waiting CTAs need the whole grid on the GPU at once
+                assert op.launch_count - n0 == (1 if resident else 2), f"groups={groups}: {op.launch_count - n0} launches"
+                util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, what=f"groups={groups}")
+                assert np.abs(dp.lse.cpu().numpy() - lse_ref).max() < 2e-3
+    finally:
+        xch.close()
+        op.close()
+
+
+def test_fused_exchange_wait_runs_out(oracle_lib):
+    """One launch that waits for a peer which never publishes: after wait_ms it leaves O alone and the status
+    word reports it; the context keeps working (a bounded wait that runs out - no fault, no hang)."""
+    w = wl.make_pass("fxchT", 192, [(2000, 1)], 32, 8, 128, 16, wl.BF16, None)
+    ref, _ = oracle_lib.attention_f64(w)
+    op = host.AttnOp.for_workload(w)
+    xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=2)
+    try:
+        dp, args = _rank_pass(op, w, True)
+        xch.next_epoch()
+        dp.O.fill_(7.0)
+        op.forward_exchange(dp, args, xch, rank=0, phases=3, wait_ms=50)     # rank 1 stays silent
+        with pytest.raises(capi.EspError, match="peer GPU never published"):
+            op.check_status()
+        assert bool((dp.O == 7.0).all())
+        op.check_status()
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 64, 8)
+        dpw = op.upload(w, plan)
+        op.forward(dpw)                                                       # merges in the kernel with the same counters
+        op.check_status()
+        util.check_output(dpw.O.cpu().numpy().view(np.uint16), ref, w)
+    finally:
+        xch.close()
+        op.close()
+
+
+def test_two_level_merge_matches_the_combine_kernel(oracle_lib):
+    """The in-kernel merge (fuse_combine 2: groups folded as they finish, then the groups) against the
+    combine kernel (fuse_combine 0) on plans of 2 to 64 records per sequence: both within tolerance of the
+    float64 oracle, and equal to each other to fp32 rounding of the fold order."""
+    w = wl.make_pass("twolevel", 193, [(30000, 1), (700, 1), (5000, 1), (64, 1)], 32, 4, 128, 16, wl.BF16)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    for groups in (16, 128, 1184, 4096):
+        res = {}
+        for fuse in (0, 2):
+            O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=8, groups=groups, split=1 << 20,
+                                                        options={"fuse_combine": fuse})
+            assert kernel == "decode_gqa"
+            util.check_output(O, ref, w, what=f"groups={groups} fuse={fuse}")
+            assert np.abs(lse - lse_ref).max() < 2e-3
+            res[fuse] = wl.from_bits16(O, w.q_dtype)
+        assert np.abs(res[0] - res[2]).max() <= 2.0 ** -7 * np.abs(res[0]).max()
