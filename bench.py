@@ -424,6 +424,8 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
     lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
     w = r.w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
     op = r.op = host.AttnOp.for_workload(w, TILE_ROWS["c5"], B.local)
+    for kv in args.opt:
+        op.set_option(kv.split("=")[0], int(kv.split("=")[1]))
     base_plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, args.groups or 148 * 2, TILE_ROWS["c5"])
     tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
     r.plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, TILE_ROWS["c5"])
@@ -451,8 +453,10 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
             xch = None
     r.xch = xch
     if xch is not None:
-        # ONE launch per rank and step: the decode kernel folds the rank's records as its CTAs finish, stores the
-        # result into every rank's buffer over NVLink peer mappings, waits for the peers' and writes the row
+        # one call per rank and step (esp_attn_forward_exchange): the records-only pass, then ONE kernel that folds the
+        # rank's records, stores the result into every rank's buffer over NVLink peer mappings, waits for the peers'
+        # and writes the row. (With the library option fuse_exchange = 1 all of it happens inside the decode kernel, in
+        # one launch; that measured slower - 64.0 against 57.3 us per step on two GPUs - and is off by default.)
         a_x = layers.args()
         a_x.jobs, a_x.jobs_host, a_x.n_jobs = red_dev.data_ptr(), red_jobs.ctypes.data, len(red_jobs)
         r.keep = (red_jobs, red_dev)
@@ -461,7 +465,7 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
             xch.next_epoch()
             op.forward_exchange(dp, layers.next(a_x), xch)
         r.a_full = a_x
-        r.sharding = "KV range per rank; one launch per rank: records, two-level fold, NVLink peer stores, wait, final fold"
+        r.sharding = "KV range per rank; records-only pass, then one kernel per rank folds them, exchanges records over NVLink peer stores and finishes"
     else:
         def step():
             op.forward(dp, layers.next(r.a_attn))

@@ -53,7 +53,7 @@ struct esp_attn_ctx {
   // tiles and jobs are built on the host and travel through a small ring of pinned staging slots into
   // device slots of the context (see replan_pass).
   int opt_replan = 1;
-  int opt_p_f16 = 0;
+  int opt_fuse_exchange = 0;  // esp_attn_forward_exchange: 1 = merge and exchange inside the decode kernel (one launch); 0 = two kernels (measured faster)
   uint8_t* replan_dev = nullptr;
   uint8_t* replan_host = nullptr;
   cudaEvent_t replan_done[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -272,7 +272,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "fail_pass")) return &c->fail_every;
   if (!std::strcmp(name, "check_finite")) return &c->opt_check_finite;
   if (!std::strcmp(name, "replan")) return &c->opt_replan;
-  if (!std::strcmp(name, "umma_p_f16")) return &c->opt_p_f16;
+  if (!std::strcmp(name, "fuse_exchange")) return &c->opt_fuse_exchange;
   return nullptr;
 }
 
@@ -536,7 +536,6 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
-  k.p_f16 = (c->opt_p_f16 && s.q_dtype == ESP_BF16) ? 1 : 0;
 
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {
@@ -652,8 +651,10 @@ int esp_attn_forward_exchange(esp_attn_ctx* c, void* stream, const esp_attn_args
   if (x.phases == 2)  // only the second half: the records were published by an earlier launch
     return esp_attn_exchange_parts(c, stream, ap->parts, ap->X, ap->O, ap->lse, &ap->p, ap->jobs, ap->n_jobs, 1, parts_max, xp);
   bool fused = false;
-  if (int rc = forward_impl(c, stream, ap, xp, &fused)) return rc;
-  if (fused) return ESP_OK;
+  if (c->opt_fuse_exchange) {
+    if (int rc = forward_impl(c, stream, ap, xp, &fused)) return rc;
+    if (fused) return ESP_OK;
+  }
   // two kernels: the records, then merge + exchange + merge
   esp_attn_args rec = *ap;
   rec.n_jobs = 0, rec.jobs = nullptr, rec.jobs_host = nullptr;

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
     // ================= MMA issuer (one thread)
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_qk = umma_idesc<QDT>(BM, BN, 0, 0);
-      const uint32_t idesc_pv = a.p_f16 ? umma_idesc_ab(ESP_F16, QDT, BM, HD, 0, 1) : umma_idesc<QDT>(BM, HD, 0, 1);
+      constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
       // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
       // its address field (one thread issues everything, so every integer op here is latency).
       const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
@@ -406,26 +406,16 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
       float ps0 = 0.0f, ps1 = 0.0f;
       uint32_t pk[32];
-      // P is rounded to 16 bits before P.V (the reference rounds it to fp16, 40_attention.metal:297): to the
-      // pass's own type, or - option p_f16 - to fp16 against a bf16 V (the MMA takes mixed 16-bit operands).
-      if (a.p_f16) {
+      // P is rounded to the pass's 16-bit type before P.V (the reference rounds it to fp16, 40_attention.metal:297;
+      // a bf16 pass cannot do that: the MMA takes its A and B operands in one 16-bit format only - fp16 P
+      // against bf16 V raised "illegal instruction" when it was tried).
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sl2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
-          ps0 += p0;
-          ps1 += p1;
-          pk[c] = Elem16<ESP_F16>::pack2(p0, p1);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sl2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
-          ps0 += p0;
-          ps1 += p1;
-          pk[c] = QE::pack2(p0, p1);
-        }
+      for (int c = 0; c < 32; ++c) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sl2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
+        ps0 += p0;
+        ps1 += p1;
+        pk[c] = QE::pack2(p0, p1);
       }
       l_run += ps0 + ps1;
       tmem_st32(t_s, pk);  // over the scores this thread has already read

@@ -28,18 +28,13 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 // bits [4,6) D format (1 = f32), [7,10) A format, [10,13) B format (0 = f16, 1 = bf16),
 // bit 15 A major, bit 16 B major (0 = K, 1 = MN), [17,23) N >> 3, [24,29) M >> 4.
+// A and B take the same 16-bit format: fp16 A (P from tensor memory) against bf16 B (V) was tried and is
+// refused by the hardware ("illegal instruction").
 template <int DT>
 __device__ __forceinline__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, int b_mn_major) {
   const uint32_t fmt = DT == ESP_BF16 ? 1u : 0u;
   return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
          (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
-}
-
-// The same with the A and B element types chosen separately (the descriptor has one format field each).
-__device__ __forceinline__ constexpr uint32_t umma_idesc_ab(int a_dt, int b_dt, int M, int N, int a_mn_major, int b_mn_major) {
-  const uint32_t fa = a_dt == ESP_BF16 ? 1u : 0u, fb = b_dt == ESP_BF16 ? 1u : 0u;
-  return (1u << 4) | (fa << 7) | (fb << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(N >> 3) << 17) |
-         (uint32_t(M >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- MMA issue (one thread)

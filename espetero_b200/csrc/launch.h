@@ -61,7 +61,6 @@ struct KernelArgs {
   uint32_t x_tag, x_wait_ms;
   unsigned long long x_epoch_off;     // words from a buffer's start to this epoch's half
   uint2* x_records[ESP_ATTN_MAX_PEERS];
-  int32_t p_f16;       // tcgen05 kernels: round P to fp16 before P.V whatever the pass's 16-bit type (the reference rounds P to fp16, 40_attention.metal:297)
 };
 
 // Small plans travel in the kernel's parameter space (constant bank), one 64-byte line per tile

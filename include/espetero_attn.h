@@ -149,6 +149,7 @@ int esp_attn_abi_version(void);
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531), "check_finite" (1: scan every pass's
  * output for NaN / Inf, see esp_attn_finite_check; initialised from ESPETERO_CHECK_FINITE; default 0),
+ * "fuse_exchange" (see esp_attn_forward_exchange; default 0),
  * "attn_vec" (the reference's alternative decode schedule, src/model/impl/model.h:590, off there by
  * default and not built here: 0 is accepted, anything else answers ESP_ERR_UNSUPPORTED). */
 int esp_attn_set_option(esp_attn_ctx* ctx, const char* name, int value);
@@ -334,16 +335,20 @@ int esp_attn_plan_split_kv(esp_attn_tile* tiles, int32_t n_tiles, int32_t is_las
 int esp_attn_world_merge_jobs(int32_t n_groups, int32_t world, int32_t rows, esp_attn_combine* jobs, int32_t jobs_cap,
                               int32_t* n_jobs);
 
-/* The whole split-KV step of a rank in ONE launch: the decode kernel over the rank's records-only plan
- * (args: tiles tagged by esp_attn_plan_split_kv, jobs / jobs_host = its reduce job, n_jobs = 1), whose
- * CTAs fold the rank's records in two short levels as they finish (no CTA waits for another of its
- * GPU); the CTA that completes a kv head's record stores it into every rank's exchange buffer over peer
- * mappings, waits (bounded by wait_ms) for the other ranks' records of the same heads, folds them in
- * rank order and writes O / lse. Same buffers, epochs, bits-on-every-rank guarantee and failure
- * behaviour as esp_attn_exchange_parts. The waiting CTAs need the whole grid resident at once; a pass
- * whose grid is larger, or that the decode kernel does not take, runs as esp_attn_forward (records only)
- * followed by esp_attn_exchange_parts inside this call. phases = 1 publishes without waiting, phases = 2
- * runs only the second half (both for tests that emulate several ranks on one GPU). */
+/* The whole split-KV step of a rank in one call: args carry the rank's records-only plan (tiles tagged by
+ * esp_attn_plan_split_kv) and its reduce job (jobs / jobs_host, n_jobs = 1). By default the call runs the
+ * records-only pass and then esp_attn_exchange_parts (two launches). With the context option
+ * "fuse_exchange" = 1 everything happens inside the decode kernel, in ONE launch: its CTAs fold the rank's
+ * records in two short levels as they finish (no CTA waits for another of its GPU); the CTA that completes
+ * a kv head's record stores it into every rank's exchange buffer over peer mappings, waits (bounded by
+ * wait_ms) for the other ranks' records of the same heads, folds them in rank order and writes O / lse. The
+ * waiting CTAs need the whole grid resident at once; a pass whose grid is larger, or that the decode
+ * kernel does not take, falls back to the two launches. The one-launch form measured slower (64.0 against
+ * 57.3 us per step for a 131072-key E4M3 sequence over two GPUs: its chain of fence, ticket and bulk copy
+ * per level costs more than a kernel boundary), which is why it is off by default. Same buffers, epochs,
+ * bits-on-every-rank guarantee and failure behaviour as esp_attn_exchange_parts either way. phases = 1
+ * publishes without waiting, phases = 2 runs only the second half (both for tests that emulate several
+ * ranks on one GPU). */
 int esp_attn_forward_exchange(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args, const esp_attn_exchange* x);
 
 /* Device memory another process of the same box can map: cudaMalloc + zero fill + an IPC handle

@@ -195,3 +195,20 @@ def e4m3x2(w: int):
     lo, hi = C.c_float(), C.c_float()
     load().ref_e4m3x2(C.c_uint(w), C.byref(lo), C.byref(hi))
     return lo.value, hi.value
+
+
+def attention(w, tiles, n_parts: int, which: str = "flash"):
+    """The reference's flash_attention<G> ("flash") or attn_decode_gqa<G> ("decode") run by the SIMT emulator over
+    `tiles` of a workload (256-dim fp16 heads with gate: the kernels' fixed shape). Returns (O bits, parts)."""
+    assert w.HD == 256 and w.q_dtype == 0 and w.kv_dtype == 0 and w.X is not None and w.bt > 0
+    from oracle import Params
+    tiles = np.ascontiguousarray(tiles)
+    O = np.zeros((w.n_rows, w.q_ld), dtype=np.uint16)
+    parts = np.zeros(max(1, n_parts) * w.Hkv * 8 * w.G * 258, dtype=np.float32)
+    p = Params(w.H, w.Hkv, w.q_ld, w.kv_ld, w.g_ld, w.bt, w.kv_base)
+    X = np.ascontiguousarray(w.X, dtype=np.float32)
+    rc = load().ref_attention(0 if which == "flash" else 1, w.G, _p(w.Q), _p(w.Kb), _p(w.Vb), _p(w.kv), _p(w.blocks), _p(w.desc), _p(X), _p(O),
+                              C.byref(p), _p(tiles), len(tiles), _p(w.trees), _p(parts))
+    if rc != 0:
+        raise RuntimeError(f"the reference does not instantiate G = {w.G}")
+    return O, parts

@@ -59,6 +59,7 @@ def main():
     assert bool((every == every[0]).all()), "ranks hold different outputs"
     # the one-launch route (esp_attn_forward_exchange: records, two-level fold, peer stores, wait and final fold in
     # the decode kernel): correct, identical on every rank, the same over several epochs, and one launch per step
+    op.set_option("fuse_exchange", 1)
     dpf = op.upload(sub, host.Plan(tiles, jobs, n_parts, 8))
     args_f = op.make_args(dpf)
     fused = []

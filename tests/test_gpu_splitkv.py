@@ -182,6 +182,7 @@ def test_fused_exchange_emulated_ranks(oracle_lib, world, fp8, groups):
     ref, lse_ref = oracle_lib.attention_f64(w)
     ranges = shard.split_kv_range(P, world, w.bt)
     op = host.AttnOp.for_workload(w)
+    op.set_option("fuse_exchange", 1)
     xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=world)
     try:
         passes = [_rank_pass(op, _rank_workload(w, lo, hi), r == world - 1, groups) for r, (lo, hi) in enumerate(ranges)]
@@ -213,6 +214,7 @@ def test_fused_exchange_one_rank_one_launch_and_many_parts(oracle_lib):
     w = wl.make_pass("fxch1", 191, [(9000, 1)], 32, 8, 128, 16, wl.BF16, None)
     ref, lse_ref = oracle_lib.attention_f64(w)
     op = host.AttnOp.for_workload(w)
+    op.set_option("fuse_exchange", 1)
     xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=1)
     try:
         for groups in (8, 40, 296, 512):
@@ -239,6 +241,7 @@ def test_fused_exchange_wait_runs_out(oracle_lib):
     w = wl.make_pass("fxchT", 192, [(2000, 1)], 32, 8, 128, 16, wl.BF16, None)
     ref, _ = oracle_lib.attention_f64(w)
     op = host.AttnOp.for_workload(w)
+    op.set_option("fuse_exchange", 1)
     xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=2)
     try:
         dp, args = _rank_pass(op, w, True)
@@ -275,3 +278,23 @@ def test_two_level_merge_matches_the_combine_kernel(oracle_lib):
             assert np.abs(lse - lse_ref).max() < 2e-3
             res[fuse] = wl.from_bits16(O, w.q_dtype)
         assert np.abs(res[0] - res[2]).max() <= 2.0 ** -7 * np.abs(res[0]).max()
+
+
+def test_forward_exchange_default_route_is_two_kernels(oracle_lib):
+    """Without the option esp_attn_forward_exchange runs the records-only pass and the exchange kernel (the route
+    that measured faster); same result."""
+    w = wl.make_pass("fxch2k", 194, [(6000, 1)], 32, 8, 128, 16, wl.BF16, None)
+    ref, _ = oracle_lib.attention_f64(w)
+    op = host.AttnOp.for_workload(w)
+    xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=1)
+    try:
+        dp, args = _rank_pass(op, w, True)
+        xch.next_epoch()
+        n0 = op.launch_count
+        op.forward_exchange(dp, args, xch, rank=0, phases=3)
+        op.check_status()
+        assert op.launch_count - n0 == 2
+        util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w)
+    finally:
+        xch.close()
+        op.close()

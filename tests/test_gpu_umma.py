@@ -281,24 +281,3 @@ def test_records_only_plans_are_not_replanned():
         assert op.last_kernel == "flash_general"
     finally:
         op.close()
-
-
-@pytest.mark.parametrize("case", ["prefill", "verify"])
-def test_p_rounded_to_fp16_against_bf16_values(oracle_lib, case):
-    """Option umma_p_f16: a bf16 pass rounds P to fp16 (as the reference does, kernels/40_attention.metal:297)
-    and multiplies it with bf16 V in one mixed-operand MMA. The result must meet the tolerance with the
-    fp16 rounding unit (2^-12) in place of bf16's (2^-9) in the P-rounding term."""
-    if case == "prefill":
-        w, tr = wl.config_c3(n_seqs=2, rows=600), 128
-    else:
-        w, tr = wl.config_c4(n_seqs=3, prefix=1500), 16
-    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
-    for kern in (1, 2):
-        O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=tr, groups=148, split=1 << 20,
-                                                    options={"umma_p_f16": 1, "umma_kernel": kern})
-        assert kernel == ("flash_umma" if kern == 1 else "flash_umma_pair")
-        got = wl.from_bits16(O, w.q_dtype).astype(np.float64)
-        allow = util.TOL_16 + util.out_ulp_half(ref, w.q_dtype) + 2.0 ** -12 * ref_abs
-        err = np.abs(got - ref)
-        assert (err <= allow).all(), f"{case}/{kernel}: max abs err {err.max():.3e}, {(err > allow).sum()} elements off"
-        assert np.abs(lse - lse_ref).max() < 2e-3
