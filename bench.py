@@ -422,6 +422,8 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
     r.name, r.split_kv, r.scaling = "c5", True, "strong"
     ctx_all = 8192 if small else 131072
     lo, hi = shard.split_kv_range(ctx_all, world, 16)[rank]
+    if args.ctx > 0 and world == 1:
+        lo, hi = 0, args.ctx
     w = r.w = wl.config_c5(0xE5B205 + 1000 * rank, ctx=hi - lo)
     op = r.op = host.AttnOp.for_workload(w, TILE_ROWS["c5"], B.local)
     for kv in args.opt:
@@ -430,8 +432,9 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
     tiles, red_jobs, n_parts = shard.local_decode_plan(base_plan.tiles, is_last_rank=(rank == world - 1))
     r.plan = host.Plan(tiles, np.zeros(0, dtype=wl.COMBINE_DT), n_parts, TILE_ROWS["c5"])
     dp = r.dp = op.upload(w, r.plan)
-    for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
-        dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
+    if world > 1:
+        for t in (dp.Q, dp.Kb, dp.Vb):  # the query row is replicated: every rank uses rank 0's
+            dist.broadcast(t.view(torch.uint8), src=0)  # NCCL has no 16-bit integer type
     layers = r.layers = LayerCycle(op, dp, w)
     r.a_attn = layers.args()
     r.a_full = r.a_attn
@@ -440,7 +443,9 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
     rec_local = torch.zeros(op.parts_floats(1), dtype=torch.float32, device=dev)
     rec_world = torch.zeros(world * op.parts_floats(1), dtype=torch.float32, device=dev)
     xch = None
-    if args.exchange == "p2p":
+    if world == 1:
+        xch = host.PeerExchange.emulated(op, n_jobs=1, rows_max=1, world=1)
+    elif args.exchange == "p2p":
         try:
             xch = host.PeerExchange(op, n_jobs=1, rows_max=1)
             ok = 1
@@ -463,7 +468,7 @@ def setup_split_kv(B: Bench, small: bool) -> Run:
 
         def step():
             xch.next_epoch()
-            op.forward_exchange(dp, layers.next(a_x), xch)
+            op.forward_exchange(dp, layers.next(a_x), xch, rank=rank)
         r.a_full = a_x
         r.sharding = "KV range per rank; records-only pass, then one kernel per rank folds them, exchanges records over NVLink peer stores and finishes"
     else:
@@ -631,6 +636,8 @@ def main():
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="split-KV record exchange at N > 1 (c5)")
     ap.add_argument("--fuse", type=int, default=-1, help="option fuse_combine of the library (0 off, 1 small passes, 2 always); -1: its default")
+    ap.add_argument("--ctx", type=int, default=0, help="c5 on one GPU: run the split-KV step of ONE rank holding this many keys (records-only pass + "
+                    "exchange with itself): the latency chain of a rank at N GPUs without the NVLink hop, for tuning")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="set a library option (esp_attn_set_option) on the pass's context")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
@@ -643,7 +650,7 @@ def main():
     rank, world, dev = B.rank, B.world, B.dev
     W = max(3, args.warmup)
 
-    if args.workload == "c5" and world > 1:
+    if args.workload == "c5" and (world > 1 or args.ctx > 0):
         r = setup_split_kv(B, args.small)
     else:
         w = build_workload(args.workload, rank, args.small, world)
@@ -675,7 +682,7 @@ def main():
 
     # ---- parity of exactly this pass (plan, options, sizes) with the float64 oracle, off the timed region
     parity = None
-    if world == 1 and not args.no_check:
+    if world == 1 and not args.no_check and not r.split_kv:
         r.dp.O.zero_()
         r.dp.lse.zero_()
         a = r.layers.args()
@@ -735,7 +742,7 @@ def main():
         if parity is not None:
             line["parity"] = parity
         line.update(extra)
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.ctx:
             v, threads, sample, dt = time_cpu(args.workload)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
         print(json.dumps(line), flush=True)

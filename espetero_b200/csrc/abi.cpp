@@ -53,6 +53,7 @@ struct esp_attn_ctx {
   // tiles and jobs are built on the host and travel through a small ring of pinned staging slots into
   // device slots of the context (see replan_pass).
   int opt_replan = 1;
+  int opt_pair_merge = 1;  // flash_umma: passes whose jobs all have two records merge them inside a cluster pair (distributed shared memory)
   int opt_fuse_exchange = 0;  // esp_attn_forward_exchange: 1 = merge and exchange inside the decode kernel (one launch); 0 = two kernels (measured faster)
   uint8_t* replan_dev = nullptr;
   uint8_t* replan_host = nullptr;
@@ -273,6 +274,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "check_finite")) return &c->opt_check_finite;
   if (!std::strcmp(name, "replan")) return &c->opt_replan;
   if (!std::strcmp(name, "fuse_exchange")) return &c->opt_fuse_exchange;
+  if (!std::strcmp(name, "pair_merge")) return &c->opt_pair_merge;
   return nullptr;
 }
 
@@ -536,6 +538,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   k.q_dtype = s.q_dtype, k.kv_dtype = s.kv_dtype, k.n_blocks = a.n_blocks, k.scale = s.scale;
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
+  k.pair_merge = c->opt_pair_merge;
 
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {

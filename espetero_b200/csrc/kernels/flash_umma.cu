@@ -85,6 +85,24 @@ static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// Thread-block cluster: rank of this CTA, a barrier over every thread of the cluster (release / acquire), the
+// address of a shared-memory location in another CTA of the cluster, and a 16-byte store to it.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map_shared(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, const float4& v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 
 template <int QDT>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -135,6 +153,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int bt = inl ? int(ts.bt) : p.bt;
   const int G = inl ? int(ts.G) : a.G, TR = inl ? int(ts.tile_rows) : a.tile_rows, HPC = BM / TR;
   const int fix_parts = inl ? int(ts.fix_parts) : 0;  // > 0: the last CTA of this tile's merge job finishes the rows
+  // Pair mode (a.fuse == 2): the two tiles of every job run as one thread-block cluster of two CTAs on neighbouring
+  // SMs; the second CTA hands its record to the first through distributed shared memory and the first finishes the
+  // rows - no record in global memory, no fence, no ticket. Uniform over the grid.
+  const bool pair_mode = a.fuse == 2 && fix_parts == 2 && tile.part >= 0 && HPC == G;
   const int kvh = (int(blockIdx.y) * HPC) / G;
   const int end = tree.base + tree.M;
   const int rows_live = min(TR, end - tile.r0);
@@ -599,7 +621,64 @@ __global__ void __launch_bounds__(kThreads, 1)
           a.lse[size_t(row) * p.H + head] = l_tot > 0.0f ? M * kLn2 + __logf(l_tot) : -INFINITY;
         }
       }
-      if (staged) {
+      if (staged && pair_mode) {
+        // Both CTAs of the pair have staged their record in their own (idle) K ring. Barrier 1: both are past their
+        // last MMA, so the first CTA's rings may be written. The second CTA copies its record into the first one's
+        // `other` area over distributed shared memory; barrier 2 makes it visible; the first CTA folds the two records
+        // in record order and writes the rows.
+        named_barrier(2, kSoftmaxThreads);
+        cluster_sync_all();
+        float* other = stage + BM * (HD + 2);
+        const uint32_t me = cluster_ctarank();
+        if (me != 0) {
+          const uint32_t dst = cluster_map_shared(other, 0);
+          const float4* src = reinterpret_cast<const float4*>(stage);
+          for (int i = tid; i < BM * (HD + 2) / 4; i += kSoftmaxThreads) st_cluster_f4(dst + 16u * uint32_t(i), src[i]);
+        }
+        cluster_sync_all();
+        if (me == 0) {
+          float Mx = -INFINITY, L = 0.0f;
+          float acc[BH];
+#pragma unroll
+          for (int i = 0; i < BH; ++i) acc[i] = 0.0f;
+#pragma unroll 1
+          for (int s2 = 0; s2 < 2; ++s2) {
+            const float* rp = ((tile.pad1 + s2 == tile.part) ? stage : other) + srow * (HD + 2);
+            const float m_s = rp[HD];
+            if (m_s == -INFINITY) continue;  // an empty record adds nothing
+            if (m_s > Mx) {                    // rescale what has been summed so far
+              const float f = __expf(Mx - m_s);  // 0 for the first record
+              L *= f;
+#pragma unroll
+              for (int i = 0; i < BH; ++i) acc[i] *= f;
+              Mx = m_s;
+            }
+            const float w = __expf(m_s - Mx);
+            L += w * rp[HD + 1];
+#pragma unroll
+            for (int i = 0; i < BH; i += 2) {
+              const float2 o2 = *reinterpret_cast<const float2*>(rp + BH * half + i);
+              acc[i] += w * o2.x, acc[i + 1] += w * o2.y;
+            }
+          }
+          if (row_ok) {
+            const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+            for (int i = 0; i < BH; i += 8) {
+              float o[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                o[k] = acc[i + k] * inv;
+                if (gp) o[k] *= sigmoid_gate(gp[BH * half + i + k]);
+              }
+              uint4 w4;
+              w4.x = QE::pack2(o[0], o[1]), w4.y = QE::pack2(o[2], o[3]), w4.z = QE::pack2(o[4], o[5]), w4.w = QE::pack2(o[6], o[7]);
+              *reinterpret_cast<uint4*>(op + BH * half + i) = w4;
+            }
+            if (half == 0 && a.lse) a.lse[size_t(row) * p.H + head] = L > 0.0f ? Mx + __logf(L) : -INFINITY;
+          }
+        }
+      } else if (staged) {
         // 128 records x (HD + 2) floats, contiguous and 16-byte aligned in `parts`: coalesced copy
         named_barrier(2, kSoftmaxThreads);
         const float4* src = reinterpret_cast<const float4*>(stage);
@@ -685,6 +764,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   }
+  if (pair_mode && !is_softmax) {  // the softmax warps pass the same two barriers inside their epilogue
+    __syncwarp();
+    cluster_sync_all();
+    cluster_sync_all();
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks + 1] = global_timer_ns();
@@ -761,8 +845,27 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
   *merged = fuse;
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
-  const cudaError_t e = a.q_dtype == ESP_F16 ? launch_pdl(flash_umma_kernel<ESP_F16>, grid, block, SMEM_BYTES, stream, pool_map, kb_map, vb_map, plan, a)
-                                             : launch_pdl(flash_umma_kernel<ESP_BF16>, grid, block, SMEM_BYTES, stream, pool_map, kb_map, vb_map, plan, a);
+  // Pair mode: every job has exactly two records, written by the tiles 2 j and 2 j + 1 (the kernel walks the tiles
+  // from the last one down: cluster ranks 0 and 1 are the tiles 2 j + 1 and 2 j).
+  bool pairs = fuse && a.pair_merge && a.n_tiles % 2 == 0;
+  for (int i = 0; pairs && i < a.n_tiles; i += 2)
+    pairs = plan.start[i].fix_parts == 2 && plan.start[i + 1].fix_parts == 2 && plan.start[i].fix_job == plan.start[i + 1].fix_job;
+  KernelArgs k = a;
+  k.fuse = pairs ? 2 : (fuse ? 1 : 0);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = SMEM_BYTES, cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  if (pairs) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_F16>, pool_map, kb_map, vb_map, plan, k)
+                                       : cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_BF16>, pool_map, kb_map, vb_map, plan, k);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;
 }

@@ -35,7 +35,9 @@ struct KernelArgs {
   int* status;  // device status word of the context
   int* counters;  // kFixupCounters zeroed ints of the context (arrival counters of fused merges), or NULL
   const esp_attn_combine* jobs;  // device copy of the combine jobs (decode kernel, fused merge)
-  int32_t fuse;                  // 1: tiles carry their job in pad1 and the last CTA of a job merges
+  int32_t fuse;                  // 1: tiles carry their job in pad1 and the last CTA of a job merges (flash_umma: 2 = the two tiles
+                                 // of every job run as a cluster pair and merge through distributed shared memory)
+  int32_t pair_merge;            // flash_umma: allow the cluster-pair merge (context option "pair_merge")
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
   int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2

@@ -281,3 +281,43 @@ def test_records_only_plans_are_not_replanned():
         assert op.last_kernel == "flash_general"
     finally:
         op.close()
+
+
+@pytest.mark.parametrize("gate", [False, True], ids=["plain", "gate"])
+def test_two_record_jobs_merge_inside_a_cluster_pair(oracle_lib, gate):
+    """A verify pass whose every row group is split in two: the two CTAs of a job run as a thread-block cluster and
+    merge through distributed shared memory (option pair_merge, on by default) - one launch, nothing written to
+    `parts`. Same results as the ticket merge through global memory (pair_merge 0) and as the combine kernel
+    (fuse_combine 0), all within tolerance of the float64 oracle; rows of short trees and an odd tree out included."""
+    trees = [(2048, 16), (1500, 16), (2048, 7), (2048, 16)]
+    w = wl.make_pass("pairs", 601, trees, 32, 4, 128, 16, wl.BF16, mask="tree", gate=gate)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    outs = {}
+    for name, options in (("pair", {}), ("ticket", {"pair_merge": 0}), ("combine", {"fuse_combine": 0})):
+        op = host.AttnOp.for_workload(w, 16)
+        try:
+            for k, v in options.items():
+                op.set_option(k, v)
+            plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1024, 32, 32, 16)
+            assert len(plan.tiles) == 8 and all(int(j["nparts"]) == 2 for j in plan.jobs)
+            dp = op.upload(w, plan)
+            dp.parts.fill_(-7.0)
+            n0 = op.launch_count
+            op.forward(dp)
+            op.check_status()
+            torch.cuda.synchronize()
+            assert op.last_kernel == "flash_umma" and op.launch_count - n0 == (2 if name == "combine" else 1)
+            if name == "pair":
+                assert bool((dp.parts == -7.0).all()), "the pair merge wrote records to global memory"
+            O, lse = dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy()
+            util.check_output(O, ref, w, what=name)
+            assert np.abs(lse - lse_ref).max() < 2e-3
+            outs[name] = wl.from_bits16(O, w.q_dtype)
+            for _ in range(3):                               # back to back on the same context
+                op.forward(dp)
+            op.check_status()
+            assert np.array_equal(dp.O.cpu().numpy().view(np.uint16), O)
+        finally:
+            op.close()
+    assert np.abs(outs["pair"] - outs["ticket"]).max() <= 2.0 ** -7 * np.abs(outs["pair"]).max()
+    assert np.abs(outs["pair"] - outs["combine"]).max() <= 2.0 ** -7 * np.abs(outs["pair"]).max()
