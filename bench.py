@@ -623,12 +623,67 @@ def strong_scaling_legs(B: Bench, steps: int):
     return out
 
 
+PREP_LAYOUTS = {
+    # name: H, Hkv, HD, rot_half, gate interleaved with the query heads, default rows
+    "plain128": (64, 8, 128, 64, False, 32768),   # the causal-prefill shape (C3) with full rotary
+    "gated256": (32, 8, 256, 32, True, 8192),     # the layout of kernels/40_attention.metal:23-102
+}
+
+
+def run_prep(args):
+    """--workload prep: esp_attn_prep alone (the step right before the attention pass; not part of the headline
+    metric). Per row the kernel reads (H + 2 Hkv) * HD floats of the fused projection and writes as many 16-bit
+    elements: HBM-bound. One JSON line per layout."""
+    import torch
+    from espetero_b200 import capi, host, workloads as wl
+    hbm_peak, _, which = measured_peaks()
+    for layout in (sorted(PREP_LAYOUTS) if args.layout == "all" else [args.layout]):
+        H, Hkv, HD, rot_half, gated, rows = PREP_LAYOUTS[layout]
+        rows = args.rows or rows
+        q_stride = 2 * HD if gated else HD
+        k_off = H * q_stride
+        v_off = k_off + Hkv * HD
+        ld = v_off + Hkv * HD
+        op = host.AttnOp(H, Hkv, HD, 16, wl.BF16, wl.BF16, 1.0)
+        try:
+            dev = op.device
+            X = torch.randn(rows, ld, device=dev)
+            qn, kn = torch.ones(HD, device=dev), torch.ones(HD, device=dev)
+            pos = torch.randint(0, 100000, (rows, 4), dtype=torch.int32, device=dev)
+            inv = torch.tensor((1e6 ** (-np.arange(rot_half) / rot_half)).astype(np.float32), device=dev)
+            sel = torch.zeros(rot_half, dtype=torch.int32, device=dev)
+            Q = torch.zeros(rows, H * HD, dtype=torch.int16, device=dev)
+            Kb = torch.zeros(rows, Hkv * HD, dtype=torch.int16, device=dev)
+            Vb = torch.zeros_like(Kb)
+            pp = capi.PrepParams(H, Hkv, ld, 0, q_stride, k_off, v_off, H * HD, Hkv * HD, rot_half, 1e-6, 1.0, 16, 0, 0)
+            for _ in range(max(3, args.warmup)):
+                op.attn_prep(X, qn, kn, pos, inv, sel, Q, Kb, Vb, pp)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            e0.record()
+            for _ in range(args.steps):
+                op.attn_prep(X, qn, kn, pos, inv, sel, Q, Kb, Vb, pp)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1) / args.steps
+            nbytes = rows * (H + 2 * Hkv) * HD * (4 + 2)
+            print(json.dumps({"metric": "attn_prep_hbm_bandwidth", "value": nbytes / ms / 1e6, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                              "ms_per_step": ms, "config": {"workload": "attn_prep", "layout": layout, "rows": rows, "H": H, "Hkv": Hkv, "HD": HD,
+                                                            "l2": "inputs larger than L2" if nbytes > 2 * L2_BYTES else "inputs fit L2"},
+                              "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak,
+                                           "peak_source": which, "kernel": "attn_prep", "ms_per_launch": ms, "algorithmic_bytes": nbytes}}), flush=True)
+        finally:
+            op.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "prep"])
+    ap.add_argument("--layout", default="all", choices=["all"] + sorted(PREP_LAYOUTS), help="--workload prep: which projection layout")
+    ap.add_argument("--rows", type=int, default=0, help="--workload prep: rows (0: the layout's default)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -643,6 +698,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "prep":
+        return run_prep(args)
 
     B = Bench(args)
     torch, dist = B.torch, B.dist

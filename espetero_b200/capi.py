@@ -67,7 +67,9 @@ class Args(C.Structure):
                 ("n_tiles", C.c_int32), ("n_trees", C.c_int32), ("n_jobs", C.c_int32), ("n_rows", C.c_int32),
                 ("n_blocks", C.c_int32), ("n_block_entries", C.c_int32), ("n_parts", C.c_int32), ("reserved", C.c_int32),
                 ("p", Params), ("pos", C.c_void_p), ("window", C.c_int32), ("ring", C.c_int32), ("bidi", C.c_int32),
-                ("reserved2", C.c_int32), ("dequant_scratch", C.c_void_p), ("dequant_scratch_bytes", C.c_uint64)]
+                ("reserved2", C.c_int32), ("dequant_scratch", C.c_void_p), ("dequant_scratch_bytes", C.c_uint64),
+                ("qsa_tlist", C.c_void_p), ("qsa_tcount", C.c_void_p), ("qsa_rinfo", C.c_void_p), ("qsa_sel", C.c_void_p),
+                ("qsa_nbw", C.c_int32), ("qsa_n_lists", C.c_int32)]
 
 
 class PrepParams(C.Structure):
@@ -144,6 +146,12 @@ PROTOTYPES = {
     "esp_forest_anc_masks": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "esp_attn_decode_static": (C.c_int, [C.POINTER(Shape), C.c_void_p, C.POINTER(Args)]),
     "esp_attn_decode_static_status": (C.c_int, [C.c_void_p]),
+    "esp_qsa_plan": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                               C.c_void_p, C.c_int32, C.c_void_p]),
+    "esp_attn_plan_qsa": (C.c_int, [C.POINTER(Tree), C.c_int32, C.c_int32, C.POINTER(PlanOpts), C.c_void_p, C.POINTER(Tile), C.c_int32,
+                                    C.POINTER(Combine), C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "esp_qsa_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
+    "esp_qsa_tiles": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]),
     "esp_attn_finite_check": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_int32, C.c_float, C.c_void_p]),
     "esp_attn_set_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "esp_attn_stamp": (C.c_int, [C.c_void_p, C.c_void_p]),

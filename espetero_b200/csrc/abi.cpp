@@ -104,6 +104,8 @@ int check_params(const esp_attn_ctx* c, const esp_attn_params& p) {
   return ESP_OK;
 }
 
+bool windowed_lists(const esp_attn_args& a) { return a.qsa_tlist != nullptr; }
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -124,6 +126,12 @@ int esp::validate_pass(const esp_attn_shape& s, int TR, bool deep, const esp_att
   if (a.window < 0 || a.ring < 0) return fail(ESP_ERR_INVALID, "forward: window=%d ring=%d", a.window, a.ring);
   if (a.window > 0 && !a.pos) return fail(ESP_ERR_INVALID, "forward: a sliding window needs the rows' positions (pos)");
   if (a.bidi && (s.flags & ESP_ATTN_FLAG_ANC_MASK)) return fail(ESP_ERR_UNSUPPORTED, "forward: bidi uses desc.w and cannot be combined with ancestor masks");
+  if (a.qsa_tlist) {
+    if (!a.qsa_tcount || !a.qsa_rinfo || !a.qsa_sel || a.qsa_nbw <= 0 || a.qsa_n_lists <= 0)
+      return fail(ESP_ERR_INVALID, "forward: sparse attention needs tlist, tcount, rinfo, sel, nbw and the list count together");
+    if (s.flags & ESP_ATTN_FLAG_ANC_MASK) return fail(ESP_ERR_UNSUPPORTED, "forward: sparse attention reads the rows' desc records, not ancestor masks");
+    if (a.window > 0 || a.ring > 0 || a.bidi) return fail(ESP_ERR_UNSUPPORTED, "forward: sparse attention and sliding-window layers do not combine");
+  }
   if (!deep || !a.trees_host || !a.tiles_host) return ESP_OK;
   bool any_cached = false;
   for (int i = 0; i < a.n_trees; ++i) {
@@ -146,7 +154,12 @@ int esp::validate_pass(const esp_attn_shape& s, int TR, bool deep, const esp_att
     if (t.tree < 0 || t.tree >= a.n_trees) return fail(ESP_ERR_INVALID, "tile %d: tree %d of %d", i, t.tree, a.n_trees);
     const esp_attn_tree& tr = a.trees_host[t.tree];
     if (t.r0 < tr.base || t.r0 >= tr.base + tr.M) return fail(ESP_ERR_INVALID, "tile %d: first row %d outside its tree [%d, %d)", i, t.r0, tr.base, tr.base + tr.M);
-    if (t.k0 < 0 || t.k0 > t.k1 || t.k1 > tr.P) return fail(ESP_ERR_INVALID, "tile %d: key range [%d, %d) outside [0, %d]", i, t.k0, t.k1, tr.P);
+    if (a.qsa_tlist && t.pad0 != 0) {  // Qwen sparse attention: k0 / k1 are entries of union list pad1 (the last part is open-ended)
+      if (t.k0 < 0 || t.k0 > t.k1) return fail(ESP_ERR_INVALID, "tile %d: list entries [%d, %d)", i, t.k0, t.k1);
+      if (t.pad1 < 0 || t.pad1 >= a.qsa_n_lists) return fail(ESP_ERR_INVALID, "tile %d: union list %d of %d", i, t.pad1, a.qsa_n_lists);
+    } else if (t.k0 < 0 || t.k0 > t.k1 || t.k1 > tr.P) {
+      return fail(ESP_ERR_INVALID, "tile %d: key range [%d, %d) outside [0, %d]", i, t.k0, t.k1, tr.P);
+    }
     if (t.part >= a.n_parts) return fail(ESP_ERR_INVALID, "tile %d: record %d of %d", i, t.part, a.n_parts);
     if (t.part >= 0 && !a.parts) return fail(ESP_ERR_INVALID, "tile %d: writes a record but parts is null", i);
   }
@@ -498,12 +511,13 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   int TR = c->tile_rows;
 
-  const bool windowed = a.window > 0 || a.ring > 0 || a.bidi != 0;  // the generic kernel's layer options (80_gemma.metal)
+  // the generic kernel's layer options (80_gemma.metal) and the sparse-attention lists (45_qsa.metal) live on the general kernel
+  const bool windowed = a.window > 0 || a.ring > 0 || a.bidi != 0 || a.qsa_tlist != nullptr;
 
   // Kernel choice, as forest.h:2864-2868: single-row trees with G <= 8 take the decode kernel.
   bool single = c->G <= 8 && a.trees_host != nullptr && a.tiles_host != nullptr;
   for (int i = 0; single && i < a.n_trees; ++i) single = a.trees_host[i].M == 1;
-  bool decode = single && c->opt_attn_gqa && esp::decode_gqa_supports(s.HD, c->G, s.bt, s.q_dtype, s.kv_dtype) && a.kv != nullptr && a.n_blocks > 0 &&
+  bool decode = single && !windowed_lists(a) && c->opt_attn_gqa && esp::decode_gqa_supports(s.HD, c->G, s.bt, s.q_dtype, s.kv_dtype) && a.kv != nullptr && a.n_blocks > 0 &&
                 (size_t(a.p.kv_ld) * elem_bytes(s.kv_dtype)) % 128 == 0 && (a.p.kv_base * elem_bytes(s.kv_dtype)) % 128 == 0;
   // (a tile may start at any key: sliding-window plans begin at the row's first visible key)
 
@@ -539,6 +553,8 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
   k.pair_merge = c->opt_pair_merge;
+  k.qsa_tlist = a.qsa_tlist, k.qsa_tcount = a.qsa_tcount, k.qsa_rinfo = a.qsa_rinfo, k.qsa_sel = a.qsa_sel;
+  k.qsa_nbw = a.qsa_nbw, k.qsa_n_lists = a.qsa_n_lists;
 
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {
@@ -663,6 +679,24 @@ int esp_attn_forward_exchange(esp_attn_ctx* c, void* stream, const esp_attn_args
   rec.n_jobs = 0, rec.jobs = nullptr, rec.jobs_host = nullptr;
   if (int rc = forward_impl(c, stream, &rec, nullptr, nullptr)) return rc;
   return esp_attn_exchange_parts(c, stream, ap->parts, ap->X, ap->O, ap->lse, &ap->p, ap->jobs, ap->n_jobs, 1, parts_max, xp);
+}
+
+int esp_qsa_select(void* stream, const float* scores, const int32_t* srows, const int32_t* rinfo, uint32_t* sel, int32_t n_sparse, int32_t nbmax,
+                   int32_t nbw) {
+  if (n_sparse <= 0) return ESP_OK;
+  if (!scores || !srows || !rinfo || !sel || nbmax <= 0 || nbw < (nbmax + 31) / 32) return fail(ESP_ERR_INVALID, "esp_qsa_select: null pointer, or nbw < ceil(nbmax / 32)");
+  const cudaError_t e = esp::launch_qsa_select(scores, srows, rinfo, sel, n_sparse, nbmax, nbw, static_cast<cudaStream_t>(stream), nullptr);
+  if (e != cudaSuccess) return cuda_fail(e, "qsa_select");
+  return ESP_OK;
+}
+
+int esp_qsa_tiles(void* stream, const uint32_t* sel, const esp_attn_tree* trees, const int32_t* rinfo, const esp_qsa_tile* qtiles, int32_t n_qtiles,
+                  uint32_t* tlist, uint32_t* tcount, int32_t nbmax, int32_t nbw) {
+  if (n_qtiles <= 0) return ESP_OK;
+  if (!sel || !trees || !rinfo || !qtiles || !tlist || !tcount || nbmax <= 0 || nbw <= 0) return fail(ESP_ERR_INVALID, "esp_qsa_tiles: null pointer or bad size");
+  const cudaError_t e = esp::launch_qsa_tiles(sel, trees, rinfo, qtiles, n_qtiles, tlist, tcount, nbmax, nbw, static_cast<cudaStream_t>(stream), nullptr);
+  if (e != cudaSuccess) return cuda_fail(e, "qsa_tiles");
+  return ESP_OK;
 }
 
 int esp_attn_finite_check(void* stream, const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int32_t dtype, float threshold,

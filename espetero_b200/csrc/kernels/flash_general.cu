@@ -8,6 +8,11 @@
 // tile key ranges that do not start on a 16-key boundary), and the second, independent
 // GPU implementation the tests cross-check the fast kernels against.
 //
+// With the Qwen sparse-attention arguments (KernelArgs::qsa_*) it is also flash_attention_qsa
+// (kernels/45_qsa.metal:452-690): a tile with pad0 = 1 reads the cached keys of its union list - entries
+// [k0, k1) of list pad1, each one block of 4 keys with an 8-bit row mask - and a sparse row counts a batch key
+// only if the key's block is selected for it or lies in its tail.
+//
 // One warp owns one (row, head) pair at a time: 32 keys per step, lane = key for the
 // scores (K rows read straight from the pool, 16 bytes per load), warp-shuffle online
 // softmax in the exp2 domain, lane = slice of HD / 32 dims for P.V.
@@ -112,7 +117,58 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
       }
     };
 
-    // ---- cached keys [k0, k1)
+    // ---- cached keys: of the tile's union list (Qwen sparse attention), else [k0, k1)
+    const bool sparse_tile = a.qsa_tlist != nullptr && tile.pad0 != 0;
+    int4 ri = make_int4(0, 0, -1, 0);
+    if (a.qsa_rinfo) ri = reinterpret_cast<const int4*>(a.qsa_rinfo)[row];
+    const bool row_sparse = sparse_tile && ri.z >= 0;
+    if (sparse_tile) {
+      // 8 entries = 32 keys per step: lane -> entry lane / 4, key lane % 4 of its block
+      const bool list_ok = tile.pad1 >= 0 && tile.pad1 < a.qsa_n_lists;
+      const uint32_t* tl = a.qsa_tlist + size_t(list_ok ? tile.pad1 : 0) * ESP_QSA_LMAX;
+      const int e_end = list_ok ? min(min(tile.k1, int(min(a.qsa_tcount[tile.pad1], uint32_t(ESP_QSA_LMAX)))), ESP_QSA_LMAX) : 0;
+      for (int e0 = tile.k0; e0 < e_end; e0 += 8) {
+        const int e = e0 + (lane >> 2);
+        const uint32_t ent = e < e_end ? tl[e] : 0xFFFFFFFFu;
+        const int j = int(ent >> 8) * 4 + (lane & 3);
+        float s = -INFINITY;
+        bool b_ok = false;
+        const bool vis = ent != 0xFFFFFFFFu && j < tree.P && ((ent >> uint32_t(fm)) & 1u);
+        const size_t b = vis ? block_of(j, b_ok) : 0;
+        if (b_ok) {
+          const size_t off = p.kv_base + (b * 2) * blk_elems + size_t(j % p.bt) * p.kv_ld + size_t(kvh) * HD;
+          float dot = 0.0f;
+          if constexpr (KVDT == ESP_E4M3) {
+            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(a.kv) + off);
+#pragma unroll 4
+            for (int c = 0; c < HD / 16; ++c) dot_e4m3(src[c], q + 16 * c, dot);
+            dot *= a.kv_scales[(b * 2) * p.Hkv + kvh];
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.kv) + off);
+#pragma unroll 4
+            for (int c = 0; c < HD / 8; ++c) dot16<KVDT>(src[c], q + 8 * c, dot);
+          }
+          s = dot * sl2;
+        }
+        softmax_pv(s, [&](int jj, float pj) {
+          const uint32_t ent_j = __shfl_sync(0xffffffffu, ent, jj & ~3);  // (every lane of an entry holds it)
+          const int jk = int(ent_j >> 8) * 4 + (jj & 3);
+          bool v_ok;
+          const size_t bv = block_of(jk, v_ok);  // valid: its score was finite
+          const size_t off = p.kv_base + (bv * 2 + 1) * blk_elems + size_t(jk % p.bt) * p.kv_ld + size_t(kvh) * HD + lane * DPL;
+          if constexpr (KVDT == ESP_E4M3) {
+            const float w = pj * a.kv_scales[(bv * 2 + 1) * p.Hkv + kvh];
+            const uint8_t* src = static_cast<const uint8_t*>(a.kv) + off;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] = fmaf(w, e4m3_to_f32(src[i]), acc[i]);
+          } else {
+            const typename Elem16<KVDT>::T* src = static_cast<const typename Elem16<KVDT>::T*>(a.kv) + off;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pj, Elem16<KVDT>::to_f32(src[i]), acc[i]);
+          }
+        });
+      }
+    } else
     for (int j0 = tile.k0; j0 < tile.k1; j0 += 32) {
       const int j = j0 + lane;
       float s = -INFINITY;
@@ -170,6 +226,12 @@ __global__ void __launch_bounds__(kWarps * 32) flash_general_kernel(const Kernel
         if (a.anc_mask) vis = vis && ((am >> j) & 1ull);
         else vis = vis && ((j < d.z) || (j >= d.x && (j <= rr || (a.bidi && j < d.w))));
         if (a.window > 0 && vis) vis = qpos - a.pos[4 * size_t(tree.base + j)] < a.window;
+        if (vis && row_sparse) {
+          // the key's sequence index on this row's path, its block: in the tail (past 4 nb) or selected
+          const int sj = tree.P + (j < d.z ? j : d.z + (j - d.x));
+          const int bj = sj >> 2;
+          vis = sj >= 4 * ri.y || ((a.qsa_sel[size_t(ri.z) * a.qsa_nbw + (bj >> 5)] >> uint32_t(bj & 31)) & 1u);
+        }
         float s = -INFINITY;
         if (vis) {
           const uint4* src =

@@ -57,6 +57,12 @@ struct KernelArgs {
   int32_t window;      // > 0: keys `window` or more positions behind the query are masked
   int32_t ring;        // > 0: cached key j lives in block table + (j / bt) % ring (no page table)
   int32_t bidi;        // rows of an image also see the image's later rows (desc.w)
+  // Qwen sparse attention (general kernel): lists, their lengths, per-row records and selection bitmaps; NULL otherwise
+  const uint32_t* qsa_tlist;
+  const uint32_t* qsa_tcount;
+  const int32_t* qsa_rinfo;
+  const uint32_t* qsa_sel;
+  int32_t qsa_nbw, qsa_n_lists;
   // Peer exchange at the end of the decode kernel's fused merge (one sequence's keys split over several GPUs);
   // x_world = 0: none. Buffers hold 8-byte words {value, tag}, laid out [epoch parity][rank][record slot].
   int32_t x_world, x_rank, x_phases;  // phases: 1 publish, 2 wait for the world's records and finish the row, 3 both
@@ -227,6 +233,11 @@ cudaError_t launch_kv_dequant(const void* kv, const float* kv_scales, const int3
 cudaError_t launch_kv_copy_blocks(void* kv, const int32_t* pairs, int32_t n_pairs, const esp_attn_params& p,
                                   uint64_t region_elems, int32_t n_layers, int32_t elem_bytes, cudaStream_t stream,
                                   uint64_t* launches);
+
+cudaError_t launch_qsa_select(const float* scores, const int32_t* srows, const int32_t* rinfo, uint32_t* sel, int32_t n_sparse, int32_t nbmax,
+                              int32_t nbw, cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_qsa_tiles(const uint32_t* sel, const esp_attn_tree* trees, const int32_t* rinfo, const esp_qsa_tile* qtiles, int32_t n_qtiles,
+                             uint32_t* tlist, uint32_t* tcount, int32_t nbmax, int32_t nbw, cudaStream_t stream, uint64_t* launches);
 
 // finite_check over rows x cols elements (row stride ld, in elements) into the 4-word record `rec`.
 cudaError_t launch_finite_check(const void* x, uint32_t rows, uint32_t cols, uint64_t ld, int dtype, uint32_t thr_bits, uint32_t* rec,

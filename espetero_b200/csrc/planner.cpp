@@ -52,9 +52,29 @@ inline int32_t ceil_div(int64_t a, int64_t b) { return int32_t((a + b - 1) / b);
 
 }  // namespace
 
+static int plan_impl(const esp_attn_tree* trees, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts, const int32_t* qt,
+                     esp_attn_tile* tiles, int32_t tiles_cap, esp_attn_combine* jobs, int32_t jobs_cap,
+                     int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts);
+
 extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts,
                              esp_attn_tile* tiles, int32_t tiles_cap, esp_attn_combine* jobs, int32_t jobs_cap,
                              int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts) {
+  return plan_impl(trees, n_trees, Hkv, opts, nullptr, tiles, tiles_cap, jobs, jobs_cap, n_tiles, n_jobs, n_parts);
+}
+
+// plan_tiles with its sparse-attention branch (forest.h:1392-1412): qt = per tree, per 8-row group, the union list of the
+// group or -1 (flattened).
+extern "C" int esp_attn_plan_qsa(const esp_attn_tree* trees, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts, const int32_t* qt,
+                                 esp_attn_tile* tiles, int32_t tiles_cap, esp_attn_combine* jobs, int32_t jobs_cap, int32_t* n_tiles,
+                                 int32_t* n_jobs, int32_t* n_parts) {
+  if (qt && opts && (opts->mode != ESP_PLAN_REFERENCE || (opts->tile_rows != 0 && opts->tile_rows != 8)))
+    return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_plan_qsa: sparse groups are planned by the reference planner with 8-row tiles");
+  return plan_impl(trees, n_trees, Hkv, opts, qt, tiles, tiles_cap, jobs, jobs_cap, n_tiles, n_jobs, n_parts);
+}
+
+static int plan_impl(const esp_attn_tree* trees, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts, const int32_t* qt,
+                     esp_attn_tile* tiles, int32_t tiles_cap, esp_attn_combine* jobs, int32_t jobs_cap,
+                     int32_t* n_tiles, int32_t* n_jobs, int32_t* n_parts) {
   if (!opts || (!trees && n_trees > 0) || n_trees < 0 || Hkv <= 0 || !n_tiles || !n_jobs || !n_parts)
     return esp::fail(ESP_ERR_INVALID, "esp_attn_plan: null or negative argument");
   const int32_t mode = opts->mode;
@@ -78,6 +98,7 @@ extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_
     for (int32_t i = 0; i < n_trees; ++i) total += (trees[i].M + count_rows - 1) / count_rows;
     const int32_t budget = int32_t(std::max<int64_t>(1, groups / std::max<int64_t>(1, int64_t(Hkv) * total)));
     if (mode == ESP_PLAN_G4 && budget != 1) TR = 8;
+    size_t qt_at = 0;
     for (int32_t ti = 0; ti < n_trees; ++ti) {
       const esp_attn_tree& t = trees[ti];
       int32_t ns = 1;
@@ -85,7 +106,34 @@ extern "C" int esp_attn_plan(const esp_attn_tree* trees, int32_t n_trees, int32_
         const int32_t chunk = std::max(std::max(32, min_chunk), std::min(split, (ceil_div(t.P, budget) + 31) / 32 * 32));
         ns = std::min({ceil_div(t.P, chunk), budget, 64});
       }
-      for (int32_t r = 0; r < t.M; r += TR) E.group(ti, t, r, std::min(mode == ESP_PLAN_G4 ? 8 : TR, t.M - r), ns);
+      for (int32_t r = 0; r < t.M; r += TR) {
+        const int32_t q = qt ? qt[qt_at + r / 8] : -1;
+        if (q < 0) {
+          E.group(ti, t, r, std::min(mode == ESP_PLAN_G4 ? 8 : TR, t.M - r), ns);
+          continue;
+        }
+        // A group with rows past the dense range reads the entries of union list q (4 keys each; its length is known
+        // only on the device: splits assume 513 entries for one row and 128 more per further row, the last part is open).
+        const int32_t rows = std::min(8, t.M - r);
+        const int32_t est = 516 + 128 * (rows - 1);
+        int32_t nq = 1;
+        if (split > 0 && budget > 1) {
+          const int32_t chunk = std::max(16, std::min(split / 4, (ceil_div(est, budget) + 3) / 4 * 4));
+          nq = std::min({ceil_div(est, chunk), budget, 64});
+        }
+        if (nq == 1) {
+          E.tile({ti, t.base + r, 0, 1 << 30, -1, 1, 1, q});
+          continue;
+        }
+        const int32_t step = (ceil_div(est, nq) + 3) / 4 * 4;
+        const int32_t part0 = E.np;
+        for (int32_t k = 0; k < nq; ++k) {
+          const bool lastp = k + 1 == nq;
+          E.tile({ti, t.base + r, k * step, lastp ? (1 << 30) : (k + 1) * step, E.np++, lastp ? 1 : 0, 1, q});
+        }
+        E.job({t.base + r, rows, part0, nq});
+      }
+      if (qt) qt_at += (t.M + 7) / 8;
     }
   } else {
     E.tag_jobs = true;

@@ -244,6 +244,17 @@ typedef struct esp_attn_args {
    * the general kernel. Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
   void* dequant_scratch;
   uint64_t dequant_scratch_bytes;
+  /* Qwen sparse attention (flash_attention_qsa, kernels/45_qsa.metal:452-690; the extra bindings 12-16 of its
+   * dispatch, src/model/impl/forest.h:1646-1656). NULL / 0 for ordinary passes. With them, a tile whose pad0 is 1
+   * reads the cached keys of a union list instead of a key range: k0 / k1 are entries of list pad1 (an entry = one
+   * block of 4 keys with an 8-bit row mask), and a sparse row counts a batch key only if the key's block is selected
+   * for it or lies in its tail. Tiles with pad0 = 0 are dense as ever. Such passes run on the general kernel. */
+  const uint32_t* qsa_tlist;  /* [tiles][ESP_QSA_LMAX] entries (block << 8) | row mask, ascending (esp_qsa_tiles) */
+  const uint32_t* qsa_tcount; /* [tiles] entries of each list */
+  const int32_t* qsa_rinfo;   /* int4 per pass row: sequence index s, nb = (s + 1) / 4, sparse row or -1, tree (esp_qsa_plan) */
+  const uint32_t* qsa_sel;    /* [sparse rows][qsa_nbw] selection bitmaps (esp_qsa_select) */
+  int32_t qsa_nbw;            /* bitmap words per sparse row */
+  int32_t qsa_n_lists;        /* lists in qsa_tlist (bounds tile.pad1) */
 } esp_attn_args;
 
 /* Bytes of dequant_scratch for a pass whose block table has n_block_entries entries (pool rows of
@@ -532,6 +543,51 @@ int esp_forest_anc_masks(const int32_t* parents, int32_t n, uint64_t* masks);
 #define ESP_ATTN_STATIC_PARTS_FLOATS (4u << 20)
 int esp_attn_decode_static(const esp_attn_shape* shape, void* stream, const esp_attn_args* args);
 int esp_attn_decode_static_status(void* stream);
+
+/* ---- Qwen sparse attention (kernels/45_qsa.metal; host src/model/impl/forest.h:1462-1676): a query row at
+ * sequence index s sees s + 1 tokens; once its nb = (s + 1) / 4 complete blocks of 4 tokens exceed 512 it attends
+ * only the 512 blocks its indexer scores highest plus its tail (the tokens past 4 nb). This library takes the
+ * indexer's scores as an input (computing them - qsa_prep, qsa_pool, qsa_score_* - is the model's projection work)
+ * and provides everything from there: the per-row records and tiles (esp_qsa_plan = qsa_plan, forest.h:1489-1543),
+ * the planner branch for such tiles (esp_attn_plan_qsa = plan_tiles with `qt`, forest.h:1392-1412), the top-512
+ * selection (esp_qsa_select = qsa_select: radix select on the fp32 bit patterns, ties to the lowest blocks), the
+ * tiles' union lists (esp_qsa_tiles = qsa_tiles) and the attention over them (esp_attn_forward with the qsa_*
+ * arguments = flash_attention_qsa). All integer results are bit-identical to the reference's. */
+#define ESP_QSA_TOPK 512
+#define ESP_QSA_LMAX 4112 /* union entries per 8-row tile (QSA_LMAX) */
+typedef struct esp_qsa_tile {
+  int32_t tree;
+  int32_t r0;   /* absolute first row */
+  int32_t rows; /* <= 8 */
+  int32_t pad;
+} esp_qsa_tile;
+typedef struct esp_qsa_counts {
+  int32_t M;        /* pass rows covered by the trees */
+  int32_t n_sparse; /* rows with nb > 512 */
+  int32_t nbmax;    /* largest nb of a sparse row: row stride of `scores` */
+  int32_t nbb;      /* most blocks of a sparse row that end in pass rows */
+  int32_t ncb;      /* most cached blocks (P / 4) of a tree with sparse rows */
+  int32_t n_tiles;  /* 8-row tiles that hold sparse rows */
+} esp_qsa_counts;
+/* qsa_plan (pure host). desc: int4 per row (segment start, 0, root rows, 0) or NULL for chains; sparse = 0: records
+ * only (no row is sparse). Outputs: rinfo int4 per row [0, M); srows (the pass row of each sparse row); qtiles; qt_of:
+ * per tree, per 8-row group, its tile or -1, flattened (the `qt` of esp_attn_plan_qsa). Arrays may be NULL to size
+ * them: counts is always filled; ESP_ERR_CAPACITY if a given array is too small. */
+int esp_qsa_plan(const esp_attn_tree* trees, int32_t n_trees, const int32_t* desc, int32_t sparse, int32_t* rinfo, int32_t rows_cap,
+                 int32_t* srows, int32_t srows_cap, esp_qsa_tile* qtiles, int32_t qtiles_cap, int32_t* qt_of, int32_t qt_cap,
+                 esp_qsa_counts* counts);
+/* plan_tiles with its sparse branch (forest.h:1378-1433): opts->mode must be ESP_PLAN_REFERENCE and tile_rows 8; qt as
+ * esp_qsa_plan's qt_of (NULL: exactly esp_attn_plan). A group with qt >= 0 gets tiles over entries of list qt (pad0 = 1,
+ * pad1 = qt; the last part open-ended: the list's length is known only on the device). */
+int esp_attn_plan_qsa(const esp_attn_tree* trees_host, int32_t n_trees, int32_t Hkv, const esp_plan_opts* opts, const int32_t* qt,
+                      esp_attn_tile* tiles_host, int32_t tiles_cap, esp_attn_combine* jobs_host, int32_t jobs_cap, int32_t* n_tiles,
+                      int32_t* n_jobs, int32_t* n_parts);
+/* qsa_select: scores [n_sparse][nbmax] fp32 >= 0 -> sel [n_sparse][nbw] bitmaps (nbw = (nbmax + 31) / 32). One launch. */
+int esp_qsa_select(void* stream, const float* scores, const int32_t* srows, const int32_t* rinfo, uint32_t* sel, int32_t n_sparse,
+                   int32_t nbmax, int32_t nbw);
+/* qsa_tiles: per tile the cached blocks any of its rows reads -> tlist [n_qtiles][ESP_QSA_LMAX], tcount [n_qtiles]. One launch. */
+int esp_qsa_tiles(void* stream, const uint32_t* sel, const esp_attn_tree* trees, const int32_t* rinfo, const esp_qsa_tile* qtiles,
+                  int32_t n_qtiles, uint32_t* tlist, uint32_t* tcount, int32_t nbmax, int32_t nbw);
 
 /* ---- NaN / Inf / outlier detector, for debugging: the reference's finite_check
  * (src/model/impl/finite_check.h:4-18, kernels/05_finite_check.metal; the attention output is its site

@@ -212,3 +212,56 @@ def attention(w, tiles, n_parts: int, which: str = "flash"):
     if rc != 0:
         raise RuntimeError(f"the reference does not instantiate G = {w.G}")
     return O, parts
+
+
+class QsaParams(C.Structure):  # kernels/45_qsa.metal:36-46
+    _fields_ = [("ld", C.c_int), ("bt", C.c_int), ("iblk", C.c_int), ("pool_off", C.c_int), ("pos_off", C.c_int), ("nbmax", C.c_int), ("nbw", C.c_int),
+                ("eps", C.c_float), ("ibase", C.c_ulonglong)]
+
+
+def qsa_plan(trees, desc, sparse=True):
+    """The reference's qsa_plan: dict(rinfo [M, 4], srows, qtiles [n, 4], qt_of (flattened), counts = M, n_sparse, nbmax, nbb, ncb, n_tiles)."""
+    trees = np.ascontiguousarray(trees)
+    M = int(max(int(t["base"]) + int(t["M"]) for t in trees))
+    groups = int(sum((int(t["M"]) + 7) // 8 for t in trees))
+    rinfo, srows = np.zeros((M, 4), dtype=np.int32), np.zeros(max(1, M), dtype=np.int32)
+    qtiles, qt_of, counts = np.zeros((max(1, groups), 4), dtype=np.int32), np.zeros(max(1, groups), dtype=np.int32), np.zeros(6, dtype=np.int32)
+    d = None if desc is None else np.ascontiguousarray(desc, dtype=np.int32)
+    _check(load().ref_qsa_plan(_p(trees), len(trees), _p(d), int(sparse), _p(rinfo), _p(srows), _p(qtiles), _p(qt_of), _p(counts)))
+    return dict(rinfo=rinfo, srows=srows[:counts[1]], qtiles=qtiles[:counts[5]], qt_of=qt_of[:groups], counts=[int(x) for x in counts])
+
+
+def qsa_select(scores, srows, rinfo, nbmax):
+    nbw = (nbmax + 31) // 32
+    sel = np.zeros((len(srows), nbw), dtype=np.uint32)
+    p = QsaParams(0, 16, 0, 0, 0, nbmax, nbw, 1e-6, 0)
+    load().ref_qsa_select(_p(np.ascontiguousarray(scores, dtype=np.float32)), _p(np.ascontiguousarray(srows, dtype=np.int32)), _p(rinfo), _p(sel),
+                          C.byref(p), len(srows))
+    return sel
+
+
+def qsa_tiles(sel, trees, rinfo, qtiles, nbmax):
+    nbw = (nbmax + 31) // 32
+    tlist = np.zeros((max(1, len(qtiles)), 4112), dtype=np.uint32)
+    tcount = np.zeros(max(1, len(qtiles)), dtype=np.uint32)
+    p = QsaParams(0, 16, 0, 0, 0, nbmax, nbw, 1e-6, 0)
+    load().ref_qsa_tiles(_p(sel), _p(np.ascontiguousarray(trees)), _p(rinfo), _p(np.ascontiguousarray(qtiles)), len(qtiles), _p(tlist), _p(tcount),
+                         C.byref(p))
+    return tlist, tcount
+
+
+def attention_qsa(w, tiles, n_parts, tlist, tcount, rinfo, sel, nbmax):
+    """The reference's flash_attention_qsa<G> (SIMT emulator) over `tiles`. Returns (O bits, parts)."""
+    assert w.HD == 256 and w.q_dtype == 0 and w.kv_dtype == 0 and w.X is not None
+    from oracle import Params
+    tiles = np.ascontiguousarray(tiles)
+    O = np.zeros((w.n_rows, w.q_ld), dtype=np.uint16)
+    parts = np.zeros(max(1, n_parts) * w.Hkv * 8 * w.G * 258, dtype=np.float32)
+    p = Params(w.H, w.Hkv, w.q_ld, w.kv_ld, w.g_ld, w.bt, w.kv_base)
+    qp = QsaParams(0, w.bt, 0, 0, 0, nbmax, (nbmax + 31) // 32, 1e-6, 0)
+    X = np.ascontiguousarray(w.X, dtype=np.float32)
+    rc = load().ref_attention_qsa(w.G, _p(w.Q), _p(w.Kb), _p(w.Vb), _p(w.kv), _p(w.blocks), _p(w.desc), _p(X), _p(O), C.byref(p), _p(tiles), len(tiles),
+                                  _p(w.trees), _p(parts), _p(tlist), _p(tcount), _p(rinfo), _p(sel), C.byref(qp))
+    if rc != 0:
+        raise RuntimeError(f"the reference does not instantiate G = {w.G}")
+    return O, parts

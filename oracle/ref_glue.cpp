@@ -32,9 +32,14 @@ struct VisionCfg {
 struct Vision {
   VisionCfg c;
 };
+struct Config {
+  int idx_heads = 4, idx_kv = 1, idx_hd = 128;  // the indexer's geometry (kernels/45_qsa.metal:33-34)
+};
 struct Model {
   KVPool kv;
   Vision vis;
+  Config cfg;
+  bool qsa = true;
 #include "_ref/ref_model_kv.inc"
 };
 struct HostBuf {
@@ -57,6 +62,23 @@ struct Forest {
 };
 
 #include "_ref/ref_funcs.inc"
+
+// qsa_plan keeps its tables in a pass arena of GPU-visible buffers: plain host memory here
+struct Buf {
+  std::vector<unsigned char>* bytes = nullptr;
+};
+inline void* ptr(const Buf& b) { return b.bytes->data(); }
+struct PassArena {
+  std::vector<std::vector<unsigned char>*> owned;
+  Buf alloc(Model&, size_t n) {
+    owned.push_back(new std::vector<unsigned char>(n));
+    return Buf{owned.back()};
+  }
+  ~PassArena() {
+    for (auto* v : owned) delete v;
+  }
+};
+#include "_ref/ref_qsa_plan.inc"
 
 inline void pool_init(Model& m, int n_blocks, int bt) {
   KVPool& K = m.kv;
@@ -337,6 +359,25 @@ int ref_block_tables(void* mv, int n_trees, const int32_t* parent_blocks, const 
       for (int b : trees[size_t(i)].dst_blocks)
         if (int(d) < dst_cap) dst_blocks[d++] = b;
     }
+  });
+}
+
+// qsa_plan (forest.h:1489-1543): per row (s, nb, sparse row or -1, tree), the sparse rows, the 8-row tiles that hold
+// sparse rows and, per tree and 8-row group, its tile or -1 (flattened). counts = {M, n_sparse, nbmax, nbb, ncb, n_tiles}.
+int ref_qsa_plan(const AttnTreeRec* trees, int n_trees, const int32_t* desc, int sparse, int32_t* rows4, int32_t* srows, int32_t* qtiles4,
+                 int32_t* qt_flat, int32_t* counts) {
+  return guarded([&] {
+    Model m;
+    PassArena arena;
+    QsaSet q;
+    qsa_plan(m, arena, q, std::vector<AttnTreeRec>(trees, trees + n_trees), desc, sparse != 0);
+    counts[0] = q.M, counts[1] = q.n_sparse, counts[2] = q.nbmax, counts[3] = q.nbb, counts[4] = q.ncb, counts[5] = int(q.tiles.size());
+    std::memcpy(rows4, ptr(q.rows), size_t(q.M) * 16);
+    if (q.n_sparse) std::memcpy(srows, ptr(q.srows), size_t(q.n_sparse) * 4);
+    if (!q.tiles.empty()) std::memcpy(qtiles4, q.tiles.data(), q.tiles.size() * 16);
+    size_t at = 0;
+    for (const auto& v : q.qt_of)
+      for (int x : v) qt_flat[at++] = x;
   });
 }
 

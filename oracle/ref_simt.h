@@ -26,7 +26,7 @@
 namespace simt {
 
 constexpr int kSimd = 32;
-constexpr size_t kStackBytes = 256 * 1024;
+constexpr size_t kStackBytes = 64 * 1024;  // per fiber; the largest threadgroup (qsa_select) has 1024
 
 struct Fiber {
   ucontext_t ctx;
@@ -243,6 +243,32 @@ inline float simd_sum(float v) {
   float s = 0.0f;
   for (int l = 0; l < simt::kSimd; ++l) s += all[l][0];  // lane order (the hardware's reduction tree is not documented)
   return s;
+}
+
+inline uint simd_prefix_inclusive_sum(uint v) {
+  const float f = as_type<float>(v);  // the exchange carries 32-bit patterns
+  const float(*all)[4] = simt::exchange(&f, 1);
+  uint s = 0;
+  for (unsigned l = 0; l <= simt::this_tid() % simt::kSimd; ++l) s += as_type<uint>(all[l][0]);
+  return s;
+}
+inline uint simd_prefix_exclusive_sum(uint v) { return simd_prefix_inclusive_sum(v) - v; }
+inline uint popcount(uint v) { return uint(__builtin_popcount(v)); }
+inline uint ctz(uint v) { return uint(__builtin_ctz(v)); }
+template <class T>
+inline T clamp(T v, T lo, T hi) { return v < lo ? lo : (hi < v ? hi : v); }
+
+// threadgroup atomics: the fibers of a group run one at a time, so plain memory is atomic enough
+struct atomic_uint {
+  uint v;
+};
+enum memory_order { memory_order_relaxed };
+inline void atomic_store_explicit(atomic_uint* a, uint v, memory_order) { a->v = v; }
+inline uint atomic_load_explicit(const atomic_uint* a, memory_order) { return a->v; }
+inline uint atomic_fetch_add_explicit(atomic_uint* a, uint v, memory_order) {
+  const uint old = a->v;
+  a->v += v;
+  return old;
 }
 
 // 8 x 8 matrix spread over the 32 lanes, two elements per lane.

@@ -5,6 +5,8 @@
 // oracle/_ref/libplan_ref.so; only tests/ load it. These kernels are the 256-dim, fp16, gated originals.
 #include "ref_simt.h"
 
+#include <type_traits>
+
 namespace ref_kernels {
 using namespace metal_emu;
 using uint = metal_emu::uint;  // (the C library declares names of its own for these four)
@@ -106,6 +108,42 @@ void ref_attn_prep(const float* X, const float* qn_w, const float* kn_w, const i
                   reinterpret_cast<half*>(Vb), *p, rope_sel, reinterpret_cast<const int4*>(ktab), reinterpret_cast<half*>(kv), uint2(x, y), tid / 32,
                   tid % 32);
       });
+}
+
+
+// ---- Qwen sparse attention (kernels/45_qsa.metal:281-690; host dispatch src/model/impl/forest.h:1586-1644)
+// qsa_select: one threadgroup of 1024 threads per sparse row; qsa_tiles: one of 256 per tile.
+void ref_qsa_select(const float* scores, const int32_t* srows, const int32_t* rinfo, uint32_t* sel, const QsaParams* p, int n_sparse) {
+  for (unsigned g = 0; g < unsigned(n_sparse); ++g)
+    simt::run_threadgroup(1024, [&](unsigned tid) { qsa_select(scores, srows, reinterpret_cast<const int4*>(rinfo), sel, *p, g, tid, tid / 32, tid % 32); });
+}
+void ref_qsa_tiles(const uint32_t* sel, const AttnTree* trees, const int32_t* rinfo, const QsaTile* qtiles, int n_qtiles, uint32_t* tlist, uint32_t* tcount,
+                   const QsaParams* p) {
+  for (unsigned g = 0; g < unsigned(n_qtiles); ++g)
+    simt::run_threadgroup(256, [&](unsigned tid) { qsa_tiles(sel, trees, reinterpret_cast<const int4*>(rinfo), qtiles, tlist, tcount, *p, g, tid, tid / 32, tid % 32); });
+}
+// flash_attention_qsa<G> over grid (Hkv, n_tiles), 64 * G threads per threadgroup.
+int ref_attention_qsa(int G, const uint16_t* Q, const uint16_t* Kb, const uint16_t* Vb, const uint16_t* kv, const int32_t* blocks, const int32_t* desc,
+                      const float* X, uint16_t* O, const AttnParams* p, const AttnTile* tiles, int n_tiles, const AttnTree* trees, float* parts,
+                      const uint32_t* tlist, const uint32_t* tcount, const int32_t* rinfo, const uint32_t* sel, const QsaParams* qp) {
+  auto group = [&](auto g_tag, unsigned gx, unsigned gy) {
+    constexpr int GG = decltype(g_tag)::value;
+    simt::run_threadgroup(64 * GG, [&](unsigned tid) {
+      flash_attention_qsa<GG, 1>(reinterpret_cast<const half*>(Q), reinterpret_cast<const half*>(Kb), reinterpret_cast<const half*>(Vb),
+                                 reinterpret_cast<const half*>(kv), blocks, reinterpret_cast<const int4*>(desc), X, reinterpret_cast<half*>(O), *p, tiles,
+                                 trees, parts, tlist, tcount, reinterpret_cast<const int4*>(rinfo), sel, *qp, uint2(gx, gy), tid, tid / 32, tid % 32);
+    });
+  };
+  for (unsigned y = 0; y < unsigned(n_tiles); ++y)
+    for (unsigned x = 0; x < unsigned(p->Hkv); ++x) switch (G) {
+        case 1: group(std::integral_constant<int, 1>{}, x, y); break;
+        case 2: group(std::integral_constant<int, 2>{}, x, y); break;
+        case 4: group(std::integral_constant<int, 4>{}, x, y); break;
+        case 6: group(std::integral_constant<int, 6>{}, x, y); break;
+        case 8: group(std::integral_constant<int, 8>{}, x, y); break;
+        default: return -1;
+      }
+  return 0;
 }
 
 }  // extern "C"
