@@ -78,6 +78,10 @@ class PrepParams(C.Structure):
                 ("eps", C.c_float), ("qscale", C.c_float), ("bt", C.c_int32), ("reserved", C.c_int32), ("kv_base", C.c_uint64)]
 
 
+class ProfileEntry(C.Structure):
+    _fields_ = [("kernel", C.c_char * 32), ("launches", C.c_uint32), ("gpu_ms", C.c_float)]
+
+
 class Exchange(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phases", C.c_int32), ("wait_ms", C.c_int32), ("epoch", C.c_uint64),
                 ("records", C.c_void_p * 8)]
@@ -157,6 +161,8 @@ PROTOTYPES = {
     "esp_attn_stamp": (C.c_int, [C.c_void_p, C.c_void_p]),
     "esp_attn_last_kernel": (C.c_char_p, [C.c_void_p]),
     "esp_attn_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "esp_attn_set_profile": (C.c_int, [C.c_void_p, C.c_int]),
+    "esp_attn_get_profile": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
     "esp_attn_launch_count": (C.c_uint64, [C.c_void_p]),
 }
 

@@ -2,6 +2,7 @@
 // kernel selection and launches. Mirrors the attention() / kv_save() / kv_cow_copy()
 // dispatch code of the reference (src/model/impl/forest.h:2855-2947, :1438-1449).
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -21,7 +22,7 @@ struct esp_attn_ctx {
   int opt_attn_gqa = 1;
   int opt_attn_umma = 1;
   int opt_validate = 1;
-  int opt_umma_kernel = 0;  // 0: choose by the pass, 1: flash_umma (HBM streaming), 2: flash_umma_pair (L2-resident keys)
+  int opt_umma_kernel = 0;  // 0: choose by the pass, 1: flash_umma (HBM streaming), 2: flash_umma_pair (L2-resident keys), 3: flash_umma_duo (two query tiles per CTA)
   // host-side fault injection: every Nth pass of 64 rows or more fails before launch
   // (ESPETERO_FAIL_PASS of the reference, forest.h:2521-2531)
   int fail_every = 0;
@@ -62,7 +63,51 @@ struct esp_attn_ctx {
   int replan_next = 0;
   std::vector<esp_attn_tile> rp_tiles;
   std::vector<esp_attn_combine> rp_jobs;
+  // Per-dispatch GPU time (esp_attn_set_profile; the reference's set_profile, src/model/model.mm:1041-1054): an event
+  // pair around every launch while profiling is on, summed per kernel name when the profile is read.
+  bool profiling = false;
+  struct ProfSpan {
+    const char* kernel;
+    cudaEvent_t t0, t1;
+  };
+  std::vector<ProfSpan> prof_pending;
+  std::vector<cudaEvent_t> prof_free;
+  struct ProfSum {
+    const char* kernel;
+    uint32_t launches;
+    double ms;
+  };
+  std::vector<ProfSum> prof_sums;
 };
+
+namespace {
+// Brackets the launches made while it lives with an event pair on `stream` (profiling on), else does nothing.
+struct ProfScope {
+  esp_attn_ctx* c;
+  cudaStream_t stream;
+  const char* kernel;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  static cudaEvent_t take(esp_attn_ctx* c) {
+    if (!c->prof_free.empty()) {
+      cudaEvent_t e = c->prof_free.back();
+      c->prof_free.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    return cudaEventCreate(&e) == cudaSuccess ? e : nullptr;
+  }
+  ProfScope(esp_attn_ctx* ctx, cudaStream_t s, const char* k) : c(ctx), stream(s), kernel(k) {
+    if (!c->profiling) return;
+    t0 = take(c), t1 = take(c);
+    if (t0 && t1) cudaEventRecord(t0, stream);
+  }
+  ~ProfScope() {
+    if (!c->profiling || !t0 || !t1) return;
+    cudaEventRecord(t1, stream);
+    c->prof_pending.push_back({kernel, t0, t1});
+  }
+};
+}  // namespace
 
 namespace {
 
@@ -333,7 +378,8 @@ int esp_attn_create(esp_attn_ctx** out, int device, const esp_attn_shape* shape)
     delete c;
     return cuda_fail(e, "decode kernel setup");
   }
-  if ((e = esp::flash_umma_setup()) != cudaSuccess || (e = esp::flash_umma_pair_setup()) != cudaSuccess) {
+  if ((e = esp::flash_umma_setup()) != cudaSuccess || (e = esp::flash_umma_pair_setup()) != cudaSuccess ||
+      (e = esp::flash_umma_duo_setup()) != cudaSuccess) {
     delete c;
     return cuda_fail(e, "tcgen05 kernel setup");
   }
@@ -363,6 +409,8 @@ int esp_attn_destroy(esp_attn_ctx* c) {
   cudaSetDevice(c->device);
   for (int i = 0; i < kReplanSlots; ++i)
     if (c->replan_done[i]) cudaEventDestroy(c->replan_done[i]);
+  for (auto& sp : c->prof_pending) cudaEventDestroy(sp.t0), cudaEventDestroy(sp.t1);
+  for (cudaEvent_t e : c->prof_free) cudaEventDestroy(e);
   if (c->replan_dev) cudaFree(c->replan_dev);
   if (c->replan_host) cudaFreeHost(c->replan_host);
   if (c->d_status) cudaFree(c->d_status);
@@ -559,6 +607,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_pool) {
     int32_t* identity = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.dequant_scratch) + widened_pool_bytes);
+    ProfScope prof(c, stream, "kv_dequant");
     const cudaError_t de = esp::launch_kv_dequant(a.kv, a.kv_scales, a.blocks, a.n_block_entries, a.dequant_scratch, identity, a.p, s.HD,
                                                   a.n_blocks, s.q_dtype, stream, &c->launches);
     if (de != cudaSuccess) return cuda_fail(de, "kv_dequant");
@@ -570,6 +619,8 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
 
   cudaError_t e;
   bool merged = false;  // the attention kernel merged the split-K records itself: no combine launch
+  {
+  ProfScope prof(c, stream, decode ? "decode_gqa" : (umma ? "flash_umma*" : "flash_general"));
   if (decode) {
     if (int rc = pool_tensor_map(c, a)) return rc;
     c->last_kernel = "decode_gqa";
@@ -615,7 +666,14 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     }
     // 256-dim heads run on flash_umma_pair only (one CTA per SM there: its tiles take the whole SM).
     const bool stream_hbm = s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch));
-    if (stream_hbm) {
+    // Passes whose keys are mostly their own rows (prefill) are compute-bound: two query tiles per CTA where the
+    // heads allow it (128-dim heads, 2 * (128 / tile_rows) heads within one kv head), else two CTAs per SM.
+    const bool duo = !stream_hbm && (c->opt_umma_kernel == 3 || c->opt_umma_kernel == 0) &&
+                     esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, fp8_pool ? s.q_dtype : s.kv_dtype);
+    if (duo) {
+      c->last_kernel = "flash_umma_duo";
+      e = esp::launch_flash_umma_duo(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+    } else if (stream_hbm) {
       c->last_kernel = "flash_umma";
       e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees,
                                  c->opt_fuse_combine ? a.jobs_host : nullptr, a.n_jobs, &merged, stream, &c->launches);
@@ -627,6 +685,8 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     c->last_kernel = "flash_general";
     e = esp::launch_flash_general(k, stream, &c->launches);
   }
+  prof.kernel = c->last_kernel;
+  }
   if (e != cudaSuccess) return cuda_fail(e, c->last_kernel);
   if (a.n_jobs > 0 && !merged) {
     int rows_max = TR, parts_max = 64;
@@ -637,6 +697,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
         parts_max = a.jobs_host[i].nparts > parts_max ? a.jobs_host[i].nparts : parts_max;
       }
     }
+    ProfScope prof(c, stream, "attention_combine");
     if (int rc = combine_impl(c, stream_v, a.parts, a.X, a.O, a.lse, &a.p, a.jobs, a.n_jobs, rows_max, parts_max, nullptr, 0, a.jobs_host, TR)) return rc;
   }
   if (replan_slot >= 0) cudaEventRecord(c->replan_done[replan_slot], stream);  // the slot's tiles and jobs have been read
@@ -679,6 +740,45 @@ int esp_attn_forward_exchange(esp_attn_ctx* c, void* stream, const esp_attn_args
   rec.n_jobs = 0, rec.jobs = nullptr, rec.jobs_host = nullptr;
   if (int rc = forward_impl(c, stream, &rec, nullptr, nullptr)) return rc;
   return esp_attn_exchange_parts(c, stream, ap->parts, ap->X, ap->O, ap->lse, &ap->p, ap->jobs, ap->n_jobs, 1, parts_max, xp);
+}
+
+int esp_attn_set_profile(esp_attn_ctx* c, int on) {
+  if (!c) return fail(ESP_ERR_INVALID, "esp_attn_set_profile: null context");
+  for (auto& sp : c->prof_pending) c->prof_free.push_back(sp.t0), c->prof_free.push_back(sp.t1);
+  c->prof_pending.clear();
+  c->prof_sums.clear();
+  c->profiling = on != 0;
+  return ESP_OK;
+}
+
+int esp_attn_get_profile(esp_attn_ctx* c, esp_attn_profile_entry* out, int32_t cap, int32_t* n) {
+  if (!c || !n) return fail(ESP_ERR_INVALID, "esp_attn_get_profile: null argument");
+  for (auto& sp : c->prof_pending) {
+    cudaError_t e = cudaEventSynchronize(sp.t1);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, sp.t0, sp.t1);
+    c->prof_free.push_back(sp.t0), c->prof_free.push_back(sp.t1);
+    if (e != cudaSuccess) {
+      c->prof_pending.clear();
+      return cuda_fail(e, "esp_attn_get_profile");
+    }
+    bool found = false;
+    for (auto& s : c->prof_sums)
+      if (!std::strcmp(s.kernel, sp.kernel)) {
+        ++s.launches, s.ms += ms, found = true;
+        break;
+      }
+    if (!found) c->prof_sums.push_back({sp.kernel, 1u, double(ms)});
+  }
+  c->prof_pending.clear();
+  *n = int32_t(c->prof_sums.size());
+  for (int32_t i = 0; out && i < cap && i < *n; ++i) {
+    std::snprintf(out[i].kernel, sizeof(out[i].kernel), "%s", c->prof_sums[size_t(i)].kernel);
+    out[i].launches = c->prof_sums[size_t(i)].launches;
+    out[i].gpu_ms = float(c->prof_sums[size_t(i)].ms);
+  }
+  if (out && *n > cap) return fail(ESP_ERR_CAPACITY, "esp_attn_get_profile: %d kernels, room for %d", *n, cap);
+  return ESP_OK;
 }
 
 int esp_qsa_select(void* stream, const float* scores, const int32_t* srows, const int32_t* rinfo, uint32_t* sel, int32_t n_sparse, int32_t nbmax,
@@ -771,7 +871,11 @@ int esp_attn_exchange_parts(esp_attn_ctx* c, void* stream, const float* parts, c
   if (esp::exchange_grid_ctas(k.c) > 296)
     return fail(ESP_ERR_UNSUPPORTED, "esp_attn_exchange_parts: %lld CTAs cannot be resident at once; gather the records with a collective and call esp_attn_combine_parts",
                 (long long)esp::exchange_grid_ctas(k.c));
-  const cudaError_t e = esp::launch_exchange(k, static_cast<cudaStream_t>(stream), &c->launches);
+  cudaError_t e;
+  {
+    ProfScope prof(c, static_cast<cudaStream_t>(stream), "exchange_parts");
+    e = esp::launch_exchange(k, static_cast<cudaStream_t>(stream), &c->launches);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "exchange_parts");
   return ESP_OK;
 }

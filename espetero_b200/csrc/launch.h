@@ -253,6 +253,12 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
 cudaError_t flash_umma_pair_setup();
+// flash_umma_duo: one CTA per SM, two 128-lane query tiles (two head groups of one kv head) against the same 128-key
+// blocks; for compute-bound passes (prefill). HD 128 only; a CTA's 2 * (128 / tile_rows) heads must share a kv head.
+cudaError_t launch_flash_umma_duo(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
+                                  const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
+cudaError_t flash_umma_duo_setup();
+bool flash_umma_duo_supports(int32_t HD, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype);
 // Shapes the tcgen05 kernels cover: HD 128 (both kernels) or 256 (flash_umma_pair), 16-bit pool of the
 // pass's type, tiles of 16..128 rows whose 128 / tile_rows heads belong to one kv head.
 bool flash_umma_supports(int32_t HD, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype);

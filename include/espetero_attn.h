@@ -140,7 +140,8 @@ int esp_attn_abi_version(void);
  * default 1), "replan" (1: a context with tile_rows 8 plans plain full-attention passes again for the
  * tcgen05 kernels instead of running their 8-row tiles on the CUDA-core kernel - see esp_attn_forward;
  * default 1), "umma_kernel" (which tcgen05 kernel: 0 by the pass, 1 flash_umma - cached keys
- * streamed from HBM, 2 flash_umma_pair - keys of the pass itself; default 0), "fuse_combine"
+ * streamed from HBM, 2 flash_umma_pair - keys of the pass itself, two CTAs per SM, 3 flash_umma_duo - keys of the
+ * pass itself, two query tiles per CTA, where the heads allow it, else as 2; default 0), "fuse_combine"
  * (passes whose split tiles name their combine job in pad1 can merge their records inside the
  * attention kernel and launch no combine kernel: 0 never, 1 where it measured faster - small passes
  * and decode passes with many jobs -, 2 whenever possible; default 1), "trace_ctas" (see
@@ -610,7 +611,7 @@ int esp_attn_finite_check(void* stream, const void* x, uint32_t rows, uint32_t c
                           esp_finite_rec* rec_device);
 
 /* Name of the attention kernel the last esp_attn_forward on this context
- * launched ("decode_gqa", "flash_umma", "flash_umma_pair", "flash_general"), for tests and traces. */
+ * launched ("decode_gqa", "flash_umma", "flash_umma_pair", "flash_umma_duo", "flash_general"), for tests and traces. */
 const char* esp_attn_last_kernel(const esp_attn_ctx* ctx);
 
 /* Reads and clears the context's device status word: a kernel whose bounded wait ran
@@ -633,6 +634,20 @@ int esp_attn_set_trace(esp_attn_ctx* ctx, void* device_buffer, int32_t n_blocks)
 /* Enqueue a one-thread kernel that stores %globaltimer (the trace's clock) into *device_slot:
  * before and after a pass it brackets the pass in the trace's time base. */
 int esp_attn_stamp(void* stream, uint64_t* device_slot);
+
+/* Per-dispatch GPU time, as NativeModel::set_profile / profile_json (src/model/model.mm:1041-1054: every dispatch timed
+ * on its own, summed per kernel). esp_attn_set_profile(ctx, 1) clears the sums and makes every later launch of the
+ * context's entry points carry a CUDA event pair; esp_attn_get_profile waits for the pairs recorded so far and reports,
+ * per kernel name, its launches and summed milliseconds (n = kernels; ESP_ERR_CAPACITY if cap is too small). Timing
+ * events keep consecutive kernels from overlapping (programmatic dependent launch), so a profiled pass is slower
+ * than an unprofiled one: a tool for shares, like the reference's. Off by default: nothing is recorded. */
+typedef struct esp_attn_profile_entry {
+  char kernel[32];
+  uint32_t launches;
+  float gpu_ms;
+} esp_attn_profile_entry;
+int esp_attn_set_profile(esp_attn_ctx* ctx, int on);
+int esp_attn_get_profile(esp_attn_ctx* ctx, esp_attn_profile_entry* out, int32_t cap, int32_t* n);
 
 /* Kernel launches enqueued by this context since creation. */
 uint64_t esp_attn_launch_count(const esp_attn_ctx* ctx);

@@ -104,3 +104,32 @@ def test_attn_vec_option_has_a_defined_answer():
         assert e.value.code == capi.ESP_ERR_UNSUPPORTED
     finally:
         op.close()
+
+
+def test_profile_reports_gpu_time_per_kernel():
+    """esp_attn_set_profile / esp_attn_get_profile (the reference's set_profile, src/model/model.mm:1041-1054): every
+    launch timed on its own, summed per kernel name."""
+    lib = capi.load()
+    w = wl.make_pass("prof", 75, [(5000, 1), (3000, 1)], 32, 8, 256, 16, wl.BF16, wl.E4M3)
+    op = host.AttnOp.for_workload(w)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv)               # split by the reference planner: decode + combine
+        dp = op.upload(w, plan)
+        op.forward(dp)                                       # not profiled
+        capi.check(lib.esp_attn_set_profile(op.ctx, 1))
+        for _ in range(5):
+            op.forward(dp)
+        ents = (capi.ProfileEntry * 8)()
+        n = C.c_int32()
+        capi.check(lib.esp_attn_get_profile(op.ctx, ents, 8, C.byref(n)))
+        got = {ents[i].kernel.decode(): (ents[i].launches, ents[i].gpu_ms) for i in range(n.value)}
+        assert set(got) == {"decode_gqa", "attention_combine"}
+        assert got["decode_gqa"][0] == 5 and got["attention_combine"][0] == 5
+        assert 0.0 < got["attention_combine"][1] < got["decode_gqa"][1] < 50.0
+        capi.check(lib.esp_attn_set_profile(op.ctx, 0))      # off: the sums are cleared, nothing more is recorded
+        op.forward(dp)
+        capi.check(lib.esp_attn_get_profile(op.ctx, ents, 8, C.byref(n)))
+        assert n.value == 0
+        op.check_status()
+    finally:
+        op.close()

@@ -30,7 +30,7 @@ def _forward(name, w):
         op.close()
 
 
-@pytest.mark.parametrize("name,kernel", [("c2", "decode_gqa"), ("c4", "flash_umma"), ("c5", "decode_gqa"), ("c3", "flash_umma_pair")])
+@pytest.mark.parametrize("name,kernel", [("c2", "decode_gqa"), ("c4", "flash_umma"), ("c5", "decode_gqa"), ("c3", "flash_umma_duo")])
 def test_bench_configuration_at_full_size_matches_oracle(oracle_lib, name, kernel):
     w = bench.build_workload(name, rank=0)
     if name == "c2":
