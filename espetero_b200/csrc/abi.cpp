@@ -54,6 +54,7 @@ struct esp_attn_ctx {
   // tiles and jobs are built on the host and travel through a small ring of pinned staging slots into
   // device slots of the context (see replan_pass).
   int opt_replan = 1;
+  int opt_fp8_direct = 1;  // E4M3 pools: passes over mostly cached keys read the codes inside flash_umma (no widening pre-pass)
   int opt_pair_merge = 1;  // flash_umma: passes whose jobs all have two records merge them inside a cluster pair (distributed shared memory)
   int opt_fuse_exchange = 0;  // esp_attn_forward_exchange: 1 = merge and exchange inside the decode kernel (one launch); 0 = two kernels (measured faster)
   uint8_t* replan_dev = nullptr;
@@ -333,6 +334,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "replan")) return &c->opt_replan;
   if (!std::strcmp(name, "fuse_exchange")) return &c->opt_fuse_exchange;
   if (!std::strcmp(name, "pair_merge")) return &c->opt_pair_merge;
+  if (!std::strcmp(name, "fp8_direct")) return &c->opt_fp8_direct;
   return nullptr;
 }
 
@@ -577,7 +579,20 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool widen = fp8_pool && a.dequant_scratch != nullptr && a.n_block_entries > 0 && a.kv != nullptr && a.blocks != nullptr &&
                      a.dequant_scratch_bytes >= widened_pool_bytes + ((size_t(a.n_block_entries) * 4 + 127) / 128) * 128 &&
                      (reinterpret_cast<uintptr_t>(a.dequant_scratch) & 127) == 0 && a.p.kv_ld % 8 == 0 && a.p.kv_base % 8 == 0;
-  const bool umma_ok = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen) &&
+  // Where the tiles' keys come from: cached keys are streamed from HBM, the pass's own rows sit in L2.
+  int64_t keys_cached = 0, keys_batch = 0;
+  if (a.tiles_host && a.trees_host)
+    for (int i = 0; i < a.n_tiles; ++i) {
+      const esp_attn_tile& t = a.tiles_host[i];
+      keys_cached += t.k1 - t.k0;
+      if (t.last) keys_batch += a.trees_host[t.tree].M;
+    }
+  // E4M3 pools under passes over mostly cached keys (verify, chunked prefill over a long prefix): flash_umma reads the
+  // codes itself. Other passes over such pools widen the blocks they touch into the caller's scratch first.
+  const bool fp8_direct = fp8_pool && c->opt_fp8_direct && s.HD == 128 && a.kv != nullptr && a.kv_scales != nullptr && a.n_blocks > 0 &&
+                          a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 && c->opt_umma_kernel <= 1 &&
+                          keys_cached > 2 * keys_batch;
+  const bool umma_ok = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen || fp8_direct) &&
                        a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.
   int replan_slot = -1;
@@ -605,7 +620,9 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   k.qsa_nbw = a.qsa_nbw, k.qsa_n_lists = a.qsa_n_lists;
 
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
-  if (umma && fp8_pool) {
+  if (umma && fp8_direct) {
+    widened.kv = nullptr;  // no 16-bit map of the pool: the kernel takes the byte map the decode kernel uses
+  } else if (umma && fp8_pool) {
     int32_t* identity = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.dequant_scratch) + widened_pool_bytes);
     ProfScope prof(c, stream, "kv_dequant");
     const cudaError_t de = esp::launch_kv_dequant(a.kv, a.kv_scales, a.blocks, a.n_block_entries, a.dequant_scratch, identity, a.p, s.HD,
@@ -658,14 +675,10 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     if (int rc = umma_tensor_maps(c, widened)) return rc;
     // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
     // from HBM, the pass's own rows sit in L2), unless the "umma_kernel" option forces one.
-    int64_t cached = 0, batch = 0;
-    for (int i = 0; i < a.n_tiles; ++i) {
-      const esp_attn_tile& t = a.tiles_host[i];
-      cached += t.k1 - t.k0;
-      if (t.last) batch += a.trees_host[t.tree].M;
-    }
     // 256-dim heads run on flash_umma_pair only (one CTA per SM there: its tiles take the whole SM).
-    const bool stream_hbm = s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && cached > 2 * batch));
+    const bool stream_hbm = s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && keys_cached > 2 * keys_batch));
+    if (fp8_direct)
+      if (int rc = pool_tensor_map(c, a)) return rc;
     // Passes whose keys are mostly their own rows (prefill) are compute-bound: two query tiles per CTA where the
     // heads allow it (128-dim heads, 2 * (128 / tile_rows) heads within one kv head), else two CTAs per SM.
     const bool duo = !stream_hbm && (c->opt_umma_kernel == 3 || c->opt_umma_kernel == 0) &&
@@ -675,7 +688,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
       e = esp::launch_flash_umma_duo(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
     } else if (stream_hbm) {
       c->last_kernel = "flash_umma";
-      e = esp::launch_flash_umma(k, c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees,
+      e = esp::launch_flash_umma(k, fp8_direct ? c->pool_map : c->upool_map, c->kb_map, c->vb_map, a.tiles_host, a.trees_host, a.n_trees,
                                  c->opt_fuse_combine ? a.jobs_host : nullptr, a.n_jobs, &merged, stream, &c->launches);
     } else {
       c->last_kernel = "flash_umma_pair";

@@ -32,6 +32,16 @@
 // and tree blocks) take a path with no per-key predicate.
 // Every wait is bounded: after a timeout the CTA records a status code, stops waiting,
 // finishes its loop, frees its tensor memory and returns.
+//
+// E4M3 pools (template flag F8; the reference dequantises in its attention kernels too,
+// kernels/80_dsv4.metal:22-33 for the codec): the pages arrive by TMA as raw codes (2 KB per page and
+// kv head: half the bytes of a 16-bit pool) into rings of two 16 KB tiles; two converter warps (one
+// for K, one for V, four key rows per lane) turn them into fp16 tiles - code x the page's scale for
+// the kv head, which the producer fetched while it waited for the slot - in the 128-byte-swizzled
+// layout the MMAs read, and the whole pass computes in fp16 (Q is converted when it is staged, P is
+// fp16; accumulation and the records stay fp32). One producer warp serves both rings (lanes 0-7 K,
+// 8-15 V), so the CTA keeps 12 warps and its registers. Batch keys (the pass's own rows) are few in
+// the passes this variant is for: the converter warps fetch them from Kb / Vb themselves.
 #include "umma.cuh"
 #include "../launch.h"
 
@@ -46,7 +56,10 @@ constexpr int Q_BYTES = BM * HD * 2;        // [2 halves of 64 dims][128 rows][1
 constexpr int KV_TILE = BN * HD * 2;        // [2 halves of 64 dims][128 rows][128 B]
 constexpr int HALF_T = 128 * 128;           // bytes between the 64-dim halves of a tile
 constexpr int KS = 3, VS = 3;               // K and V ring depths
+constexpr int KS8 = 2, RS8 = 2;             // E4M3 pools: converted tiles per ring, raw tiles per ring
+constexpr int RAW_TILE = BN * HD;           // 128 keys x 128 codes
 constexpr int TILES_BYTES = Q_BYTES + (KS + VS) * KV_TILE;
+static_assert(Q_BYTES + 2 * KS8 * KV_TILE + 2 * RS8 * RAW_TILE == TILES_BYTES, "both layouts fill the same window");
 constexpr int SMEM_BYTES = TILES_BYTES + 384;  // + mbarriers and bookkeeping; no static shared memory
 constexpr uint32_t TMEM_COLS = 512;
 // Two S buffers of 128 fp32 columns (the P of a half is written over the first 32 columns of that
@@ -60,6 +73,9 @@ constexpr int kMmaWarp = 8;                 // MMA issue (one thread), owns tens
 constexpr int kTmaWarpK = 9;                // TMA producer of K tiles (lanes 0-7, one 16-key page each)
 constexpr int kTmaWarpV = 10;               // TMA producer of V tiles
 constexpr int kThreads = 11 * 32;
+constexpr int kCvtWarp0 = 10, kCvtWarps = 4;   // E4M3 pools: warp 9 produces both rings, warps 10-13 convert (even: K, odd: V)
+constexpr int kThreadsF8 = (kCvtWarp0 + kCvtWarps) * 32;
+constexpr int kCvtLanes = kCvtWarps / 2 * 32;  // converter lanes per tile
 constexpr int kPages = BN / 16;             // TMA pages per tile
 
 // The n lowest bits set (n <= 0: none, n >= 64: all).
@@ -76,6 +92,8 @@ struct PageRef {  // where one 16-key page of a key block comes from
 // swizzled tiles need.
 struct Shared {
   uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], pv_done, o_full, meta_ready;
+  uint64_t raw_full[2][RS8], raw_empty[2][RS8];  // E4M3 pools: [K / V][slot]
+  float scl[2][RS8][kPages];                     // ... the scale of each page in a raw slot
   uint32_t tmem_slot;
   int red[4];  // anc_max, seg_min, anc_min, seg_max
   volatile int dead;
@@ -104,11 +122,14 @@ __device__ __forceinline__ void st_cluster_f4(uint32_t addr, const float4& v) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-template <int QDT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int QDT, bool F8>
+__global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
     flash_umma_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const __grid_constant__ InlinePlan plan, const KernelArgs a) {
-  using QE = Elem16<QDT>;
+  using QE = Elem16<QDT>;                      // Q and O in memory
+  constexpr int CDT = F8 ? ESP_F16 : QDT;      // what the MMAs compute in
+  using PE = Elem16<CDT>;
+  constexpr int KSx = F8 ? KS8 : KS, VSx = F8 ? KS8 : VS;
   extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: both halves of P in buffer i written (256 arrivals); pv_done: P.V of a block
@@ -131,8 +152,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     return;
   }
   uint8_t* q_sm = smem;
-  uint8_t* k_sm = smem + Q_BYTES;                 // KS tiles
-  uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS tiles
+  uint8_t* k_sm = smem + Q_BYTES;                  // KSx tiles
+  uint8_t* v_sm = smem + Q_BYTES + KSx * KV_TILE;  // VSx tiles
+  uint8_t* raw_sm = v_sm + VSx * KV_TILE;          // E4M3 pools: RS8 raw K tiles, then RS8 raw V tiles
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const esp_attn_params& p = a.p;
@@ -175,13 +197,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- set-up, step 1: barriers, then everybody may start
   if (tid == 0) {
     for (int s = 0; s < KS; ++s) {
-      mbar_init(&k_full[s], kPages);
+      mbar_init(&k_full[s], F8 ? kCvtLanes : kPages);  // E4M3 pools: the lanes of the tile's converter warps
       mbar_init(&k_empty[s], 1);
     }
     for (int s = 0; s < VS; ++s) {
-      mbar_init(&v_full[s], kPages);
+      mbar_init(&v_full[s], F8 ? kCvtLanes : kPages);
       mbar_init(&v_empty[s], 1);
     }
+    for (int i = 0; i < 2; ++i)
+      for (int s = 0; s < RS8; ++s) {
+        mbar_init(&sh.raw_full[i][s], kPages);
+        mbar_init(&sh.raw_empty[i][s], kCvtLanes);
+      }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], kSoftmaxThreads);
@@ -244,7 +271,125 @@ __global__ void __launch_bounds__(kThreads, 1)
   };
   auto batch_j0 = [&](const Meta& m, int i) { return BN * (i < m.a_hi ? i : m.b_lo + (i - m.a_hi)); };
 
-  if (warp == kTmaWarpK || warp == kTmaWarpV) {
+  if (F8 && warp == kTmaWarpK) {
+    // ================= E4M3 pools: one producer warp for both raw rings (lanes 0-7 the K pages of a block, lanes 8-15
+    // its V pages); batch blocks are left to the converter warps.
+    if (lane == 0) tma_prefetch_desc(&pool_map);
+    const int is_v = (lane >> 3) & 1, pg = lane & 7;
+    uint64_t* full = sh.raw_full[is_v];
+    uint64_t* empty = sh.raw_empty[is_v];
+    uint8_t* ring = raw_sm + is_v * RS8 * RAW_TILE;
+    int stage = 0;
+    uint32_t par = 1;  // the first use of a slot finds it empty
+    auto load_group = [&](int g) {
+      const int b = 4 * g + (lane >> 3);
+      const int j = tile.k0 + BN * b + 16 * (lane & 7);
+      return (b < nbc && j < tile.k1) ? page_table[tree.table + j / bt] : -1;
+    };
+    pdl_wait();
+    int g_cur = load_group(0), g_nxt = load_group(1);
+    for (int b = 0; b < nbc; ++b) {
+      if (b && (b & 3) == 0) {
+        g_cur = g_nxt;
+        g_nxt = load_group((b >> 2) + 1);
+      }
+      const int raw = __shfl_sync(0xffffffffu, g_cur, ((b & 3) << 3) | pg);
+      if (lane < 2 * kPages) {
+        const bool ok = raw >= 0 && raw < a.n_blocks;
+        float sc = 0.0f;  // the page's scale for this kv head: on its way while the lane waits for the slot
+        if (ok) sc = a.kv_scales[(size_t(raw) * 2 + is_v) * p.Hkv + kvh];
+        wait_bar(&empty[stage], par, kStatusMmaTimeout);
+        if (!ok) {
+          mbar_arrive(&full[stage]);
+        } else {
+          sh.scl[is_v][stage][pg] = sc;
+          const int y = (raw * 2 + is_v) * bt + (tile.k0 + BN * b + 16 * pg) % bt;
+          mbar_arrive_expect_tx(&full[stage], 2048);
+          tma_load_3d(ring + stage * RAW_TILE + pg * 2048, &pool_map, &full[stage], 0, y, kvh);
+        }
+        if (++stage == RS8) stage = 0, par ^= 1;
+      }
+    }
+  } else if (F8 && warp >= kCvtWarp0) {
+    // ================= E4M3 pools: converter warps. Warps 10 and 12 turn raw K tiles into fp16 K tiles, 11 and 13 do
+    // V (the four sit on the four schedulers: the conversion instruction runs on the exp2 unit's pipe); a warp owns
+    // 64 key rows of every block, two per lane. A row's 128 codes are 8 chunks of 16 in the raw tile's 128-byte
+    // line and become 16 chunks of 8 halves in the two 64-dim halves of the 16-bit tile.
+    const int is_v = (warp - kCvtWarp0) & 1, row0 = ((warp - kCvtWarp0) >> 1) * (BN / (kCvtWarps / 2));
+    uint64_t* full = is_v ? v_full : k_full;
+    uint64_t* empty = is_v ? v_empty : k_empty;
+    uint8_t* ring = is_v ? v_sm : k_sm;
+    const uint8_t* raw_ring = raw_sm + is_v * RS8 * RAW_TILE;
+    pdl_wait();
+    if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
+    const Meta m = make_meta();
+    const int nb = nbc + m.nbb;
+    int rst = 0, cst = 0;
+    uint32_t rpar = 0, cpar = 1;  // the first use of a converted slot finds it empty
+    for (int b = 0; b < nb; ++b) {
+      const bool cached = b < nbc;
+      const int j0 = cached ? tile.k0 + BN * b : batch_j0(m, b - nbc);
+      const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, m.k_last + 1 - j0);
+      if (cached) wait_bar(&sh.raw_full[is_v][rst], rpar, kStatusTmaTimeout);
+      wait_bar(&empty[cst], cpar, kStatusMmaTimeout);
+      uint8_t* dst = ring + cst * KV_TILE;
+#pragma unroll 1
+      for (int q = 0; q < BN / kCvtLanes; ++q) {
+        const int r = row0 + lane + 32 * q;
+        uint8_t* drow = dst + r * 128;
+        if (r >= n_valid) {
+          // rows past the range: zeros (stale bytes could be NaN patterns, and 0 x NaN must not happen)
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_T + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+        } else if (cached) {
+          const uint8_t* srow = raw_ring + rst * RAW_TILE + r * 128;
+          const __half2 sc2 = __float2half2_rn(sh.scl[is_v][rst][r >> 4]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t h[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t lo = e4m3x2_to_f16x2(uint16_t(w[i] & 0xFFFFu)), hi = e4m3x2_to_f16x2(uint16_t(w[i] >> 16));
+              __half2 a2 = __hmul2(*reinterpret_cast<__half2*>(&lo), sc2), b2 = __hmul2(*reinterpret_cast<__half2*>(&hi), sc2);
+              h[2 * i] = *reinterpret_cast<uint32_t*>(&a2), h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            // codes 16 c .. 16 c + 15 = dims of half (c >> 2), 16-byte chunks (2 c) & 7 and (2 c + 1) & 7 of the row's line
+            uint8_t* dh = drow + (c >> 2) * HALF_T;
+            *reinterpret_cast<uint4*>(dh + ((((2 * c) & 7) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(dh + ((((2 * c + 1) & 7) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+          }
+        } else {
+          // a batch key: the pass's own row, in the Q type
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(is_v ? a.Vb : a.Kb) +
+                                                            size_t(tree.base + j0 + r) * p.kv_ld + size_t(kvh) * HD);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            uint4 v = src[c];
+            if constexpr (QDT == ESP_BF16) {
+              uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = QE::unpack2(w[i]);
+                w[i] = PE::pack2(f.x, f.y);
+              }
+            }
+            *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_T + (((c & 7) ^ (r & 7)) << 4)) = v;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      if (cached) {
+        mbar_arrive(&sh.raw_empty[is_v][rst]);
+        if (++rst == RS8) rst = 0, rpar ^= 1;
+      }
+      mbar_arrive(&full[cst]);
+      if (lane == 0 && row0 == 0) stamp(b, is_v ? 7 : 6);  // timeline: the block's K / V tile converted
+      if (++cst == KS8) cst = 0, cpar ^= 1;
+    }
+  } else if (!F8 && (warp == kTmaWarpK || warp == kTmaWarpV)) {
     // ================= TMA producers: warp 9 fills the K ring, warp 10 the V ring, each on its own
     // schedule (a K tile is free as soon as its Q.K^T is done, a V tile only after its P.V);
     // lane w loads the w-th 16-key page of every block. They start right after the barriers
@@ -342,8 +487,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       // this thread's half of its Q row into the K-major swizzled tile
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD) + half * 8;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<uint4*>(q_sm + half * HALF_T + srow * 128 + ((i ^ (srow & 7)) << 4)) = src[i];
+      for (int i = 0; i < 8; ++i) {
+        uint4 v = src[i];
+        if constexpr (F8 && QDT == ESP_BF16) {  // the pass computes in fp16
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = QE::unpack2(w[k]);
+            w[k] = PE::pack2(f.x, f.y);
+          }
+        }
+        *reinterpret_cast<uint4*>(q_sm + half * HALF_T + srow * 128 + ((i ^ (srow & 7)) << 4)) = v;
+      }
       fence_proxy_async_smem();
       if (tile.last) {
         if (use_anc) am = a.anc_mask[row];
@@ -377,8 +532,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kMmaWarp) {
       // ================= MMA issuer (one thread)
       if (lane == 0 && nb > 0) {
-        constexpr uint32_t idesc_qk = umma_idesc<QDT>(BM, BN, 0, 0);
-        constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
+        constexpr uint32_t idesc_qk = umma_idesc<CDT>(BM, BN, 0, 0);
+        constexpr uint32_t idesc_pv = umma_idesc<CDT>(BM, HD, 0, 1);
         // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
         // its address field (one thread issues everything, so every integer op here is latency).
         const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
@@ -398,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
           umma_commit(&s_full[b & 1]);
-          if (++kst == KS) kst = 0, kpar ^= 1;
+          if (++kst == KSx) kst = 0, kpar ^= 1;
         };
         // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
         // MMAs run in issue order, so Q.K^T of block b + 2 overwrites buffer b & 1 only after
@@ -423,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                       ks > 0 ? 1u : acc);
           umma_commit(&v_empty[vst]);
           umma_commit(&pv_done);
-          if (++vst == VS) vst = 0, vpar ^= 1;
+          if (++vst == VSx) vst = 0, vpar ^= 1;
           if (b + 2 < nb) issue_qk(b + 2);
           if (b + 1 == nb) umma_commit(&o_full);
           stamp(b, 5);
@@ -508,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
           ps0 += p0;
           ps1 += p1;
-          pk[c] = QE::pack2(p0, p1);
+          pk[c] = PE::pack2(p0, p1);
         }
         l_run += ps0 + ps1;
         tmem_st32(t_s, pk);  // over the scores this thread has already read
@@ -529,7 +684,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         tmem_wait_st();
-        if (n_valid < BN) {
+        if (!F8 && n_valid < BN) {  // (E4M3 pools: the converter warps write zeros there)
           // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
           wait_bar(&v_full[vst], vpar, kStatusTmaTimeout);
           const int n = (BN - n_valid) * 16;  // 16-byte chunks: 2 dim halves x 8 per row
@@ -539,7 +694,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           fence_proxy_async_smem();
         }
-        if (++vst == VS) vst = 0, vpar ^= 1;
+        if (++vst == VSx) vst = 0, vpar ^= 1;
         tc_fence_before_sync();
         mbar_arrive(&p_full[sb]);
         if (tid == 0) stamp(b, 2);
@@ -787,9 +942,11 @@ bool flash_umma_supports(int32_t HDim, int32_t G, int32_t tile_rows, int32_t bt,
 }
 
 cudaError_t flash_umma_setup() {
-  cudaError_t e = cudaFuncSetAttribute(flash_umma_kernel<ESP_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(flash_umma_kernel<ESP_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(flash_umma_kernel<ESP_F16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_kernel<ESP_BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_kernel<ESP_F16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_kernel<ESP_BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  return e;
 }
 
 cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map, const CUtensorMap& vb_map,
@@ -844,7 +1001,8 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
   }
   *merged = fuse;
   const int hpc = BM / a.tile_rows;
-  const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
+  const bool f8 = a.kv_dtype == ESP_E4M3;  // pool_map is then the byte map of the pool (16-row boxes of 128-byte lines)
+  const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(f8 ? kThreadsF8 : kThreads);
   // Pair mode: every job has exactly two records, written by the tiles 2 j and 2 j + 1 (the kernel walks the tiles
   // from the last one down: cluster ranks 0 and 1 are the tiles 2 j + 1 and 2 j).
   bool pairs = fuse && a.pair_merge && a.n_tiles % 2 == 0;
@@ -863,8 +1021,13 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
     attr[1].val.clusterDim.x = 2, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
     cfg.numAttrs = 2;
   }
-  cudaError_t e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_F16>, pool_map, kb_map, vb_map, plan, k)
-                                       : cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_BF16>, pool_map, kb_map, vb_map, plan, k);
+  cudaError_t e;
+  if (f8)
+    e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_F16, true>, pool_map, kb_map, vb_map, plan, k)
+                             : cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_BF16, true>, pool_map, kb_map, vb_map, plan, k);
+  else
+    e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_F16, false>, pool_map, kb_map, vb_map, plan, k)
+                             : cudaLaunchKernelEx(&cfg, flash_umma_kernel<ESP_BF16, false>, pool_map, kb_map, vb_map, plan, k);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

@@ -150,7 +150,9 @@ int esp_attn_abi_version(void);
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531), "check_finite" (1: scan every pass's
  * output for NaN / Inf, see esp_attn_finite_check; initialised from ESPETERO_CHECK_FINITE; default 0),
- * "fuse_exchange" (see esp_attn_forward_exchange; default 0),
+ * "fuse_exchange" (see esp_attn_forward_exchange; default 0), "fp8_direct" (1: multi-row passes over an E4M3 pool
+ * with 128-dim heads and mostly cached keys dequantise inside the tcgen05 kernel instead of widening the pool into
+ * dequant_scratch first; default 1),
  * "attn_vec" (the reference's alternative decode schedule, src/model/impl/model.h:590, off there by
  * default and not built here: 0 is accepted, anything else answers ESP_ERR_UNSUPPORTED). */
 int esp_attn_set_option(esp_attn_ctx* ctx, const char* name, int value);
@@ -239,10 +241,12 @@ typedef struct esp_attn_args {
   int32_t bidi;            /* 1: rows of an image also see the image's later rows (desc.w = end of the row's
                               image, 0 outside images) */
   int32_t reserved2;
-  /* Optional scratch for multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys): with
-   * it the pass first widens the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into
-   * the scratch and runs the tensor-core kernels on that copy; without it (NULL) such passes run on
-   * the general kernel. Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
+  /* Multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys). 128-dim heads, keys mostly cached
+   * (more than twice the pass's own rows): the tcgen05 kernel reads the codes itself and needs nothing here
+   * (option "fp8_direct", default 1). Other such passes use this optional scratch: with it the pass first widens
+   * the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into the scratch and runs the
+   * tensor-core kernels on that copy; without it (NULL) they run on the general kernel.
+   * Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
   void* dequant_scratch;
   uint64_t dequant_scratch_bytes;
   /* Qwen sparse attention (flash_attention_qsa, kernels/45_qsa.metal:452-690; the extra bindings 12-16 of its

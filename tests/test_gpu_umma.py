@@ -184,17 +184,22 @@ def test_hd256_on_tensor_cores(oracle_lib, case):
         assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
 
 
-@pytest.mark.parametrize("case", ["verify128", "verify256", "chunked_prefill"])
-def test_e4m3_pool_on_tensor_cores_through_scratch(oracle_lib, case):
-    """Multi-row passes over an E4M3 pool: with the caller's scratch the blocks of the pass are widened
-    to the 16-bit type (code * scale) and the tcgen05 kernels run on that copy; without scratch the same
-    pass runs on the general kernel. Both within the E4M3 tolerance of the oracle, which reads the codes."""
+@pytest.mark.parametrize("case", ["verify128", "verify128_f16", "verify256", "chunked_prefill"])
+def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
+    """Multi-row passes over an E4M3 pool. 128-dim heads over mostly cached keys: flash_umma reads the codes itself
+    (raw pages by TMA, converter warps, fp16 MMAs; option fp8_direct, default on) - no scratch needed. Otherwise, and
+    with fp8_direct = 0: with the caller's scratch the blocks of the pass are widened to the 16-bit type (code * scale)
+    and the tcgen05 kernels run on that copy; without scratch the pass runs on the general kernel. All within the E4M3
+    tolerance of the oracle, which reads the codes."""
     if case == "verify128":
         w, tr = wl.make_pass("fp8_v128", 95, [(1500, 16), (333, 16), (70, 5)], 32, 4, 128, 16, wl.BF16, wl.E4M3, mask="tree"), 16
+    elif case == "verify128_f16":
+        w, tr = wl.make_pass("fp8_v128h", 98, [(2100, 16), (128, 16), (15, 3)], 16, 2, 128, 16, wl.F16, wl.E4M3, mask="tree"), 16
     elif case == "verify256":
         w, tr = wl.make_pass("fp8_v256", 96, [(900, 16), (200, 16)], 32, 8, 256, 16, wl.F16, wl.E4M3, mask="tree"), 32
     else:
         w, tr = wl.make_pass("fp8_chunk", 97, [(700, 150)], 8, 2, 128, 16, wl.BF16, wl.E4M3), 128
+    direct_ok = w.HD == 128
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
     for groups in (8, 592):
         op = host.AttnOp.for_workload(w, tr)
@@ -202,19 +207,25 @@ def test_e4m3_pool_on_tensor_cores_through_scratch(oracle_lib, case):
             plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups, tr)
             dp = op.upload(w, plan)
             assert dp.scratch is not None
-            op.forward(dp)
-            op.check_status()
-            assert op.last_kernel in ("flash_umma", "flash_umma_pair", "flash_umma_duo")
-            O, lse = dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy()
-            util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}")
-            assert np.abs(lse - lse_ref).max() < 1e-2
+            for direct in ((1, 0) if direct_ok else (0,)):
+                op.set_option("fp8_direct", direct)
+                dp.O.zero_()
+                op.forward(dp)
+                op.check_status()
+                assert op.last_kernel == ("flash_umma" if direct else op.last_kernel)
+                assert op.last_kernel in ("flash_umma", "flash_umma_pair", "flash_umma_duo")
+                O, lse = dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy()
+                util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}/direct{direct}")
+                assert np.abs(lse - lse_ref).max() < 1e-2
             a = op.make_args(dp)
-            a.dequant_scratch, a.dequant_scratch_bytes = None, 0          # no scratch: the general kernel
-            dp.O.zero_()
-            op.forward(dp, a)
-            op.check_status()
-            assert op.last_kernel == "flash_general"
-            util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=f"{w.name}/general")
+            a.dequant_scratch, a.dequant_scratch_bytes = None, 0          # no scratch
+            for direct in ((1, 0) if direct_ok else (0,)):
+                op.set_option("fp8_direct", direct)
+                dp.O.zero_()
+                op.forward(dp, a)
+                op.check_status()
+                assert op.last_kernel == ("flash_umma" if direct else "flash_general")
+                util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=f"{w.name}/noscratch/direct{direct}")
         finally:
             op.close()
 
