@@ -592,8 +592,13 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool fp8_direct = fp8_pool && c->opt_fp8_direct && s.HD == 128 && a.kv != nullptr && a.kv_scales != nullptr && a.n_blocks > 0 &&
                           a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 && c->opt_umma_kernel <= 1 &&
                           keys_cached > 2 * keys_batch;
-  const bool umma_ok = !decode && !windowed && c->opt_attn_umma && a.tiles_host != nullptr && (!fp8_pool || widen || fp8_direct) &&
-                       a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
+  // Sliding-window layers (window masks, ring addressing; not image rows, not sparse lists) with 128-dim heads over a
+  // 16-bit pool have their own instantiation of the two-tile tcgen05 kernel, for plans with tcgen05-sized tiles
+  // (esp_attn_plan_window with rows = 128 gives them to passes of 256 row groups or more).
+  const bool win_tc = windowed && !a.bidi && a.qsa_tlist == nullptr && !fp8_pool && c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 &&
+                      esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, s.kv_dtype);
+  const bool umma_ok = !decode && (!windowed || win_tc) && c->opt_attn_umma && a.tiles_host != nullptr &&
+                       (!fp8_pool || widen || fp8_direct) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.
   int replan_slot = -1;
   if (umma_ok && TR == 8 && c->opt_replan && !single && full_attention_plan(a, TR)) {
@@ -602,7 +607,8 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     else if (rrc != ESP_OK) return rrc;
   }
   bool umma = umma_ok && esp::flash_umma_supports(s.HD, c->G, TR, s.bt, s.q_dtype, fp8_pool ? s.q_dtype : s.kv_dtype);
-  for (int i = 0; umma && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
+  // (sliding-window tiles start at any key: their kernel loads from the page boundary below and masks)
+  for (int i = 0; umma && !win_tc && i < a.n_tiles; ++i) umma = a.tiles_host[i].k0 % esp::kDecodeKeyBlock == 0;
 
   esp::KernelArgs k{};
   k.Q = a.Q, k.Kb = a.Kb, k.Vb = a.Vb, k.kv = a.kv, k.kv_scales = a.kv_scales, k.blocks = a.blocks;
@@ -676,7 +682,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
     // from HBM, the pass's own rows sit in L2), unless the "umma_kernel" option forces one.
     // 256-dim heads run on flash_umma_pair only (one CTA per SM there: its tiles take the whole SM).
-    const bool stream_hbm = s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && keys_cached > 2 * keys_batch));
+    const bool stream_hbm = !win_tc && s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && keys_cached > 2 * keys_batch));
     if (fp8_direct)
       if (int rc = pool_tensor_map(c, a)) return rc;
     // Passes whose keys are mostly their own rows (prefill) are compute-bound: two query tiles per CTA where the

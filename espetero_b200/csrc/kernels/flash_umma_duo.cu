@@ -35,6 +35,9 @@
 // (it completes the third warpgroup, which hands most of its registers to the softmax warpgroups).
 // They hand tiles to one another through mbarriers only. Every wait is bounded: after a timeout the CTA
 // records a status code, stops waiting, finishes its loop, frees its tensor memory and returns.
+#include <climits>
+#include <cstddef>
+
 #include "umma.cuh"
 #include "../launch.h"
 
@@ -61,6 +64,7 @@ constexpr int kTmaWarpK = 9;
 constexpr int kTmaWarpV = 10;
 constexpr int kThreads = 12 * 32;            // warps 8-11 form the third warpgroup; warp 11 only gives up its registers
 constexpr int kPages = BN / 16;             // TMA pages per tile
+constexpr int kPosSlots = 4;                // batch blocks whose key positions are kept (two in the K ring, two in the softmax)
 // Registers move from the third warpgroup (MMA issue, TMA producers) to the softmax warpgroups once the kernel runs
 // (setmaxnreg): a softmax thread holds its 128 scores at once. 128 x 96 + 256 x 192 <= 64 K registers.
 constexpr int kRegsAux = 96, kRegsSoftmax = 192;
@@ -76,10 +80,15 @@ struct PageRef {  // where one 16-key page of a key block comes from
 struct Shared {
   uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[NQ], p_full[NQ][2], o_full, meta_ready;
   uint32_t tmem_slot;
-  int red[4];  // anc_max, seg_min, anc_min, seg_max
+  int red[6];  // anc_max, seg_min, anc_min, seg_max, latest query position of the tile (sliding-window layers)
   volatile int dead;
+  // sliding-window layers only (the launch reserves this part for them alone): the positions of a batch block's keys
+  uint64_t kpos_full[kPosSlots];
+  int kpos_min[kPosSlots];
+  int kpos[kPosSlots][BN];
 };
-static_assert(sizeof(Shared) <= 256, "bookkeeping must fit behind the tiles");
+static_assert(offsetof(Shared, kpos_full) <= 256, "bookkeeping must fit behind the tiles");
+constexpr int SMEM_BYTES_WIN = TILES_BYTES + int((sizeof(Shared) + 127) / 128 * 128);
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -111,7 +120,7 @@ __device__ __forceinline__ void tmem_wait_ld_of(uint32_t (&r)[32]) {
                : "memory");
 }
 
-template <int QDT>
+template <int QDT, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
     flash_umma_duo_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                           const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
@@ -177,7 +186,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(&o_full, 1);
     mbar_init(&meta_ready, 1);
     mbar_fence_init();
-    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0;
+    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0, red[4] = INT_MIN;
+    if constexpr (WIN)
+      for (int i = 0; i < kPosSlots; ++i) mbar_init(&sh.kpos_full[i], 1);
     dead = 0;
   }
   __syncthreads();
@@ -207,13 +218,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   phase(0);
 
   // Block list: cached 128-key blocks first, then the batch blocks some row of the tile can see.
-  const int nbc = (tile.k1 - tile.k0 + BN - 1) / BN;
+  // Sliding-window layers (kernels/80_gemma.metal:123-142, :284-285; planner src/model/impl/gemma.h:77-116): a key
+  // `window` or more positions behind the query is masked. Their tiles start at the first cached key a row can see,
+  // at any alignment: pages are loaded from the 16-key boundary below it (the keys in between are behind every
+  // row's window), and batch blocks below the first batch key worth scanning (tile.pad0) are left out.
+  const bool windowed = WIN && a.window > 0;
+  const int k0a = WIN ? (tile.k0 & ~15) : tile.k0;
+  const int nbc = (tile.k1 - k0a + BN - 1) / BN;
   const int r_first = tile.r0 - tree.base, r_last = r_first + rows_live - 1;
   struct Meta {
-    int k_last, a_hi, b_lo, nbb, anc_min, seg_max;
+    int k_last, a_lo, a_hi, b_lo, nbb, anc_min, seg_max, lo_max;
   };
   auto make_meta = [&]() {
-    Meta m{-1, 0, 0, 0, 0, 0};
+    Meta m{-1, 0, 0, 0, 0, 0, 0, INT_MIN};
+    if (windowed) m.lo_max = red[4] - a.window + 1;  // the latest row's first visible position
     if (!tile.last) return m;
     if (use_anc) {
       m.k_last = min(tree.M, 64) - 1;
@@ -228,10 +246,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     m.a_hi = min((anc_max + BN - 1) / BN, n_all);  // blocks below the ancestor range
     m.b_lo = max(m.a_hi, seg_min / BN);            // blocks of the rows' own segments
     const int b_hi = min(r_last / BN, n_all - 1);
-    m.nbb = m.a_hi + max(0, b_hi - m.b_lo + 1);
+    if (windowed) {
+      const int f = max(0, tile.pad0) / BN;
+      m.a_lo = min(m.a_hi, f);
+      m.b_lo = max(m.b_lo, f);
+    }
+    m.nbb = (m.a_hi - m.a_lo) + max(0, b_hi - m.b_lo + 1);
     return m;
   };
-  auto batch_j0 = [&](const Meta& m, int i) { return BN * (i < m.a_hi ? i : m.b_lo + (i - m.a_hi)); };
+  auto batch_j0 = [&](const Meta& m, int i) { return BN * (i < m.a_hi - m.a_lo ? m.a_lo + i : m.b_lo + (i - (m.a_hi - m.a_lo))); };
 
   if (warp >= kMmaWarp) {
   setmaxnreg_dec<kRegsAux>();  // the whole third warpgroup, warp 11 included
@@ -269,8 +292,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // page l % 8), two groups ahead of their use.
     auto load_group = [&](int g) {
       const int b = 4 * g + (lane >> 3);
-      const int j = tile.k0 + BN * b + 16 * (lane & 7);
-      return (b < nbc && j < tile.k1) ? a.blocks[tree.table + j / bt] : -1;
+      const int j = k0a + BN * b + 16 * (lane & 7);
+      if (!(b < nbc && j < tile.k1)) return -1;
+      if (WIN && a.ring > 0) return tree.table + (j / bt) % a.ring;  // a sliding layer's blocks: the slot's ring, no page table
+      return a.blocks[tree.table + j / bt];
     };
     int g_cur = load_group(0), g_nxt = load_group(1);
     for (int b = 0; b < nbc; ++b) {
@@ -280,17 +305,37 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const int raw = __shfl_sync(0xffffffffu, g_cur, ((b & 3) << 3) | (lane & 7));
       if (lane < kPages) {
-        const PageRef r{raw, (tile.k0 + BN * b + 16 * lane) % bt, raw >= 0 ? 0 : -1};
+        const PageRef r{raw, (k0a + BN * b + 16 * lane) % bt, raw >= 0 ? 0 : -1};
         issue(r);
       }
     }
-    if (tile.last && lane < kPages) {
-      if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
+    if (tile.last) {
+      if (desc_mask || windowed) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
       const Meta m = make_meta();
       for (int i = 0; i < m.nbb; ++i) {
-        const int j = batch_j0(m, i) + 16 * lane;
-        PageRef r{tree.base + j, 0, j <= m.k_last ? 1 : -1};
-        issue(r);
+        const int jb = batch_j0(m, i);
+        if (lane < kPages) {
+          const int j = jb + 16 * lane;
+          PageRef r{tree.base + j, 0, j <= m.k_last ? 1 : -1};
+          issue(r);
+        }
+        if (windowed && !is_v) {
+          // the positions of the block's keys, and the earliest of them, for the softmax warps' window masks
+          const int slot = i % kPosSlots;
+          int lowest = INT_MAX;
+#pragma unroll
+          for (int q = 0; q < BN / 32; ++q) {
+            const int j = jb + lane + 32 * q;
+            const int kp = j <= m.k_last ? a.pos[4 * size_t(tree.base + j)] : INT_MAX;
+            sh.kpos[slot][lane + 32 * q] = kp;
+            lowest = min(lowest, kp);
+          }
+#pragma unroll
+          for (int o = 16; o; o >>= 1) lowest = min(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
+          if (lane == 0) sh.kpos_min[slot] = lowest;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh.kpos_full[slot]);
+        }
       }
     }
   } else if (warp == kMmaWarp) {
@@ -368,6 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // set-up: the two Q tiles, mask bounds
     int4 d = make_int4(0, 0, 0, 0);
     uint64_t am = 0;
+    int qpos = 0;  // sliding-window layers: the row's position
     {
       // this thread's Q row into its tile (K-major, 128-byte swizzle)
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD);
@@ -379,6 +425,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (tile.last) {
         if (use_anc) am = a.anc_mask[row];
         else d = reinterpret_cast<const int4*>(a.desc)[row];
+      }
+      if (windowed) {
+        qpos = a.pos[4 * size_t(row)];
+        int latest = qpos;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) latest = max(latest, __shfl_xor_sync(0xffffffffu, latest, o));
+        if (lane == 0 && qt == 0) atomicMax(&red[4], latest);
       }
       if (desc_mask && qt == 0) {  // both query tiles hold the same rows
         int v0 = d.z, v1 = d.x, v2 = d.z, v3 = d.x;
@@ -400,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_before_sync();
     named_barrier(1, kSoftmaxThreads + 32);  // softmax warps + the MMA warp
     tc_fence_after_sync();
-    if (tid == 0 && desc_mask) mbar_arrive(&meta_ready);  // the producers may plan the batch blocks
+    if (tid == 0 && (desc_mask || windowed)) mbar_arrive(&meta_ready);  // the producers may plan the batch blocks
     phase(1);
     const Meta meta = make_meta();
     const int nb = nbc + meta.nbb;
@@ -416,12 +469,26 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       for (int b = 0; b < nb; ++b) {
         const bool cached = b < nbc;
-        const int j0 = cached ? tile.k0 + BN * b : batch_j0(meta, b - nbc);
+        const int j0 = cached ? k0a + BN * b : batch_j0(meta, b - nbc);
         const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, meta.k_last + 1 - j0);
         bool need_mask = n_valid < BN;
         if (!cached) {
           if (use_anc) need_mask = true;
           else need_mask = need_mask || !((j0 + BN - 1 < meta.anc_min) || (j0 >= meta.seg_max && j0 + BN - 1 <= r_first));
+        }
+        // Sliding-window layers: a cached key sits at position j, so a block needs the window's lower edge when the
+        // latest row's first visible position lies beyond its first key; a batch key sits at its row's position, which
+        // the K producer left in shared memory with the block's earliest one.
+        bool win_keys = false;
+        const int wslot = (b - nbc) % kPosSlots;
+        if (windowed) {
+          if (cached) {
+            need_mask = need_mask || j0 < meta.lo_max;
+          } else {
+            wait_bar(&sh.kpos_full[wslot], uint32_t((b - nbc) / kPosSlots) & 1u, kStatusTmaTimeout);
+            win_keys = sh.kpos_min[wslot] < meta.lo_max;
+            need_mask = need_mask || win_keys;
+          }
         }
         // visibility of this row's 128 columns, 32 per word (only read when need_mask)
         uint32_t vw[4] = {~0u, ~0u, ~0u, ~0u};
@@ -437,6 +504,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int jb = j0 + c0;  // batch key of the half's first column
                 vm &= low_bits64(d.z - jb) | (low_bits64(rr - jb + 1) & ~low_bits64(d.x - jb));  // j < d.z || d.x <= j <= rr
               }
+              if (win_keys) {
+                uint64_t wm = 0;
+                for (int c = 0; c < 64; ++c) wm |= uint64_t(qpos - sh.kpos[wslot][c0 + c] < a.window) << c;
+                vm &= wm;
+              }
+            } else if (windowed) {
+              vm &= ~low_bits64(qpos - a.window + 1 - (j0 + c0));  // j >= the row's first visible position
             }
             vw[2 * hf] = uint32_t(vm), vw[2 * hf + 1] = uint32_t(vm >> 32);
           }
@@ -630,24 +704,32 @@ bool flash_umma_duo_supports(int32_t HDim, int32_t G, int32_t tile_rows, int32_t
 }
 
 cudaError_t flash_umma_duo_setup() {
-  cudaError_t e = cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_F16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_F16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_WIN);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_umma_duo_kernel<ESP_BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_WIN);
+  return e;
 }
 
 cudaError_t launch_flash_umma_duo(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
   const int hpc2 = NQ * BM / a.tile_rows;
+  const bool win = a.window > 0 || a.ring > 0;  // sliding-window layers: their own instantiation, the rest pays nothing
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(unsigned(a.n_tiles), unsigned(a.p.H / hpc2)), cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = SMEM_BYTES, cfg.stream = stream;
+  cfg.dynamicSmemBytes = win ? SMEM_BYTES_WIN : SMEM_BYTES, cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = 1;
-  cudaError_t e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_F16>, pool_map, kb_map, vb_map, a)
-                                       : cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_BF16>, pool_map, kb_map, vb_map, a);
+  cudaError_t e;
+  if (win)
+    e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_F16, true>, pool_map, kb_map, vb_map, a)
+                             : cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_BF16, true>, pool_map, kb_map, vb_map, a);
+  else
+    e = a.q_dtype == ESP_F16 ? cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_F16, false>, pool_map, kb_map, vb_map, a)
+                             : cudaLaunchKernelEx(&cfg, flash_umma_duo_kernel<ESP_BF16, false>, pool_map, kb_map, vb_map, a);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;
   return e;

@@ -107,3 +107,38 @@ def test_window_needs_positions():
         assert e.value.code == capi.ESP_ERR_INVALID
     finally:
         op.close()
+
+
+@pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16_gate", "ring", "positions_with_gaps"])
+def test_window_layers_on_the_tensor_cores(oracle_lib, case):
+    """Sliding-window passes planned with tcgen05-sized tiles (esp_attn_plan_window, rows = 128: the generic planner
+    gives its caller's tile height to passes of 256 row groups x kv heads or more) run on flash_umma_duo: window edge
+    inside cached blocks (tiles start at unaligned keys), inside batch blocks (per-key positions), ring addressing,
+    batch blocks below the window skipped. Against the float64 oracle and against the general kernel on an 8-row plan."""
+    gate = False
+    if case == "prefill":
+        w = wl.make_window_pass("winp", 31, [(0, 1500), (0, 700)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
+    elif case == "chunked":
+        w = wl.make_window_pass("winc", 32, [(1234, 600), (77, 900)], 8, 2, 128, 16, wl.BF16, 517, scale=128 ** -0.5)
+    elif case == "chunked_f16_gate":
+        w = wl.make_window_pass("wing", 33, [(2000, 1100)], 16, 4, 128, 16, wl.F16, 1024, scale=128 ** -0.5)
+    elif case == "ring":
+        w = wl.make_window_pass("winr", 34, [(640, 1300)], 8, 2, 128, 16, wl.BF16, 256, ring=48, scale=128 ** -0.5)
+        w.blocks[:] = -1                               # the page table must not be read
+    else:
+        # positions that are not the row index plus P (the later rows sit 100 positions earlier than their index says):
+        # the window mask of a batch block comes from the keys' own positions. (Positions may lag behind P + j, never
+        # run ahead of it: the planner's first batch key, gemma.h:89-94, assumes no key is later than that.)
+        w = wl.make_window_pass("winj", 35, [(300, 1400)], 8, 2, 128, 16, wl.BF16, 350, scale=128 ** -0.5)
+        pos = w.extra["window"]["pos"]
+        pos[700:, 0:3] -= 100
+    win = w.extra["window"]
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=128, window=win["window"], pos=win["pos"])
+    assert plan.tile_rows == 128
+    if case != "positions_with_gaps":
+        assert any(int(t["k0"]) % 16 for t in plan.tiles) or any(int(t["pad0"]) > 0 for t in plan.tiles)
+    O = _check(oracle_lib, w, plan, "flash_umma_duo")
+    small = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=win["window"], pos=win["pos"])
+    O8 = _check(oracle_lib, w, small, "flash_general")
+    a, b = wl.from_bits16(O, w.q_dtype), wl.from_bits16(O8, w.q_dtype)
+    assert (np.abs(a - b) <= 2 * util.TOL_16 + 2.0 ** -7 * np.abs(b)).all()   # two roundings to the output type: one ulp
