@@ -592,10 +592,10 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool fp8_direct = fp8_pool && c->opt_fp8_direct && s.HD == 128 && a.kv != nullptr && a.kv_scales != nullptr && a.n_blocks > 0 &&
                           a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 && c->opt_umma_kernel <= 1 &&
                           keys_cached > 2 * keys_batch;
-  // Sliding-window layers (window masks, ring addressing; not image rows, not sparse lists) with 128-dim heads over a
+  // Sliding-window layers (window masks, ring addressing, image rows; not sparse lists) with 128-dim heads over a
   // 16-bit pool have their own instantiation of the two-tile tcgen05 kernel, for plans with tcgen05-sized tiles
   // (esp_attn_plan_window with rows = 128 gives them to passes of 256 row groups or more).
-  const bool win_tc = windowed && !a.bidi && a.qsa_tlist == nullptr && !fp8_pool && c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 &&
+  const bool win_tc = windowed && a.qsa_tlist == nullptr && !fp8_pool && c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 &&
                       esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, s.kv_dtype);
   const bool umma_ok = !decode && (!windowed || win_tc) && c->opt_attn_umma && a.tiles_host != nullptr &&
                        (!fp8_pool || widen || fp8_direct) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);

@@ -78,9 +78,9 @@ struct PageRef {  // where one 16-key page of a key block comes from
 };
 
 struct Shared {
-  uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[NQ], p_full[NQ][2], o_full, meta_ready;
+  uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[NQ], p_full[NQ][2], o_full;
   uint32_t tmem_slot;
-  int red[6];  // anc_max, seg_min, anc_min, seg_max, latest query position of the tile (sliding-window layers)
+  int red[6];  // anc_max, seg_min, anc_min, seg_max; sliding-window layers: latest query position, furthest image end
   volatile int dead;
   // sliding-window layers only (the launch reserves this part for them alone): the positions of a batch block's keys
   uint64_t kpos_full[kPosSlots];
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   using QE = Elem16<QDT>;
   extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[t]: S_t written; p_full[t]: P_t written
-  // (128 arrivals); o_full: last P.V done; meta_ready: the mask bounds of the tile are known
+  // (128 arrivals); o_full: last P.V done
   Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
   uint64_t* k_full = sh.k_full;
   uint64_t* k_empty = sh.k_empty;
@@ -136,7 +136,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* s_full = sh.s_full;
   uint64_t (*p_full)[2] = sh.p_full;
   uint64_t& o_full = sh.o_full;
-  uint64_t& meta_ready = sh.meta_ready;
   int* red = sh.red;
   volatile int& dead = sh.dead;
   if ((smem_u32(smem) & 1023u) != 0) {  // never expected; the tiles' swizzle would be wrong
@@ -184,9 +183,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&p_full[i][1], BM);
     }
     mbar_init(&o_full, 1);
-    mbar_init(&meta_ready, 1);
     mbar_fence_init();
-    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0, red[4] = INT_MIN;
+    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0, red[4] = INT_MIN, red[5] = 0;
     if constexpr (WIN)
       for (int i = 0; i < kPosSlots; ++i) mbar_init(&sh.kpos_full[i], 1);
     dead = 0;
@@ -223,15 +221,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   // at any alignment: pages are loaded from the 16-key boundary below it (the keys in between are behind every
   // row's window), and batch blocks below the first batch key worth scanning (tile.pad0) are left out.
   const bool windowed = WIN && a.window > 0;
+  const bool bidi = WIN && a.bidi != 0 && a.anc_mask == nullptr;  // image rows see their whole image (desc.w = its end)
   const int k0a = WIN ? (tile.k0 & ~15) : tile.k0;
   const int nbc = (tile.k1 - k0a + BN - 1) / BN;
   const int r_first = tile.r0 - tree.base, r_last = r_first + rows_live - 1;
   struct Meta {
     int k_last, a_lo, a_hi, b_lo, nbb, anc_min, seg_max, lo_max;
   };
-  auto make_meta = [&]() {
+  auto make_meta_from = [&](int anc_max, int seg_min, int anc_min, int seg_max, int latest, int img_end) {
     Meta m{-1, 0, 0, 0, 0, 0, 0, INT_MIN};
-    if (windowed) m.lo_max = red[4] - a.window + 1;  // the latest row's first visible position
+    if (windowed) m.lo_max = latest - a.window + 1;  // the latest row's first visible position
     if (!tile.last) return m;
     if (use_anc) {
       m.k_last = min(tree.M, 64) - 1;
@@ -239,13 +238,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       m.nbb = m.a_hi;
       return m;
     }
-    const int anc_max = red[0], seg_min = red[1];
-    m.anc_min = red[2], m.seg_max = red[3];
-    m.k_last = min(tree.M - 1, max(r_last, anc_max - 1));
+    m.anc_min = anc_min, m.seg_max = seg_max;
+    // (image rows of a bidirectional layer also see the later rows of their image, up to desc.w: img_end is the
+    // furthest such end among the tile's rows, 0 otherwise)
+    const int reach = max(r_last, img_end - 1);
+    m.k_last = min(tree.M - 1, max(reach, anc_max - 1));
     const int n_all = (m.k_last + BN) / BN;
     m.a_hi = min((anc_max + BN - 1) / BN, n_all);  // blocks below the ancestor range
     m.b_lo = max(m.a_hi, seg_min / BN);            // blocks of the rows' own segments
-    const int b_hi = min(r_last / BN, n_all - 1);
+    const int b_hi = min(reach / BN, n_all - 1);
     if (windowed) {
       const int f = max(0, tile.pad0) / BN;
       m.a_lo = min(m.a_hi, f);
@@ -253,6 +254,30 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     m.nbb = (m.a_hi - m.a_lo) + max(0, b_hi - m.b_lo + 1);
     return m;
+  };
+  auto make_meta = [&]() { return make_meta_from(red[0], red[1], red[2], red[3], red[4], red[5]); };  // after the set-up barrier
+  // The same bounds straight from the rows' records, by one warp: the TMA producers do not wait for the softmax
+  // warps' set-up to know which batch blocks to fetch.
+  auto warp_meta = [&]() {
+    int v0 = 0, v1 = 1 << 30, v2 = 1 << 30, v3 = 0, q = INT_MIN, w_end = 0;
+    for (int r = lane; r < rows_live; r += 32) {
+      if (desc_mask) {
+        const int4 d = reinterpret_cast<const int4*>(a.desc)[tile.r0 + r];
+        v0 = max(v0, d.z), v1 = min(v1, d.x), v2 = min(v2, d.z), v3 = max(v3, d.x);
+        if (bidi) w_end = max(w_end, d.w);
+      }
+      if (windowed) q = max(q, a.pos[4 * size_t(tile.r0 + r)]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      v0 = max(v0, __shfl_xor_sync(0xffffffffu, v0, o));
+      v1 = min(v1, __shfl_xor_sync(0xffffffffu, v1, o));
+      v2 = min(v2, __shfl_xor_sync(0xffffffffu, v2, o));
+      v3 = max(v3, __shfl_xor_sync(0xffffffffu, v3, o));
+      q = max(q, __shfl_xor_sync(0xffffffffu, q, o));
+      w_end = max(w_end, __shfl_xor_sync(0xffffffffu, w_end, o));
+    }
+    return make_meta_from(v0, v1, v2, v3, q, w_end);
   };
   auto batch_j0 = [&](const Meta& m, int i) { return BN * (i < m.a_hi - m.a_lo ? m.a_lo + i : m.b_lo + (i - (m.a_hi - m.a_lo))); };
 
@@ -310,8 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     if (tile.last) {
-      if (desc_mask || windowed) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
-      const Meta m = make_meta();
+      const Meta m = warp_meta();
       for (int i = 0; i < m.nbb; ++i) {
         const int jb = batch_j0(m, i);
         if (lane < kPages) {
@@ -448,12 +472,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           atomicMin(&red[2], v2);
           atomicMax(&red[3], v3);
         }
+        if (bidi) {
+          int w_end = d.w;
+#pragma unroll
+          for (int o = 16; o; o >>= 1) w_end = max(w_end, __shfl_xor_sync(0xffffffffu, w_end, o));
+          if (lane == 0) atomicMax(&red[5], w_end);
+        }
       }
     }
     tc_fence_before_sync();
     named_barrier(1, kSoftmaxThreads + 32);  // softmax warps + the MMA warp
     tc_fence_after_sync();
-    if (tid == 0 && (desc_mask || windowed)) mbar_arrive(&meta_ready);  // the producers may plan the batch blocks
     phase(1);
     const Meta meta = make_meta();
     const int nb = nbc + meta.nbb;
@@ -502,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 vm &= hf == 0 ? am : 0ull;  // one block, j0 = 0
               } else {
                 const int jb = j0 + c0;  // batch key of the half's first column
-                vm &= low_bits64(d.z - jb) | (low_bits64(rr - jb + 1) & ~low_bits64(d.x - jb));  // j < d.z || d.x <= j <= rr
+                const int own_end = bidi ? max(rr + 1, d.w) : rr + 1;  // an image row's segment reaches the image's end
+                vm &= low_bits64(d.z - jb) | (low_bits64(own_end - jb) & ~low_bits64(d.x - jb));  // j < d.z || d.x <= j < own_end
               }
               if (win_keys) {
                 uint64_t wm = 0;
@@ -640,8 +670,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int hg = head % G;
       const bool to_rec = tile.part >= 0;
       float* rec = to_rec ? a.parts + (size_t(tile.part) * p.Hkv + kvh) * TR * G * (HD + 2) + (size_t(fm) * G + hg) * (HD + 2) : nullptr;
-      typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(head) * HD;
       const float* gp = a.X ? a.X + size_t(row) * p.g_ld + size_t(head) * 2 * HD + HD : nullptr;
+      typename QE::T* op = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(head) * HD;
+      // (Staging the rows in the idle K ring and writing them out two whole rows per instruction measured slower than
+      // these per-thread 16-byte stores: 6.8 us against 4.8 us of epilogue.)
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         const int d0 = 32 * c;
@@ -715,7 +747,7 @@ cudaError_t launch_flash_umma_duo(const KernelArgs& a, const CUtensorMap& pool_m
                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
   const int hpc2 = NQ * BM / a.tile_rows;
-  const bool win = a.window > 0 || a.ring > 0;  // sliding-window layers: their own instantiation, the rest pays nothing
+  const bool win = a.window > 0 || a.ring > 0 || a.bidi != 0;  // sliding-window layers: their own instantiation, the rest pays nothing
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(unsigned(a.n_tiles), unsigned(a.p.H / hpc2)), cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = win ? SMEM_BYTES_WIN : SMEM_BYTES, cfg.stream = stream;

@@ -109,12 +109,12 @@ def test_window_needs_positions():
         op.close()
 
 
-@pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16_gate", "ring", "positions_with_gaps"])
+@pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16_gate", "ring", "positions_with_gaps", "images"])
 def test_window_layers_on_the_tensor_cores(oracle_lib, case):
     """Sliding-window passes planned with tcgen05-sized tiles (esp_attn_plan_window, rows = 128: the generic planner
     gives its caller's tile height to passes of 256 row groups x kv heads or more) run on flash_umma_duo: window edge
     inside cached blocks (tiles start at unaligned keys), inside batch blocks (per-key positions), ring addressing,
-    batch blocks below the window skipped. Against the float64 oracle and against the general kernel on an 8-row plan."""
+    batch blocks below the window skipped, image rows that see their whole image. Against the float64 oracle and against the general kernel on an 8-row plan."""
     gate = False
     if case == "prefill":
         w = wl.make_window_pass("winp", 31, [(0, 1500), (0, 700)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
@@ -122,6 +122,10 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case):
         w = wl.make_window_pass("winc", 32, [(1234, 600), (77, 900)], 8, 2, 128, 16, wl.BF16, 517, scale=128 ** -0.5)
     elif case == "chunked_f16_gate":
         w = wl.make_window_pass("wing", 33, [(2000, 1100)], 16, 4, 128, 16, wl.F16, 1024, scale=128 ** -0.5)
+    elif case == "images":
+        # rows 100..419 and 600..700 are images: their rows see the whole image (blocks beyond the diagonal)
+        w = wl.make_window_pass("wini", 36, [(200, 900), (0, 300)], 8, 2, 128, 16, wl.BF16, 4096, images={0: (100, 420), 1: (130, 290)},
+                                scale=128 ** -0.5)
     elif case == "ring":
         w = wl.make_window_pass("winr", 34, [(640, 1300)], 8, 2, 128, 16, wl.BF16, 256, ring=48, scale=128 ** -0.5)
         w.blocks[:] = -1                               # the page table must not be read
@@ -135,7 +139,7 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case):
     win = w.extra["window"]
     plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=128, window=win["window"], pos=win["pos"])
     assert plan.tile_rows == 128
-    if case != "positions_with_gaps":
+    if case not in ("positions_with_gaps", "images"):
         assert any(int(t["k0"]) % 16 for t in plan.tiles) or any(int(t["pad0"]) > 0 for t in plan.tiles)
     O = _check(oracle_lib, w, plan, "flash_umma_duo")
     small = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=win["window"], pos=win["pos"])
