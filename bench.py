@@ -76,7 +76,7 @@ def measured_peaks():
 measured_peaks.sustained_tflops = None
 
 
-def build_workload(name: str, rank: int, small: bool = False, world: int = 1):
+def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv: str = ""):
     from espetero_b200 import shard, workloads as wl
     seed_shift = 1000 * rank
     if name == "c1":
@@ -92,7 +92,8 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1):
         mine = shard.lpt_partition(lens, world)[rank]
         return wl.config_c2(0xE5B202 + seed_shift, lens=lens[mine])
     if name == "c4":
-        return wl.config_c4(0xE5B204 + seed_shift, n_seqs=2 if small else 16, prefix=512 if small else 4096)
+        return wl.config_c4(0xE5B204 + seed_shift, n_seqs=2 if small else 16, prefix=512 if small else 4096,
+                            kv_dtype=wl.E4M3 if kv == "e4m3" else None)
     if name == "c5":
         return wl.config_c5(0xE5B205 + seed_shift, ctx=8192 if small else 131072)
     if name == "c3":
@@ -689,6 +690,7 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="--workload prep: rows (0: the layout's default)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
+    ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c4 only: the verify pass over an FP8 E4M3 pool instead of bf16")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
@@ -713,7 +715,7 @@ def main():
     if args.workload == "c5" and (world > 1 or args.ctx > 0):
         r = setup_split_kv(B, args.small)
     else:
-        w = build_workload(args.workload, rank, args.small, world)
+        w = build_workload(args.workload, rank, args.small, world, args.kv)
         sharding = "sequences per rank, no collective" + (
             "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
         r = setup_sequences(B, args.workload, w, "weak", sharding)
@@ -767,7 +769,7 @@ def main():
         value = bytes_all / t_step / 1e9
         achieved = bytes_step / t_attn / 1e9
         flops = attention_flops(w)
-        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv) else None
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv or args.kv) else None
         tensor = {"tflops": flops / t_attn / 1e12, "peak_tflops": tf_peak, "frac": flops / t_attn / 1e12 / tf_peak,
                   "flops_per_step": flops}
         if measured_peaks.sustained_tflops:  # the denominator for a kernel timed inside a long, power-capped run

@@ -270,9 +270,11 @@ def config_c3(seed: int = 0xE5B203, n_seqs: int = 4, rows: int = 8192) -> Worklo
     return make_pass("c3_causal_prefill", seed, [(0, rows)] * n_seqs, 64, 8, 128, 16, BF16, spare_blocks=n_seqs * ((rows + 15) // 16))
 
 
-def config_c4(seed: int = 0xE5B204, n_seqs: int = 16, prefix: int = 4096, nodes: int = 16) -> Workload:
-    """Forest tree-verify: 16 sequences, 4096-token prefix + 16-node draft tree (random parents)."""
-    return make_pass("c4_tree_verify", seed, [(prefix, nodes)] * n_seqs, 32, 4, 128, 16, BF16, mask="tree")
+def config_c4(seed: int = 0xE5B204, n_seqs: int = 16, prefix: int = 4096, nodes: int = 16, kv_dtype: int | None = None) -> Workload:
+    """Forest tree-verify: 16 sequences, 4096-token prefix + 16-node draft tree (random parents). kv_dtype = E4M3: the
+    same pass over an FP8 pool (not one of the five configurations: the tcgen05 kernel's own dequantisation)."""
+    name = "c4_tree_verify" if kv_dtype in (None, BF16) else "c4_tree_verify_e4m3"
+    return make_pass(name, seed, [(prefix, nodes)] * n_seqs, 32, 4, 128, 16, BF16, kv_dtype=kv_dtype, mask="tree")
 
 
 def config_c5(seed: int = 0xE5B205, ctx: int = 131072, lo: int = 0, hi: int | None = None) -> Workload:
