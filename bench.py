@@ -495,6 +495,9 @@ def time_run(B: Bench, r: Run, steps: int, W: int, solo: bool = False):
     n0 = r.op.launch_count
     t_total = B.timed(r.step, steps, solo=solo)
     launches = r.op.launch_count - n0
+    if launches == steps and int(getattr(r.a_full, "n_jobs", 1)) == 0:
+        # the step IS the attention kernel (one launch, no records to merge): its timed region is the kernel's
+        return t_total / steps, t_total / steps, launches
     for _ in range(3):
         r.step_attn()
     t_attn = B.timed(r.step_attn, steps, solo=solo) / steps
