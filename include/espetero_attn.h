@@ -630,6 +630,10 @@ int esp_attn_check_status(esp_attn_ctx* ctx, void* stream);
  * 1 scores in registers, 2 P handed over, 3 P seen by the MMA thread, 4 V tile seen,
  * 5 MMAs of the block issued, 6 K tile requested, 7 V tile requested; slot 8 * n_blocks holds
  * the CTA's start and slot 8 * n_blocks + 1 its end. n_blocks = 0 switches tracing off.
+ * flash_umma over an E4M3 pool: 6 / 7 = the block's K / V tile converted. flash_umma_duo (two query tiles):
+ * 0 / 1 / 2 = tile 0's scores ready, row maxima known, P handed over; 3 / 4 = P of tile 0 / tile 1 seen by the MMA
+ * thread; 5 as above; 6 / 7 = tile 1's scores ready, P handed over; the table's last row (b = n_blocks - 1) holds
+ * phases of the CTA instead: 0 plan read, 1 set-up done, 2 last P handed over, 3 rows written.
  * With the option "trace_ctas" = N (> 0) the flash_umma kernel also stores four stamps for each of
  * its first N CTAs (linear CTA index c) at [8 * n_blocks + 2 + 4 * c + e]: e = 0 start, 1 first
  * scores seen, 2 last block handed over, 3 exit; the buffer must then hold
