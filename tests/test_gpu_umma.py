@@ -198,7 +198,7 @@ def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
     elif case == "verify256":
         w, tr = wl.make_pass("fp8_v256", 96, [(900, 16), (200, 16)], 32, 8, 256, 16, wl.F16, wl.E4M3, mask="tree"), 32
     else:
-        w, tr = wl.make_pass("fp8_chunk", 97, [(700, 150)], 8, 2, 128, 16, wl.BF16, wl.E4M3), 128
+        w, tr = wl.make_pass("fp8_chunk", 97, [(700, 150)], 8, 2, 128, 16, wl.BF16, wl.E4M3, gate=True), 128
     direct_ok = w.HD == 128
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
     for groups in (8, 592):

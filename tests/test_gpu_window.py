@@ -109,19 +109,23 @@ def test_window_needs_positions():
         op.close()
 
 
-@pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16_gate", "ring", "positions_with_gaps", "images"])
+@pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16", "ring", "positions_with_gaps", "images", "rows64"])
 def test_window_layers_on_the_tensor_cores(oracle_lib, case):
     """Sliding-window passes planned with tcgen05-sized tiles (esp_attn_plan_window, rows = 128: the generic planner
     gives its caller's tile height to passes of 256 row groups x kv heads or more) run on flash_umma_duo: window edge
     inside cached blocks (tiles start at unaligned keys), inside batch blocks (per-key positions), ring addressing,
     batch blocks below the window skipped, image rows that see their whole image. Against the float64 oracle and against the general kernel on an 8-row plan."""
-    gate = False
+    rows = 128
     if case == "prefill":
         w = wl.make_window_pass("winp", 31, [(0, 1500), (0, 700)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
     elif case == "chunked":
         w = wl.make_window_pass("winc", 32, [(1234, 600), (77, 900)], 8, 2, 128, 16, wl.BF16, 517, scale=128 ** -0.5)
-    elif case == "chunked_f16_gate":
+    elif case == "chunked_f16":
         w = wl.make_window_pass("wing", 33, [(2000, 1100)], 16, 4, 128, 16, wl.F16, 1024, scale=128 ** -0.5)
+    elif case == "rows64":
+        # 64-row tiles: a query tile is 64 rows x 2 heads, a CTA covers 4 heads of the kv group
+        w = wl.make_window_pass("win64", 37, [(500, 2100)], 8, 2, 128, 16, wl.BF16, 700, scale=128 ** -0.5)
+        rows = 64
     elif case == "images":
         # rows 100..419 and 600..700 are images: their rows see the whole image (blocks beyond the diagonal)
         w = wl.make_window_pass("wini", 36, [(200, 900), (0, 300)], 8, 2, 128, 16, wl.BF16, 4096, images={0: (100, 420), 1: (130, 290)},
@@ -137,8 +141,8 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case):
         pos = w.extra["window"]["pos"]
         pos[700:, 0:3] -= 100
     win = w.extra["window"]
-    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=128, window=win["window"], pos=win["pos"])
-    assert plan.tile_rows == 128
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=rows, window=win["window"], pos=win["pos"])
+    assert plan.tile_rows == rows
     if case not in ("positions_with_gaps", "images"):
         assert any(int(t["k0"]) % 16 for t in plan.tiles) or any(int(t["pad0"]) > 0 for t in plan.tiles)
     O = _check(oracle_lib, w, plan, "flash_umma_duo")
