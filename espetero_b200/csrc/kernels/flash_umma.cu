@@ -35,12 +35,12 @@
 //
 // E4M3 pools (template flag F8; the reference dequantises in its attention kernels too,
 // kernels/80_dsv4.metal:22-33 for the codec): the pages arrive by TMA as raw codes (2 KB per page and
-// kv head: half the bytes of a 16-bit pool) into rings of two 16 KB tiles; two converter warps (one
-// for K, one for V, four key rows per lane) turn them into fp16 tiles - code x the page's scale for
+// kv head: half the bytes of a 16-bit pool) into rings of two 16 KB tiles; six converter warps (three
+// for K, three for V, each taking every third page) turn them into fp16 tiles - code x the page's scale for
 // the kv head, which the producer fetched while it waited for the slot - in the 128-byte-swizzled
 // layout the MMAs read, and the whole pass computes in fp16 (Q is converted when it is staged, P is
 // fp16; accumulation and the records stay fp32). One producer warp serves both rings (lanes 0-7 K,
-// 8-15 V), so the CTA keeps 12 warps and its registers. Batch keys (the pass's own rows) are few in
+// 8-15 V); with 16 warps the kernel runs in 128 registers per thread. Batch keys (the pass's own rows) are few in
 // the passes this variant is for: the converter warps fetch them from Kb / Vb themselves.
 #include "umma.cuh"
 #include "../launch.h"
@@ -73,7 +73,7 @@ constexpr int kMmaWarp = 8;                 // MMA issue (one thread), owns tens
 constexpr int kTmaWarpK = 9;                // TMA producer of K tiles (lanes 0-7, one 16-key page each)
 constexpr int kTmaWarpV = 10;               // TMA producer of V tiles
 constexpr int kThreads = 11 * 32;
-constexpr int kCvtWarp0 = 10, kCvtWarps = 4;   // E4M3 pools: warp 9 produces both rings, warps 10-13 convert (even: K, odd: V)
+constexpr int kCvtWarp0 = 10, kCvtWarps = 6;   // E4M3 pools: warp 9 produces both rings, warps 10-15 convert (even: K, odd: V)
 constexpr int kThreadsF8 = (kCvtWarp0 + kCvtWarps) * 32;
 constexpr int kCvtLanes = kCvtWarps / 2 * 32;  // converter lanes per tile
 constexpr int kPages = BN / 16;             // TMA pages per tile
@@ -311,11 +311,11 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
       }
     }
   } else if (F8 && warp >= kCvtWarp0) {
-    // ================= E4M3 pools: converter warps. Warps 10 and 12 turn raw K tiles into fp16 K tiles, 11 and 13 do
-    // V (the four sit on the four schedulers: the conversion instruction runs on the exp2 unit's pipe); a warp owns
-    // 64 key rows of every block, two per lane. A row's 128 codes are 8 chunks of 16 in the raw tile's 128-byte
-    // line and become 16 chunks of 8 halves in the two 64-dim halves of the 16-bit tile.
-    const int is_v = (warp - kCvtWarp0) & 1, row0 = ((warp - kCvtWarp0) >> 1) * (BN / (kCvtWarps / 2));
+    // ================= E4M3 pools: converter warps. Warps 10, 12, 14 turn raw K tiles into fp16 K tiles, 11, 13, 15 do
+    // V (spread over the four schedulers: the conversion instruction runs on the exp2 unit's pipe); a warp takes
+    // every third 16-key page of a block. A row's 128 codes are 8 chunks of 16 in the raw tile's 128-byte line and
+    // become 16 chunks of 8 halves in the two 64-dim halves of the 16-bit tile.
+    const int is_v = (warp - kCvtWarp0) & 1, wi = (warp - kCvtWarp0) >> 1;
     uint64_t* full = is_v ? v_full : k_full;
     uint64_t* empty = is_v ? v_empty : k_empty;
     uint8_t* ring = is_v ? v_sm : k_sm;
@@ -333,20 +333,21 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
       if (cached) wait_bar(&sh.raw_full[is_v][rst], rpar, kStatusTmaTimeout);
       wait_bar(&empty[cst], cpar, kStatusMmaTimeout);
       uint8_t* dst = ring + cst * KV_TILE;
+      // a warp takes whole 16-key pages: lane l converts half of row (l % 16) of the page - 4 of its 8 raw chunks
 #pragma unroll 1
-      for (int q = 0; q < BN / kCvtLanes; ++q) {
-        const int r = row0 + lane + 32 * q;
-        uint8_t* drow = dst + r * 128;
+      for (int pg = wi; pg < kPages; pg += kCvtWarps / 2) {
+        const int r = 16 * pg + (lane & 15), cg = lane >> 4;
+        uint8_t* drow = dst + r * 128 + cg * HALF_T;  // codes 64 cg .. 64 cg + 63 = the dims of half cg
         if (r >= n_valid) {
           // rows past the range: zeros (stale bytes could be NaN patterns, and 0 x NaN must not happen)
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_T + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(drow + ((c ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
         } else if (cached) {
           const uint8_t* srow = raw_ring + rst * RAW_TILE + r * 128;
-          const __half2 sc2 = __float2half2_rn(sh.scl[is_v][rst][r >> 4]);
+          const __half2 sc2 = __float2half2_rn(sh.scl[is_v][rst][pg]);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = 4 * cg + cc;  // the row's raw chunk: codes 16 c .. 16 c + 15
             const uint4 v = *reinterpret_cast<const uint4*>(srow + ((c ^ (r & 7)) << 4));
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             uint32_t h[8];
@@ -356,17 +357,16 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
               __half2 a2 = __hmul2(*reinterpret_cast<__half2*>(&lo), sc2), b2 = __hmul2(*reinterpret_cast<__half2*>(&hi), sc2);
               h[2 * i] = *reinterpret_cast<uint32_t*>(&a2), h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b2);
             }
-            // codes 16 c .. 16 c + 15 = dims of half (c >> 2), 16-byte chunks (2 c) & 7 and (2 c + 1) & 7 of the row's line
-            uint8_t* dh = drow + (c >> 2) * HALF_T;
-            *reinterpret_cast<uint4*>(dh + ((((2 * c) & 7) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<uint4*>(dh + ((((2 * c + 1) & 7) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+            // ... = the 16-byte chunks 2 cc and 2 cc + 1 of the half's 128-byte line
+            *reinterpret_cast<uint4*>(drow + (((2 * cc) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(drow + (((2 * cc + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
           }
         } else {
           // a batch key: the pass's own row, in the Q type
           const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(is_v ? a.Vb : a.Kb) +
-                                                            size_t(tree.base + j0 + r) * p.kv_ld + size_t(kvh) * HD);
+                                                            size_t(tree.base + j0 + r) * p.kv_ld + size_t(kvh) * HD) + 8 * cg;
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 8; ++c) {
             uint4 v = src[c];
             if constexpr (QDT == ESP_BF16) {
               uint32_t* w = reinterpret_cast<uint32_t*>(&v);
@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
                 w[i] = PE::pack2(f.x, f.y);
               }
             }
-            *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_T + (((c & 7) ^ (r & 7)) << 4)) = v;
+            *reinterpret_cast<uint4*>(drow + ((c ^ (r & 7)) << 4)) = v;
           }
         }
       }
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
         if (++rst == RS8) rst = 0, rpar ^= 1;
       }
       mbar_arrive(&full[cst]);
-      if (lane == 0 && row0 == 0) stamp(b, is_v ? 7 : 6);  // timeline: the block's K / V tile converted
+      if (lane == 0 && wi == 0) stamp(b, is_v ? 7 : 6);  // timeline: the block's K / V tile converted
       if (++cst == KS8) cst = 0, cpar ^= 1;
     }
   } else if (!F8 && (warp == kTmaWarpK || warp == kTmaWarpV)) {
