@@ -50,6 +50,12 @@ def attention_flops(w) -> float:
     """Algorithmic flops of one pass: 2 flop per MAC, Q.K^T and P.V, over the visible (row, key)
     pairs (cached keys + causal / ancestor batch keys)."""
     pairs = 0
+    win = w.extra.get("window") if isinstance(getattr(w, "extra", None), dict) else None
+    if win and win["window"] > 0:  # causal rows at positions P + r behind P cached keys, `window` positions visible
+        for t in w.trees:
+            P, M = int(t["P"]), int(t["M"])
+            pairs += int(np.minimum(P + np.arange(M) + 1, win["window"]).sum())
+        return 4.0 * pairs * w.H * w.HD
     for i, t in enumerate(w.trees):
         P, M = int(t["P"]), int(t["M"])
         if w.anc_mask is not None and (w.flags & 2):
@@ -76,7 +82,7 @@ def measured_peaks():
 measured_peaks.sustained_tflops = None
 
 
-def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv: str = ""):
+def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv: str = "", window: int = 0):
     from espetero_b200 import shard, workloads as wl
     seed_shift = 1000 * rank
     if name == "c1":
@@ -97,7 +103,11 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
     if name == "c5":
         return wl.config_c5(0xE5B205 + seed_shift, ctx=8192 if small else 131072)
     if name == "c3":
-        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=1 if small else 4, rows=2048 if small else 8192)
+        n, rows = (1, 2048) if small else (4, 8192)
+        if window > 0:  # the same prefill through a sliding-window layer (not one of the five configurations)
+            return wl.make_window_pass("c3_causal_prefill_window", 0xE5B203 + seed_shift, [(0, rows)] * n, 64, 8, 128, 16, wl.BF16,
+                                       window, scale=128 ** -0.5)
+        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=n, rows=rows)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -292,6 +302,9 @@ def bench_plan(name: str, w, groups: int = 0):
     """The plan the bench runs a workload with (the full-size parity tests use the same one)."""
     from espetero_b200 import capi, host
     tile_rows = TILE_ROWS[name]
+    win = w.extra.get("window") if isinstance(getattr(w, "extra", None), dict) else None
+    if win and win["window"] > 0:  # the generic planner's window branch, with tcgen05-sized tiles
+        return host.plan_window(w.trees, groups=w.Hkv, split=512, rows=tile_rows, window=win["window"], pos=win["pos"])
     return host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, groups or default_groups(name), tile_rows)
 
 
@@ -694,6 +707,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c4 only: the verify pass over an FP8 E4M3 pool instead of bf16")
+    ap.add_argument("--window", type=int, default=0, help="c3 only: the prefill through a sliding-window layer of this many positions")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
@@ -718,7 +732,7 @@ def main():
     if args.workload == "c5" and (world > 1 or args.ctx > 0):
         r = setup_split_kv(B, args.small)
     else:
-        w = build_workload(args.workload, rank, args.small, world, args.kv)
+        w = build_workload(args.workload, rank, args.small, world, args.kv, args.window)
         sharding = "sequences per rank, no collective" + (
             "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
         r = setup_sequences(B, args.workload, w, "weak", sharding)
@@ -772,7 +786,7 @@ def main():
         value = bytes_all / t_step / 1e9
         achieved = bytes_step / t_attn / 1e9
         flops = attention_flops(w)
-        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv or args.kv) else None
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv or args.kv or args.window) else None
         tensor = {"tflops": flops / t_attn / 1e12, "peak_tflops": tf_peak, "frac": flops / t_attn / 1e12 / tf_peak,
                   "flops_per_step": flops}
         if measured_peaks.sustained_tflops:  # the denominator for a kernel timed inside a long, power-capped run
@@ -783,7 +797,8 @@ def main():
             "ms_per_step": 1e3 * t_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16" if w.kv_dtype != wl.E4M3 else "e4m3->f16", "data": "synthetic",
             "config": workload_config(w),
-            "plan": {"planner": "ESP_PLAN_B200", "tiles": len(plan.tiles), "parts": plan.n_parts, "kernel": kernel_name,
+            "plan": {"planner": "esp_attn_plan_window (rows 128)" if args.window else "ESP_PLAN_B200", "tiles": len(plan.tiles),
+                     "parts": plan.n_parts, "kernel": kernel_name,
                      "sharding": sharding},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": traffic, "peak_source": which, "kernel": kernel_name, "ms_per_launch": 1e3 * t_attn,
