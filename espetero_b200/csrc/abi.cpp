@@ -55,6 +55,7 @@ struct esp_attn_ctx {
   // device slots of the context (see replan_pass).
   int opt_replan = 1;
   int opt_fp8_direct = 1;  // E4M3 pools: passes over mostly cached keys read the codes inside flash_umma (no widening pre-pass)
+  int opt_stable_cache = 0;  // see KernelArgs::stable_cache
   int opt_pair_merge = 1;  // flash_umma: passes whose jobs all have two records merge them inside a cluster pair (distributed shared memory)
   int opt_fuse_exchange = 0;  // esp_attn_forward_exchange: 1 = merge and exchange inside the decode kernel (one launch); 0 = two kernels (measured faster)
   uint8_t* replan_dev = nullptr;
@@ -334,6 +335,7 @@ int* option_slot(esp_attn_ctx* c, const char* name) {
   if (!std::strcmp(name, "replan")) return &c->opt_replan;
   if (!std::strcmp(name, "fuse_exchange")) return &c->opt_fuse_exchange;
   if (!std::strcmp(name, "pair_merge")) return &c->opt_pair_merge;
+  if (!std::strcmp(name, "stable_cache")) return &c->opt_stable_cache;
   if (!std::strcmp(name, "fp8_direct")) return &c->opt_fp8_direct;
   return nullptr;
 }
@@ -622,6 +624,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   k.n_trees = a.n_trees, k.n_block_entries = a.n_block_entries;
   k.pos = a.pos, k.window = a.window, k.ring = a.ring, k.bidi = a.bidi;
   k.pair_merge = c->opt_pair_merge;
+  k.stable_cache = c->opt_stable_cache;
   k.qsa_tlist = a.qsa_tlist, k.qsa_tcount = a.qsa_tcount, k.qsa_rinfo = a.qsa_rinfo, k.qsa_sel = a.qsa_sel;
   k.qsa_nbw = a.qsa_nbw, k.qsa_n_lists = a.qsa_n_lists;
 

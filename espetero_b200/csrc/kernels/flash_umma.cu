@@ -161,6 +161,10 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
   const int tile_i = int(gridDim.x) - 1 - int(blockIdx.x);  // long (late) tiles first
   const TileStart& ts = plan.start[min(tile_i, kInlinePlanMax - 1)];
   const bool inl = ts.valid == tile_i + 1;  // small plan: everything for the first loads sits in one parameter line
+  // The caller's promise (option "stable_cache"): the kernel before this pass writes neither the block table nor the
+  // cached keys. With the plan in the parameters the producers then start fetching the cached key blocks while that
+  // kernel still drains; the batch keys, Q and the mask records wait for it as ever.
+  const bool early = inl && a.stable_cache != 0;
   esp_attn_tile tile;
   esp_attn_tree tree;
   if (inl) {
@@ -286,7 +290,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
       const int j = tile.k0 + BN * b + 16 * (lane & 7);
       return (b < nbc && j < tile.k1) ? page_table[tree.table + j / bt] : -1;
     };
-    pdl_wait();
+    if (!early) pdl_wait();
     int g_cur = load_group(0), g_nxt = load_group(1);
     for (int b = 0; b < nbc; ++b) {
       if (b && (b & 3) == 0) {
@@ -320,8 +324,8 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
     uint64_t* empty = is_v ? v_empty : k_empty;
     uint8_t* ring = is_v ? v_sm : k_sm;
     const uint8_t* raw_ring = raw_sm + is_v * RS8 * RAW_TILE;
-    pdl_wait();
-    if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
+    if (!early) pdl_wait();
+    if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);  // (arrives after the softmax warps' own dependency wait)
     const Meta m = make_meta();
     const int nb = nbc + m.nbb;
     int rst = 0, cst = 0;
@@ -331,6 +335,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
       const int j0 = cached ? tile.k0 + BN * b : batch_j0(m, b - nbc);
       const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, m.k_last + 1 - j0);
       if (cached) wait_bar(&sh.raw_full[is_v][rst], rpar, kStatusTmaTimeout);
+      else if (early && b == nbc) pdl_wait();  // the batch keys are what the kernel before this pass has written
       wait_bar(&empty[cst], cpar, kStatusMmaTimeout);
       uint8_t* dst = ring + cst * KV_TILE;
       // a warp takes whole 16-key pages: lane l converts half of row (l % 16) of the page - 4 of its 8 raw chunks
@@ -449,7 +454,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
           }
         }
       }
-      pdl_wait();  // everything above used only parameters, shared memory and hints
+      if (!early) pdl_wait();  // everything above used only parameters, shared memory and hints
       int g_cur = load_group(0), g_nxt = load_group(1);
       for (int b = 0; b < nbc; ++b) {
         if (b && (b & 3) == 0) {
@@ -462,6 +467,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
           issue(r, b);
         }
       }
+      if (early) pdl_wait();  // the batch keys are what the kernel before this pass has written
       if (tile.last && lane < kPages) {
         if (desc_mask) wait_bar(&meta_ready, 0, kStatusMmaTimeout);
         const Meta m = make_meta();

@@ -38,6 +38,9 @@ struct KernelArgs {
   int32_t fuse;                  // 1: tiles carry their job in pad1 and the last CTA of a job merges (flash_umma: 2 = the two tiles
                                  // of every job run as a cluster pair and merge through distributed shared memory)
   int32_t pair_merge;            // flash_umma: allow the cluster-pair merge (context option "pair_merge")
+  int32_t stable_cache;          // the caller's promise (context option "stable_cache"): the kernel before this pass on the
+                                 // stream writes neither the block table nor the cached keys [0, P) of any tree (nor their
+                                 // scales), so flash_umma may fetch them before that kernel has completed
   unsigned long long* trace;  // optional: CTA (0, 0) writes %globaltimer stamps here (8 events per key block)
   int32_t trace_blocks;       // key blocks the trace buffer holds
   int32_t trace_ctas;         // CTAs whose 4 stamps (start, first scores, loop end, exit) follow at 8 * trace_blocks + 2

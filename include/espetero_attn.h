@@ -150,7 +150,11 @@ int esp_attn_abi_version(void);
  * is launched; initialised from the ESPETERO_FAIL_PASS environment variable, the
  * reference's host-side fault injection, forest.h:2521-2531), "check_finite" (1: scan every pass's
  * output for NaN / Inf, see esp_attn_finite_check; initialised from ESPETERO_CHECK_FINITE; default 0),
- * "fuse_exchange" (see esp_attn_forward_exchange; default 0), "fp8_direct" (1: multi-row passes over an E4M3 pool
+ * "fuse_exchange" (see esp_attn_forward_exchange; default 0), "stable_cache" (1: the caller promises that the kernel
+ * enqueued before a pass on its stream writes neither the block table nor the cached keys [0, P) of any tree of the
+ * pass, nor their E4M3 scales - in the reference's layer the kernel before attention is attn_prep, which writes this
+ * pass's rows only; the verify kernel then starts fetching cached key blocks while that kernel still drains
+ * (programmatic dependent launch); Q, Kb, Vb and the mask records are waited for as ever; default 0), "fp8_direct" (1: multi-row passes over an E4M3 pool
  * with 128-dim heads and mostly cached keys dequantise inside the tcgen05 kernel instead of widening the pool into
  * dequant_scratch first; default 1),
  * "attn_vec" (the reference's alternative decode schedule, src/model/impl/model.h:590, off there by

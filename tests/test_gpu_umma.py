@@ -361,3 +361,28 @@ def test_prefill_records_meet_the_plain_tolerance(oracle_lib, umma_kernel):
     assert np.abs(lse64 - lse_ref).max() < 1e-3
     over = (err > util.TOL_16).any(axis=1)
     print(f"prefill records ({kernel}): {(err > util.TOL_16).mean():.2e} of the elements beyond plain 2e-3, the last such row is {int(np.flatnonzero(over).max()) if over.any() else -1}")
+
+
+@pytest.mark.parametrize("kv", [None, wl.E4M3], ids=["bf16", "fp8"])
+def test_stable_cache_option_gives_the_same_results(oracle_lib, kv):
+    """Option stable_cache lets the verify kernel fetch cached key blocks before the previous kernel of the stream has
+    completed; with a pool nobody writes between the passes the results are those of the default order, pass after pass
+    (several passes back to back on one stream, so that the early fetches do overlap a running kernel)."""
+    w = wl.make_pass("stable", 99, [(3000, 16), (1500, 16), (700, 9)], 32, 4, 128, 16, wl.BF16, kv, mask="tree")
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    op = host.AttnOp.for_workload(w, 16)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 148, 16)
+        dp = op.upload(w, plan)
+        outs = {}
+        for stable in (0, 1):
+            op.set_option("stable_cache", stable)
+            for _ in range(6):
+                op.forward(dp)
+            op.check_status()
+            assert op.last_kernel == "flash_umma"
+            outs[stable] = dp.O.cpu().numpy().view(np.uint16).copy()
+            util.check_output(outs[stable], ref, w, ref_abs=ref_abs, what=f"stable_cache={stable}")
+        assert np.array_equal(outs[0], outs[1])
+    finally:
+        op.close()
