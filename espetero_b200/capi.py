@@ -69,7 +69,7 @@ class Args(C.Structure):
                 ("p", Params), ("pos", C.c_void_p), ("window", C.c_int32), ("ring", C.c_int32), ("bidi", C.c_int32),
                 ("reserved2", C.c_int32), ("dequant_scratch", C.c_void_p), ("dequant_scratch_bytes", C.c_uint64),
                 ("qsa_tlist", C.c_void_p), ("qsa_tcount", C.c_void_p), ("qsa_rinfo", C.c_void_p), ("qsa_sel", C.c_void_p),
-                ("qsa_nbw", C.c_int32), ("qsa_n_lists", C.c_int32)]
+                ("qsa_nbw", C.c_int32), ("qsa_n_lists", C.c_int32), ("pos_host", C.c_void_p)]
 
 
 class PrepParams(C.Structure):

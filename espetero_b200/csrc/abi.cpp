@@ -292,15 +292,27 @@ constexpr size_t kReplanSlotBytes = size_t(kReplanTiles) * sizeof(esp_attn_tile)
 // range in order and are all merged by one job of this pass), batch keys scanned by the tile that
 // ends at P? That is what the reference's planners emit (plan_tiles, src/model/impl/forest.h:1378-1433);
 // such a pass may be re-planned freely: only O and lse are its results.
-bool full_attention_plan(const esp_attn_args& a, int TR) {
+// With `windowed` (a sliding-window layer whose positions the caller mirrors in pos_host) the same for what the
+// generic planner emits (g4_plan_tiles, src/model/impl/gemma.h:77-116): the cached range of a row group starts at
+// the first key its earliest row can still see, and pad0 carries the first batch key worth scanning.
+bool full_attention_plan(const esp_attn_args& a, int TR, bool windowed = false) {
   if (!a.tiles_host || !a.trees_host || (a.n_jobs > 0 && !a.jobs_host)) return false;
+  if (windowed && (!a.pos_host || a.window <= 0)) return false;
   int ti = 0, ji = 0;
   for (int t = 0; t < a.n_trees; ++t) {
     const esp_attn_tree& tr = a.trees_host[t];
     for (int r = 0; r < tr.M; r += TR) {
       if (ti >= a.n_tiles) return false;
       const esp_attn_tile& first = a.tiles_host[ti];
-      if (first.tree != t || first.r0 != tr.base + r || first.pad0 != 0 || first.k0 != 0) return false;
+      int32_t k_first = 0, b_first = 0;
+      if (windowed) {
+        int32_t lowest = INT32_MAX;
+        for (int i = r; i < std::min(tr.M, r + TR); ++i) lowest = std::min(lowest, a.pos_host[4 * size_t(tr.base + i)]);
+        const int64_t start = int64_t(lowest) - a.window + 1;
+        k_first = int32_t(std::clamp<int64_t>(start, 0, tr.P));
+        b_first = int32_t(std::max<int64_t>(0, start - tr.P));
+      }
+      if (first.tree != t || first.r0 != tr.base + r || first.pad0 != b_first || first.k0 != k_first) return false;
       if (first.part < 0) {
         if (first.k1 != tr.P || !first.last) return false;
         ++ti;
@@ -309,11 +321,11 @@ bool full_attention_plan(const esp_attn_args& a, int TR) {
       if (ji >= a.n_jobs) return false;
       const esp_attn_combine& job = a.jobs_host[ji++];
       if (job.r0 != tr.base + r || job.rows != std::min(TR, tr.M - r) || job.part0 != first.part || job.nparts < 1) return false;
-      int k = 0;
+      int k = k_first;
       for (int s2 = 0; s2 < job.nparts; ++s2, ++ti) {
         if (ti >= a.n_tiles) return false;
         const esp_attn_tile& x = a.tiles_host[ti];
-        if (x.tree != t || x.r0 != tr.base + r || x.part != job.part0 + s2 || x.k0 != k || x.k1 <= x.k0 || x.pad0 != 0) return false;
+        if (x.tree != t || x.r0 != tr.base + r || x.part != job.part0 + s2 || x.k0 != k || x.k1 <= x.k0 || x.pad0 != b_first) return false;
         if ((x.last != 0) != (x.k1 == tr.P)) return false;
         k = x.k1;
       }
@@ -486,6 +498,22 @@ int esp_attn_check_status(esp_attn_ctx* c, void* stream) {
 // 128 / G rows with the G heads of a kv head for passes over a cached prefix (verify) - and the new
 // tiles and jobs replace the caller's for this call. Records go to the caller's `parts` in the new
 // tiles' layout (the split is chosen so that they fit). Returns false when the pass stays as it is.
+static bool stage_plan(esp_attn_ctx* c, esp_attn_args& a, int& TR, int new_TR, int32_t nt, int32_t nj, cudaStream_t stream, int* rc);
+
+// A sliding-window pass planned the reference's way (8-row tiles, g4_plan_tiles) planned again with 128-row tiles for
+// the tcgen05 kernel: the generic planner with a group count that leaves it no budget to split (its tiles then take
+// the caller's height), on the caller's host mirror of the positions.
+static bool replan_window_pass(esp_attn_ctx* c, esp_attn_args& a, int& TR, cudaStream_t stream, int* rc) {
+  *rc = ESP_OK;
+  const int new_TR = 128;
+  int32_t nt = 0, nj = 0, np = 0, rows = 0;
+  c->rp_tiles.resize(kReplanTiles), c->rp_jobs.resize(kReplanJobs);
+  const int prc = esp_attn_plan_window(a.trees_host, a.n_trees, 256, 0, new_TR, a.window, a.pos_host, c->rp_tiles.data(), kReplanTiles,
+                                       c->rp_jobs.data(), kReplanJobs, &nt, &nj, &np, &rows);
+  if (prc != ESP_OK || rows != new_TR || nj != 0 || np != 0) return false;
+  return stage_plan(c, a, TR, new_TR, nt, nj, stream, rc);
+}
+
 static bool replan_pass(esp_attn_ctx* c, esp_attn_args& a, int& TR, cudaStream_t stream, int* rc) {
   *rc = ESP_OK;
   const esp_attn_shape& s = c->shape;
@@ -515,6 +543,12 @@ static bool replan_pass(esp_attn_ctx* c, esp_attn_args& a, int& TR, cudaStream_t
     if (attempt == 1) return false;
     o.split = 0;
   }
+  return stage_plan(c, a, TR, new_TR, nt, nj, stream, rc);
+}
+
+// The new tiles and jobs (in rp_tiles / rp_jobs) through a staging slot into device memory; `a` and TR become the
+// pass as it runs.
+static bool stage_plan(esp_attn_ctx* c, esp_attn_args& a, int& TR, int new_TR, int32_t nt, int32_t nj, cudaStream_t stream, int* rc) {
   // a free staging slot (its previous pass has run)
   const int slot = c->replan_next;
   c->replan_next = (slot + 1) % kReplanSlots;
@@ -594,6 +628,16 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool fp8_direct = fp8_pool && c->opt_fp8_direct && s.HD == 128 && a.kv != nullptr && a.kv_scales != nullptr && a.n_blocks > 0 &&
                           a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 && c->opt_umma_kernel <= 1 &&
                           keys_cached > 2 * keys_batch;
+  // Reference-shaped sliding-window plans (8-row tiles) are planned again for the tensor cores when the caller mirrors
+  // the positions on the host.
+  int replan_slot = -1;
+  if (windowed && TR == 8 && c->opt_replan && !single && !decode && a.window > 0 && a.pos_host && a.qsa_tlist == nullptr && !fp8_pool &&
+      c->opt_attn_umma && c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 && a.p.kv_ld % 64 == 0 && a.p.kv_base % 64 == 0 &&
+      esp::flash_umma_duo_supports(s.HD, c->G, 128, s.bt, s.q_dtype, s.kv_dtype) && full_attention_plan(a, TR, true)) {
+    int rrc = ESP_OK;
+    if (replan_window_pass(c, a, TR, stream, &rrc)) replan_slot = rrc - 1;
+    else if (rrc != ESP_OK) return rrc;
+  }
   // Sliding-window layers (window masks, ring addressing, image rows; not sparse lists) with 128-dim heads over a
   // 16-bit pool have their own instantiation of the two-tile tcgen05 kernel, for plans with tcgen05-sized tiles
   // (esp_attn_plan_window with rows = 128 gives them to passes of 256 row groups or more).
@@ -602,7 +646,6 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool umma_ok = !decode && (!windowed || win_tc) && c->opt_attn_umma && a.tiles_host != nullptr &&
                        (!fp8_pool || widen || fp8_direct) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.
-  int replan_slot = -1;
   if (umma_ok && TR == 8 && c->opt_replan && !single && full_attention_plan(a, TR)) {
     int rrc = ESP_OK;
     if (replan_pass(c, a, TR, stream, &rrc)) replan_slot = rrc - 1;

@@ -220,6 +220,8 @@ class AttnOp:
             a.dequant_scratch, a.dequant_scratch_bytes = dp.scratch.data_ptr(), dp.scratch.numel()
         if dp.win:
             a.pos, a.window, a.ring, a.bidi = _ptr(dp.pos), dp.win["window"], dp.win["ring"], dp.win["bidi"]
+            dp.pos_host = np.ascontiguousarray(dp.win["pos"], dtype=np.int32)   # kept alive with the pass
+            a.pos_host = dp.pos_host.ctypes.data
         a.p = self.params(w)
         return a
 

@@ -264,6 +264,10 @@ typedef struct esp_attn_args {
   const uint32_t* qsa_sel;    /* [sparse rows][qsa_nbw] selection bitmaps (esp_qsa_select) */
   int32_t qsa_nbw;            /* bitmap words per sparse row */
   int32_t qsa_n_lists;        /* lists in qsa_tlist (bounds tile.pad1) */
+  /* Optional host mirror of `pos` (int4 per row, as the engine builds it before the upload, forest.h:2374-2450).
+   * With it a context with tile_rows 8 can plan a sliding-window pass again for the tcgen05 kernel, as it does for
+   * plain passes (see esp_attn_forward); without it such plans run on the general kernel as given. */
+  const int32_t* pos_host;
 } esp_attn_args;
 
 /* Bytes of dequant_scratch for a pass whose block table has n_block_entries entries (pool rows of

@@ -45,10 +45,13 @@ def test_window_masks_multi_row(oracle_lib, HD, window):
     win = w.extra["window"]
     plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=window, pos=win["pos"])
     assert any(int(t["k0"]) % 16 for t in plan.tiles) or window >= 1000
-    _check(oracle_lib, w, plan, "flash_general")
+    # (128-dim heads: the harness mirrors the positions on the host, so the 8-row plan is planned again for the tcgen05
+    # kernel - test_reference_shaped_window_plans_reach_the_tensor_cores; option replan = 0 keeps the plan as given)
+    _check(oracle_lib, w, plan, "flash_umma_duo" if HD == 128 else "flash_general")
+    _check(oracle_lib, w, plan, "flash_general", options={"replan": 0})
     # the mask alone (no help from the plan): full-range tiles give the same answer
     full = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=0, pos=None)
-    _check(oracle_lib, w, full, "flash_general")
+    _check(oracle_lib, w, full, "flash_general", options={"replan": 0})
 
 
 def test_window_changes_the_result(oracle_lib):
@@ -147,6 +150,42 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case):
         assert any(int(t["k0"]) % 16 for t in plan.tiles) or any(int(t["pad0"]) > 0 for t in plan.tiles)
     O = _check(oracle_lib, w, plan, "flash_umma_duo")
     small = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=win["window"], pos=win["pos"])
-    O8 = _check(oracle_lib, w, small, "flash_general")
+    O8 = _check(oracle_lib, w, small, "flash_general", options={"replan": 0})
     a, b = wl.from_bits16(O, w.q_dtype), wl.from_bits16(O8, w.q_dtype)
     assert (np.abs(a - b) <= 2 * util.TOL_16 + 2.0 ** -7 * np.abs(b)).all()   # two roundings to the output type: one ulp
+
+
+@pytest.mark.parametrize("case", ["prefill", "chunked_ring"])
+def test_reference_shaped_window_plans_reach_the_tensor_cores(oracle_lib, case):
+    """A drop-in caller plans a sliding-window layer the reference's way (g4_plan_tiles, gemma.h:77-116: 8-row tiles) on
+    a context with tile_rows 8. With the host mirror of the positions (pos_host) the library plans the pass again with
+    128-row tiles and runs the tcgen05 kernel; without it the pass runs on the general kernel as given. Same results."""
+    if case == "prefill":
+        w = wl.make_window_pass("win8", 41, [(0, 1500), (0, 900)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
+    else:
+        w = wl.make_window_pass("win8r", 42, [(640, 1300)], 8, 2, 128, 16, wl.BF16, 256, ring=48, scale=128 ** -0.5)
+        w.blocks[:] = -1
+    win = w.extra["window"]
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=win["window"], pos=win["pos"])
+    assert plan.tile_rows == 8
+    op = host.AttnOp.for_workload(w, 8)
+    try:
+        dp = op.upload(w, plan)
+        tiles_before = dp.tiles.clone()
+        for _ in range(6):                                   # several passes reuse the staging slots
+            op.forward(dp)
+        op.check_status()
+        assert op.last_kernel == "flash_umma_duo", "a reference-shaped window plan fell onto the CUDA-core kernel"
+        assert torch.equal(dp.tiles, tiles_before)           # the caller's plan is read, never written
+        O = dp.O.cpu().numpy().view(np.uint16).copy()
+        util.check_output(O, ref, w, ref_abs=ref_abs, what=case)
+        a = op.make_args(dp)
+        a.pos_host = None                                     # no mirror: as given, on the general kernel
+        dp.O.zero_()
+        op.forward(dp, a)
+        op.check_status()
+        assert op.last_kernel == "flash_general"
+        util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=case + "/general")
+    finally:
+        op.close()
