@@ -284,8 +284,11 @@ size_t esp_attn_dequant_scratch_bytes(const esp_attn_shape* shape, int32_t n_blo
  * planned again inside this call for those kernels (tiles of 128 rows, or of 128 / G rows x G heads
  * over a cached prefix); the new tiles travel through pinned staging slots the context owns. The
  * caller's tiles / jobs are only read; `parts` is then scratch in the new tiles' layout and its
- * contents after the call are unspecified. Any other plan (records without jobs, sliding-window
- * plans, hand-made tilings) runs as given. Option "replan" = 0 switches this off. */
+ * contents after the call are unspecified. The plans of the generic planner's window branch
+ * (g4_plan_tiles, gemma.h:77-116: ranges that start at a row group's first visible key, pad0 = first
+ * batch key) are treated the same way when args->pos_host mirrors the rows' positions. Any other plan
+ * (records without jobs, window plans without that mirror, sparse plans, hand-made tilings) runs as
+ * given. Option "replan" = 0 switches this off. */
 int esp_attn_forward(esp_attn_ctx* ctx, void* stream, const esp_attn_args* args);
 
 /* Only the merge step (attention_combine): used after records of other GPUs
