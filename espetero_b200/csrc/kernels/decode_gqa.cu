@@ -526,7 +526,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     if (n_groups > 1) {
       // the group's record, unnormalised, over the group's first slot (its own records are spent)
       float* gout = kvh_base + size_t(part0 + grp * S) * part_stride;
-      __syncthreads();  // every thread is done reading the staged records of the last round
+      __syncthreads();  // every thread is done reading the staged records of the previous iteration
 #pragma unroll
       for (int k = 0; k < MAXI; ++k) {
         const int item = threadIdx.x + k * (NW * 32);
