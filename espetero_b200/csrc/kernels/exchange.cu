@@ -7,8 +7,8 @@
 //   step 2  store it into slot `rank` of every rank's exchange buffer through peer mappings
 //           (NVLink) as 8-byte words {value, tag}: the tag is the call's epoch, so every word
 //           says by itself whether it has arrived - no fence, no separate flag, one hop
-//   step 3  read the `world` records from the local exchange buffer, polling each word until it
-//           carries the tag, merge them in rank order and finish the row.
+//   step 3  read the `world` records from the local exchange buffer, polling the words (of all ranks
+//           still missing at once) until they carry the tag, merge them in rank order and finish the row.
 // A thread waits only for words that the same head's CTA on another GPU stores; nothing waits on
 // another CTA of its own GPU, and the whole grid is resident, so the wait cannot starve the
 // sender. The wait is bounded by a timer: on expiry the CTA writes the status word and returns
@@ -18,6 +18,8 @@
 
 namespace esp {
 namespace {
+
+constexpr int kMaxRanks = ESP_ATTN_MAX_PEERS;  // slots of ExchangeArgs::records
 
 template <int QDT>
 __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const ExchangeArgs x) {
@@ -68,25 +70,41 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const Exchang
       const uint2* rec0 = x.records[x.rank] + epoch_off + size_t(job_i) * stride + rec_off;
       const uint64_t t0 = global_timer_ns();
       const uint64_t limit = uint64_t(x.wait_ms) * 1000000ull;
-      for (int q = 0; ok && q < x.world; ++q) {
-        const uint2* rec = rec0 + size_t(q) * rank_words;
-        uint2 w[6];
-        for (;;) {
+      // Every look asks for the words of ALL ranks that are still missing at once (one trip to memory per look,
+      // not one per rank); what has arrived is kept, and the merge below runs over the ranks in order.
+      float v[kMaxRanks][6];
+      uint32_t have = 0;
+      const uint32_t every = x.world >= 32 ? ~0u : (1u << x.world) - 1u;
+      for (;;) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) w[i] = ld_word(rec + 4 * d4 + i);
-          w[4] = ld_word(rec + HD), w[5] = ld_word(rec + HD + 1);
-          bool all = true;
+        for (int q = 0; q < kMaxRanks; ++q) {
+          if (q < x.world && !((have >> q) & 1u)) {
+            const uint2* rec = rec0 + size_t(q) * rank_words;
+            uint2 w[6];
 #pragma unroll
-          for (int i = 0; i < 6; ++i) all = all && w[i].y == tag;
-          if (all) break;
-          if (global_timer_ns() - t0 > limit) {
-            ok = false;
-            break;
+            for (int i = 0; i < 4; ++i) w[i] = ld_word(rec + 4 * d4 + i);
+            w[4] = ld_word(rec + HD), w[5] = ld_word(rec + HD + 1);
+            bool all = true;
+#pragma unroll
+            for (int i = 0; i < 6; ++i) all = all && w[i].y == tag;
+            if (all) {
+              have |= 1u << q;
+#pragma unroll
+              for (int i = 0; i < 6; ++i) v[q][i] = __uint_as_float(w[i].x);
+            }
           }
-          __nanosleep(32);
         }
-        if (!ok) break;
-        const float m_q = __uint_as_float(w[4].x);
+        if (have == every) break;
+        if (global_timer_ns() - t0 > limit) {
+          ok = false;
+          break;
+        }
+        __nanosleep(32);
+      }
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q) {
+        if (!ok || q >= x.world) continue;
+        const float m_q = v[q][4];
         if (m_q == -INFINITY) continue;  // an empty record adds nothing
         if (m_q > m.M) {                  // rescale what has been summed so far
           const float f = __expf(m.M - m_q);  // 0 for the first record
@@ -94,9 +112,9 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_kernel(const Exchang
           m.M = m_q;
         }
         const float wq = __expf(m_q - m.M);
-        m.L += wq * __uint_as_float(w[5].x);
-        m.acc.x += wq * __uint_as_float(w[0].x), m.acc.y += wq * __uint_as_float(w[1].x);
-        m.acc.z += wq * __uint_as_float(w[2].x), m.acc.w += wq * __uint_as_float(w[3].x);
+        m.L += wq * v[q][5];
+        m.acc.x += wq * v[q][0], m.acc.y += wq * v[q][1];
+        m.acc.z += wq * v[q][2], m.acc.w += wq * v[q][3];
       }
     }
     if (tracing) x.trace[3] = global_timer_ns();  // every rank's records are here
