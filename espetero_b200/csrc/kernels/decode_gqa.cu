@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(C::NW * 32, (C::SMEM_BYTES <= 110 * 1024) ? 2 
     const uint32_t rec_bytes = uint32_t(G) * (HD + 2) * 4;
     float* const kvh_base = a.parts + size_t(kvh) * a.tile_rows * G * (HD + 2);  // record 0 of this kv head
     float* stage = reinterpret_cast<float*>(smem);
-    constexpr int MAXI = HD / 64;              // items per thread at most: G * HD / 4 items over 128 threads
+    constexpr int MAXI = (8 * HD / 4 + NW * 32 - 1) / (NW * 32);  // items per thread at most: G * HD / 4 items (G <= 8) over the CTA's threads
     const int n_items = G * HD / 4;
     float st_m[MAXI], st_l[MAXI];
     float4 st_acc[MAXI];
@@ -656,11 +656,18 @@ using D128EH = DecodeCfg<128, ESP_E4M3, ESP_F16, 4, 4>;
 using D128EB = DecodeCfg<128, ESP_E4M3, ESP_BF16, 4, 4>;
 using D256EH = DecodeCfg<256, ESP_E4M3, ESP_F16, 4, 3>;
 using D256EB = DecodeCfg<256, ESP_E4M3, ESP_BF16, 4, 3>;
+// 512-dim heads (the global layers of kernels/80_gemma.metal, HD = 512 instantiations): a 16-key block is
+// 32 KB of 16-bit keys and values, so three warps with two blocks each fill the SM's shared memory (one CTA
+// per SM, 192 KB in flight); E4M3 blocks are half that and two CTAs fit.
+using D512H = DecodeCfg<512, ESP_F16, ESP_F16, 3, 2>;
+using D512B = DecodeCfg<512, ESP_BF16, ESP_BF16, 3, 2>;
+using D512EH = DecodeCfg<512, ESP_E4M3, ESP_F16, 3, 2>;
+using D512EB = DecodeCfg<512, ESP_E4M3, ESP_BF16, 3, 2>;
 
 }  // namespace
 
 bool decode_gqa_supports(int32_t HD, int32_t G, int32_t bt, int32_t q_dtype, int32_t kv_dtype) {
-  if (HD != 128 && HD != 256) return false;
+  if (HD != 128 && HD != 256 && HD != 512) return false;
   if (G < 1 || G > 8) return false;
   if (bt <= 0 || bt % 16 != 0) return false;
   if (q_dtype != ESP_F16 && q_dtype != ESP_BF16) return false;
@@ -676,7 +683,11 @@ cudaError_t decode_gqa_setup() {
   if ((e = setup_one<D128EH>()) != cudaSuccess) return e;
   if ((e = setup_one<D128EB>()) != cudaSuccess) return e;
   if ((e = setup_one<D256EH>()) != cudaSuccess) return e;
-  return setup_one<D256EB>();
+  if ((e = setup_one<D256EB>()) != cudaSuccess) return e;
+  if ((e = setup_one<D512H>()) != cudaSuccess) return e;
+  if ((e = setup_one<D512B>()) != cudaSuccess) return e;
+  if ((e = setup_one<D512EH>()) != cudaSuccess) return e;
+  return setup_one<D512EB>();
 }
 
 cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream, uint64_t* launches) {
@@ -686,9 +697,11 @@ cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& m, cudaStr
   if (a.kv_dtype == ESP_E4M3) {
     if (a.HD == 128) e = f16 ? launch_one<D128EH>(a, m, stream) : launch_one<D128EB>(a, m, stream);
     else if (a.HD == 256) e = f16 ? launch_one<D256EH>(a, m, stream) : launch_one<D256EB>(a, m, stream);
+    else if (a.HD == 512) e = f16 ? launch_one<D512EH>(a, m, stream) : launch_one<D512EB>(a, m, stream);
   } else {
     if (a.HD == 128) e = f16 ? launch_one<D128H>(a, m, stream) : launch_one<D128B>(a, m, stream);
     else if (a.HD == 256) e = f16 ? launch_one<D256H>(a, m, stream) : launch_one<D256B>(a, m, stream);
+    else if (a.HD == 512) e = f16 ? launch_one<D512H>(a, m, stream) : launch_one<D512B>(a, m, stream);
   }
   if (e == cudaSuccess) ++*launches;
   return e;

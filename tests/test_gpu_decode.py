@@ -25,6 +25,11 @@ CASES = [
     ("hd128_fp8_f16q", [(700, 1), (5000, 1)], 16, 2, 128, 16, wl.F16, wl.E4M3, False),
     ("g1_bt64", [(1000, 1), (130, 1)], 4, 4, 128, 64, wl.BF16, None, True),
     ("g2_bt32", [(555, 1)], 8, 4, 128, 32, wl.F16, None, False),
+    # 512-dim heads: the global layers of kernels/80_gemma.metal (HD = 512 instantiations, gemma.h:119-147)
+    ("hd512_bf16", [(900, 1), (64, 1), (5000, 1)], 8, 2, 512, 16, wl.BF16, None, False),
+    ("hd512_f16_gate_g8", [(300, 1), (1000, 1)], 16, 2, 512, 16, wl.F16, None, True),
+    ("hd512_fp8", [(700, 1), (3000, 1)], 8, 1, 512, 16, wl.BF16, wl.E4M3, False),
+    ("hd512_fp8_f16q_bt32", [(2100, 1)], 4, 2, 512, 32, wl.F16, wl.E4M3, False),
 ]
 
 
@@ -48,7 +53,7 @@ def test_decode_matches_oracle(oracle_lib, case, mode):
 
 @pytest.mark.parametrize("P", [0, 1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100])
 def test_decode_edge_context_lengths(oracle_lib, P):
-    for dt, kvdt, HD in ((wl.BF16, None, 128), (wl.F16, wl.E4M3, 256)):
+    for dt, kvdt, HD in ((wl.BF16, None, 128), (wl.F16, wl.E4M3, 256), (wl.F16, None, 512), (wl.BF16, wl.E4M3, 512)):
         w = wl.make_pass("edge", 77 + P, [(P, 1), (max(0, P - 1), 1)], 8, 2, HD, 16, dt, kvdt)
         ref, lse_ref = oracle_lib.attention_f64(w)
         O, lse, _, plan, kernel = _run(w)
