@@ -744,6 +744,13 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
                                  c->opt_fuse_combine ? a.jobs_host : nullptr, a.n_jobs, &merged, stream, &c->launches);
     } else {
       c->last_kernel = "flash_umma_pair";
+      // 256-dim verify passes (tiles of 128 / G rows x G heads, one wave of CTAs): split tiles that name their jobs
+      // merge their records inside the kernel - no second launch, and no pass of the combine kernel over 1 KB records.
+      k.jobs = a.jobs;
+      k.fuse = s.HD == 256 && c->opt_fuse_combine && 128 / TR == c->G && a.n_jobs > 0 && a.jobs &&
+               (c->opt_fuse_combine == 2 || int64_t(a.n_tiles) * s.Hkv <= 148) &&
+               esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
+      merged = k.fuse != 0;
       e = esp::launch_flash_umma_pair(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
     }
   } else {

@@ -42,7 +42,10 @@ constexpr int BM = 128;  // (row, head) pairs per CTA
 constexpr int BN = 64;   // keys per block
 // The head dim is a template parameter (128: two CTAs per SM; 256: the whole SM for one CTA). Tiles
 // are stored as HD / 64 chunks of 64 dims, each [rows][128 B] with the 128-byte swizzle.
-constexpr int q_bytes(int hd) { return BM * hd * 2; }
+// 256-dim heads keep the Q tile in tensor memory (A operand of Q.K^T from there): its 64 KB of shared memory
+// go to the K / V rings instead, and Q.K^T reads only the K tile through the shared-memory port.
+constexpr bool q_in_tmem(int hd) { return hd == 256; }
+constexpr int q_bytes(int hd) { return q_in_tmem(hd) ? 0 : BM * hd * 2; }
 constexpr int kv_tile(int hd) { return BN * hd * 2; }
 constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim chunks of the Q tile
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
@@ -57,7 +60,12 @@ constexpr int smem_bytes(int hd, int ks, int vs) { return tiles_bytes(hd, ks, vs
 // (allocations are powers of two: 256 columns for 128-dim heads, 512 for 256-dim heads).
 constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 constexpr uint32_t COL_S = 0, COL_O = 128;
+constexpr uint32_t COL_Q = 384;             // 256-dim heads: the Q tile as 16-bit pairs, 128 columns behind O
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 // The n lowest bits set (n <= 0: none, n >= 64: all).
 __device__ __forceinline__ uint64_t low_bits64(int n) { return n <= 0 ? 0ull : (n >= 64 ? ~0ull : ((1ull << n) - 1ull)); }
@@ -78,7 +86,7 @@ constexpr int kThreads = 7 * 32;
 // memory the dynamic window starts on a 1024-byte boundary (checked at run time), which the
 // swizzled tiles need, and two CTAs of 112.4 KB fit one SM.
 struct Shared {
-  uint64_t k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages], s_full[2], p_full[2], pv_done, o_full;
+  uint64_t k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages], s_full[2], p_full[2], pv_done, o_full, q_full, fix_bar;
   uint32_t tmem_slot;
   int red[4];  // anc_max, seg_min, anc_min, seg_max
   volatile int dead;
@@ -151,6 +159,8 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
     }
     mbar_init(&pv_done, 1);
     mbar_init(&o_full, 1);
+    mbar_init(&sh.q_full, kSoftmaxThreads);
+    mbar_init(&sh.fix_bar, 1);
     mbar_fence_init();
     red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0;
     dead = 0;
@@ -166,15 +176,22 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   }
   int4 d = make_int4(0, 0, 0, 0);
   uint64_t am = 0;
+  constexpr bool QT = q_in_tmem(HD);
+  uint4 qreg[QT ? HD / 8 : 1];  // Q in tensor memory: the row waits in registers until the allocation is known
   if (tid < BM) {
-    // Q row of this thread into the K-major swizzled tile
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(a.Q) + size_t(row) * p.q_ld + size_t(head) * HD);
+    if constexpr (QT) {
 #pragma unroll
-    for (int c = 0; c < NCH; ++c)
+      for (int i = 0; i < HD / 8; ++i) qreg[i] = __ldg(src + i);
+    } else {
+      // Q row of this thread into the K-major swizzled tile
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<uint4*>(q_sm + c * HALF_Q + tid * 128 + ((i ^ (tid & 7)) << 4)) = src[c * 8 + i];
-    fence_proxy_async_smem();
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(q_sm + c * HALF_Q + tid * 128 + ((i ^ (tid & 7)) << 4)) = src[c * 8 + i];
+      fence_proxy_async_smem();
+    }
     if (tile.last) {
       if (use_anc) am = a.anc_mask[row];
       else d = reinterpret_cast<const int4*>(a.desc)[row];
@@ -183,6 +200,26 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if constexpr (QT) {
+    // Lane i of tensor memory holds row i: column c = dims (2c, 2c + 1), the layout an A operand from tensor
+    // memory has (the same as P). The MMA thread learns of it through q_full (128 arrivals).
+    if (tid < BM) {
+      const uint32_t t_q = tmem_slot + (uint32_t(warp * 32) << 16) + COL_Q;
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          w[4 * i] = qreg[8 * c + i].x, w[4 * i + 1] = qreg[8 * c + i].y;
+          w[4 * i + 2] = qreg[8 * c + i].z, w[4 * i + 3] = qreg[8 * c + i].w;
+        }
+        tmem_st32(t_q + 32 * c, w);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&sh.q_full);
+    }
+  }
   if (tile.last && !use_anc) {
     if (tid < BM) {
       int v0 = d.z, v1 = d.x, v2 = d.z, v3 = d.x;
@@ -313,9 +350,13 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         const uint32_t td = tmem + COL_S + stage * BN;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
           const uint64_t db = kd + uint64_t(((ks >> 2) * HALF_KV + (ks & 3) * 32) >> 4);
-          umma_ss(td, da, db, idesc_qk, ks > 0);
+          if constexpr (QT) {
+            umma_ts(td, tmem + COL_Q + ks * 8, db, idesc_qk, ks > 0);
+          } else {
+            const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
+            umma_ss(td, da, db, idesc_qk, ks > 0);
+          }
         }
         umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
         umma_commit(&s_full[stage]);
@@ -323,6 +364,10 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
       // MMAs run in issue order, so Q.K^T of block b + 2 overwrites buffer b & 1 only after
       // P.V of block b has read P from it.
+      if constexpr (QT) {
+        wait_bar(&sh.q_full, 0, kStatusMmaTimeout);  // the Q tile is in tensor memory
+        tc_fence_after_sync();
+      }
       issue_qk(0);
       if (nb > 1) issue_qk(1);
       for (int b = 0; b < nb; ++b) {
@@ -468,8 +513,139 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       if (a.X) gp = a.X + size_t(row) * p.g_ld + size_t(head) * 2 * HD + HD;
     }
     const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    // ---- merge inside the kernel (what attention_combine does, kernels/40_attention.metal:811-864): tiles of 128 / G
+    // rows x G heads, whose 128 records are one contiguous range of `parts`. Every CTA stages its records in the idle
+    // tile memory, writes them with coalesced stores and draws a ticket of its (job, kv head); whoever draws the last
+    // one folds the job's records in record order - each brought back by one bulk copy, summed in tensor memory with
+    // weights e^(m_s - M) - and writes the rows. Nobody waits for anybody; the result does not depend on who came last.
+    // (256-dim heads only: 128-dim verify passes run on flash_umma, which has its own merge.)
+    bool merged_here = false;
+    if (QT && a.fuse != 0 && rec != nullptr && HPC == G) {
+      named_barrier(2, kSoftmaxThreads);
+      if (tid == 0) red[0] = dead;
+      named_barrier(2, kSoftmaxThreads);
+      merged_here = red[0] == 0;  // after a timed-out wait loads may still be in flight into the tile memory: plain route
+    }
+    if (QT && merged_here) {
+      constexpr int RW = HD + 2;                       // floats per record
+      constexpr uint32_t kRecBytes = BM * RW * 4;      // the CTA's records
+      float* stage = reinterpret_cast<float*>(smem);   // every issued load was consumed by an MMA that has completed
+      float* rec0 = a.parts + (size_t(tile.part) * p.Hkv + kvh) * TR * G * RW;
 #pragma unroll 1
-    for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        if (nb > 0) {  // tensor-memory loads are warp-wide: every lane takes part, rows past the tree store zeros
+          tmem_ld32(t_lane + COL_O + 32 * c, o);
+          tmem_wait_ld();
+        }
+        if (nb <= 0 || !row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) *reinterpret_cast<float2*>(stage + tid * RW + 32 * c + i) = make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
+      }
+      *reinterpret_cast<float2*>(stage + tid * RW + HD) = row_ok ? make_float2(m_ref * kLn2, l_run) : make_float2(-INFINITY, 0.0f);
+      named_barrier(2, kSoftmaxThreads);
+      {
+        const float4* src = reinterpret_cast<const float4*>(stage);
+        float4* dst = reinterpret_cast<float4*>(rec0);
+        for (int i = tid; i < BM * RW / 4; i += kSoftmaxThreads) dst[i] = src[i];
+      }
+      const esp_attn_combine job = a.jobs[tile.pad1 - 1];
+      int* ticket = a.counters + (size_t(tile.pad1 - 1) * p.Hkv + kvh) * kFixupPerJob;
+      __threadfence();
+      named_barrier(2, kSoftmaxThreads);
+      if (tid == 0) {
+        const int prev = atomicAdd(ticket, 1);
+        if (prev == job.nparts - 1) *ticket = 0;  // ready for the next pass on this stream
+        red[0] = prev;
+      }
+      named_barrier(2, kSoftmaxThreads);
+      if (red[0] == job.nparts - 1) {
+        __threadfence();
+        // weights: M and L over the job's records of this (row, head)
+        const float* recs = a.parts + (size_t(job.part0) * p.Hkv + kvh) * TR * G * RW;
+        const size_t part_stride = size_t(p.Hkv) * TR * G * RW;
+        float M = -INFINITY, L = 0.0f;
+#pragma unroll 1
+        for (int s2 = 0; s2 < job.nparts; ++s2) M = fmaxf(M, __ldcg(recs + size_t(s2) * part_stride + tid * RW + HD));
+#pragma unroll 1
+        for (int s2 = 0; s2 < job.nparts; ++s2) {
+          const float2 ml = __ldcg(reinterpret_cast<const float2*>(recs + size_t(s2) * part_stride + tid * RW + HD));
+          if (ml.x != -INFINITY) L = fmaf(__expf(ml.x - M), ml.y, L);
+        }
+        bool alive = true;
+#pragma unroll 1
+        for (int s2 = 0; s2 < job.nparts; ++s2) {
+          named_barrier(2, kSoftmaxThreads);  // the record in `stage` has been consumed
+          if (tid == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
+            mbar_arrive_expect_tx(&sh.fix_bar, kRecBytes);
+            bulk_load(stage, recs + size_t(s2) * part_stride, kRecBytes, &sh.fix_bar);
+          }
+          if (!mbar_wait(&sh.fix_bar, s2 & 1)) {
+            dead = 1;
+            atomicExch(a.status, kStatusTmaTimeout);
+          }
+          named_barrier(2, kSoftmaxThreads);
+          if (dead) {  // one verdict for all: the rows are left alone, the status word says why
+            alive = false;
+            break;
+          }
+          const float m_s = stage[tid * RW + HD];
+          const float w = m_s == -INFINITY ? 0.0f : __expf(m_s - M);
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            if (s2 > 0) {
+              tmem_ld32(t_lane + COL_O + 32 * c, o);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = 0;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float2 v = *reinterpret_cast<const float2*>(stage + tid * RW + 32 * c + i);
+              o[i] = __float_as_uint(fmaf(w, v.x, __uint_as_float(o[i])));
+              o[i + 1] = __float_as_uint(fmaf(w, v.y, __uint_as_float(o[i + 1])));
+            }
+            tmem_st32(t_lane + COL_O + 32 * c, o);
+          }
+          tmem_wait_st();
+        }
+        if (alive) {  // (warp-wide tensor-memory loads again: only the stores depend on the row)
+          const float inv_L = L > 0.0f ? 1.0f / L : 0.0f;
+          typename QE::T* orow = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(head) * HD;
+          const float* gate = a.X ? a.X + size_t(row) * p.g_ld + size_t(head) * 2 * HD + HD : nullptr;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_lane + COL_O + 32 * c, o);
+            tmem_wait_ld();
+            if (row_ok) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  v[k] = __uint_as_float(o[i + k]) * inv_L;
+                  if (gate) v[k] *= sigmoid_gate(gate[32 * c + i + k]);
+                }
+                uint4 w4;
+                w4.x = QE::pack2(v[0], v[1]), w4.y = QE::pack2(v[2], v[3]), w4.z = QE::pack2(v[4], v[5]), w4.w = QE::pack2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(orow + 32 * c + i) = w4;
+              }
+            }
+            __syncwarp();
+          }
+          if (row_ok && a.lse) a.lse[size_t(row) * p.H + head] = L > 0.0f ? M + __logf(L) : -INFINITY;
+        }
+      }
+    }
+#pragma unroll 1
+    for (int c = 0; c < (merged_here ? 0 : HD / 32); ++c) {
       uint32_t o[32];
       if (nb > 0) {
         tmem_ld32(t_lane + COL_O + 32 * c, o);
@@ -498,7 +674,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         }
       }
     }
-    if (row_ok) {
+    if (row_ok && !merged_here) {
       if (rec) {
         rec[HD] = m_ref * kLn2;  // -inf stays -inf
         rec[HD + 1] = l_run;
@@ -523,14 +699,14 @@ cudaError_t setup_variant() {
 cudaError_t flash_umma_pair_setup() {
   cudaError_t e = setup_variant<ESP_F16, 128, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 128, 3, 2>();
-  if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 2, 2>();
-  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 2, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 4, 3>();
+  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 4, 3>();
   return e;
 }
 
 // 128-dim heads: rings of 3 K and 2 V tiles, two CTAs per SM. 256-dim heads (the head dim of
-// kernels/40_attention.metal's flash_attention): a 64 KB Q tile, rings of 2 + 2 tiles of 32 KB, 384
-// tensor-memory columns: one CTA per SM.
+// kernels/40_attention.metal's flash_attention): the Q tile in tensor memory (128 columns behind two S buffers
+// and O: all 512), rings of 4 K + 3 V tiles of 32 KB (224 KB: the SM's shared memory), one CTA per SM.
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
                                    const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
@@ -542,9 +718,9 @@ cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_
     if (f16) flash_umma_pair_kernel<ESP_F16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
     else flash_umma_pair_kernel<ESP_BF16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
   } else {
-    constexpr int smem = smem_bytes(256, 2, 2);
-    if (f16) flash_umma_pair_kernel<ESP_F16, 256, 2, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
-    else flash_umma_pair_kernel<ESP_BF16, 256, 2, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    constexpr int smem = smem_bytes(256, 4, 3);
+    if (f16) flash_umma_pair_kernel<ESP_F16, 256, 4, 3><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_pair_kernel<ESP_BF16, 256, 4, 3><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
   }
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;

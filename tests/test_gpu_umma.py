@@ -163,6 +163,43 @@ def test_fused_merge_matches_separate_combine(oracle_lib, gate):
     assert np.abs(outs[1][1] - lse_ref).max() < 2e-3
 
 
+@pytest.mark.parametrize("gate,dt", [(False, wl.BF16), (True, wl.F16)], ids=["bf16", "f16_gate"])
+def test_hd256_verify_merges_inside_the_kernel(oracle_lib, gate, dt):
+    """256-dim verify passes of one wave (flash_umma_pair, tiles of 16 rows x 8 heads): the CTA that draws the last
+    ticket of a (job, kv head) folds the job's records in record order and writes the rows - one launch per pass.
+    Same contract as the two-kernel route: agreement to one output ulp, bit-identical repeats, and the oracle."""
+    w = wl.make_pass("fused256", 78, [(1500, 16), (777, 16), (2100, 9)], 32, 4, 256, 16, dt, mask="tree", gate=gate)
+    ref, lse_ref = oracle_lib.attention_f64(w)
+    outs = {}
+    for fuse in (1, 0):
+        op = host.AttnOp.for_workload(w, 16)
+        try:
+            op.set_option("fuse_combine", fuse)
+            plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 28, 16)
+            assert plan.n_parts > 0 and len(plan.tiles) * w.Hkv <= 148
+            assert max(int(j["nparts"]) for j in plan.jobs) >= 3      # more than a pair: the fold runs over several records
+            dp = op.upload(w, plan)
+            n0 = op.launch_count
+            seen = []
+            for _ in range(3):
+                dp.O.zero_()
+                op.forward(dp)
+                op.check_status()
+                seen.append(dp.O.cpu().numpy().view(np.uint16).copy())
+            assert np.array_equal(seen[0], seen[1]) and np.array_equal(seen[0], seen[2])
+            assert op.last_kernel == "flash_umma_pair"
+            assert op.launch_count - n0 == (3 if fuse else 6)
+            outs[fuse] = (dp.O.cpu().numpy().view(np.uint16).copy(), dp.lse.cpu().numpy().copy())
+        finally:
+            op.close()
+    fa, fb = wl.from_bits16(outs[1][0], w.q_dtype), wl.from_bits16(outs[0][0], w.q_dtype)
+    ulp = 2.0 ** -7 if dt == wl.BF16 else 2.0 ** -10
+    assert np.all(np.abs(fa - fb) <= ulp * np.maximum(np.abs(fa), np.abs(fb)) + 1e-30)
+    assert np.abs(outs[1][1] - outs[0][1]).max() < 1e-5
+    util.check_output(outs[1][0], ref, w)
+    assert np.abs(outs[1][1] - lse_ref).max() < 2e-3
+
+
 @pytest.mark.parametrize("case", ["prefill", "verify", "chunked_gate_f16", "forest"])
 def test_hd256_on_tensor_cores(oracle_lib, case):
     """256-dim heads (the head dim of the reference's flash_attention, kernels/40_attention.metal:156)
