@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS stages
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();  // (256-dim heads are launched with programmatic stream serialization: the launch itself hides behind the previous kernel)
   const esp_attn_params& p = a.p;
   const int G = a.G, TR = a.tile_rows, HPC = BM / TR;
   const esp_attn_tile tile = a.tiles[a.n_tiles - 1 - int(blockIdx.x)];  // long (late) tiles first
@@ -276,6 +277,13 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
     if (tracing && b < a.trace_blocks) a.trace[8 * b + ev] = global_timer_ns();
   };
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks] = global_timer_ns();
+  // Per-CTA stamps (option "trace_ctas"): start, loop done (O complete), records published or rows written, exit.
+  const int cta_lin = blockIdx.y * gridDim.x + blockIdx.x;
+  const bool cta_tracing = a.trace != nullptr && cta_lin < a.trace_ctas;
+  auto cta_stamp = [&](int ev) {
+    if (cta_tracing) a.trace[8 * a.trace_blocks + 2 + 4 * cta_lin + ev] = global_timer_ns();
+  };
+  if (tid == 0) cta_stamp(0);
 
   if (warp == kTmaWarpK || warp == kTmaWarpV) {
     // ================= TMA producers: warp 5 fills the K ring, warp 6 the V ring, each on its own
@@ -503,6 +511,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       wait_bar(&o_full, 0, kStatusMmaTimeout);
       tc_fence_after_sync();
     }
+    if (tid == 0) cta_stamp(1);
     const int hg = head % G;
     float* rec = nullptr;
     typename QE::T* op = nullptr;
@@ -562,11 +571,25 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         red[0] = prev;
       }
       named_barrier(2, kSoftmaxThreads);
+      if (tid == 0) cta_stamp(2);
       if (red[0] == job.nparts - 1) {
         __threadfence();
         // weights: M and L over the job's records of this (row, head)
         const float* recs = a.parts + (size_t(job.part0) * p.Hkv + kvh) * TR * G * RW;
         const size_t part_stride = size_t(p.Hkv) * TR * G * RW;
+        // The sum is built in the tensor-memory columns of S and Q (idle now), so this CTA's own O stays where it is and
+        // is folded from there when its turn comes; only the other records travel (one bulk copy each into `stage`,
+        // the next one requested as soon as the last was consumed).
+        auto acc_col = [&](int c) { return c < 4 ? COL_S + 32u * uint32_t(c) : COL_Q + 32u * uint32_t(c - 4); };
+        const int own = tile.part - job.part0;
+        auto request = [&](int s2) {  // thread 0
+          asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
+          mbar_arrive_expect_tx(&sh.fix_bar, kRecBytes);
+          bulk_load(stage, recs + size_t(s2) * part_stride, kRecBytes, &sh.fix_bar);
+        };
+        auto next_other = [&](int s2) { return s2 == own ? s2 + 1 : s2; };
+        named_barrier(2, kSoftmaxThreads);  // everybody has copied its share of `stage` to the records
+        if (tid == 0 && next_other(0) < job.nparts) request(next_other(0));
         float M = -INFINITY, L = 0.0f;
 #pragma unroll 1
         for (int s2 = 0; s2 < job.nparts; ++s2) M = fmaxf(M, __ldcg(recs + size_t(s2) * part_stride + tid * RW + HD));
@@ -576,44 +599,107 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
           if (ml.x != -INFINITY) L = fmaf(__expf(ml.x - M), ml.y, L);
         }
         bool alive = true;
-#pragma unroll 1
-        for (int s2 = 0; s2 < job.nparts; ++s2) {
-          named_barrier(2, kSoftmaxThreads);  // the record in `stage` has been consumed
-          if (tid == 0) {
-            asm volatile("fence.proxy.async;" ::: "memory");  // the records were written through the generic proxy
-            mbar_arrive_expect_tx(&sh.fix_bar, kRecBytes);
-            bulk_load(stage, recs + size_t(s2) * part_stride, kRecBytes, &sh.fix_bar);
-          }
-          if (!mbar_wait(&sh.fix_bar, s2 & 1)) {
+        uint32_t par = 0;
+        if (job.nparts == 2) {
+          // The common case (a prefix cut in two): one sweep over the dims with both records at hand - this CTA's O in
+          // tensor memory, the other one in `stage` - summed in record order like the general loop below, and written.
+          if (!mbar_wait(&sh.fix_bar, par)) {
             dead = 1;
             atomicExch(a.status, kStatusTmaTimeout);
           }
           named_barrier(2, kSoftmaxThreads);
-          if (dead) {  // one verdict for all: the rows are left alone, the status word says why
-            alive = false;
-            break;
+          if (!dead) {
+            const float m_own = row_ok ? m_ref * kLn2 : -INFINITY, m_oth = stage[tid * RW + HD];
+            const float w_own = m_own == -INFINITY ? 0.0f : __expf(m_own - M), w_oth = m_oth == -INFINITY ? 0.0f : __expf(m_oth - M);
+            const float w0 = own == 0 ? w_own : w_oth, w1 = own == 0 ? w_oth : w_own;
+            const float inv_L = L > 0.0f ? 1.0f / L : 0.0f;
+            typename QE::T* orow = static_cast<typename QE::T*>(a.O) + size_t(row) * p.q_ld + size_t(head) * HD;
+            const float* gate = a.X ? a.X + size_t(row) * p.g_ld + size_t(head) * 2 * HD + HD : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t v[32];
+              if (nb > 0) {
+                tmem_ld32(t_lane + COL_O + 32 * c, v);
+                tmem_wait_ld();
+              }
+              if (row_ok) {
+                float o[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  const float2 x = *reinterpret_cast<const float2*>(stage + tid * RW + 32 * c + i);
+                  const float a0 = own == 0 ? __uint_as_float(v[i]) : x.x, b0 = own == 0 ? x.x : __uint_as_float(v[i]);
+                  const float a1 = own == 0 ? __uint_as_float(v[i + 1]) : x.y, b1 = own == 0 ? x.y : __uint_as_float(v[i + 1]);
+                  float s0 = w0 != 0.0f ? w0 * a0 : 0.0f, s1 = w0 != 0.0f ? w0 * a1 : 0.0f;
+                  if (w1 != 0.0f) s0 = fmaf(w1, b0, s0), s1 = fmaf(w1, b1, s1);
+                  o[i] = s0 * inv_L, o[i + 1] = s1 * inv_L;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  if (gate) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o[i + k] *= sigmoid_gate(gate[32 * c + i + k]);
+                  }
+                  uint4 w4;
+                  w4.x = QE::pack2(o[i], o[i + 1]), w4.y = QE::pack2(o[i + 2], o[i + 3]);
+                  w4.z = QE::pack2(o[i + 4], o[i + 5]), w4.w = QE::pack2(o[i + 6], o[i + 7]);
+                  *reinterpret_cast<uint4*>(orow + 32 * c + i) = w4;
+                }
+              }
+              __syncwarp();
+            }
+            if (row_ok && a.lse) a.lse[size_t(row) * p.H + head] = L > 0.0f ? M + __logf(L) : -INFINITY;
           }
-          const float m_s = stage[tid * RW + HD];
+          alive = false;  // done (or given up): the general loop and its write-out are skipped
+        }
+#pragma unroll 1
+        for (int s2 = 0; alive && s2 < job.nparts; ++s2) {
+          const bool mine = s2 == own;
+          float m_s;
+          if (mine) {
+            m_s = row_ok ? m_ref * kLn2 : -INFINITY;
+          } else {
+            if (!mbar_wait(&sh.fix_bar, par)) {
+              dead = 1;
+              atomicExch(a.status, kStatusTmaTimeout);
+            }
+            par ^= 1;
+            named_barrier(2, kSoftmaxThreads);
+            if (dead) {  // one verdict for all: the rows are left alone, the status word says why
+              alive = false;
+              break;
+            }
+            m_s = stage[tid * RW + HD];
+          }
           const float w = m_s == -INFINITY ? 0.0f : __expf(m_s - M);
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
-            uint32_t o[32];
-            if (s2 > 0) {
-              tmem_ld32(t_lane + COL_O + 32 * c, o);
-              tmem_wait_ld();
-            } else {
+            uint32_t o[32], v[32];
+            if (s2 > 0) tmem_ld32(t_lane + acc_col(c), o);
+            if (mine && nb > 0) tmem_ld32(t_lane + COL_O + 32 * c, v);
+            if (s2 > 0 || (mine && nb > 0)) tmem_wait_ld();
+            if (s2 == 0) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = 0;
             }
+            if (!mine) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float2 v = *reinterpret_cast<const float2*>(stage + tid * RW + 32 * c + i);
-              o[i] = __float_as_uint(fmaf(w, v.x, __uint_as_float(o[i])));
-              o[i + 1] = __float_as_uint(fmaf(w, v.y, __uint_as_float(o[i + 1])));
+              for (int i = 0; i < 32; i += 2) {
+                const float2 x = *reinterpret_cast<const float2*>(stage + tid * RW + 32 * c + i);
+                v[i] = __float_as_uint(x.x), v[i + 1] = __float_as_uint(x.y);
+              }
             }
-            tmem_st32(t_lane + COL_O + 32 * c, o);
+            if (w != 0.0f) {  // (a record that weighs nothing may hold anything)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(fmaf(w, __uint_as_float(v[i]), __uint_as_float(o[i])));
+            }
+            __syncwarp();
+            tmem_st32(t_lane + acc_col(c), o);
           }
           tmem_wait_st();
+          if (!mine) {
+            named_barrier(2, kSoftmaxThreads);  // the record in `stage` has been consumed
+            if (tid == 0 && next_other(s2 + 1) < job.nparts) request(next_other(s2 + 1));
+          }
         }
         if (alive) {  // (warp-wide tensor-memory loads again: only the stores depend on the row)
           const float inv_L = L > 0.0f ? 1.0f / L : 0.0f;
@@ -622,7 +708,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t o[32];
-            tmem_ld32(t_lane + COL_O + 32 * c, o);
+            tmem_ld32(t_lane + acc_col(c), o);
             tmem_wait_ld();
             if (row_ok) {
 #pragma unroll
@@ -686,6 +772,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   tc_fence_before_sync();
   __syncthreads();
   if (tracing && tid == 0) a.trace[8 * a.trace_blocks + 1] = global_timer_ns();
+  if (tid == 0) cta_stamp(3);
   if (warp == kMmaWarp) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -719,8 +806,10 @@ cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_
     else flash_umma_pair_kernel<ESP_BF16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
   } else {
     constexpr int smem = smem_bytes(256, 4, 3);
-    if (f16) flash_umma_pair_kernel<ESP_F16, 256, 4, 3><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
-    else flash_umma_pair_kernel<ESP_BF16, 256, 4, 3><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    cudaError_t e = f16 ? launch_pdl(flash_umma_pair_kernel<ESP_F16, 256, 4, 3>, grid, block, smem, stream, pool_map, kb_map, vb_map, a)
+                        : launch_pdl(flash_umma_pair_kernel<ESP_BF16, 256, 4, 3>, grid, block, smem, stream, pool_map, kb_map, vb_map, a);
+    if (e == cudaSuccess) ++*launches;
+    return e;
   }
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) ++*launches;

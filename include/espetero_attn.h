@@ -648,7 +648,8 @@ int esp_attn_check_status(esp_attn_ctx* ctx, void* stream);
  * With the option "trace_ctas" = N (> 0) the flash_umma kernel also stores four stamps for each of
  * its first N CTAs (linear CTA index c) at [8 * n_blocks + 2 + 4 * c + e]: e = 0 start, 1 first
  * scores seen, 2 last block handed over, 3 exit; the buffer must then hold
- * 8 * n_blocks + 2 + 4 * N values. */
+ * 8 * n_blocks + 2 + 4 * N values. flash_umma_pair stores at the same place: e = 0 start, 1 last block's
+ * O complete, 2 records published (passes that merge inside the kernel), 3 exit. */
 int esp_attn_set_trace(esp_attn_ctx* ctx, void* device_buffer, int32_t n_blocks);
 /* Enqueue a one-thread kernel that stores %globaltimer (the trace's clock) into *device_slot:
  * before and after a pass it brackets the pass in the trace's time base. */
