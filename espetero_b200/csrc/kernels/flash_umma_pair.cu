@@ -2,6 +2,9 @@
 // passes whose keys are mostly the pass's own rows (causal prefill): two CTAs per SM, 64-key
 // blocks, short K/V rings (the keys sit in L2). flash_umma.cu holds the variant that streams a
 // long cached prefix from HBM (one CTA per SM, 128-key blocks, deep rings); both compute the same.
+// 256-dim heads (every pass with them runs here) take the whole SM for one CTA: the Q tile sits in tensor
+// memory as the A operand of Q.K^T, the rings hold 4 K + 3 V tiles, and one-wave verify passes merge their
+// split-K records inside the kernel.
 //
 // Computes what flash_attention computes (kernels/40_attention.metal:156-343 of the
 // reference; generic head dim kernels/80_gemma.metal:157-342): the tile's rows attend to the
