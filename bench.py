@@ -82,7 +82,7 @@ def measured_peaks():
 measured_peaks.sustained_tflops = None
 
 
-def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv: str = "", window: int = 0):
+def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv: str = "", window: int = 0, hd: int = 128):
     from espetero_b200 import shard, workloads as wl
     seed_shift = 1000 * rank
     if name == "c1":
@@ -99,7 +99,7 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
         return wl.config_c2(0xE5B202 + seed_shift, lens=lens[mine])
     if name == "c4":
         return wl.config_c4(0xE5B204 + seed_shift, n_seqs=2 if small else 16, prefix=512 if small else 4096,
-                            kv_dtype=wl.E4M3 if kv == "e4m3" else None)
+                            kv_dtype=wl.E4M3 if kv == "e4m3" else None, hd=hd)
     if name == "c5":
         return wl.config_c5(0xE5B205 + seed_shift, ctx=8192 if small else 131072)
     if name == "c3":
@@ -107,7 +107,7 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
         if window > 0:  # the same prefill through a sliding-window layer (not one of the five configurations)
             return wl.make_window_pass("c3_causal_prefill_window", 0xE5B203 + seed_shift, [(0, rows)] * n, 64, 8, 128, 16, wl.BF16,
                                        window, scale=128 ** -0.5)
-        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=n, rows=rows)
+        return wl.config_c3(0xE5B203 + seed_shift, n_seqs=n, rows=rows, hd=hd)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -162,18 +162,22 @@ class ClockSampler:
         return out
 
 
+CPU_SAMPLE_HD = 128  # --hd: the CPU arm times the same head dim
+
+
 def cpu_sample_workload(name: str):
     """A bounded sample of the workload for the CPU arm (about 10-30 s of host work)."""
     from espetero_b200 import workloads as wl
+    hd = CPU_SAMPLE_HD
     if name == "c2":
         return wl.config_c2(0xE5B202, n_seqs=32, hi=32768), "the full batch: 32 sequences, context ~ U[512, 32768]"
     if name == "c1":
         return wl.config_c1(), "full"
     if name == "c4":
-        return wl.config_c4(), "full"
+        return wl.config_c4(hd=hd), "full"
     if name == "c5":
         return wl.config_c5(), "full"
-    return wl.config_c3(n_seqs=1, rows=4096), "1 sequence x 4096 rows (a 16th of the pass's flops)"
+    return wl.config_c3(n_seqs=1, rows=4096, hd=hd), "1 sequence x 4096 rows (a 16th of the pass's flops)"
 
 
 _CPU_CASES = {}
@@ -708,6 +712,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c4 only: the verify pass over an FP8 E4M3 pool instead of bf16")
     ap.add_argument("--window", type=int, default=0, help="c3 only: the prefill through a sliding-window layer of this many positions")
+    ap.add_argument("--hd", type=int, default=128, choices=[128, 256], help="c3 / c4 only: the pass with 256-dim heads (the reference kernels' own head dim)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
@@ -718,6 +723,10 @@ def main():
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="set a library option (esp_attn_set_option) on the pass's context")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
+    if args.hd != 128 and args.workload not in ("c3", "c4"):
+        raise SystemExit("--hd applies to c3 and c4")
+    global CPU_SAMPLE_HD
+    CPU_SAMPLE_HD = args.hd
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.workload == "prep":
@@ -732,7 +741,7 @@ def main():
     if args.workload == "c5" and (world > 1 or args.ctx > 0):
         r = setup_split_kv(B, args.small)
     else:
-        w = build_workload(args.workload, rank, args.small, world, args.kv, args.window)
+        w = build_workload(args.workload, rank, args.small, world, args.kv, args.window, args.hd)
         sharding = "sequences per rank, no collective" + (
             "; the box's batch spread by total context length (LPT)" if world > 1 and args.workload == "c2" else "")
         r = setup_sequences(B, args.workload, w, "weak", sharding)
@@ -786,7 +795,7 @@ def main():
         value = bytes_all / t_step / 1e9
         achieved = bytes_step / t_attn / 1e9
         flops = attention_flops(w)
-        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv or args.kv or args.window) else None
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if not (args.small or split_kv or args.kv or args.window or args.hd != 128) else None
         tensor = {"tflops": flops / t_attn / 1e12, "peak_tflops": tf_peak, "frac": flops / t_attn / 1e12 / tf_peak,
                   "flops_per_step": flops}
         if measured_peaks.sustained_tflops:  # the denominator for a kernel timed inside a long, power-capped run

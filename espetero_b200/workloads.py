@@ -265,16 +265,23 @@ def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 3
     return w
 
 
-def config_c3(seed: int = 0xE5B203, n_seqs: int = 4, rows: int = 8192) -> Workload:
-    """Causal prefill: 4 sequences of 8192 tokens, no cached prefix, H64/Hkv8/HD128 bf16."""
+def config_c3(seed: int = 0xE5B203, n_seqs: int = 4, rows: int = 8192, hd: int = 128) -> Workload:
+    """Causal prefill: 4 sequences of 8192 tokens, no cached prefix, H64/Hkv8/HD128 bf16. hd = 256: the same pass with
+    the reference kernels' own head dim (H32/Hkv4/HD256: as many flops; not one of the five configurations)."""
+    if hd == 256:
+        return make_pass("c3_causal_prefill_hd256", seed, [(0, rows)] * n_seqs, 32, 4, 256, 16, BF16, spare_blocks=n_seqs * ((rows + 15) // 16))
     return make_pass("c3_causal_prefill", seed, [(0, rows)] * n_seqs, 64, 8, 128, 16, BF16, spare_blocks=n_seqs * ((rows + 15) // 16))
 
 
-def config_c4(seed: int = 0xE5B204, n_seqs: int = 16, prefix: int = 4096, nodes: int = 16, kv_dtype: int | None = None) -> Workload:
+def config_c4(seed: int = 0xE5B204, n_seqs: int = 16, prefix: int = 4096, nodes: int = 16, kv_dtype: int | None = None,
+              hd: int = 128) -> Workload:
     """Forest tree-verify: 16 sequences, 4096-token prefix + 16-node draft tree (random parents). kv_dtype = E4M3: the
-    same pass over an FP8 pool (not one of the five configurations: the tcgen05 kernel's own dequantisation)."""
+    same pass over an FP8 pool (not one of the five configurations: the tcgen05 kernel's own dequantisation).
+    hd = 256: the same pass with the reference kernels' own head dim (twice the key bytes; not one of the five either)."""
     name = "c4_tree_verify" if kv_dtype in (None, BF16) else "c4_tree_verify_e4m3"
-    return make_pass(name, seed, [(prefix, nodes)] * n_seqs, 32, 4, 128, 16, BF16, kv_dtype=kv_dtype, mask="tree")
+    if hd != 128:
+        name += f"_hd{hd}"
+    return make_pass(name, seed, [(prefix, nodes)] * n_seqs, 32, 4, hd, 16, BF16, kv_dtype=kv_dtype, mask="tree")
 
 
 def config_c5(seed: int = 0xE5B205, ctx: int = 131072, lo: int = 0, hi: int | None = None) -> Workload:

@@ -43,3 +43,13 @@ def test_the_fp8_variant_of_the_verify_workload():
     pages = sum((int(t["P"]) + w.bt - 1) // w.bt for t in w.trees)
     assert w16.name == "c4_tree_verify" and w.kv_bytes_read() == w16.kv_bytes_read() // 2 + pages * 2 * w.Hkv * 4   # codes + scales
     assert np.array_equal(w.trees[["P", "M"]], w16.trees[["P", "M"]])
+
+
+def test_hd_flag_builds_the_256_dim_passes():
+    """--hd 256: c3 / c4 with the reference kernels' own head dim; c3 keeps its flops (half the heads), c4 doubles its key bytes."""
+    a, b = bench.build_workload("c3", 0, True), bench.build_workload("c3", 0, True, hd=256)
+    assert (b.HD, b.H, b.Hkv) == (256, 32, 4) and b.name.endswith("_hd256")
+    assert bench.attention_flops(a) == bench.attention_flops(b)
+    a, b = bench.build_workload("c4", 0, True), bench.build_workload("c4", 0, True, hd=256)
+    assert (b.HD, b.H, b.Hkv) == (256, 32, 4) and b.name == "c4_tree_verify_hd256"
+    assert 2 * a.kv_bytes_read() == b.kv_bytes_read()
