@@ -1,6 +1,6 @@
 """Debug and robustness surfaces of the C ABI on the GPU: the NaN / Inf detector over the attention
 output (the reference's finite_check, site "attn_out"), block ids outside the pool caught by the
-general kernel instead of read, 512-dim heads on the general kernel, and the attn_vec option."""
+general kernel instead of read, 512-dim heads, and the attn_vec option."""
 import ctypes as C
 
 import numpy as np
@@ -83,13 +83,15 @@ def test_block_id_outside_the_pool_is_caught_not_read():
         op.close()
 
 
-def test_512_dim_heads_on_the_general_kernel(oracle_lib):
-    """The reference's Gemma global layers (src/model/impl/gemma.h:119-147): HD 512, decode and multi-row."""
-    for trees in ([(700, 1), (33, 1)], [(100, 9)]):
+def test_512_dim_heads(oracle_lib):
+    """The reference's Gemma global layers (src/model/impl/gemma.h:119-147): HD 512. Single-row trees take the decode
+    kernel, multi-row tiles the general one (and the general one is the decode kernel's cross-check)."""
+    for trees, options, want in (([(700, 1), (33, 1)], None, "decode_gqa"), ([(700, 1), (33, 1)], {"attn_gqa": 0}, "flash_general"),
+                                 ([(100, 9)], None, "flash_general")):
         w = wl.make_pass("hd512", 73, trees, 4, 2, 512, 16, wl.BF16, scale=1.0 / np.sqrt(512.0))
         ref, lse_ref = oracle_lib.attention_f64(w)
-        O, lse, _, plan, kernel = host.run_pass(w)
-        assert kernel == "flash_general"
+        O, lse, _, plan, kernel = host.run_pass(w, options=options)
+        assert kernel == want
         util.check_output(O, ref, w, what="hd512")
         assert np.abs(lse - lse_ref).max() < 2e-3
 
