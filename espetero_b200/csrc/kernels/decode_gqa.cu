@@ -663,11 +663,16 @@ using D512H = DecodeCfg<512, ESP_F16, ESP_F16, 3, 2>;
 using D512B = DecodeCfg<512, ESP_BF16, ESP_BF16, 3, 2>;
 using D512EH = DecodeCfg<512, ESP_E4M3, ESP_F16, 3, 2>;
 using D512EB = DecodeCfg<512, ESP_E4M3, ESP_BF16, 3, 2>;
+// 64-dim heads (kernels/90_lfm2.metal:160-161), 16-bit pools: a 16-key block is 4 KB, so the rings are six deep
+// (96 KB per CTA, two CTAs per SM). A row of an E4M3 pool would be half a 128-byte line: the general kernel keeps those.
+using D64H = DecodeCfg<64, ESP_F16, ESP_F16, 4, 6>;
+using D64B = DecodeCfg<64, ESP_BF16, ESP_BF16, 4, 6>;
 
 }  // namespace
 
 bool decode_gqa_supports(int32_t HD, int32_t G, int32_t bt, int32_t q_dtype, int32_t kv_dtype) {
-  if (HD != 128 && HD != 256 && HD != 512) return false;
+  if (HD != 64 && HD != 128 && HD != 256 && HD != 512) return false;
+  if (HD == 64 && kv_dtype == ESP_E4M3) return false;
   if (G < 1 || G > 8) return false;
   if (bt <= 0 || bt % 16 != 0) return false;
   if (q_dtype != ESP_F16 && q_dtype != ESP_BF16) return false;
@@ -687,7 +692,9 @@ cudaError_t decode_gqa_setup() {
   if ((e = setup_one<D512H>()) != cudaSuccess) return e;
   if ((e = setup_one<D512B>()) != cudaSuccess) return e;
   if ((e = setup_one<D512EH>()) != cudaSuccess) return e;
-  return setup_one<D512EB>();
+  if ((e = setup_one<D512EB>()) != cudaSuccess) return e;
+  if ((e = setup_one<D64H>()) != cudaSuccess) return e;
+  return setup_one<D64B>();
 }
 
 cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& m, cudaStream_t stream, uint64_t* launches) {
@@ -702,6 +709,7 @@ cudaError_t launch_decode_gqa(const KernelArgs& a, const CUtensorMap& m, cudaStr
     if (a.HD == 128) e = f16 ? launch_one<D128H>(a, m, stream) : launch_one<D128B>(a, m, stream);
     else if (a.HD == 256) e = f16 ? launch_one<D256H>(a, m, stream) : launch_one<D256B>(a, m, stream);
     else if (a.HD == 512) e = f16 ? launch_one<D512H>(a, m, stream) : launch_one<D512B>(a, m, stream);
+    else if (a.HD == 64) e = f16 ? launch_one<D64H>(a, m, stream) : launch_one<D64B>(a, m, stream);
   }
   if (e == cudaSuccess) ++*launches;
   return e;

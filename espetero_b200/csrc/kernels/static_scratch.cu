@@ -96,7 +96,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   const int G = s.H / s.Hkv;
   const int esz = s.kv_dtype == ESP_E4M3 ? 1 : 2;
   if (!esp::decode_gqa_supports(s.HD, G, s.bt, s.q_dtype, s.kv_dtype) || !(s.scale > 0.0f))
-    return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: shape outside the decode kernel (HD 128/256/512, G <= 8, bt %% 16 == 0)");
+    return esp::fail(ESP_ERR_UNSUPPORTED, "esp_attn_decode_static: shape outside the decode kernel (HD 64/128/256/512, G <= 8, bt %% 16 == 0)");
   if (a.n_tiles <= 0) return ESP_OK;
   if (!a.Q || !a.Kb || !a.Vb || !a.O || !a.kv || !a.blocks || !a.tiles || !a.trees || !a.tiles_host || !a.trees_host || a.n_blocks <= 0)
     return esp::fail(ESP_ERR_INVALID, "esp_attn_decode_static: null input / output / plan pointer");

@@ -1,6 +1,6 @@
 """Debug and robustness surfaces of the C ABI on the GPU: the NaN / Inf detector over the attention
 output (the reference's finite_check, site "attn_out"), block ids outside the pool caught by the
-general kernel instead of read, 512-dim heads, and the attn_vec option."""
+general kernel instead of read, 64- and 512-dim heads, and the attn_vec option."""
 import ctypes as C
 
 import numpy as np
@@ -93,6 +93,19 @@ def test_512_dim_heads(oracle_lib):
         O, lse, _, plan, kernel = host.run_pass(w, options=options)
         assert kernel == want
         util.check_output(O, ref, w, what="hd512")
+        assert np.abs(lse - lse_ref).max() < 2e-3
+
+
+def test_64_dim_heads(oracle_lib):
+    """64-dim heads (kernels/90_lfm2.metal:160-161): single-row trees over 16-bit pools take the decode kernel; E4M3
+    pools (a row is half a 128-byte line) and multi-row tiles the general one."""
+    for trees, kvdt, want in (([(700, 1), (33, 1)], None, "decode_gqa"), ([(700, 1), (33, 1)], wl.E4M3, "flash_general"),
+                              ([(100, 9), (0, 40)], None, "flash_general")):
+        w = wl.make_pass("hd64", 76, trees, 8, 2, 64, 16, wl.BF16, kvdt)
+        ref, lse_ref = oracle_lib.attention_f64(w)
+        O, lse, _, plan, kernel = host.run_pass(w)
+        assert kernel == want
+        util.check_output(O, ref, w, what="hd64")
         assert np.abs(lse - lse_ref).max() < 2e-3
 
 

@@ -30,6 +30,9 @@ CASES = [
     ("hd512_f16_gate_g8", [(300, 1), (1000, 1)], 16, 2, 512, 16, wl.F16, None, True),
     ("hd512_fp8", [(700, 1), (3000, 1)], 8, 1, 512, 16, wl.BF16, wl.E4M3, False),
     ("hd512_fp8_f16q_bt32", [(2100, 1)], 4, 2, 512, 32, wl.F16, wl.E4M3, False),
+    # 64-dim heads (kernels/90_lfm2.metal:160-161), 16-bit pools
+    ("hd64_bf16", [(900, 1), (64, 1), (7000, 1)], 16, 4, 64, 16, wl.BF16, None, False),
+    ("hd64_f16_gate_g8", [(300, 1), (1000, 1)], 16, 2, 64, 16, wl.F16, None, True),
 ]
 
 
@@ -53,7 +56,7 @@ def test_decode_matches_oracle(oracle_lib, case, mode):
 
 @pytest.mark.parametrize("P", [0, 1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100])
 def test_decode_edge_context_lengths(oracle_lib, P):
-    for dt, kvdt, HD in ((wl.BF16, None, 128), (wl.F16, wl.E4M3, 256), (wl.F16, None, 512), (wl.BF16, wl.E4M3, 512)):
+    for dt, kvdt, HD in ((wl.BF16, None, 128), (wl.F16, wl.E4M3, 256), (wl.F16, None, 512), (wl.BF16, wl.E4M3, 512), (wl.BF16, None, 64)):
         w = wl.make_pass("edge", 77 + P, [(P, 1), (max(0, P - 1), 1)], 8, 2, HD, 16, dt, kvdt)
         ref, lse_ref = oracle_lib.attention_f64(w)
         O, lse, _, plan, kernel = _run(w)
