@@ -789,6 +789,8 @@ cudaError_t setup_variant() {
 cudaError_t flash_umma_pair_setup() {
   cudaError_t e = setup_variant<ESP_F16, 128, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 128, 3, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_F16, 64, 3, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 64, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 4, 3>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 4, 3>();
   return e;
@@ -807,6 +809,10 @@ cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_
     constexpr int smem = smem_bytes(128, 3, 2);
     if (f16) flash_umma_pair_kernel<ESP_F16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
     else flash_umma_pair_kernel<ESP_BF16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  } else if (a.HD == 64) {  // kernels/90_lfm2.metal:160-161: one 64-dim chunk per row, 56 KB per CTA
+    constexpr int smem = smem_bytes(64, 3, 2);
+    if (f16) flash_umma_pair_kernel<ESP_F16, 64, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_pair_kernel<ESP_BF16, 64, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
   } else {
     constexpr int smem = smem_bytes(256, 4, 3);
     cudaError_t e = f16 ? launch_pdl(flash_umma_pair_kernel<ESP_F16, 256, 4, 3>, grid, block, smem, stream, pool_map, kb_map, vb_map, a)
