@@ -562,6 +562,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
       {
         const float4* src = reinterpret_cast<const float4*>(stage);
         float4* dst = reinterpret_cast<float4*>(rec0);
+#pragma unroll 8
         for (int i = tid; i < BM * RW / 4; i += kSoftmaxThreads) dst[i] = src[i];
       }
       const esp_attn_combine job = a.jobs[tile.pad1 - 1];
