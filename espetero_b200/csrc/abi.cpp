@@ -625,9 +625,10 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     }
   // E4M3 pools under passes over mostly cached keys (verify, chunked prefill over a long prefix): flash_umma reads the
   // codes itself. Other passes over such pools widen the blocks they touch into the caller's scratch first.
-  const bool fp8_direct = fp8_pool && c->opt_fp8_direct && s.HD == 128 && a.kv != nullptr && a.kv_scales != nullptr && a.n_blocks > 0 &&
-                          a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 && c->opt_umma_kernel <= 1 &&
-                          keys_cached > 2 * keys_batch;
+  // (128-dim heads: flash_umma; 256-dim heads: flash_umma_pair, whatever "umma_kernel" says - they have no other kernel.)
+  const bool fp8_direct = fp8_pool && c->opt_fp8_direct && (s.HD == 128 || s.HD == 256) && a.kv != nullptr && a.kv_scales != nullptr &&
+                          a.n_blocks > 0 && a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 &&
+                          (s.HD == 256 || c->opt_umma_kernel <= 1) && keys_cached > 2 * keys_batch;
   // Reference-shaped sliding-window plans (8-row tiles) are planned again for the tensor cores when the caller mirrors
   // the positions on the host.
   int replan_slot = -1;
@@ -751,7 +752,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
                (c->opt_fuse_combine == 2 || int64_t(a.n_tiles) * s.Hkv <= 148) &&
                esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
       merged = k.fuse != 0;
-      e = esp::launch_flash_umma_pair(k, c->upool_map, c->kb_map, c->vb_map, stream, &c->launches);
+      e = esp::launch_flash_umma_pair(k, fp8_direct ? c->pool_map : c->upool_map, c->kb_map, c->vb_map, fp8_direct, stream, &c->launches);
     }
   } else {
     c->last_kernel = "flash_general";

@@ -4,7 +4,8 @@
 // long cached prefix from HBM (one CTA per SM, 128-key blocks, deep rings); both compute the same.
 // 256-dim heads (every pass with them runs here) take the whole SM for one CTA: the Q tile sits in tensor
 // memory as the A operand of Q.K^T, the rings hold 4 K + 3 V tiles, and one-wave verify passes merge their
-// split-K records inside the kernel.
+// split-K records inside the kernel. Over an E4M3 pool (F8 instantiation) the producers fetch the raw pages,
+// converter warps write the fp16 tiles (code x page scale) and the pass computes in fp16.
 //
 // Computes what flash_attention computes (kernels/40_attention.metal:156-343 of the
 // reference; generic head dim kernels/80_gemma.metal:157-342): the tile's rows attend to the
@@ -79,11 +80,26 @@ struct PageRef {  // where one 16-key page of a key block comes from
   int kind;       // -1: nothing to load, 0: paged pool, 1: Kb / Vb
 };
 
+// E4M3 pools (F8 instantiation, 256-dim heads): the producers bring the pool's raw pages (16 keys x 256 codes of one
+// kv head: the byte map the decode kernel uses) into rings of two 16 KB tiles behind the 16-bit rings; four converter
+// warps turn them into the fp16 tiles the MMAs read (code x page scale), and the pass computes in fp16.
+constexpr int kRawStages = 2;
+constexpr int kCvtWarp0 = 7, kCvtWarps = 4;  // warps 7, 9: K tiles; 8, 10: V tiles
+constexpr int kCvtLanes = kCvtWarps / 2 * 32;
+constexpr int raw_tile(int hd) { return BN * hd; }
+constexpr int smem_bytes_f8(int hd, int ks, int vs) { return tiles_bytes(hd, ks, vs) + 2 * kRawStages * raw_tile(hd) + 384 + 128; }
+struct SharedF8 {
+  uint64_t raw_full[2][kRawStages], raw_empty[2][kRawStages];
+  float scl[2][kRawStages][4];  // scale of each raw page of a slot
+};
+static_assert(sizeof(SharedF8) <= 128, "E4M3 bookkeeping must fit behind the other");
+
 constexpr int kSoftmaxThreads = BM;          // warps 0-3: one thread per (row, head) pair
 constexpr int kMmaWarp = 4;                  // warp 4: MMA issue (one thread), owns tensor memory
 constexpr int kTmaWarpK = 5;                 // warp 5: TMA producer of K tiles (lanes 0-3, one 16-key page each)
 constexpr int kTmaWarpV = 6;                 // warp 6: TMA producer of V tiles
 constexpr int kThreads = 7 * 32;
+constexpr int kThreadsF8 = (kCvtWarp0 + kCvtWarps) * 32;
 
 // Barriers and bookkeeping live behind the tiles in dynamic shared memory: with no static shared
 // memory the dynamic window starts on a 1024-byte boundary (checked at run time), which the
@@ -96,11 +112,14 @@ struct Shared {
 };
 static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
 
-template <int QDT, int HD, int KS, int VS>
-__global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 1024) ? 2 : 1)
+template <int QDT, int HD, int KS, int VS, bool F8 = false>
+__global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes(HD, KS, VS) <= 114 * 1024) ? 2 : 1)
     flash_umma_pair_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
+  constexpr int CDT = F8 ? ESP_F16 : QDT;  // type of the MMA operands (E4M3 pools: fp16, exact for the codes)
+  using PE = Elem16<CDT>;
+  static_assert(!F8 || q_in_tmem(HD), "the E4M3 instantiation is for 256-dim heads");
   extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
@@ -109,7 +128,11 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   constexpr int Q_BYTES = q_bytes(HD), KV_TILE = kv_tile(HD);
   constexpr uint32_t TMEM_COLS = tmem_cols(HD);
   constexpr int TILES_BYTES = tiles_bytes(HD, KS, VS);
-  Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES);
+  constexpr int RAW_TILE = raw_tile(HD);
+  constexpr int RAW_BYTES = F8 ? 2 * kRawStages * RAW_TILE : 0;
+  uint8_t* raw_sm = smem + TILES_BYTES;  // F8: K slots, then V slots
+  Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES + RAW_BYTES);
+  SharedF8& sh8 = *reinterpret_cast<SharedF8*>(smem + TILES_BYTES + RAW_BYTES + 384);
   uint64_t* k_full = sh.k_full;
   uint64_t* k_empty = sh.k_empty;
   uint64_t* v_full = sh.v_full;
@@ -150,12 +173,19 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   // ---- set-up
   if (tid == 0) {
     for (int s = 0; s < KS; ++s) {
-      mbar_init(&k_full[s], 4);
+      mbar_init(&k_full[s], F8 ? kCvtLanes : 4);  // E4M3 pools: the lanes of the tile's converter warps
       mbar_init(&k_empty[s], 1);
     }
     for (int s = 0; s < VS; ++s) {
-      mbar_init(&v_full[s], 4);
+      mbar_init(&v_full[s], F8 ? kCvtLanes : 4);
       mbar_init(&v_empty[s], 1);
+    }
+    if constexpr (F8) {
+      for (int t = 0; t < 2; ++t)
+        for (int s = 0; s < kRawStages; ++s) {
+          mbar_init(&sh8.raw_full[t][s], 4);
+          mbar_init(&sh8.raw_empty[t][s], kCvtLanes);
+        }
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -216,6 +246,13 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         for (int i = 0; i < 8; ++i) {
           w[4 * i] = qreg[8 * c + i].x, w[4 * i + 1] = qreg[8 * c + i].y;
           w[4 * i + 2] = qreg[8 * c + i].z, w[4 * i + 3] = qreg[8 * c + i].w;
+        }
+        if constexpr (F8 && QDT != CDT) {  // a bf16 pass over an E4M3 pool computes in fp16
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float2 f = QE::unpack2(w[i]);
+            w[i] = PE::pack2(f.x, f.y);
+          }
         }
         tmem_st32(t_q + 32 * c, w);
       }
@@ -288,7 +325,118 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   };
   if (tid == 0) cta_stamp(0);
 
-  if (warp == kTmaWarpK || warp == kTmaWarpV) {
+  if (F8 && (warp == kTmaWarpK || warp == kTmaWarpV)) {
+    // ================= E4M3 pools: warp 5 fills the raw K ring, warp 6 the raw V ring; lane w loads the w-th 16-key
+    // page of every cached block (one load: 16 rows x 2 lines of 128 codes) and leaves the page's scale beside it.
+    // Batch blocks (the pass's own rows, in the Q type) are fetched by the converter warps.
+    if (lane < 4 && nbc > 0) {
+      const int is_v = warp == kTmaWarpV ? 1 : 0;
+      uint64_t* full = sh8.raw_full[is_v];
+      uint64_t* empty = sh8.raw_empty[is_v];
+      uint8_t* ring = raw_sm + is_v * kRawStages * RAW_TILE;
+      auto page_of = [&](int b) {
+        const int j = tile.k0 + BN * b + 16 * lane;
+        return (b < nbc && j < tile.k1) ? a.blocks[tree.table + j / p.bt] : -1;
+      };
+      int cur = page_of(0), nxt = page_of(1), nx2 = page_of(2);
+      int stage = 0;
+      uint32_t par = 1;  // the first use of a slot finds it empty
+      for (int b = 0; b < nbc; ++b) {
+        const bool ok = cur >= 0 && cur < a.n_blocks;
+        float sc = 0.0f;  // on its way while the lane waits for the slot
+        if (ok) sc = a.kv_scales[(size_t(cur) * 2 + is_v) * p.Hkv + kvh];
+        wait_bar(&empty[stage], par, kStatusMmaTimeout);
+        if (!ok) {
+          if (cur >= a.n_blocks) atomicExch(a.status, kStatusBadBlock);
+          sh8.scl[is_v][stage][lane] = 0.0f;
+          mbar_arrive(&full[stage]);
+        } else {
+          sh8.scl[is_v][stage][lane] = sc;
+          const int y = (cur * 2 + is_v) * p.bt + (tile.k0 + BN * b + 16 * lane) % p.bt;
+          mbar_arrive_expect_tx(&full[stage], 16 * HD);
+          tma_load_3d(ring + stage * RAW_TILE + lane * 16 * HD, &pool_map, &full[stage], 0, y, kvh * (HD / 128));
+        }
+        if (lane == 0) stamp(b, is_v ? 7 : 6);
+        cur = nxt;
+        nxt = nx2;
+        nx2 = page_of(b + 3);
+        if (++stage == kRawStages) stage = 0, par ^= 1;
+      }
+    }
+  } else if (F8 && warp >= kCvtWarp0) {
+    // ================= E4M3 pools: converter warps. Warps 7, 9 turn raw K tiles into fp16 K tiles, 8, 10 do V (spread
+    // over the schedulers: the conversion instruction runs on the exp2 unit's pipe); a warp takes every second 16-key
+    // page of a block, lane l one of the two 128-code lines (l / 16) of row l % 16: 8 raw chunks of 16 codes become
+    // 16 chunks of 8 halves in two 64-dim chunks of the 16-bit tile.
+    const int is_v = (warp - kCvtWarp0) & 1, wi = (warp - kCvtWarp0) >> 1;
+    uint64_t* full = is_v ? v_full : k_full;
+    uint64_t* empty = is_v ? v_empty : k_empty;
+    uint8_t* ring = is_v ? v_sm : k_sm;
+    const int depth = is_v ? VS : KS;
+    const uint8_t* raw_ring = raw_sm + is_v * kRawStages * RAW_TILE;
+    int rst = 0, cst = 0;
+    uint32_t rpar = 0, cpar = 1;  // the first use of a converted slot finds it empty
+    for (int b = 0; b < nb; ++b) {
+      const bool cached = b < nbc;
+      const int j0 = cached ? tile.k0 + BN * b : batch_j0(b - nbc);
+      const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, k_last + 1 - j0);
+      if (cached) wait_bar(&sh8.raw_full[is_v][rst], rpar, kStatusTmaTimeout);
+      wait_bar(&empty[cst], cpar, kStatusMmaTimeout);
+      uint8_t* dst = ring + cst * KV_TILE;
+#pragma unroll 1
+      for (int pg = wi; pg < 4; pg += kCvtWarps / 2) {
+        const int rl = lane & 15, r = 16 * pg + rl, cg = lane >> 4;
+        uint8_t* drow = dst + (2 * cg) * HALF_KV + r * 128;  // dims 128 cg .. 128 cg + 127 = chunks 2 cg and 2 cg + 1
+        if (r >= n_valid) {
+          // rows past the range: zeros (stale bytes could be NaN patterns, and 0 x NaN must not happen)
+#pragma unroll
+          for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_KV + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+        } else if (cached) {
+          const uint8_t* srow = raw_ring + rst * RAW_TILE + pg * 16 * HD + cg * 2048 + rl * 128;
+          const __half2 sc2 = __float2half2_rn(sh8.scl[is_v][rst][pg]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {  // the line's raw chunk c: codes 16 c .. 16 c + 15
+            const uint4 v = *reinterpret_cast<const uint4*>(srow + ((c ^ (rl & 7)) << 4));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t h[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t lo = e4m3x2_to_f16x2(uint16_t(w[i] & 0xFFFFu)), hi = e4m3x2_to_f16x2(uint16_t(w[i] >> 16));
+              __half2 a2 = __hmul2(*reinterpret_cast<__half2*>(&lo), sc2), b2 = __hmul2(*reinterpret_cast<__half2*>(&hi), sc2);
+              h[2 * i] = *reinterpret_cast<uint32_t*>(&a2), h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            uint8_t* dch = drow + (c >> 2) * HALF_KV;  // 64-dim chunk 2 cg + c / 4; pieces 2 (c % 4) and 2 (c % 4) + 1 of its line
+            *reinterpret_cast<uint4*>(dch + (((2 * (c & 3)) ^ (r & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(dch + (((2 * (c & 3) + 1) ^ (r & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+          }
+        } else {
+          // a batch key: the pass's own row, in the Q type
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const typename QE::T*>(is_v ? a.Vb : a.Kb) +
+                                                            size_t(tree.base + j0 + r) * p.kv_ld + size_t(kvh) * HD) + 16 * cg;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            uint4 v = src[c];
+            if constexpr (QDT != CDT) {
+              uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = QE::unpack2(w[i]);
+                w[i] = PE::pack2(f.x, f.y);
+              }
+            }
+            *reinterpret_cast<uint4*>(drow + (c >> 3) * HALF_KV + (((c & 7) ^ (r & 7)) << 4)) = v;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      if (cached) {
+        mbar_arrive(&sh8.raw_empty[is_v][rst]);
+        if (++rst == kRawStages) rst = 0, rpar ^= 1;
+      }
+      mbar_arrive(&full[cst]);
+      if (++cst == depth) cst = 0, cpar ^= 1;
+    }
+  } else if (!F8 && (warp == kTmaWarpK || warp == kTmaWarpV)) {
     // ================= TMA producers: warp 5 fills the K ring, warp 6 the V ring, each on its own
     // schedule (a K tile is free as soon as its Q.K^T is done, a V tile only after its P.V);
     // lane w loads the w-th 16-key page of every block.
@@ -345,8 +493,8 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer (one thread)
     if (lane == 0 && nb > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc<QDT>(BM, BN, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc<QDT>(BM, HD, 0, 1);
+      constexpr uint32_t idesc_qk = umma_idesc<CDT>(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc<CDT>(BM, HD, 0, 1);
       // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
       // its address field (one thread issues everything, so every integer op here is latency).
       const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
@@ -471,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sl2, neg_m));
         ps0 += p0;
         ps1 += p1;
-        pk[c] = QE::pack2(p0, p1);
+        pk[c] = PE::pack2(p0, p1);
       }
       l_run += ps0 + ps1;
       tmem_st32(t_s, pk);  // over the scores this thread has already read
@@ -492,7 +640,7 @@ __global__ void __launch_bounds__(kThreads, (smem_bytes(HD, KS, VS) <= 114 * 102
         }
       }
       tmem_wait_st();
-      if (n_valid < BN) {
+      if (!F8 && n_valid < BN) {  // (E4M3 pools: the converter warps write zeros there)
         // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
         const int vst = b % VS;
         wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
@@ -794,6 +942,10 @@ cudaError_t flash_umma_pair_setup() {
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 64, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 4, 3>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 4, 3>();
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_F16, 256, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_f8(256, 2, 2));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_BF16, 256, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_f8(256, 2, 2));
   return e;
 }
 
@@ -801,11 +953,19 @@ cudaError_t flash_umma_pair_setup() {
 // kernels/40_attention.metal's flash_attention): the Q tile in tensor memory (128 columns behind two S buffers
 // and O: all 512), rings of 4 K + 3 V tiles of 32 KB (224 KB: the SM's shared memory), one CTA per SM.
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
-                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches) {
+                                   const CUtensorMap& vb_map, bool e4m3_direct, cudaStream_t stream, uint64_t* launches) {
   if (a.n_tiles <= 0) return cudaSuccess;
   const int hpc = BM / a.tile_rows;
   const dim3 grid(unsigned(a.n_tiles), unsigned(a.p.H / hpc)), block(kThreads);
   const bool f16 = a.q_dtype == ESP_F16;
+  if (e4m3_direct) {  // 256-dim heads over an E4M3 pool: pool_map is the pool's byte map (16 rows x 2 lines per page and kv head)
+    if (a.HD != 256 || a.kv_dtype != ESP_E4M3 || a.kv_scales == nullptr) return cudaErrorInvalidValue;
+    constexpr int smem = smem_bytes_f8(256, 2, 2);
+    cudaError_t e = f16 ? launch_pdl(flash_umma_pair_kernel<ESP_F16, 256, 2, 2, true>, grid, dim3(kThreadsF8), smem, stream, pool_map, kb_map, vb_map, a)
+                        : launch_pdl(flash_umma_pair_kernel<ESP_BF16, 256, 2, 2, true>, grid, dim3(kThreadsF8), smem, stream, pool_map, kb_map, vb_map, a);
+    if (e == cudaSuccess) ++*launches;
+    return e;
+  }
   if (a.HD == 128) {
     constexpr int smem = smem_bytes(128, 3, 2);
     if (f16) flash_umma_pair_kernel<ESP_F16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);

@@ -253,8 +253,9 @@ cudaError_t launch_flash_umma(const KernelArgs& a, const CUtensorMap& pool_map, 
                               const esp_attn_tile* tiles_host, const esp_attn_tree* trees_host, int32_t n_trees,
                               const esp_attn_combine* jobs_host, int32_t n_jobs, bool* merged, cudaStream_t stream,
                               uint64_t* launches);
+// e4m3_direct: 256-dim heads over an E4M3 pool read directly; pool_map is then the pool's byte map (the decode kernel's).
 cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_map, const CUtensorMap& kb_map,
-                                   const CUtensorMap& vb_map, cudaStream_t stream, uint64_t* launches);
+                                   const CUtensorMap& vb_map, bool e4m3_direct, cudaStream_t stream, uint64_t* launches);
 cudaError_t flash_umma_pair_setup();
 // flash_umma_duo: one CTA per SM, two 128-lane query tiles (two head groups of one kv head) against the same 128-key
 // blocks; for compute-bound passes (prefill). HD 128 only; a CTA's 2 * (128 / tile_rows) heads must share a kv head.

@@ -155,7 +155,7 @@ int esp_attn_abi_version(void);
  * pass, nor their E4M3 scales - in the reference's layer the kernel before attention is attn_prep, which writes this
  * pass's rows only; the verify kernel then starts fetching cached key blocks while that kernel still drains
  * (programmatic dependent launch); Q, Kb, Vb and the mask records are waited for as ever; default 0), "fp8_direct" (1: multi-row passes over an E4M3 pool
- * with 128-dim heads and mostly cached keys dequantise inside the tcgen05 kernel instead of widening the pool into
+ * with 128- or 256-dim heads and mostly cached keys dequantise inside the tcgen05 kernel instead of widening the pool into
  * dequant_scratch first; default 1),
  * "attn_vec" (the reference's alternative decode schedule, src/model/impl/model.h:590, off there by
  * default and not built here: 0 is accepted, anything else answers ESP_ERR_UNSUPPORTED). */
@@ -245,7 +245,7 @@ typedef struct esp_attn_args {
   int32_t bidi;            /* 1: rows of an image also see the image's later rows (desc.w = end of the row's
                               image, 0 outside images) */
   int32_t reserved2;
-  /* Multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys). 128-dim heads, keys mostly cached
+  /* Multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys). 128- or 256-dim heads, keys mostly cached
    * (more than twice the pass's own rows): the tcgen05 kernel reads the codes itself and needs nothing here
    * (option "fp8_direct", default 1). Other such passes use this optional scratch: with it the pass first widens
    * the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into the scratch and runs the

@@ -241,9 +241,10 @@ def test_hd256_on_tensor_cores(oracle_lib, case):
         assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
 
 
-@pytest.mark.parametrize("case", ["verify128", "verify128_f16", "verify256", "chunked_prefill"])
+@pytest.mark.parametrize("case", ["verify128", "verify128_f16", "verify256", "verify256_bf16", "chunked_prefill"])
 def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
-    """Multi-row passes over an E4M3 pool. 128-dim heads over mostly cached keys: flash_umma reads the codes itself
+    """Multi-row passes over an E4M3 pool. Mostly cached keys: flash_umma (128-dim heads) and flash_umma_pair (256-dim
+    heads) read the codes themselves
     (raw pages by TMA, converter warps, fp16 MMAs; option fp8_direct, default on) - no scratch needed. Otherwise, and
     with fp8_direct = 0: with the caller's scratch the blocks of the pass are widened to the 16-bit type (code * scale)
     and the tcgen05 kernels run on that copy; without scratch the pass runs on the general kernel. All within the E4M3
@@ -254,9 +255,12 @@ def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
         w, tr = wl.make_pass("fp8_v128h", 98, [(2100, 16), (128, 16), (15, 3)], 16, 2, 128, 16, wl.F16, wl.E4M3, mask="tree"), 16
     elif case == "verify256":
         w, tr = wl.make_pass("fp8_v256", 96, [(900, 16), (200, 16)], 32, 8, 256, 16, wl.F16, wl.E4M3, mask="tree"), 32
+    elif case == "verify256_bf16":   # 16 rows x 8 heads, a ragged tree, prefixes that end inside a page and inside a block
+        w, tr = wl.make_pass("fp8_v256b", 99, [(1500, 16), (333, 16), (70, 5)], 32, 4, 256, 16, wl.BF16, wl.E4M3, mask="tree", gate=True), 16
     else:
         w, tr = wl.make_pass("fp8_chunk", 97, [(700, 150)], 8, 2, 128, 16, wl.BF16, wl.E4M3, gate=True), 128
-    direct_ok = w.HD == 128
+    direct_ok = True
+    direct_kernel = "flash_umma" if w.HD == 128 else "flash_umma_pair"
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
     for groups in (8, 592):
         op = host.AttnOp.for_workload(w, tr)
@@ -269,7 +273,7 @@ def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
                 dp.O.zero_()
                 op.forward(dp)
                 op.check_status()
-                assert op.last_kernel == ("flash_umma" if direct else op.last_kernel)
+                assert op.last_kernel == (direct_kernel if direct else op.last_kernel)
                 assert op.last_kernel in ("flash_umma", "flash_umma_pair", "flash_umma_duo")
                 O, lse = dp.O.cpu().numpy().view(np.uint16), dp.lse.cpu().numpy()
                 util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}/direct{direct}")
@@ -281,7 +285,7 @@ def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
                 dp.O.zero_()
                 op.forward(dp, a)
                 op.check_status()
-                assert op.last_kernel == ("flash_umma" if direct else "flash_general")
+                assert op.last_kernel == (direct_kernel if direct else "flash_general")
                 util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what=f"{w.name}/noscratch/direct{direct}")
         finally:
             op.close()
