@@ -629,6 +629,8 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool fp8_direct = fp8_pool && c->opt_fp8_direct && (s.HD == 128 || s.HD == 256) && a.kv != nullptr && a.kv_scales != nullptr &&
                           a.n_blocks > 0 && a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 &&
                           (s.HD == 256 || c->opt_umma_kernel <= 1) && keys_cached > 2 * keys_batch;
+  // A pass that reads no cached key (a prefill from position 0) never touches the pool: its E4M3 type is beside the point.
+  const bool pool_unused = fp8_pool && a.tiles_host != nullptr && a.trees_host != nullptr && keys_cached == 0;
   // Reference-shaped sliding-window plans (8-row tiles) are planned again for the tensor cores when the caller mirrors
   // the positions on the host.
   int replan_slot = -1;
@@ -645,7 +647,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   const bool win_tc = windowed && a.qsa_tlist == nullptr && !fp8_pool && c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 &&
                       esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, s.kv_dtype);
   const bool umma_ok = !decode && (!windowed || win_tc) && c->opt_attn_umma && a.tiles_host != nullptr &&
-                       (!fp8_pool || widen || fp8_direct) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
+                       (!fp8_pool || widen || fp8_direct || pool_unused) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.
   if (umma_ok && TR == 8 && c->opt_replan && !single && full_attention_plan(a, TR)) {
     int rrc = ESP_OK;
@@ -675,6 +677,9 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   esp_attn_args widened = a;  // the pass as the tcgen05 kernels see it when the pool was widened
   if (umma && fp8_direct) {
     widened.kv = nullptr;  // no 16-bit map of the pool: the kernel takes the byte map the decode kernel uses
+  } else if (umma && pool_unused) {
+    widened.kv = nullptr, widened.kv_scales = nullptr;  // no map of the pool at all: no tile has cached keys
+    k.kv = nullptr, k.kv_scales = nullptr, k.kv_dtype = s.q_dtype;
   } else if (umma && fp8_pool) {
     int32_t* identity = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.dequant_scratch) + widened_pool_bytes);
     ProfScope prof(c, stream, "kv_dequant");

@@ -247,7 +247,8 @@ typedef struct esp_attn_args {
   int32_t reserved2;
   /* Multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys). 128- or 256-dim heads, keys mostly cached
    * (more than twice the pass's own rows): the tcgen05 kernel reads the codes itself and needs nothing here
-   * (option "fp8_direct", default 1). Other such passes use this optional scratch: with it the pass first widens
+   * (option "fp8_direct", default 1); a pass without cached keys never reads the pool and needs nothing either.
+   * Other such passes use this optional scratch: with it the pass first widens
    * the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into the scratch and runs the
    * tensor-core kernels on that copy; without it (NULL) they run on the general kernel.
    * Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
