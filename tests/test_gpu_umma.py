@@ -233,8 +233,9 @@ def test_hd256_on_tensor_cores(oracle_lib, case):
     else:
         w, tr = wl.make_pass("hd256_forest", 94, [(70, 40), (0, 33)], 8, 2, 256, 16, wl.BF16, mask="forest"), 32
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
-    for groups in (8, 592):                                  # unsplit, and split with records + merge
-        O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=tr, split=1 << 20, groups=groups)
+    # unsplit; split with records + merge; split with the merge forced into the kernel whatever the number of CTAs
+    for groups, options in ((8, None), (592, None), (592, {"fuse_combine": 2})):
+        O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=tr, split=1 << 20, groups=groups, options=options)
         assert kernel == "flash_umma_pair"
         util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}")
         fin = np.isfinite(lse_ref)
