@@ -36,6 +36,8 @@
 // columns each) so that one CTA's softmax overlaps the other's MMAs.
 // Every wait is bounded: after a timeout the CTA records a status code, stops waiting,
 // finishes its loop, frees its tensor memory and returns.
+#include <climits>
+
 #include "umma.cuh"
 #include "../launch.h"
 
@@ -94,6 +96,17 @@ struct SharedF8 {
 };
 static_assert(sizeof(SharedF8) <= 128, "E4M3 bookkeeping must fit behind the other");
 
+// Sliding-window layers (WIN instantiation, 256-dim heads; kernels/80_gemma.metal:123-142, :250, :284-285): the K producer
+// leaves the positions of a batch block's keys in one of kPosSlots slots for the softmax warps' window masks. With a K
+// ring of 3 the producer is at most 4 blocks ahead of the block the softmax warps work on.
+constexpr int kPosSlots = 8;
+struct SharedWin {
+  uint64_t kpos_full[kPosSlots];
+  int kpos_min[kPosSlots];
+  int kpos[kPosSlots][BN];
+};
+constexpr int smem_bytes_win(int hd, int ks, int vs) { return tiles_bytes(hd, ks, vs) + 384 + 128 + int(sizeof(SharedWin)); }
+
 constexpr int kSoftmaxThreads = BM;          // warps 0-3: one thread per (row, head) pair
 constexpr int kMmaWarp = 4;                  // warp 4: MMA issue (one thread), owns tensor memory
 constexpr int kTmaWarpK = 5;                 // warp 5: TMA producer of K tiles (lanes 0-3, one 16-key page each)
@@ -107,19 +120,20 @@ constexpr int kThreadsF8 = (kCvtWarp0 + kCvtWarps) * 32;
 struct Shared {
   uint64_t k_full[kMaxStages], k_empty[kMaxStages], v_full[kMaxStages], v_empty[kMaxStages], s_full[2], p_full[2], pv_done, o_full, q_full, fix_bar;
   uint32_t tmem_slot;
-  int red[4];  // anc_max, seg_min, anc_min, seg_max
+  int red[6];  // anc_max, seg_min, anc_min, seg_max; sliding-window layers: the latest row position, the furthest image end
   volatile int dead;
 };
 static_assert(sizeof(Shared) <= 384, "bookkeeping must fit behind the tiles");
 
-template <int QDT, int HD, int KS, int VS, bool F8 = false>
-__global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes(HD, KS, VS) <= 114 * 1024) ? 2 : 1)
+template <int QDT, int HD, int KS, int VS, bool F8 = false, bool WIN = false>
+__global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && smem_bytes(HD, KS, VS) <= 114 * 1024) ? 2 : 1)
     flash_umma_pair_kernel(const __grid_constant__ CUtensorMap pool_map, const __grid_constant__ CUtensorMap kb_map,
                       const __grid_constant__ CUtensorMap vb_map, const KernelArgs a) {
   using QE = Elem16<QDT>;
   constexpr int CDT = F8 ? ESP_F16 : QDT;  // type of the MMA operands (E4M3 pools: fp16, exact for the codes)
   using PE = Elem16<CDT>;
   static_assert(!F8 || q_in_tmem(HD), "the E4M3 instantiation is for 256-dim heads");
+  static_assert(!WIN || (q_in_tmem(HD) && !F8 && KS <= 3), "the sliding-window instantiation is for 256-dim heads over 16-bit pools");
   extern __shared__ __align__(1024) uint8_t smem[];
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
@@ -133,6 +147,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
   uint8_t* raw_sm = smem + TILES_BYTES;  // F8: K slots, then V slots
   Shared& sh = *reinterpret_cast<Shared*>(smem + TILES_BYTES + RAW_BYTES);
   SharedF8& sh8 = *reinterpret_cast<SharedF8*>(smem + TILES_BYTES + RAW_BYTES + 384);
+  SharedWin& shw = *reinterpret_cast<SharedWin*>(smem + TILES_BYTES + RAW_BYTES + 384 + 128);  // WIN only
   uint64_t* k_full = sh.k_full;
   uint64_t* k_empty = sh.k_empty;
   uint64_t* v_full = sh.v_full;
@@ -195,8 +210,10 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
     mbar_init(&o_full, 1);
     mbar_init(&sh.q_full, kSoftmaxThreads);
     mbar_init(&sh.fix_bar, 1);
+    if constexpr (WIN)
+      for (int i = 0; i < kPosSlots; ++i) mbar_init(&shw.kpos_full[i], 1);
     mbar_fence_init();
-    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0;
+    red[0] = 0, red[1] = 1 << 30, red[2] = 1 << 30, red[3] = 0, red[4] = INT_MIN, red[5] = 0;
     dead = 0;
   }
   if (warp == kMmaWarp) {
@@ -210,6 +227,11 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
   }
   int4 d = make_int4(0, 0, 0, 0);
   uint64_t am = 0;
+  // Sliding-window layers: a key `window` or more positions behind the query is masked; ring: a sequence's blocks sit
+  // in place (no page table); bidi: image rows see their whole image (desc.w = its end).
+  const bool windowed = WIN && a.window > 0;
+  const bool bidi = WIN && a.bidi != 0 && !use_anc;
+  int qpos = 0;
   constexpr bool QT = q_in_tmem(HD);
   uint4 qreg[QT ? HD / 8 : 1];  // Q in tensor memory: the row waits in registers until the allocation is known
   if (tid < BM) {
@@ -229,6 +251,13 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
     if (tile.last) {
       if (use_anc) am = a.anc_mask[row];
       else d = reinterpret_cast<const int4*>(a.desc)[row];
+    }
+    if (windowed) {  // the row's position; the latest one of the tile bounds every row's window from above
+      qpos = a.pos[4 * size_t(row)];
+      int latest = qpos;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) latest = max(latest, __shfl_xor_sync(0xffffffffu, latest, o));
+      if (lane == 0) atomicMax(&red[4], latest);
     }
   }
   tc_fence_before_sync();
@@ -261,8 +290,8 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
       mbar_arrive(&sh.q_full);
     }
   }
-  if (tile.last && !use_anc) {
-    if (tid < BM) {
+  if ((tile.last && !use_anc) || windowed) {
+    if (tid < BM && tile.last && !use_anc) {
       int v0 = d.z, v1 = d.x, v2 = d.z, v3 = d.x;
 #pragma unroll
       for (int o = 16; o; o >>= 1) {
@@ -277,6 +306,12 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
         atomicMin(&red[2], v2);
         atomicMax(&red[3], v3);
       }
+      if (bidi) {
+        int w_end = d.w;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) w_end = max(w_end, __shfl_xor_sync(0xffffffffu, w_end, o));
+        if (lane == 0) atomicMax(&red[5], w_end);
+      }
     }
     __syncthreads();
   }
@@ -285,24 +320,34 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
   // ---- block list: cached 64-key blocks, then the batch blocks some row of the tile can see
   const int r_first = tile.r0 - tree.base, r_last = r_first + rows_live - 1;
   const int anc_max = red[0], seg_min = red[1], anc_min = red[2], seg_max = red[3];
-  int k_last = -1, a_hi = 0, b_lo = 0, nbb = 0;
+  int k_last = -1, a_lo = 0, a_hi = 0, b_lo = 0, nbb = 0;
+  const int lo_max = windowed ? red[4] - a.window + 1 : INT_MIN;  // the latest row's first visible position
   if (tile.last) {
     if (use_anc) {
       k_last = min(tree.M, 64) - 1;
       a_hi = (k_last + BN) / BN;
       nbb = a_hi;
     } else {
-      k_last = min(tree.M - 1, max(r_last, anc_max - 1));
+      const int reach = max(r_last, red[5] - 1);  // (image rows also see the later rows of their image)
+      k_last = min(tree.M - 1, max(reach, anc_max - 1));
       const int n_all = (k_last + BN) / BN;
       a_hi = min((anc_max + BN - 1) / BN, n_all);                 // blocks below the ancestor range
       b_lo = max(a_hi, seg_min / BN);                             // blocks of the rows' own segments
-      const int b_hi = min(r_last / BN, n_all - 1);
-      nbb = a_hi + max(0, b_hi - b_lo + 1);
+      const int b_hi = min(reach / BN, n_all - 1);
+      if (windowed) {  // batch blocks below the first batch key worth scanning (tile.pad0) are left out
+        const int f = max(0, tile.pad0) / BN;
+        a_lo = min(a_hi, f);
+        b_lo = max(b_lo, f);
+      }
+      nbb = (a_hi - a_lo) + max(0, b_hi - b_lo + 1);
     }
   }
-  const int nbc = (tile.k1 - tile.k0 + BN - 1) / BN;
+  // A sliding-window tile starts at the first cached key one of its rows can see, at any alignment: pages are loaded
+  // from the 16-key boundary below it (the keys in between are behind every row's window).
+  const int k0a = WIN ? (tile.k0 & ~15) : tile.k0;
+  const int nbc = (tile.k1 - k0a + BN - 1) / BN;
   const int nb = nbc + nbb;
-  auto batch_j0 = [&](int i) { return BN * (i < a_hi ? i : b_lo + (i - a_hi)); };
+  auto batch_j0 = [&](int i) { return BN * (i < a_hi - a_lo ? a_lo + i : b_lo + (i - (a_hi - a_lo))); };
   auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
     if (mbar_try_wait(bar, parity)) return;  // the common case costs one shared-memory round trip
     if (dead) return;
@@ -440,7 +485,10 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
     // ================= TMA producers: warp 5 fills the K ring, warp 6 the V ring, each on its own
     // schedule (a K tile is free as soon as its Q.K^T is done, a V tile only after its P.V);
     // lane w loads the w-th 16-key page of every block.
-    if (lane < 4 && nb > 0) {
+    // (Sliding-window layers: the whole K producer warp walks the blocks - after the four page lanes have issued a batch
+    // block, all lanes leave the positions of its 64 keys, and the earliest of them, for the softmax warps.)
+    const bool pos_lanes = WIN && windowed && warp == kTmaWarpK;
+    if ((lane < 4 || pos_lanes) && nb > 0) {
       const bool is_v = warp == kTmaWarpV;
       const int depth = is_v ? VS : KS;
       uint64_t* full = is_v ? v_full : k_full;
@@ -451,11 +499,12 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
       // issued, so the load's latency stays off the critical path.
       auto page_of = [&](int b) {
         PageRef r{0, 0, -1};
-        if (b >= nb) return r;
+        if (b >= nb || lane >= 4) return r;
         if (b < nbc) {
-          const int j = tile.k0 + BN * b + 16 * lane;
+          const int j = k0a + BN * b + 16 * lane;
           if (j < tile.k1) {
-            r.raw = a.blocks[tree.table + j / p.bt];
+            // ring layers (kernels/80_gemma.metal:429) keep a sequence's blocks in place: no page table
+            r.raw = (WIN && a.ring > 0) ? tree.table + (j / p.bt) % a.ring : a.blocks[tree.table + j / p.bt];
             r.off = j % p.bt;
             r.kind = 0;
           }
@@ -472,22 +521,45 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
       int stage = 0;
       uint32_t par = 1;  // the first use of a stage finds it empty
       for (int b = 0; b < nb; ++b) {
-        uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
-        wait_bar(&empty[stage], par, kStatusMmaTimeout);
-        if (cur.kind < 0) {
-          mbar_arrive(&full[stage]);
-        } else {
-          const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
-          const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
-          mbar_arrive_expect_tx(&full[stage], 2048 * NCH);
+        if (lane < 4) {
+          uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
+          wait_bar(&empty[stage], par, kStatusMmaTimeout);
+          if (cur.kind < 0) {
+            mbar_arrive(&full[stage]);
+          } else {
+            const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
+            const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
+            mbar_arrive_expect_tx(&full[stage], 2048 * NCH);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c);
+            for (int c = 0; c < NCH; ++c) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c);
+          }
+          if (lane == 0) stamp(b, is_v ? 7 : 6);
+          cur = nxt;
+          nxt = nx2;
+          nx2 = page_of(b + 3);
+          if (++stage == depth) stage = 0, par ^= 1;
         }
-        if (lane == 0) stamp(b, is_v ? 7 : 6);
-        cur = nxt;
-        nxt = nx2;
-        nx2 = page_of(b + 3);
-        if (++stage == depth) stage = 0, par ^= 1;
+        if constexpr (WIN) {
+          if (pos_lanes) {
+            __syncwarp();  // the page lanes have their slot: the softmax warps are at most KS + 1 blocks behind
+            if (b >= nbc) {
+              const int slot = (b - nbc) % kPosSlots, jb = batch_j0(b - nbc);
+              int lowest = INT_MAX;
+#pragma unroll
+              for (int q = 0; q < BN / 32; ++q) {
+                const int j = jb + lane + 32 * q;
+                const int kp = j <= k_last ? a.pos[4 * size_t(tree.base + j)] : INT_MAX;
+                shw.kpos[slot][lane + 32 * q] = kp;
+                lowest = min(lowest, kp);
+              }
+#pragma unroll
+              for (int o = 16; o; o >>= 1) lowest = min(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
+              if (lane == 0) shw.kpos_min[slot] = lowest;
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&shw.kpos_full[slot]);
+            }
+          }
+        }
       }
     }
   } else if (warp == kMmaWarp) {
@@ -558,12 +630,26 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
     for (int b = 0; b < nb; ++b) {
       const int stage = b & 1;
       const bool cached = b < nbc;
-      const int j0 = cached ? tile.k0 + BN * b : batch_j0(b - nbc);
+      const int j0 = cached ? k0a + BN * b : batch_j0(b - nbc);
       const int n_valid = cached ? min(BN, tile.k1 - j0) : min(BN, k_last + 1 - j0);
       bool need_mask = n_valid < BN;
       if (!cached) {
         if (use_anc) need_mask = true;
         else need_mask = need_mask || !((j0 + BN - 1 < anc_min) || (j0 >= seg_max && j0 + BN - 1 <= r_first));
+      }
+      // Sliding-window layers: a cached key sits at position j, so a block needs the window's lower edge when the latest
+      // row's first visible position lies beyond its first key; a batch key sits at its row's position, which the K
+      // producer left in shared memory with the block's earliest one.
+      bool win_keys = false;
+      const int wslot = (b - nbc) % kPosSlots;
+      if (windowed) {
+        if (cached) {
+          need_mask = need_mask || j0 < lo_max;
+        } else {
+          wait_bar(&shw.kpos_full[wslot], uint32_t((b - nbc) / kPosSlots) & 1u, kStatusTmaTimeout);
+          win_keys = shw.kpos_min[wslot] < lo_max;
+          need_mask = need_mask || win_keys;
+        }
       }
       wait_bar(&s_full[stage], (b >> 1) & 1, kStatusMmaTimeout);
       if (tid == 0) stamp(b, 0);
@@ -580,8 +666,19 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && smem_bytes
         // (a few integer operations), then one select per score
         uint64_t vm = low_bits64(n_valid);
         if (!cached) {
-          if (use_anc) vm &= am >> (j0 & 63);  // one block, j0 = 0
-          else vm &= low_bits64(d.z - j0) | (low_bits64(rr - j0 + 1) & ~low_bits64(d.x - j0));  // j < d.z || d.x <= j <= rr
+          if (use_anc) {
+            vm &= am >> (j0 & 63);  // one block, j0 = 0
+          } else {
+            const int own_end = bidi ? max(rr + 1, d.w) : rr + 1;  // an image row's segment reaches the image's end
+            vm &= low_bits64(d.z - j0) | (low_bits64(own_end - j0) & ~low_bits64(d.x - j0));  // j < d.z || d.x <= j < own_end
+          }
+          if (win_keys) {
+            uint64_t wm = 0;
+            for (int c = 0; c < 64; ++c) wm |= uint64_t(qpos - shw.kpos[wslot][c] < a.window) << c;
+            vm &= wm;
+          }
+        } else if (windowed) {
+          vm &= ~low_bits64(qpos - a.window + 1 - j0);  // j >= the row's first visible position
         }
         const uint32_t vw[2] = {uint32_t(vm), uint32_t(vm >> 32)};
 #pragma unroll
@@ -946,6 +1043,10 @@ cudaError_t flash_umma_pair_setup() {
     e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_F16, 256, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_f8(256, 2, 2));
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_BF16, 256, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_f8(256, 2, 2));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_F16, 256, 3, 3, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_win(256, 3, 3));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(flash_umma_pair_kernel<ESP_BF16, 256, 3, 3, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_win(256, 3, 3));
   return e;
 }
 
@@ -963,6 +1064,14 @@ cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_
     constexpr int smem = smem_bytes_f8(256, 2, 2);
     cudaError_t e = f16 ? launch_pdl(flash_umma_pair_kernel<ESP_F16, 256, 2, 2, true>, grid, dim3(kThreadsF8), smem, stream, pool_map, kb_map, vb_map, a)
                         : launch_pdl(flash_umma_pair_kernel<ESP_BF16, 256, 2, 2, true>, grid, dim3(kThreadsF8), smem, stream, pool_map, kb_map, vb_map, a);
+    if (e == cudaSuccess) ++*launches;
+    return e;
+  }
+  if (a.window > 0 || a.ring > 0 || a.bidi != 0) {  // sliding-window layers: their own instantiation (256-dim heads, 16-bit pools)
+    if (a.HD != 256 || a.kv_dtype == ESP_E4M3) return cudaErrorInvalidValue;
+    constexpr int smem = smem_bytes_win(256, 3, 3);
+    cudaError_t e = f16 ? launch_pdl(flash_umma_pair_kernel<ESP_F16, 256, 3, 3, false, true>, grid, block, smem, stream, pool_map, kb_map, vb_map, a)
+                        : launch_pdl(flash_umma_pair_kernel<ESP_BF16, 256, 3, 3, false, true>, grid, block, smem, stream, pool_map, kb_map, vb_map, a);
     if (e == cudaSuccess) ++*launches;
     return e;
   }

@@ -45,9 +45,9 @@ def test_window_masks_multi_row(oracle_lib, HD, window):
     win = w.extra["window"]
     plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=window, pos=win["pos"])
     assert any(int(t["k0"]) % 16 for t in plan.tiles) or window >= 1000
-    # (128-dim heads: the harness mirrors the positions on the host, so the 8-row plan is planned again for the tcgen05
-    # kernel - test_reference_shaped_window_plans_reach_the_tensor_cores; option replan = 0 keeps the plan as given)
-    _check(oracle_lib, w, plan, "flash_umma_duo" if HD == 128 else "flash_general")
+    # (the harness mirrors the positions on the host, so the 8-row plan is planned again for the tcgen05 kernels -
+    # test_reference_shaped_window_plans_reach_the_tensor_cores; option replan = 0 keeps the plan as given)
+    _check(oracle_lib, w, plan, "flash_umma_duo" if HD == 128 else "flash_umma_pair")
     _check(oracle_lib, w, plan, "flash_general", options={"replan": 0})
     # the mask alone (no help from the plan): full-range tiles give the same answer
     full = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=0, pos=None)
@@ -74,7 +74,8 @@ def test_ring_addressing_and_bidi_images(oracle_lib):
     win = w.extra["window"]
     assert win["bidi"] == 1 and win["ring"] == ring
     plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=96, pos=win["pos"])
-    _check(oracle_lib, w, plan, "flash_general")
+    _check(oracle_lib, w, plan, "flash_umma_pair")                            # planned again with 128-row tiles (positions mirrored)
+    _check(oracle_lib, w, plan, "flash_general", options={"replan": 0})     # as given
 
 
 @pytest.mark.parametrize("kvdt", [None, wl.E4M3], ids=["bf16", "fp8"])
@@ -112,35 +113,37 @@ def test_window_needs_positions():
         op.close()
 
 
+@pytest.mark.parametrize("HD", [128, 256])
 @pytest.mark.parametrize("case", ["prefill", "chunked", "chunked_f16", "ring", "positions_with_gaps", "images", "rows64"])
-def test_window_layers_on_the_tensor_cores(oracle_lib, case):
+def test_window_layers_on_the_tensor_cores(oracle_lib, case, HD):
     """Sliding-window passes planned with tcgen05-sized tiles (esp_attn_plan_window, rows = 128: the generic planner
-    gives its caller's tile height to passes of 256 row groups x kv heads or more) run on flash_umma_duo: window edge
+    gives its caller's tile height to passes of 256 row groups x kv heads or more) run on flash_umma_duo (128-dim heads)
+    or flash_umma_pair (256-dim heads, the sliding layers of kernels/80_gemma.metal): window edge
     inside cached blocks (tiles start at unaligned keys), inside batch blocks (per-key positions), ring addressing,
     batch blocks below the window skipped, image rows that see their whole image. Against the float64 oracle and against the general kernel on an 8-row plan."""
     rows = 128
     if case == "prefill":
-        w = wl.make_window_pass("winp", 31, [(0, 1500), (0, 700)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
+        w = wl.make_window_pass("winp", 31, [(0, 1500), (0, 700)], 8, 2, HD, 16, wl.BF16, 300, scale=HD ** -0.5)
     elif case == "chunked":
-        w = wl.make_window_pass("winc", 32, [(1234, 600), (77, 900)], 8, 2, 128, 16, wl.BF16, 517, scale=128 ** -0.5)
+        w = wl.make_window_pass("winc", 32, [(1234, 600), (77, 900)], 8, 2, HD, 16, wl.BF16, 517, scale=HD ** -0.5)
     elif case == "chunked_f16":
-        w = wl.make_window_pass("wing", 33, [(2000, 1100)], 16, 4, 128, 16, wl.F16, 1024, scale=128 ** -0.5)
+        w = wl.make_window_pass("wing", 33, [(2000, 1100)], 16, 4, HD, 16, wl.F16, 1024, scale=HD ** -0.5)
     elif case == "rows64":
         # 64-row tiles: a query tile is 64 rows x 2 heads, a CTA covers 4 heads of the kv group
-        w = wl.make_window_pass("win64", 37, [(500, 2100)], 8, 2, 128, 16, wl.BF16, 700, scale=128 ** -0.5)
+        w = wl.make_window_pass("win64", 37, [(500, 2100)], 8, 2, HD, 16, wl.BF16, 700, scale=HD ** -0.5)
         rows = 64
     elif case == "images":
         # rows 100..419 and 600..700 are images: their rows see the whole image (blocks beyond the diagonal)
-        w = wl.make_window_pass("wini", 36, [(200, 900), (0, 300)], 8, 2, 128, 16, wl.BF16, 4096, images={0: (100, 420), 1: (130, 290)},
-                                scale=128 ** -0.5)
+        w = wl.make_window_pass("wini", 36, [(200, 900), (0, 300)], 8, 2, HD, 16, wl.BF16, 4096, images={0: (100, 420), 1: (130, 290)},
+                                scale=HD ** -0.5)
     elif case == "ring":
-        w = wl.make_window_pass("winr", 34, [(640, 1300)], 8, 2, 128, 16, wl.BF16, 256, ring=48, scale=128 ** -0.5)
+        w = wl.make_window_pass("winr", 34, [(640, 1300)], 8, 2, HD, 16, wl.BF16, 256, ring=48, scale=HD ** -0.5)
         w.blocks[:] = -1                               # the page table must not be read
     else:
         # positions that are not the row index plus P (the later rows sit 100 positions earlier than their index says):
         # the window mask of a batch block comes from the keys' own positions. (Positions may lag behind P + j, never
         # run ahead of it: the planner's first batch key, gemma.h:89-94, assumes no key is later than that.)
-        w = wl.make_window_pass("winj", 35, [(300, 1400)], 8, 2, 128, 16, wl.BF16, 350, scale=128 ** -0.5)
+        w = wl.make_window_pass("winj", 35, [(300, 1400)], 8, 2, HD, 16, wl.BF16, 350, scale=HD ** -0.5)
         pos = w.extra["window"]["pos"]
         pos[700:, 0:3] -= 100
     win = w.extra["window"]
@@ -148,22 +151,23 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case):
     assert plan.tile_rows == rows
     if case not in ("positions_with_gaps", "images"):
         assert any(int(t["k0"]) % 16 for t in plan.tiles) or any(int(t["pad0"]) > 0 for t in plan.tiles)
-    O = _check(oracle_lib, w, plan, "flash_umma_duo")
+    O = _check(oracle_lib, w, plan, "flash_umma_duo" if HD == 128 else "flash_umma_pair")
     small = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=8, window=win["window"], pos=win["pos"])
     O8 = _check(oracle_lib, w, small, "flash_general", options={"replan": 0})
     a, b = wl.from_bits16(O, w.q_dtype), wl.from_bits16(O8, w.q_dtype)
     assert (np.abs(a - b) <= 2 * util.TOL_16 + 2.0 ** -7 * np.abs(b)).all()   # two roundings to the output type: one ulp
 
 
+@pytest.mark.parametrize("HD", [128, 256])
 @pytest.mark.parametrize("case", ["prefill", "chunked_ring"])
-def test_reference_shaped_window_plans_reach_the_tensor_cores(oracle_lib, case):
+def test_reference_shaped_window_plans_reach_the_tensor_cores(oracle_lib, case, HD):
     """A drop-in caller plans a sliding-window layer the reference's way (g4_plan_tiles, gemma.h:77-116: 8-row tiles) on
     a context with tile_rows 8. With the host mirror of the positions (pos_host) the library plans the pass again with
     128-row tiles and runs the tcgen05 kernel; without it the pass runs on the general kernel as given. Same results."""
     if case == "prefill":
-        w = wl.make_window_pass("win8", 41, [(0, 1500), (0, 900)], 8, 2, 128, 16, wl.BF16, 300, scale=128 ** -0.5)
+        w = wl.make_window_pass("win8", 41, [(0, 1500), (0, 900)], 8, 2, HD, 16, wl.BF16, 300, scale=HD ** -0.5)
     else:
-        w = wl.make_window_pass("win8r", 42, [(640, 1300)], 8, 2, 128, 16, wl.BF16, 256, ring=48, scale=128 ** -0.5)
+        w = wl.make_window_pass("win8r", 42, [(640, 1300)], 8, 2, HD, 16, wl.BF16, 256, ring=48, scale=HD ** -0.5)
         w.blocks[:] = -1
     win = w.extra["window"]
     ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
@@ -176,7 +180,7 @@ def test_reference_shaped_window_plans_reach_the_tensor_cores(oracle_lib, case):
         for _ in range(6):                                   # several passes reuse the staging slots
             op.forward(dp)
         op.check_status()
-        assert op.last_kernel == "flash_umma_duo", "a reference-shaped window plan fell onto the CUDA-core kernel"
+        assert op.last_kernel == ("flash_umma_duo" if HD == 128 else "flash_umma_pair"), "a reference-shaped window plan fell onto the CUDA-core kernel"
         assert torch.equal(dp.tiles, tiles_before)           # the caller's plan is read, never written
         O = dp.O.cpu().numpy().view(np.uint16).copy()
         util.check_output(O, ref, w, ref_abs=ref_abs, what=case)
