@@ -105,8 +105,9 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
     if name == "c3":
         n, rows = (1, 2048) if small else (4, 8192)
         if window > 0:  # the same prefill through a sliding-window layer (not one of the five configurations)
-            return wl.make_window_pass("c3_causal_prefill_window", 0xE5B203 + seed_shift, [(0, rows)] * n, 64, 8, 128, 16, wl.BF16,
-                                       window, scale=128 ** -0.5)
+            H, Hkv = (32, 4) if hd == 256 else (64, 8)
+            return wl.make_window_pass("c3_causal_prefill_window" + ("_hd256" if hd == 256 else ""), 0xE5B203 + seed_shift, [(0, rows)] * n,
+                                       H, Hkv, hd, 16, wl.BF16, window, scale=hd ** -0.5)
         return wl.config_c3(0xE5B203 + seed_shift, n_seqs=n, rows=rows, hd=hd)
     raise SystemExit(f"unknown workload {name}")
 
