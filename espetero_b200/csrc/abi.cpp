@@ -634,10 +634,10 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   // Reference-shaped sliding-window plans (8-row tiles) are planned again for the tensor cores when the caller mirrors
   // the positions on the host.
   int replan_slot = -1;
-  if (windowed && TR == 8 && c->opt_replan && !single && !decode && a.window > 0 && a.pos_host && a.qsa_tlist == nullptr && !fp8_pool &&
+  if (windowed && TR == 8 && c->opt_replan && !single && !decode && a.window > 0 && a.pos_host && a.qsa_tlist == nullptr && (!fp8_pool || pool_unused) &&
       c->opt_attn_umma && a.p.kv_ld % 64 == 0 && a.p.kv_base % 64 == 0 &&
-      ((c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 && esp::flash_umma_duo_supports(s.HD, c->G, 128, s.bt, s.q_dtype, s.kv_dtype)) ||
-       (s.HD == 256 && esp::flash_umma_supports(s.HD, c->G, 128, s.bt, s.q_dtype, s.kv_dtype))) &&
+      ((c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 && esp::flash_umma_duo_supports(s.HD, c->G, 128, s.bt, s.q_dtype, pool_unused ? s.q_dtype : s.kv_dtype)) ||
+       (s.HD == 256 && esp::flash_umma_supports(s.HD, c->G, 128, s.bt, s.q_dtype, pool_unused ? s.q_dtype : s.kv_dtype))) &&
       full_attention_plan(a, TR, true)) {
     int rrc = ESP_OK;
     if (replan_window_pass(c, a, TR, stream, &rrc)) replan_slot = rrc - 1;
@@ -647,9 +647,9 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
   // 16-bit pool have their own instantiation of the two-tile tcgen05 kernel, for plans with tcgen05-sized tiles
   // (esp_attn_plan_window with rows = 128 gives them to passes of 256 row groups or more).
   // 256-dim heads (the sliding layers of kernels/80_gemma.metal) have theirs in flash_umma_pair.
-  const bool win_tc = windowed && a.qsa_tlist == nullptr && !fp8_pool &&
-                      ((c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 && esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, s.kv_dtype)) ||
-                       (s.HD == 256 && esp::flash_umma_supports(s.HD, c->G, TR, s.bt, s.q_dtype, s.kv_dtype)));
+  const bool win_tc = windowed && a.qsa_tlist == nullptr && (!fp8_pool || pool_unused) &&
+                      ((c->opt_umma_kernel != 1 && c->opt_umma_kernel != 2 && esp::flash_umma_duo_supports(s.HD, c->G, TR, s.bt, s.q_dtype, pool_unused ? s.q_dtype : s.kv_dtype)) ||
+                       (s.HD == 256 && esp::flash_umma_supports(s.HD, c->G, TR, s.bt, s.q_dtype, pool_unused ? s.q_dtype : s.kv_dtype)));
   const bool umma_ok = !decode && (!windowed || win_tc) && c->opt_attn_umma && a.tiles_host != nullptr &&
                        (!fp8_pool || widen || fp8_direct || pool_unused) && a.p.kv_ld % 64 == 0 && (fp8_pool || a.p.kv_base % 64 == 0);
   // Reference-shaped plans (8-row tiles) of plain full-attention passes are planned again for the tensor cores.

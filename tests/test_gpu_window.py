@@ -159,6 +159,15 @@ def test_window_layers_on_the_tensor_cores(oracle_lib, case, HD):
 
 
 @pytest.mark.parametrize("HD", [128, 256])
+def test_window_prefill_from_position_zero_ignores_the_pool_type(oracle_lib, HD):
+    """A sliding-window prefill with no cached keys over an E4M3 pool never reads the pool: tcgen05 kernel, no scratch."""
+    w = wl.make_window_pass("winfp8", 51, [(0, 1500), (0, 400)], 8, 2, HD, 16, wl.BF16, 300, scale=HD ** -0.5, kv_dtype=wl.E4M3)
+    win = w.extra["window"]
+    plan = host.plan_window(w.trees, groups=w.Hkv, split=512, rows=128, window=win["window"], pos=win["pos"])
+    _check(oracle_lib, w, plan, "flash_umma_duo" if HD == 128 else "flash_umma_pair")
+
+
+@pytest.mark.parametrize("HD", [128, 256])
 @pytest.mark.parametrize("case", ["prefill", "chunked_ring"])
 def test_reference_shaped_window_plans_reach_the_tensor_cores(oracle_lib, case, HD):
     """A drop-in caller plans a sliding-window layer the reference's way (g4_plan_tiles, gemma.h:77-116: 8-row tiles) on
