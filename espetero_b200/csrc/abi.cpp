@@ -625,10 +625,12 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     }
   // E4M3 pools under passes over mostly cached keys (verify, chunked prefill over a long prefix): flash_umma reads the
   // codes itself. Other passes over such pools widen the blocks they touch into the caller's scratch first.
-  // (128-dim heads: flash_umma; 256-dim heads: flash_umma_pair, whatever "umma_kernel" says - they have no other kernel.)
+  // (128-dim heads: flash_umma; 256-dim heads: flash_umma_pair, whatever "umma_kernel" says - they have no other kernel.
+  // Passes over mostly their own rows take this route only when the caller gave no scratch to widen into: the converter
+  // warps fetch batch keys with plain loads, slower than the 16-bit kernels' TMA but far ahead of the CUDA-core kernel.)
   const bool fp8_direct = fp8_pool && c->opt_fp8_direct && (s.HD == 128 || s.HD == 256) && a.kv != nullptr && a.kv_scales != nullptr &&
                           a.n_blocks > 0 && a.trees_host != nullptr && a.p.kv_ld % 128 == 0 && a.p.kv_base % 16 == 0 &&
-                          (s.HD == 256 || c->opt_umma_kernel <= 1) && keys_cached > 2 * keys_batch;
+                          (s.HD == 256 || c->opt_umma_kernel <= 1) && keys_cached > 0 && (keys_cached > 2 * keys_batch || !widen);
   // A pass that reads no cached key (a prefill from position 0) never touches the pool: its E4M3 type is beside the point.
   const bool pool_unused = fp8_pool && a.tiles_host != nullptr && a.trees_host != nullptr && keys_cached == 0;
   // Reference-shaped sliding-window plans (8-row tiles) are planned again for the tensor cores when the caller mirrors
@@ -738,7 +740,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     // Which of the two tcgen05 kernels: by where the tiles' keys come from (cached keys are streamed
     // from HBM, the pass's own rows sit in L2), unless the "umma_kernel" option forces one.
     // 256-dim heads run on flash_umma_pair only (one CTA per SM there: its tiles take the whole SM).
-    const bool stream_hbm = !win_tc && s.HD == 128 && (c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && keys_cached > 2 * keys_batch));
+    const bool stream_hbm = !win_tc && s.HD == 128 && ((fp8_direct && umma) || c->opt_umma_kernel == 1 || (c->opt_umma_kernel == 0 && keys_cached > 2 * keys_batch));
     if (fp8_direct)
       if (int rc = pool_tensor_map(c, a)) return rc;
     // Passes whose keys are mostly their own rows (prefill) are compute-bound: two query tiles per CTA where the

@@ -248,9 +248,10 @@ typedef struct esp_attn_args {
   /* Multi-row passes over an ESP_E4M3 pool (verify / prefill over FP8 keys). 128- or 256-dim heads, keys mostly cached
    * (more than twice the pass's own rows): the tcgen05 kernel reads the codes itself and needs nothing here
    * (option "fp8_direct", default 1); a pass without cached keys never reads the pool and needs nothing either.
-   * Other such passes use this optional scratch: with it the pass first widens
+   * Other such passes (mostly their own rows behind a short prefix; 64-dim heads) use this optional scratch: with it the pass first widens
    * the blocks of `blocks` to the 16-bit type (code * scale, rounded once) into the scratch and runs the
-   * tensor-core kernels on that copy; without it (NULL) they run on the general kernel.
+   * tensor-core kernels on that copy; without it (NULL) 128- and 256-dim passes still read the codes themselves,
+   * the rest run on the general kernel.
    * Size: esp_attn_dequant_scratch_bytes. Contents need not survive the call. */
   void* dequant_scratch;
   uint64_t dequant_scratch_bytes;

@@ -292,6 +292,34 @@ def test_e4m3_pool_on_tensor_cores(oracle_lib, case):
             op.close()
 
 
+@pytest.mark.parametrize("HD,expect", [(128, "flash_umma"), (256, "flash_umma_pair")])
+def test_chunked_prefill_over_few_e4m3_keys_without_scratch(oracle_lib, HD, expect):
+    """A pass over mostly its own rows behind a short E4M3 prefix: with scratch it widens the prefix and runs the 16-bit
+    kernels; without scratch the tcgen05 kernels read the codes themselves (batch keys through the converter warps)
+    rather than falling onto the CUDA-core kernel."""
+    w = wl.make_pass("fp8_short", 102, [(100, 400), (37, 130)], 8, 2, HD, 16, wl.BF16, wl.E4M3)
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    op = host.AttnOp.for_workload(w, 128)
+    try:
+        plan = host.plan_tiles(w.trees, w.Hkv, capi.ESP_PLAN_B200, 1 << 20, 32, 8, 128)
+        dp = op.upload(w, plan)
+        op.forward(dp)                                       # with the scratch
+        op.check_status()
+        assert op.last_kernel in ("flash_umma_duo", "flash_umma_pair")
+        util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what="fp8_short/widened")
+        a = op.make_args(dp)
+        a.dequant_scratch, a.dequant_scratch_bytes = None, 0
+        dp.O.zero_()
+        n0 = op.launch_count
+        op.forward(dp, a)
+        op.check_status()
+        assert op.last_kernel == expect and op.launch_count - n0 == 1
+        util.check_output(dp.O.cpu().numpy().view(np.uint16), ref, w, ref_abs=ref_abs, what="fp8_short/direct")
+        assert np.abs(dp.lse.cpu().numpy() - lse_ref).max() < 1e-2
+    finally:
+        op.close()
+
+
 @pytest.mark.parametrize("HD,expect", [(128, "flash_umma_duo"), (256, "flash_umma_pair")])
 def test_prefill_from_position_zero_ignores_the_pool_type(oracle_lib, HD, expect):
     """A prefill with no cached keys over an E4M3 pool reads nothing from the pool: it runs on the tcgen05 kernels as over
