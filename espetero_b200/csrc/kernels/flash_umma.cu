@@ -940,7 +940,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, 1)
 }  // namespace
 
 bool flash_umma_supports(int32_t HDim, int32_t G, int32_t tile_rows, int32_t bt, int32_t q_dtype, int32_t kv_dtype) {
-  if ((HDim != 64 && HDim != 128 && HDim != 256) || q_dtype != kv_dtype) return false;  // 64, 256: flash_umma_pair only
+  if ((HDim != 64 && HDim != 128 && HDim != 256 && HDim != 512) || q_dtype != kv_dtype) return false;  // 64, 256, 512: flash_umma_pair only
   if (tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128) return false;
   const int hpc = BM / tile_rows;
   if (hpc > G || G % hpc != 0) return false;

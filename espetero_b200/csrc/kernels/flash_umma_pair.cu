@@ -5,7 +5,8 @@
 // 256-dim heads (every pass with them runs here) take the whole SM for one CTA: the Q tile sits in tensor
 // memory as the A operand of Q.K^T, the rings hold 4 K + 3 V tiles, and one-wave verify passes merge their
 // split-K records inside the kernel. Over an E4M3 pool (F8 instantiation) the producers fetch the raw pages,
-// converter warps write the fp16 tiles (code x page scale) and the pass computes in fp16.
+// converter warps write the fp16 tiles (code x page scale) and the pass computes in fp16. 512-dim heads: a tile runs
+// as two CTAs, each with the whole scores and one 256-dim half of V and O.
 //
 // Computes what flash_attention computes (kernels/40_attention.metal:156-343 of the
 // reference; generic head dim kernels/80_gemma.metal:157-342): the tile's rows attend to the
@@ -53,18 +54,22 @@ constexpr int BN = 64;   // keys per block
 constexpr bool q_in_tmem(int hd) { return hd == 256; }
 constexpr int q_bytes(int hd) { return q_in_tmem(hd) ? 0 : BM * hd * 2; }
 constexpr int kv_tile(int hd) { return BN * hd * 2; }
+// 512-dim heads (the global layers of kernels/80_gemma.metal, gemma.h:119-147): O alone would fill tensor memory, so a
+// CTA computes one 256-dim half of the output (blockIdx.z) from the whole 512-dim scores: Q (128 KB, shared memory),
+// one K tile (64 KB) and one V half tile (32 KB) fill the SM; the two halves of a tile compute the same S, m and l.
+constexpr int v_dims(int hd) { return hd == 512 ? 256 : hd; }
 constexpr int HALF_Q = BM * 128;            // bytes between the 64-dim chunks of the Q tile
 constexpr int HALF_KV = BN * 128;           // ... of a K / V tile
 // Ring depths come in two flavours: (3, 2) lets two CTAs share an SM (passes whose keys sit in L2:
 // prefill), (6, 6) takes the whole SM for one CTA and keeps ~160 KB of K/V in flight (passes
 // that stream their keys from HBM: verify over a long cached prefix).
 constexpr int kMaxStages = 6;
-constexpr int tiles_bytes(int hd, int ks, int vs) { return q_bytes(hd) + (ks + vs) * kv_tile(hd); }
+constexpr int tiles_bytes(int hd, int ks, int vs) { return q_bytes(hd) + ks * kv_tile(hd) + vs * kv_tile(v_dims(hd)); }
 constexpr int smem_bytes(int hd, int ks, int vs) { return tiles_bytes(hd, ks, vs) + 384; }  // + mbarriers; no static shared memory
 // Two S buffers of 64 fp32 columns (P of a block is written over the first 32 columns of its own
 // S buffer as 16-bit pairs, once the thread holds its scores in registers), O: HD fp32 columns
 // (allocations are powers of two: 256 columns for 128-dim heads, 512 for 256-dim heads).
-constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
+constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }  // (512-dim heads: 128 + 256 columns of 512)
 constexpr uint32_t COL_S = 0, COL_O = 128;
 constexpr uint32_t COL_Q = 384;             // 256-dim heads: the Q tile as 16-bit pairs, 128 columns behind O
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
@@ -138,8 +143,13 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
   // full: TMA -> MMA; empty: MMA -> TMA (tcgen05.commit); s_full[i]: S buffer i written;
   // p_full[i]: P in buffer i written (128 arrivals); pv_done: P.V of a block complete;
   // o_full: last P.V done
-  constexpr int NCH = HD / 64;  // 64-dim chunks of a row
-  constexpr int Q_BYTES = q_bytes(HD), KV_TILE = kv_tile(HD);
+  constexpr int HV = v_dims(HD);  // dims of the V tiles and of O in this CTA
+  constexpr int NCH = HD / 64;    // 64-dim chunks of a Q / K row
+  constexpr int NCHV = HV / 64;   // ... of a V row's part
+  constexpr int Q_BYTES = q_bytes(HD), KV_TILE = kv_tile(HD), V_TILE = kv_tile(HV);
+  static_assert(HD != 512 || (!F8 && !WIN), "512-dim heads: the plain instantiation only");
+  const int vh = HD == 512 ? int(blockIdx.z) : 0;  // which half of the output dims
+  const int ho = vh * HV;
   constexpr uint32_t TMEM_COLS = tmem_cols(HD);
   constexpr int TILES_BYTES = tiles_bytes(HD, KS, VS);
   constexpr int RAW_TILE = raw_tile(HD);
@@ -165,7 +175,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
   }
   uint8_t* q_sm = smem;
   uint8_t* k_sm = smem + Q_BYTES;                 // KS stages, KV_TILE apart
-  uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS stages
+  uint8_t* v_sm = smem + Q_BYTES + KS * KV_TILE;  // VS stages, V_TILE apart
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_wait();  // (256-dim heads are launched with programmatic stream serialization: the launch itself hides behind the previous kernel)
@@ -522,16 +532,18 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
       uint32_t par = 1;  // the first use of a stage finds it empty
       for (int b = 0; b < nb; ++b) {
         if (lane < 4) {
-          uint8_t* dst = ring + stage * KV_TILE + lane * 2048;
+          const int nch = is_v ? NCHV : NCH, c0 = is_v ? vh * NCHV : 0;  // (512-dim heads: this CTA's half of the V row)
+          uint8_t* dst = ring + stage * (is_v ? V_TILE : KV_TILE) + lane * 2048;
           wait_bar(&empty[stage], par, kStatusMmaTimeout);
           if (cur.kind < 0) {
             mbar_arrive(&full[stage]);
           } else {
             const int y = cur.kind ? cur.raw : (cur.raw * 2 + (is_v ? 1 : 0)) * p.bt + cur.off;
             const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
-            mbar_arrive_expect_tx(&full[stage], 2048 * NCH);
+            mbar_arrive_expect_tx(&full[stage], 2048 * nch);
 #pragma unroll
-            for (int c = 0; c < NCH; ++c) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c);
+            for (int c = 0; c < NCH; ++c)
+              if (c < nch) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c0 + c);
           }
           if (lane == 0) stamp(b, is_v ? 7 : 6);
           cur = nxt;
@@ -566,7 +578,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
     // ================= MMA issuer (one thread)
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_qk = umma_idesc<CDT>(BM, BN, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc<CDT>(BM, HD, 0, 1);
+      constexpr uint32_t idesc_pv = umma_idesc<CDT>(BM, HV, 0, 1);
       // Descriptors are built once: inside the loop a descriptor is the base plus a constant in
       // its address field (one thread issues everything, so every integer op here is latency).
       const uint64_t q_desc = umma_smem_desc(smem_u32(q_sm), 16, 1024);
@@ -609,7 +621,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
         wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
         stamp(b, 4);
         tc_fence_after_sync();
-        const uint64_t vd = v_desc + uint64_t(vst * (KV_TILE >> 4));
+        const uint64_t vd = v_desc + uint64_t(vst * (V_TILE >> 4));
         const uint32_t tp = tmem + COL_S + stage * BN;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
@@ -727,7 +739,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
       if (b > 0 && __any_sync(0xffffffffu, grow)) {
         // O of this warp's rows *= factor (1 for rows whose reference did not move)
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HV / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(t_lane + COL_O + 32 * c, o);
           tmem_wait_ld();
@@ -741,10 +753,10 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
         // tail block: V rows past the range are stale or foreign bytes; 0 * NaN must not happen
         const int vst = b % VS;
         wait_bar(&v_full[vst], (b / VS) & 1, kStatusTmaTimeout);
-        const int n = (BN - n_valid) * 8 * NCH;  // 16-byte pieces: NCH chunks x 8 per row
+        const int n = (BN - n_valid) * 8 * NCHV;  // 16-byte pieces: NCHV chunks x 8 per row
         for (int i = tid; i < n; i += BM) {
-          const int r = n_valid + i / (8 * NCH), c = i % (8 * NCH);
-          *reinterpret_cast<uint4*>(v_sm + vst * KV_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+          const int r = n_valid + i / (8 * NCHV), c = i % (8 * NCHV);
+          *reinterpret_cast<uint4*>(v_sm + vst * V_TILE + (c >> 3) * HALF_KV + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
       }
@@ -980,7 +992,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
       }
     }
 #pragma unroll 1
-    for (int c = 0; c < (merged_here ? 0 : HD / 32); ++c) {
+    for (int c = 0; c < (merged_here ? 0 : HV / 32); ++c) {
       uint32_t o[32];
       if (nb > 0) {
         tmem_ld32(t_lane + COL_O + 32 * c, o);
@@ -993,7 +1005,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
       if (rec) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
-          *reinterpret_cast<float2*>(rec + 32 * c + i) = make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
+          *reinterpret_cast<float2*>(rec + ho + 32 * c + i) = make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
       } else {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
@@ -1001,15 +1013,15 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             v[k] = __uint_as_float(o[i + k]) * inv_l;
-            if (gp) v[k] *= sigmoid_gate(gp[32 * c + i + k]);
+            if (gp) v[k] *= sigmoid_gate(gp[ho + 32 * c + i + k]);
           }
           uint4 w;
           w.x = QE::pack2(v[0], v[1]), w.y = QE::pack2(v[2], v[3]), w.z = QE::pack2(v[4], v[5]), w.w = QE::pack2(v[6], v[7]);
-          *reinterpret_cast<uint4*>(op + 32 * c + i) = w;
+          *reinterpret_cast<uint4*>(op + ho + 32 * c + i) = w;
         }
       }
     }
-    if (row_ok && !merged_here) {
+    if (row_ok && !merged_here && vh == 0) {  // (512-dim heads: both halves hold the same m and l; the first one writes them)
       if (rec) {
         rec[HD] = m_ref * kLn2;  // -inf stays -inf
         rec[HD + 1] = l_run;
@@ -1037,6 +1049,8 @@ cudaError_t flash_umma_pair_setup() {
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 128, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_F16, 64, 3, 2>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 64, 3, 2>();
+  if (e == cudaSuccess) e = setup_variant<ESP_F16, 512, 1, 1>();
+  if (e == cudaSuccess) e = setup_variant<ESP_BF16, 512, 1, 1>();
   if (e == cudaSuccess) e = setup_variant<ESP_F16, 256, 4, 3>();
   if (e == cudaSuccess) e = setup_variant<ESP_BF16, 256, 4, 3>();
   if (e == cudaSuccess)
@@ -1075,7 +1089,12 @@ cudaError_t launch_flash_umma_pair(const KernelArgs& a, const CUtensorMap& pool_
     if (e == cudaSuccess) ++*launches;
     return e;
   }
-  if (a.HD == 128) {
+  if (a.HD == 512) {  // one CTA per (tile, head group, half of the output dims)
+    const dim3 grid2(grid.x, grid.y, 2);
+    constexpr int smem = smem_bytes(512, 1, 1);
+    if (f16) flash_umma_pair_kernel<ESP_F16, 512, 1, 1><<<grid2, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+    else flash_umma_pair_kernel<ESP_BF16, 512, 1, 1><<<grid2, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
+  } else if (a.HD == 128) {
     constexpr int smem = smem_bytes(128, 3, 2);
     if (f16) flash_umma_pair_kernel<ESP_F16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);
     else flash_umma_pair_kernel<ESP_BF16, 128, 3, 2><<<grid, block, smem, stream>>>(pool_map, kb_map, vb_map, a);

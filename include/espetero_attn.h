@@ -112,7 +112,7 @@ enum {
 typedef struct esp_attn_shape {
   int32_t H;        /* query heads */
   int32_t Hkv;      /* KV heads; G = H / Hkv in {1,2,4,8} for the decode kernel */
-  int32_t HD;       /* head dim: 64 (16-bit pools), 128, 256 or 512 on the decode kernel; 64, 128 or 256 on the tcgen05 kernels; multi-row 512 on the general kernel */
+  int32_t HD;       /* head dim: 64 (16-bit pools), 128, 256 or 512 on the decode kernel; 64, 128, 256 or 512 on the tcgen05 kernels */
   int32_t bt;       /* tokens per KV block (any value; multiples of 16 take the fast paths) */
   int32_t q_dtype;  /* ESP_F16 | ESP_BF16: Q, Kb, Vb, O */
   int32_t kv_dtype; /* pool type: same as q_dtype, or ESP_E4M3 */

@@ -164,6 +164,27 @@ def test_fused_merge_matches_separate_combine(oracle_lib, gate):
 
 
 @pytest.mark.parametrize("case", ["prefill", "verify", "chunked_gate_f16", "forest"])
+def test_hd512_on_tensor_cores(oracle_lib, case):
+    """512-dim heads (the global layers of kernels/80_gemma.metal, src/model/impl/gemma.h:119-147) on the tcgen05 kernel:
+    two CTAs per tile, each with one 256-dim half of the output and the whole 512-dim scores."""
+    if case == "prefill":
+        w, tr = wl.make_pass("hd512_prefill", 111, [(0, 300), (0, 77)], 4, 2, 512, 16, wl.BF16), 128
+    elif case == "verify":
+        w, tr = wl.make_pass("hd512_verify", 112, [(1000, 16), (333, 16), (64, 9)], 16, 2, 512, 16, wl.BF16, mask="tree"), 16
+    elif case == "chunked_gate_f16":
+        w, tr = wl.make_pass("hd512_chunk", 113, [(500, 200)], 4, 2, 512, 16, wl.F16, gate=True), 128
+    else:
+        w, tr = wl.make_pass("hd512_forest", 114, [(70, 40), (0, 33)], 8, 2, 512, 16, wl.BF16, mask="forest"), 32
+    ref, lse_ref, ref_abs = oracle_lib.attention_f64(w, with_abs=True)
+    for groups in (8, 592):                                  # unsplit, and split with records + merge
+        O, lse, parts, plan, kernel = host.run_pass(w, mode=capi.ESP_PLAN_B200, tile_rows=tr, split=1 << 20, groups=groups)
+        assert kernel == "flash_umma_pair"
+        util.check_output(O, ref, w, ref_abs=ref_abs, what=f"{w.name}/g{groups}")
+        fin = np.isfinite(lse_ref)
+        assert np.abs(lse[fin] - lse_ref[fin]).max() < 2e-3
+
+
+@pytest.mark.parametrize("case", ["prefill", "verify", "chunked_gate_f16", "forest"])
 def test_hd64_on_tensor_cores(oracle_lib, case):
     """64-dim heads (kernels/90_lfm2.metal:160-161) on the tcgen05 kernel: one 64-dim chunk per row, two CTAs per SM."""
     if case == "prefill":
