@@ -105,8 +105,8 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
     if name == "c3":
         n, rows = (1, 2048) if small else (4, 8192)
         if window > 0:  # the same prefill through a sliding-window layer (not one of the five configurations)
-            H, Hkv = (32, 4) if hd == 256 else (64, 8)
-            return wl.make_window_pass("c3_causal_prefill_window" + ("_hd256" if hd == 256 else ""), 0xE5B203 + seed_shift, [(0, rows)] * n,
+            H, Hkv = 8192 // hd, 1024 // hd
+            return wl.make_window_pass("c3_causal_prefill_window" + (f"_hd{hd}" if hd != 128 else ""), 0xE5B203 + seed_shift, [(0, rows)] * n,
                                        H, Hkv, hd, 16, wl.BF16, window, scale=hd ** -0.5)
         return wl.config_c3(0xE5B203 + seed_shift, n_seqs=n, rows=rows, hd=hd)
     raise SystemExit(f"unknown workload {name}")
@@ -713,7 +713,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c4 only: the verify pass over an FP8 E4M3 pool instead of bf16")
     ap.add_argument("--window", type=int, default=0, help="c3 only: the prefill through a sliding-window layer of this many positions")
-    ap.add_argument("--hd", type=int, default=128, choices=[128, 256], help="c3 / c4 only: the pass with 256-dim heads (the reference kernels' own head dim)")
+    ap.add_argument("--hd", type=int, default=128, choices=[64, 128, 256, 512], help="c3 / c4 only: the pass with another head dim of the reference's kernels (256: flash_attention's own)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")

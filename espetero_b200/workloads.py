@@ -266,10 +266,11 @@ def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 3
 
 
 def config_c3(seed: int = 0xE5B203, n_seqs: int = 4, rows: int = 8192, hd: int = 128) -> Workload:
-    """Causal prefill: 4 sequences of 8192 tokens, no cached prefix, H64/Hkv8/HD128 bf16. hd = 256: the same pass with
-    the reference kernels' own head dim (H32/Hkv4/HD256: as many flops; not one of the five configurations)."""
-    if hd == 256:
-        return make_pass("c3_causal_prefill_hd256", seed, [(0, rows)] * n_seqs, 32, 4, 256, 16, BF16, spare_blocks=n_seqs * ((rows + 15) // 16))
+    """Causal prefill: 4 sequences of 8192 tokens, no cached prefix, H64/Hkv8/HD128 bf16. hd = 64 / 256 / 512: the
+    same pass with another head dim of the reference's kernels (8192 / hd heads: as many flops; not one of the five configurations)."""
+    if hd != 128:  # the same Q width and flops: 8192 / hd heads
+        return make_pass(f"c3_causal_prefill_hd{hd}", seed, [(0, rows)] * n_seqs, 8192 // hd, 1024 // hd, hd, 16, BF16,
+                         spare_blocks=n_seqs * ((rows + 15) // 16))
     return make_pass("c3_causal_prefill", seed, [(0, rows)] * n_seqs, 64, 8, 128, 16, BF16, spare_blocks=n_seqs * ((rows + 15) // 16))
 
 
