@@ -90,7 +90,7 @@ def build_workload(name: str, rank: int, small: bool = False, world: int = 1, kv
     if name == "c2":
         n, hi = (4, 4096) if small else (32, 32768)
         if world == 1:
-            return wl.config_c2(0xE5B202, n_seqs=n, hi=hi)
+            return wl.config_c2(0xE5B202, n_seqs=n, hi=hi, hd=hd, kv_dtype=wl.E4M3 if kv == "e4m3" else None)
         # The box serves world x 32 sequences: every rank's draw of the configuration, spread over
         # the GPUs by total context length (longest first onto the least loaded GPU), as a
         # scheduler that batches by KV footprint would. Whole sequences move; nothing is exchanged.
@@ -171,7 +171,7 @@ def cpu_sample_workload(name: str):
     from espetero_b200 import workloads as wl
     hd = CPU_SAMPLE_HD
     if name == "c2":
-        return wl.config_c2(0xE5B202, n_seqs=32, hi=32768), "the full batch: 32 sequences, context ~ U[512, 32768]"
+        return wl.config_c2(0xE5B202, n_seqs=32, hi=32768, hd=hd), "the full batch: 32 sequences, context ~ U[512, 32768]"
     if name == "c1":
         return wl.config_c1(), "full"
     if name == "c4":
@@ -711,9 +711,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="--workload prep: rows (0: the layout's default)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
-    ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c4 only: the verify pass over an FP8 E4M3 pool instead of bf16")
+    ap.add_argument("--kv", default="", choices=["", "e4m3"], help="c2 / c4 only: the pass over an FP8 E4M3 pool instead of bf16")
     ap.add_argument("--window", type=int, default=0, help="c3 only: the prefill through a sliding-window layer of this many positions")
-    ap.add_argument("--hd", type=int, default=128, choices=[64, 128, 256, 512], help="c3 / c4 only: the pass with another head dim of the reference's kernels (256: flash_attention's own)")
+    ap.add_argument("--hd", type=int, default=128, choices=[64, 128, 256, 512], help="c2 / c3 / c4 only: the pass with another head dim of the reference's kernels (256: flash_attention's own)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the float64 oracle after the timed region")
     ap.add_argument("--no-strong", action="store_true", help="at N > 1: skip the two strong-scaling legs (c2_strong, split_kv)")
@@ -724,8 +724,8 @@ def main():
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="set a library option (esp_attn_set_option) on the pass's context")
     ap.add_argument("--groups", type=int, default=0, help="CTA target of the planner (default 8 waves of 2 CTAs per SM)")
     args = ap.parse_args()
-    if args.hd != 128 and args.workload not in ("c3", "c4"):
-        raise SystemExit("--hd applies to c3 and c4")
+    if args.hd != 128 and args.workload not in ("c2", "c3", "c4"):
+        raise SystemExit("--hd applies to c2 (one GPU), c3 and c4")
     global CPU_SAMPLE_HD
     CPU_SAMPLE_HD = args.hd
     if args.impl == "reference":

@@ -256,11 +256,14 @@ def c2_context_lengths(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi
     return np.random.default_rng(seed ^ 0x5EED).integers(lo, hi + 1, size=n_seqs)
 
 
-def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 32768, lens=None) -> Workload:
+def config_c2(seed: int = 0xE5B202, n_seqs: int = 32, lo: int = 512, hi: int = 32768, lens=None, hd: int = 128,
+              kv_dtype: int | None = None) -> Workload:
     """Batched paged decode: 32 sequences, context ~ U[512, 32768], H32/Hkv4/HD128 bf16, 16-token pages.
-    `lens` overrides the drawn lengths (a rank's share of a batch partitioned over several GPUs)."""
+    `lens` overrides the drawn lengths (a rank's share of a batch partitioned over several GPUs). hd / kv_dtype: the same
+    batch with another head dim of the reference's kernels or over an E4M3 pool (not one of the five configurations)."""
     lens = c2_context_lengths(seed, n_seqs, lo, hi) if lens is None else np.asarray(lens)
-    w = make_pass("c2_batched_decode", seed, [(int(p), 1) for p in lens], 32, 4, 128, 16, BF16)
+    name = "c2_batched_decode" + (f"_hd{hd}" if hd != 128 else "") + ("_e4m3" if kv_dtype == E4M3 else "")
+    w = make_pass(name, seed, [(int(p), 1) for p in lens], 32, 4, hd, 16, BF16, kv_dtype=kv_dtype)
     w.extra["ctx_lens"] = lens
     return w
 
