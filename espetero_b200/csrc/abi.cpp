@@ -710,7 +710,7 @@ static int forward_impl(esp_attn_ctx* c, void* stream_v, const esp_attn_args* ap
     k.jobs = a.jobs;
     // (option 2 merges in the kernel whatever the size; the records of a kv head's G heads must be a
     // multiple of 16 bytes for the bulk copies: G even)
-    k.fuse = c->opt_fuse_combine && (c->opt_fuse_combine == 2 || esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs)) && c->G % 2 == 0 &&
+    k.fuse = c->opt_fuse_combine && (c->opt_fuse_combine == 2 || esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs, s.HD == 64 || (fp8_pool && s.HD == 128))) && c->G % 2 == 0 &&
              a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
     merged = k.fuse != 0;
     if (xch) {

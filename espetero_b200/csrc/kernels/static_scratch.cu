@@ -174,7 +174,7 @@ extern "C" int esp_attn_decode_static(const esp_attn_shape* shape, void* stream_
   // Same choice as esp_attn_forward (identical bits): plans whose split tiles name their jobs are
   // merged by the attention kernel itself, others by the combine kernel.
   k.counters = slot.counters, k.jobs = a.jobs;
-  k.fuse = esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs) && G % 2 == 0 && a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
+  k.fuse = esp::decode_fuse_small(a.n_tiles, s.Hkv, a.n_jobs, s.HD == 64 || (s.kv_dtype == ESP_E4M3 && s.HD == 128)) && G % 2 == 0 && a.n_jobs > 0 && a.jobs && esp::plan_fusable(a.tiles_host, a.n_tiles, a.jobs_host, a.n_jobs, s.Hkv);
   if ((e = esp::launch_decode_gqa(k, map, stream, &launches)) != cudaSuccess) return cuda_fail(e, "decode_gqa");
   if (a.n_jobs > 0 && !k.fuse) {
     esp::CombineArgs c{};

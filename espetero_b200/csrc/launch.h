@@ -163,8 +163,10 @@ inline bool plan_fusable(const esp_attn_tile* tiles, int32_t n_tiles, const esp_
 // stream (measured on the batched decode: -1.8 us per step). A pass with a few long jobs that all end
 // together (one 131072-token sequence: 8 merges of 37 records) is faster with the combine kernel's
 // parallelism (+7 us when merged in the kernel).
-inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv, int32_t n_jobs) {
-  return int64_t(n_tiles) * Hkv <= 148 || int64_t(n_jobs) * Hkv >= 32;
+// (Instances with 4 KB key blocks - 64-dim heads, 128-dim E4M3 pools: four CTAs per SM - keep the combine kernel for
+// the many-job case too: 97.2 against 100.7 us and 114.3 against 119.2 us on the 32-sequence batch.)
+inline bool decode_fuse_small(int32_t n_tiles, int32_t Hkv, int32_t n_jobs, bool light_blocks = false) {
+  return int64_t(n_tiles) * Hkv <= 148 || (!light_blocks && int64_t(n_jobs) * Hkv >= 32);
 }
 
 // Record slices per head for the combine kernel: a slice folds up to eight records per round trip
