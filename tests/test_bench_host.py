@@ -53,3 +53,14 @@ def test_hd_flag_builds_the_256_dim_passes():
     a, b = bench.build_workload("c4", 0, True), bench.build_workload("c4", 0, True, hd=256)
     assert (b.HD, b.H, b.Hkv) == (256, 32, 4) and b.name == "c4_tree_verify_hd256"
     assert 2 * a.kv_bytes_read() == b.kv_bytes_read()
+
+
+def test_decode_batch_variants():
+    """--hd / --kv on the batched decode: the same sequences, another head dim or an E4M3 pool; bytes follow."""
+    a = bench.build_workload("c2", 0, True)
+    b = bench.build_workload("c2", 0, True, hd=512)
+    c = bench.build_workload("c2", 0, True, kv="e4m3", hd=256)
+    assert b.name == "c2_batched_decode_hd512" and c.name == "c2_batched_decode_hd256_e4m3"
+    assert [int(t["P"]) for t in a.trees] == [int(t["P"]) for t in b.trees] == [int(t["P"]) for t in c.trees]
+    assert b.kv_bytes_read() == 4 * a.kv_bytes_read()
+    assert c.kv_dtype == wl.E4M3 and a.kv_bytes_read() <= c.kv_bytes_read() < 1.1 * a.kv_bytes_read()   # half the bytes per element, twice the dims, + scales
