@@ -147,7 +147,11 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
   constexpr int NCH = HD / 64;    // 64-dim chunks of a Q / K row
   constexpr int NCHV = HV / 64;   // ... of a V row's part
   constexpr int Q_BYTES = q_bytes(HD), KV_TILE = kv_tile(HD), V_TILE = kv_tile(HV);
-  static_assert(HD != 512 || (!F8 && !WIN), "512-dim heads: the plain instantiation only");
+  static_assert(HD != 512 || (!F8 && !WIN && KS == 1), "512-dim heads: the plain instantiation only, one K tile");
+  // 512-dim heads have room for one K tile only, so the next block's K can be requested only when Q.K^T of this one
+  // has read it. The tile is handed over in four parts of two 64-dim chunks, each with its own barriers: a part is
+  // requested again as soon as its eight MMAs are done, and the next Q.K^T starts on the parts that have arrived.
+  constexpr int KSUB = HD == 512 ? 4 : 1;
   const int vh = HD == 512 ? int(blockIdx.z) : 0;  // which half of the output dims
   const int ho = vh * HV;
   constexpr uint32_t TMEM_COLS = tmem_cols(HD);
@@ -197,7 +201,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
 
   // ---- set-up
   if (tid == 0) {
-    for (int s = 0; s < KS; ++s) {
+    for (int s = 0; s < KS * KSUB; ++s) {
       mbar_init(&k_full[s], F8 ? kCvtLanes : 4);  // E4M3 pools: the lanes of the tile's converter warps
       mbar_init(&k_empty[s], 1);
     }
@@ -534,6 +538,23 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
         if (lane < 4) {
           const int nch = is_v ? NCHV : NCH, c0 = is_v ? vh * NCHV : 0;  // (512-dim heads: this CTA's half of the V row)
           uint8_t* dst = ring + stage * (is_v ? V_TILE : KV_TILE) + lane * 2048;
+          if (KSUB > 1 && !is_v) {
+            // the one K tile of a 512-dim pass, part by part (barriers 0 .. KSUB-1, the same phase for a block)
+            constexpr int CPP = NCH / KSUB;  // chunks per part
+#pragma unroll
+            for (int u = 0; u < KSUB; ++u) {
+              wait_bar(&empty[u], par, kStatusMmaTimeout);
+              if (cur.kind < 0) {
+                mbar_arrive(&full[u]);
+              } else {
+                const int y = cur.kind ? cur.raw : (cur.raw * 2) * p.bt + cur.off;
+                const CUtensorMap* m = cur.kind ? batch_map : &pool_map;
+                mbar_arrive_expect_tx(&full[u], 2048 * CPP);
+#pragma unroll
+                for (int c = u * CPP; c < (u + 1) * CPP; ++c) tma_load_3d(dst + c * HALF_KV, m, &full[u], 0, y, kvh * NCH + c);
+              }
+            }
+          } else {
           wait_bar(&empty[stage], par, kStatusMmaTimeout);
           if (cur.kind < 0) {
             mbar_arrive(&full[stage]);
@@ -544,6 +565,7 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
               if (c < nch) tma_load_3d(dst + c * HALF_KV, m, &full[stage], 0, y, kvh * NCH + c0 + c);
+          }
           }
           if (lane == 0) stamp(b, is_v ? 7 : 6);
           cur = nxt;
@@ -587,21 +609,26 @@ __global__ void __launch_bounds__(F8 ? kThreadsF8 : kThreads, (!F8 && !WIN && sm
       auto issue_qk = [&](int b) {
         const int stage = b & 1;               // S buffer
         const int kst = b % KS;                // K ring slot
-        wait_bar(&k_full[kst], (b / KS) & 1, kStatusTmaTimeout);
-        tc_fence_after_sync();
         const uint64_t kd = k_desc + uint64_t(kst * (KV_TILE >> 4));
         const uint32_t td = tmem + COL_S + stage * BN;
+        constexpr int SPP = HD / 16 / KSUB;    // MMAs per part of the K tile (all of them but for 512-dim heads)
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t db = kd + uint64_t(((ks >> 2) * HALF_KV + (ks & 3) * 32) >> 4);
-          if constexpr (QT) {
-            umma_ts(td, tmem + COL_Q + ks * 8, db, idesc_qk, ks > 0);
-          } else {
-            const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
-            umma_ss(td, da, db, idesc_qk, ks > 0);
+        for (int u = 0; u < KSUB; ++u) {
+          uint64_t* kf = KSUB > 1 ? &k_full[u] : &k_full[kst];
+          wait_bar(kf, KSUB > 1 ? uint32_t(b & 1) : uint32_t((b / KS) & 1), kStatusTmaTimeout);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int ks = u * SPP; ks < (u + 1) * SPP; ++ks) {
+            const uint64_t db = kd + uint64_t(((ks >> 2) * HALF_KV + (ks & 3) * 32) >> 4);
+            if constexpr (QT) {
+              umma_ts(td, tmem + COL_Q + ks * 8, db, idesc_qk, ks > 0);
+            } else {
+              const uint64_t da = q_desc + uint64_t(((ks >> 2) * HALF_Q + (ks & 3) * 32) >> 4);
+              umma_ss(td, da, db, idesc_qk, ks > 0);
+            }
           }
+          umma_commit(KSUB > 1 ? &k_empty[u] : &k_empty[kst]);  // the K slot (part) may be refilled once these MMAs are done
         }
-        umma_commit(&k_empty[kst]);  // the K slot may be refilled once these MMAs are done
         umma_commit(&s_full[stage]);
       };
       // S of block b + 1 is computed while the softmax warps work on block b (two S buffers);
